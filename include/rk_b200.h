@@ -1,0 +1,198 @@
+/*
+ * rk_b200 - C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and a CUDA stream (a cudaStream_t passed as void*),
+ *   - launches on that stream and returns without synchronising,
+ *   - never allocates, frees or synchronises device memory (the caller owns every buffer,
+ *     including the scratch "workspace"), so calls can be captured in a CUDA graph,
+ *   - returns RK_OK (0) or a negative RK_E* code; rk_last_error_string() describes the last
+ *     failure on the calling thread.
+ * There is no CPU fallback: unsupported shapes are errors.
+ *
+ * Each declaration names the reference interface it stands in for (path inside the reference
+ * project : line).
+ *
+ * Data conventions
+ *   bf16      : IEEE bfloat16, row-major, innermost stride 1
+ *   int8 data : [rows, Kpad], Kpad = K rounded up to 128, zero padded
+ *   int4 data : [rows, Kpad/2] bytes, two's-complement nibbles, low nibble = even k
+ *   e4m3      : OCP FP8 E4M3 (no inf, max 448)
+ *   SF buffer : block scale factors in 512-byte chunks of 128 rows x 4 factors; factor g of
+ *               row r lives at ((r/128)*kt + g/4)*512 + (r%32)*16 + ((r%128)/32)*4 + g%4,
+ *               kt = ceil(groups/4); size rk_sf_bytes(rows, groups)
+ */
+#ifndef RK_B200_H_
+#define RK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RK_OK 0
+#define RK_EINVAL (-1)      /* bad argument: null pointer, shape, alignment */
+#define RK_EUNSUPPORTED (-2) /* shape or device this build has no kernel for */
+#define RK_ECUDA (-3)       /* a CUDA runtime / driver call failed */
+#define RK_EWORKSPACE (-4)  /* workspace missing or too small */
+#define RK_EDEVICE (-5)     /* a kernel reported a bounded-wait expiry in the status word */
+
+/* Activation pre-ops of the row quantizer (reference: MODE of `_prepare`, ampere_ada/integer.py:52-72). */
+#define RK_ACT_PLAIN 0     /* v = x */
+#define RK_ACT_LUT_MUL 1   /* v = bf16(LUT[bits(x)] * up) */
+#define RK_ACT_LUT 2       /* v = LUT[bits(x)] */
+
+/* GEMM families, for rk_workspace_bytes(). */
+#define RK_OP_W8A8 0
+#define RK_OP_W4A4 1
+#define RK_OP_W4A16 2
+#define RK_OP_FP8 3
+#define RK_OP_MXFP8 4
+#define RK_OP_NVFP4 5
+
+/* Bytes at the start of every workspace reserved for the device status word. */
+#define RK_WORKSPACE_HEADER 256
+
+/* ---- library ---------------------------------------------------------------------------- */
+
+/* Library ABI version (major*1000 + minor). */
+int rk_version(void);
+/* Description of the last error on this thread ("" when none). */
+const char* rk_last_error_string(void);
+/* 1 when the kernels can run on a device of this compute capability (10.0 only).
+ * Reference: `supports_device`, blackwell/csrc/mxfp8_cutlass_linear.cu:275-277. */
+int rk_supports_device(int cc_major, int cc_minor);
+/* Size of the scratch buffer a GEMM call of this family and shape may use.  The buffer must be
+ * zero-filled once after allocation; kernels leave it zero-filled.  One buffer per stream. */
+size_t rk_workspace_bytes(int op, int64_t m, int64_t n, int64_t k);
+/* Size of a swizzled scale-factor buffer for `rows` rows and `groups` factors per row.
+ * Reference: `scale_storage_size`, blackwell/csrc/mxfp8_common.cuh:14-16. */
+size_t rk_sf_bytes(int64_t rows, int64_t groups);
+/* Reads (synchronously, after synchronising `stream`) and clears the device status word at the
+ * start of `workspace`.  Returns RK_OK or RK_EDEVICE; *code receives the raw device code. */
+int rk_read_status(void* workspace, int* code, void* stream);
+/* Bit pattern of rcp.approx.ftz.f32(448.0f) on the current device (synchronous; test aid for the
+ * MXFP8 block-scale formula, blackwell/csrc/mxfp8_common.cuh:25). */
+int rk_probe_rcp_approx_448(uint32_t* bits);
+
+/* ---- integer path ----------------------------------------------------------------------- */
+
+/* Per-row symmetric absmax quantization of bf16 rows to int8 / packed int4.
+ * Replaces `prepare_activation` + Triton `_prepare` (ampere_ada/integer.py:75-198).
+ *   x [rows, k] with row stride x_stride (elements); up (RK_ACT_LUT_MUL only) likewise;
+ *   lut: 65536 bf16 entries indexed by the bf16 bit pattern (modes 1, 2), else NULL;
+ *   q: int8 [rows, kpad] (bits 8) or uint8 [rows, kpad/2] (bits 4); scales: f32 [rows].
+ *   scale = max|v| * fl32(1/limit) (1.0 for a zero row), q = clamp(rint(v / scale)). */
+int rk_quant_rows(const void* x, int64_t rows, int64_t k, int64_t x_stride, const void* up, int64_t up_stride,
+                  const void* lut, int mode, int bits, void* q, float* scales, void* stream);
+
+/* Per-output-channel weight quantization with true division (scale = max|w| / limit).
+ * Replaces the torch ops of `IntegerLinear.from_linear` (ampere_ada/integer.py:247-263).
+ *   w bf16 [n, k] contiguous; q int8 [npad, kpad] / uint8 [npad, kpad/2]; scales f32 [npad];
+ *   npad = n rounded up to 8; padding rows get zero codes and scale 1.0. */
+int rk_quant_weight_int(const void* w, int64_t n, int64_t k, int bits, void* q, float* scales, void* stream);
+
+/* AdaLN modulation (optionally preceded by a gated residual add and a non-affine LayerNorm)
+ * fused into the row quantizer.  Replaces `prepare_modulation`, `prepare_norm_modulation`,
+ * `prepare_residual_norm_modulation` (ampere_ada/modulation.py:13-146, 149-236).
+ *   x [rows, k]; scale, shift [rows/tokens, k] (row r uses row r / tokens);
+ *   v = bf16(bf16(x' * bf16(1 + scale)) + shift), x' = x, LayerNorm(x) or LayerNorm(residual);
+ *   y, gate (both or neither): residual = bf16(x + bf16(y * gate)) is written to residual_out;
+ *   layer_norm != 0 applies LayerNorm with `eps` first. */
+int rk_quant_rows_modulated(const void* x, const void* scale, const void* shift, int64_t rows, int64_t k,
+                            int64_t tokens, int layer_norm, float eps, const void* y, const void* gate,
+                            void* residual_out, int bits, void* q, float* scales, void* stream);
+
+/* Gemma RMSNorm fused into the int8 / int4 row quantizer:
+ *   s = x, or bf16(x + residual);  inv = rsqrt(mean(s^2) + eps);
+ *   v = bf16( fl(fl(s * inv) * fl(1 + a)) (+ b) ),  every fl() an fp32 rounding;
+ *   plain norm:    a = scale[k] (the learned weight), shift = NULL, tokens = 0;
+ *   adaptive norm: a = scale[r / tokens, k], b = shift[r / tokens, k].
+ * The norm is models/pi05/modeling_gemma.py:62-106; the reference has no fused integer version,
+ * its precedent is `add_rms_norm_quantize_bf16` (blackwell/csrc/fp8_cutlass_linear.cu:145-269).
+ *   sum_out (bf16 [rows, k], may be NULL) receives s; norm_out (may be NULL) receives v. */
+int rk_rmsnorm_quant_rows(const void* x, const void* residual, const void* scale, const void* shift,
+                          int64_t tokens, int64_t rows, int64_t k, float eps, int bits, void* sum_out,
+                          void* norm_out, void* q, float* scales, void* stream);
+
+/* out[m, n] = bf16( (float(sum_k a*b) * sa[m]) * sb[n] (+ bias[n]) ), int32 accumulation.
+ * Replaces `robotics_integer::gemm` / `gemm_biasless` (ampere_ada/csrc/integer_gemm.cu:22-195).
+ *   bits 8: a int8 [m, kpad], b int8 [n, kpad].  bits 4: packed nibbles [., kpad/2].
+ *   sa f32 [m], sb f32 [n], bias bf16 [n] or NULL; out bf16 [m, n] contiguous;
+ *   kpad % 128 == 0, n % 8 == 0; tactic 0..7 is accepted and never changes the result. */
+int rk_gemm_int(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
+                int64_t m, int64_t n, int64_t kpad, int bits, int tactic, void* workspace,
+                size_t workspace_bytes, void* stream);
+/* Same product, but writes the raw int32 accumulators [m, n] (parity aid; no reference counterpart). */
+int rk_gemm_int_acc(const void* a, const void* b, int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits,
+                    int tactic, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- W4A16 int4, group 128 -------------------------------------------------------------- */
+
+/* Group-wise symmetric int4 weight packing: per (row, 128 consecutive k): s = bf16(max|w| / 7)
+ * (1.0 when zero), q = clamp(rint(w / s), -7, 7).  q uint8 [n, k/2]; scales bf16 [k/128, n].
+ * Conventions follow the reference's int4 packing (ampere_ada/integer.py:250-263) and its mixed
+ * scale orientation (blackwell/csrc/fp4_mixed_cutlass_linear.cu:89-90); k % 128 == 0. */
+int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, void* stream);
+/* out[m, n] = bf16( sum_g s[g, n] * sum_{k in g} x[m, k] * q[n, k] (+ bias[n]) ), fp32 accumulation.
+ * Stands in for `linear_w4a16` (blackwell/csrc/fp4_mixed_cutlass_linear.cu:190-410) with the
+ * int4 / group-128 format.  x bf16 [m, k] contiguous, out bf16 [m, n] contiguous. */
+int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scales, const void* bias, void* out,
+                       int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* ---- per-tensor FP8 --------------------------------------------------------------------- */
+
+/* scale = max(max|x| / 448, 1e-12) over finite values; q = e4m3(clamp(x * (1/scale), +-448)).
+ * Replaces `quantize_bf16` (blackwell/csrc/fp8_cutlass_linear.cu:61-101, 391-424).
+ *   x bf16 [elements]; q e4m3 [elements]; scale_out f32 [1]; needs a workspace (header only). */
+int rk_quant_tensor_fp8(const void* x, int64_t elements, void* q, float* scale_out, void* workspace,
+                        size_t workspace_bytes, void* stream);
+/* Same conversion with a caller-supplied scale.  Replaces `quantize_bf16_with_scale` (:885-911). */
+int rk_quant_tensor_fp8_with_scale(const void* x, int64_t elements, const float* scale, void* q, void* stream);
+/* out[m, n] = bf16( (scale_a * scale_b) * sum_k a*b (+ bias[n]) ), fp32 accumulation.
+ * Replaces `linear_forward_packed` / `fp8_gemm::run` (blackwell/csrc/fp8_cutlass_linear.cu:473-723, 1026-1154).
+ *   a e4m3 [m, k], b e4m3 [n, k]; scale_a, scale_b: device pointers to one f32; k % 16 == 0, n % 8 == 0. */
+int rk_gemm_fp8(const void* a, const float* scale_a, const void* b, const float* scale_b, const void* bias,
+                void* out, int64_t m, int64_t n, int64_t k, int tactic, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* ---- MXFP8 ------------------------------------------------------------------------------ */
+
+/* Per 32 consecutive k: SF = UE8M0 round-up of max|x| * rcp(448) (255 when the block holds a
+ * non-finite value), q = e4m3(x * 2^-(SF-127)).  Replaces `robotics_mxfp8::pack`
+ * (blackwell/csrc/mxfp8_cutlass_linear.cu:31-105).  x bf16 [rows, k], k % 32 == 0;
+ * q e4m3 [rows, k]; sf: rk_sf_bytes(rows, k/32) bytes, fully written (padding = 0). */
+int rk_pack_mxfp8(const void* x, int64_t rows, int64_t k, void* q, void* sf, void* stream);
+/* out = bf16( sum over blocks (sfa * sfb * sum_k a*b) (+ bias[n]) ).  Replaces `robotics_mxfp8::linear`
+ * (blackwell/csrc/mxfp8_cutlass_linear.cu:107-258).  k % 32 == 0, n % 8 == 0. */
+int rk_gemm_mxfp8(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias, void* out,
+                  int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* ---- NVFP4 ------------------------------------------------------------------------------ */
+
+/* Per 16 consecutive k: s = max|v| / 6 (1.0 when zero), SF = UE4M3(s), q = e2m1(v / float(SF)),
+ * sixteen codes per 64-bit word, low nibble first; v = x, or x / *global_scale when
+ * global_scale is not NULL.  Replaces `pack_linear_weight_gemm_bf16` / `pack_activation_gemm_bf16`
+ * (blackwell/csrc/fp4_cutlass_linear.cu:789-841, 1530-1587).  x bf16 [rows, k], k % 32 == 0;
+ * q uint8 [rows, k/2]; sf: rk_sf_bytes(rows, k/16) bytes, fully written. */
+int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float* global_scale, void* q, void* sf,
+                  void* stream);
+/* *scale_out = max(max|x| / (6 * 448), 1e-12): the optional fp32 per-tensor scale of an NVFP4
+ * tensor (absent from the reference, where alpha = 1: blackwell/csrc/fp4_cutlass_linear.cu:1358). */
+int rk_nvfp4_global_scale(const void* x, int64_t elements, float* scale_out, void* workspace,
+                          size_t workspace_bytes, void* stream);
+/* out = bf16( alpha * sum over blocks (sfa * sfb * sum_k a*b) (+ bias[n]) ), alpha = *ga * *gb
+ * (each NULL = 1).  Replaces `linear_forward_packed_gemm_bf16` / `gemm_bf16::run`
+ * (blackwell/csrc/fp4_cutlass_linear.cu:1199-1447, 1751-1848).  k % 32 == 0, n % 8 == 0. */
+int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, const void* b, const void* sfb,
+                  const float* gb, const void* bias, void* out, int64_t m, int64_t n, int64_t k, int tactic,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RK_B200_H_ */

@@ -1,0 +1,726 @@
+// Activation / weight quantizers and block-scale packers (HBM-bound, SIMT).
+//
+// Row quantizers: one CTA of 256 threads per row, 128-bit loads, the row cached in registers
+// (8192 elements at most on the cached path), warp-shuffle + shared-memory reductions, and the
+// producer op (GELU table, AdaLN modulation, LayerNorm, RMSNorm, gated residual) fused in front
+// of the absmax so the bf16 intermediate never round-trips through HBM.
+//
+// All divisions and reciprocals that define a stored scale or code use the IEEE-rounded
+// intrinsics (__fdiv_rn, __frcp_rn); this file must not be built with fast-math.
+
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include "rk_common.cuh"
+#include "rk_host.h"
+
+namespace rk {
+namespace {
+
+constexpr int kRowThreads = 256;
+constexpr int kMaxVec = 4;                              // 8-element vectors cached per thread
+constexpr int kCachedK = kRowThreads * kMaxVec * 8;     // 8192
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* scratch) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // scratch may still be read from a previous reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = scratch[0];
+  for (int w = 1; w < (kRowThreads >> 5); ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+  return r;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, bool vec, int valid, float (&v)[8]) {
+  if (vec && valid >= 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = bf16_bits_to_float(w[i] & 0xFFFFu);
+      v[2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = i < valid ? __bfloat162float(p[i]) : 0.0f;
+  }
+}
+
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// clamp(rint(v / scale)) as an int in [-limit, limit]
+__device__ __forceinline__ int quant_code(float v, float scale, float limit) {
+  float q = rintf(__fdiv_rn(v, scale));
+  q = fminf(fmaxf(q, -limit), limit);
+  return __float2int_rn(q);
+}
+
+// Writes eight codes starting at element index `idx` of a padded row.
+template <int BITS>
+__device__ __forceinline__ void store_codes8(uint8_t* qrow, int idx, const int (&c)[8]) {
+  if constexpr (BITS == 8) {
+    uint2 o;
+    o.x = (c[0] & 255) | ((c[1] & 255) << 8) | ((c[2] & 255) << 16) | ((c[3] & 255) << 24);
+    o.y = (c[4] & 255) | ((c[5] & 255) << 8) | ((c[6] & 255) << 16) | ((c[7] & 255) << 24);
+    *reinterpret_cast<uint2*>(qrow + idx) = o;
+  } else {
+    uint32_t o = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o |= static_cast<uint32_t>(c[i] & 15) << (4 * i);
+    *reinterpret_cast<uint32_t*>(qrow + idx / 2) = o;
+  }
+}
+
+__device__ __forceinline__ float row_scale_from_max(float maximum, float limit, bool true_division) {
+  if (!(maximum > 0.0f)) return 1.0f;
+  // activations: max * fl32(1/limit); weights: max / limit
+  return true_division ? __fdiv_rn(maximum, limit) : __fmul_rn(maximum, static_cast<float>(1.0 / limit));
+}
+
+// Common tail: absmax over cached values, scale, quantize, store (zero padding to kpad).
+template <int BITS>
+__device__ __forceinline__ void finish_row(float (&vals)[kMaxVec][8], int k, int kpad, uint8_t* qrow, float* scale_out,
+                                           bool true_division, float* scratch) {
+  const float limit = static_cast<float>((1 << (BITS - 1)) - 1);
+  float local = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) local = fmaxf(local, fabsf(vals[it][i]));
+  const float maximum = block_reduce(local, true, scratch);
+  const float scale = row_scale_from_max(maximum, limit, true_division);
+  if (threadIdx.x == 0) *scale_out = scale;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+    if (idx < kpad) {
+      int c[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) c[i] = (idx + i < k) ? quant_code(vals[it][i], scale, limit) : 0;
+      store_codes8<BITS>(qrow, idx, c);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ plain / GELU-table rows
+template <int BITS, int MODE>
+__global__ void __launch_bounds__(kRowThreads)
+quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const __nv_bfloat16* __restrict__ up,
+                  long long up_stride, const __nv_bfloat16* __restrict__ lut, int k, int kpad, int n_rows,
+                  uint8_t* __restrict__ q, float* __restrict__ scales, int true_division, int vec_ok) {
+  __shared__ float scratch[kRowThreads / 32];
+  const int row = blockIdx.x;
+  const int qbytes = BITS == 8 ? kpad : kpad / 2;
+  uint8_t* qrow = q + static_cast<long long>(row) * qbytes;
+  if (row >= n_rows) {  // padding row of a weight matrix: zero codes, unit scale
+    for (int i = threadIdx.x * 4; i < qbytes; i += kRowThreads * 4) *reinterpret_cast<uint32_t*>(qrow + i) = 0;
+    if (threadIdx.x == 0) scales[row] = 1.0f;
+    return;
+  }
+  const __nv_bfloat16* xr = x + row * x_stride;
+  const __nv_bfloat16* ur = MODE == RK_ACT_LUT_MUL ? up + row * up_stride : nullptr;
+  auto values_at = [&](int idx, float (&v)[8]) {
+    const int valid = k - idx;
+    load8(xr + idx, vec_ok, valid, v);
+    if constexpr (MODE != RK_ACT_PLAIN) {
+      float u[8];
+      if constexpr (MODE == RK_ACT_LUT_MUL) load8(ur + idx, vec_ok, valid, u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i < valid) {
+          const uint32_t bits = __float_as_uint(v[i]) >> 16;
+          float t = __bfloat162float(lut[bits]);
+          if constexpr (MODE == RK_ACT_LUT_MUL) t = round_bf16(__fmul_rn(t, u[i]));
+          v[i] = t;
+        }
+      }
+    }
+  };
+  if (k <= kCachedK) {
+    float vals[kMaxVec][8];
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int idx = (it * kRowThreads + threadIdx.x) * 8;
+      if (idx < k) {
+        values_at(idx, vals[it]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vals[it][i] = 0.0f;
+      }
+    }
+    finish_row<BITS>(vals, k, kpad, qrow, scales + row, true_division != 0, scratch);
+  } else {
+    // long rows: two passes over global memory (the second one hits L2)
+    const float limit = static_cast<float>((1 << (BITS - 1)) - 1);
+    float local = 0.0f;
+    for (int idx = threadIdx.x * 8; idx < k; idx += kRowThreads * 8) {
+      float v[8];
+      values_at(idx, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) local = fmaxf(local, fabsf(v[i]));
+    }
+    const float maximum = block_reduce(local, true, scratch);
+    const float scale = row_scale_from_max(maximum, limit, true_division != 0);
+    if (threadIdx.x == 0) scales[row] = scale;
+    for (int idx = threadIdx.x * 8; idx < kpad; idx += kRowThreads * 8) {
+      float v[8];
+      int c[8];
+      if (idx < k) {
+        values_at(idx, v);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) c[i] = (idx + i < k) ? quant_code(v[i], scale, limit) : 0;
+      store_codes8<BITS>(qrow, idx, c);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ AdaLN modulation (+LayerNorm, +gated residual)
+template <int BITS>
+__global__ void __launch_bounds__(kRowThreads)
+quant_rows_modulated_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ mod_scale,
+                            const __nv_bfloat16* __restrict__ mod_shift, int k, int kpad, int tokens, int layer_norm,
+                            float eps, const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ gate,
+                            __nv_bfloat16* __restrict__ residual_out, uint8_t* __restrict__ q,
+                            float* __restrict__ scales) {
+  __shared__ float scratch[kRowThreads / 32];
+  const int row = blockIdx.x;
+  const long long xoff = static_cast<long long>(row) * k;
+  const long long moff = static_cast<long long>(row / tokens) * k;
+  uint8_t* qrow = q + static_cast<long long>(row) * (BITS == 8 ? kpad : kpad / 2);
+  const bool vec = (k % 8) == 0;
+  float vals[kMaxVec][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vals[it][i] = 0.0f;
+    if (idx < k) {
+      const int valid = k - idx;
+      load8(x + xoff + idx, vec, valid, vals[it]);
+      if (y != nullptr) {
+        float yv[8], gv[8];
+        load8(y + xoff + idx, vec, valid, yv);
+        load8(gate + moff + idx, vec, valid, gv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          // residual = bf16(x + bf16(y * gate))
+          vals[it][i] = round_bf16(__fadd_rn(vals[it][i], round_bf16(__fmul_rn(yv[i], gv[i]))));
+          if (i < valid) residual_out[xoff + idx + i] = __float2bfloat16_rn(vals[it][i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += (i < valid) ? vals[it][i] : 0.0f;
+    }
+  }
+  if (layer_norm) {
+    const float mean = __fdiv_rn(block_reduce(sum, false, scratch), static_cast<float>(k));
+    float sq = 0.0f;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int idx = (it * kRowThreads + threadIdx.x) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = (idx + i < k) ? __fsub_rn(vals[it][i], mean) : 0.0f;
+        vals[it][i] = c;
+        sq += c * c;
+      }
+    }
+    const float var = __fdiv_rn(block_reduce(sq, false, scratch), static_cast<float>(k));
+    const float inv = rsqrtf(var + eps);
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vals[it][i] = round_bf16(__fmul_rn(vals[it][i], inv));
+  }
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+    if (idx < k) {
+      const int valid = k - idx;
+      float sc[8], sh[8];
+      load8(mod_scale + moff + idx, vec, valid, sc);
+      load8(mod_shift + moff + idx, vec, valid, sh);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        // bf16(bf16(x * bf16(1 + scale)) + shift)
+        const float factor = round_bf16(__fadd_rn(1.0f, sc[i]));
+        const float product = round_bf16(__fmul_rn(vals[it][i], factor));
+        vals[it][i] = (i < valid) ? round_bf16(__fadd_rn(product, sh[i])) : 0.0f;
+      }
+    }
+  }
+  finish_row<BITS>(vals, k, kpad, qrow, scales + row, false, scratch);
+}
+
+// ------------------------------------------------------------------ RMSNorm (Gemma) -> quantize
+// n = bf16( fl(fl(s * inv) * fl(1 + a)) + b ), inv = rsqrt(mean(s^2) + eps);
+//   plain:    a = weight[k], b absent;  adaptive: a = scale[row / tokens, k], b = shift[row / tokens, k].
+template <int BITS>
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                          const __nv_bfloat16* __restrict__ a_ptr, const __nv_bfloat16* __restrict__ b_ptr,
+                          int tokens, int k, int kpad, float eps, __nv_bfloat16* __restrict__ sum_out,
+                          __nv_bfloat16* __restrict__ norm_out, uint8_t* __restrict__ q, float* __restrict__ scales) {
+  __shared__ float scratch[kRowThreads / 32];
+  const int row = blockIdx.x;
+  const long long xoff = static_cast<long long>(row) * k;
+  const long long aoff = tokens > 0 ? static_cast<long long>(row / tokens) * k : 0;
+  uint8_t* qrow = q + static_cast<long long>(row) * (BITS == 8 ? kpad : kpad / 2);
+  const bool vec = (k % 8) == 0;
+  float vals[kMaxVec][8];
+  float sq = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vals[it][i] = 0.0f;
+    if (idx < k) {
+      const int valid = k - idx;
+      load8(x + xoff + idx, vec, valid, vals[it]);
+      if (residual != nullptr) {
+        float rv[8];
+        load8(residual + xoff + idx, vec, valid, rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vals[it][i] = round_bf16(__fadd_rn(vals[it][i], rv[i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i < valid) {
+          if (sum_out != nullptr) sum_out[xoff + idx + i] = __float2bfloat16_rn(vals[it][i]);
+          sq += vals[it][i] * vals[it][i];
+        }
+      }
+    }
+  }
+  const float var = __fdiv_rn(block_reduce(sq, false, scratch), static_cast<float>(k));
+  const float inv = rsqrtf(var + eps);
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+    if (idx < k) {
+      const int valid = k - idx;
+      float av[8], bv[8];
+      load8(a_ptr + aoff + idx, vec, valid, av);
+      if (b_ptr != nullptr) load8(b_ptr + aoff + idx, vec, valid, bv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = __fmul_rn(__fmul_rn(vals[it][i], inv), __fadd_rn(1.0f, av[i]));
+        if (b_ptr != nullptr) t = __fadd_rn(t, bv[i]);
+        t = (i < valid) ? round_bf16(t) : 0.0f;
+        vals[it][i] = t;
+        if (norm_out != nullptr && i < valid) norm_out[xoff + idx + i] = __float2bfloat16_rn(t);
+      }
+    }
+  }
+  finish_row<BITS>(vals, k, kpad, qrow, scales + row, false, scratch);
+}
+
+// ------------------------------------------------------------------ W4 group-128 weight packer
+// One warp per (row, group of 128): four consecutive elements per lane.
+__global__ void __launch_bounds__(256)
+pack_w4_g128_kernel(const __nv_bfloat16* __restrict__ w, int n, int k, uint8_t* __restrict__ q,
+                    __nv_bfloat16* __restrict__ scales) {
+  const int groups = k / 128;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= static_cast<long long>(n) * groups) return;
+  const int row = static_cast<int>(gw / groups);
+  const int g = static_cast<int>(gw % groups);
+  const __nv_bfloat16* src = w + static_cast<long long>(row) * k + g * 128 + lane * 4;
+  const uint2 u = *reinterpret_cast<const uint2*>(src);
+  float v[4] = {bf16_bits_to_float(u.x & 0xFFFFu), bf16_bits_to_float(u.x >> 16), bf16_bits_to_float(u.y & 0xFFFFu),
+                bf16_bits_to_float(u.y >> 16)};
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = warp_max(amax);
+  // s = bf16(amax / 7) (1.0 for an all-zero group); codes use float(s)
+  __nv_bfloat16 sb = __float2bfloat16_rn(amax > 0.0f ? __fdiv_rn(amax, 7.0f) : 1.0f);
+  if (!(__bfloat162float(sb) > 0.0f)) sb = __float2bfloat16_rn(1.0f);  // amax / 7 flushed to zero in bf16
+  const float s = __bfloat162float(sb);
+  if (lane == 0) scales[static_cast<long long>(g) * n + row] = sb;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) packed |= static_cast<uint32_t>(quant_code(v[i], s, 7.0f) & 15) << (4 * i);
+  *reinterpret_cast<uint16_t*>(q + static_cast<long long>(row) * (k / 2) + g * 64 + lane * 2) =
+      static_cast<uint16_t>(packed);
+}
+
+// ------------------------------------------------------------------ per-tensor FP8
+__global__ void __launch_bounds__(256)
+amax_finite_kernel(const __nv_bfloat16* __restrict__ x, long long elements, unsigned* __restrict__ amax_bits) {
+  __shared__ float scratch[8];
+  float local = 0.0f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; idx < elements;
+       idx += stride) {
+    float v[8];
+    const long long left = elements - idx;
+    load8(x + idx, true, left >= 8 ? 8 : static_cast<int>(left), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float a = fabsf(v[i]);
+      if (a <= 3.4028234664e38f) local = fmaxf(local, a);  // skips inf and NaN
+    }
+  }
+  local = warp_max(local);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float r = scratch[0];
+    for (int w = 1; w < 8; ++w) r = fmaxf(r, scratch[w]);
+    atomicMax(amax_bits, __float_as_uint(r));  // non-negative floats order like their bit patterns
+  }
+}
+
+// scale = max(amax / divisor, 1e-12); also clears the staging word for the next call
+__global__ void finalize_scale_kernel(unsigned* amax_bits, float divisor, float* scale_out) {
+  const float amax = __uint_as_float(*amax_bits);
+  *scale_out = fmaxf(__fdiv_rn(amax, divisor), 1e-12f);
+  *amax_bits = 0u;
+}
+
+__global__ void __launch_bounds__(256)
+to_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long elements, const float* __restrict__ scale,
+              uint8_t* __restrict__ q) {
+  const float inverse = __fdiv_rn(1.0f, *scale);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; idx < elements;
+       idx += stride) {
+    float v[8];
+    const long long left = elements - idx;
+    const int valid = left >= 8 ? 8 : static_cast<int>(left);
+    load8(x + idx, true, valid, v);
+    uint8_t c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float t = __fmul_rn(v[i], inverse);
+      t = fminf(448.0f, fmaxf(-448.0f, t));
+      c[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3));
+    }
+    if (valid == 8) {
+      uint2 o;
+      o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (static_cast<uint32_t>(c[3]) << 24);
+      o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (static_cast<uint32_t>(c[7]) << 24);
+      *reinterpret_cast<uint2*>(q + idx) = o;
+    } else {
+      for (int i = 0; i < valid; ++i) q[idx + i] = c[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ block-scale packers
+__device__ __forceinline__ long long sf_offset(long long row, long long group, long long kt) {
+  return ((row / 128) * kt + group / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + group % 4;
+}
+
+__device__ __forceinline__ float rcp_approx_ftz(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// smallest power of two >= x as a biased exponent byte (x >= 0, finite)
+__device__ __forceinline__ uint32_t ue8m0_roundup(float x) {
+  const uint32_t b = __float_as_uint(x);
+  const uint32_t e = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
+  uint32_t r = e == 0 ? (mant > 0x400000u ? 1u : 0u) : e + (mant != 0u ? 1u : 0u);
+  return r > 254u ? 254u : r;
+}
+
+// MXFP8: eight lanes per 32-element block, four elements per lane.  The thread grid covers the
+// padded scale-factor domain so that every byte of the SF buffer is written.
+__global__ void __launch_bounds__(256)
+pack_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, uint8_t* __restrict__ q,
+                  uint8_t* __restrict__ sf) {
+  const long long groups_padded = (k + 127) / 128 * 4;
+  const long long rows_padded = (rows + 127) / 128 * 128;
+  const long long thread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long block_index = thread / 8;
+  const int lane8 = static_cast<int>(thread % 8);
+  const long long row = block_index / groups_padded;
+  const long long group = block_index % groups_padded;
+  if (row >= rows_padded) return;
+  const long long sfi = sf_offset(row, group, groups_padded / 4);
+  if (row >= rows || group * 32 >= k) {
+    if (lane8 == 0) sf[sfi] = 0;
+    return;
+  }
+  const long long base = row * k + group * 32 + lane8 * 4;
+  const uint2 u = *reinterpret_cast<const uint2*>(x + base);
+  float v[4] = {bf16_bits_to_float(u.x & 0xFFFFu), bf16_bits_to_float(u.x >> 16), bf16_bits_to_float(u.y & 0xFFFFu),
+                bf16_bits_to_float(u.y >> 16)};
+  float amax = 0.0f;
+  unsigned invalid = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    amax = fmaxf(amax, fabsf(v[i]));
+    invalid |= !(fabsf(v[i]) <= 3.4028234664e38f);
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
+    invalid |= __shfl_xor_sync(0xffffffffu, invalid, o, 8);
+  }
+  const uint32_t e = invalid ? 255u : ue8m0_roundup(__fmul_rn(amax, rcp_approx_ftz(448.0f)));
+  if (lane8 == 0) sf[sfi] = static_cast<uint8_t>(e);
+  // inverse scale 2^(127 - e) built as the byte 254 - e (255 stays NaN)
+  const uint32_t ie = (254u - e) & 255u;
+  const float inverse = ie == 255u ? __uint_as_float(0x7FC00000u)
+                                   : (ie == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(ie << 23));
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    out |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fmul_rn(v[i], inverse), __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  *reinterpret_cast<uint32_t*>(q + base) = out;
+}
+
+// NVFP4: one thread per 16-element block (two 128-bit loads, one 64-bit store).
+__global__ void __launch_bounds__(256)
+pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, const float* __restrict__ global,
+                  uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  const long long groups = k / 16;
+  const long long groups_padded = (groups + 3) / 4 * 4;
+  const long long rows_padded = (rows + 127) / 128 * 128;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = idx / groups_padded;
+  const long long group = idx % groups_padded;
+  if (row >= rows_padded) return;
+  const long long sfi = sf_offset(row, group, groups_padded / 4);
+  if (row >= rows || group >= groups) {
+    sf[sfi] = 0;
+    return;
+  }
+  float v[16];
+  load8(x + row * k + group * 16, true, 8, *reinterpret_cast<float(*)[8]>(&v[0]));
+  load8(x + row * k + group * 16 + 8, true, 8, *reinterpret_cast<float(*)[8]>(&v[8]));
+  if (global != nullptr) {
+    const float g = *global;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __fdiv_rn(v[i], g);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 6.0f) : 1.0f;
+  const uint8_t code = static_cast<uint8_t>(__nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E4M3)) & 0x7F;
+  float deq = __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
+  if (!(deq > 0.0f)) deq = scale;
+  const float reciprocal = __fdiv_rn(1.0f, deq);
+  unsigned long long packed = 0;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const __nv_fp4x2_storage_t pair = __nv_cvt_float2_to_fp4x2(
+        make_float2(__fmul_rn(v[i], reciprocal), __fmul_rn(v[i + 1], reciprocal)), __NV_E2M1, cudaRoundNearest);
+    packed |= static_cast<unsigned long long>(static_cast<uint8_t>(pair)) << (4 * i);
+  }
+  *reinterpret_cast<unsigned long long*>(q + row * (k / 2) + group * 8) = packed;
+  sf[sfi] = code;
+}
+
+__global__ void probe_rcp_kernel(uint32_t* out) { *out = __float_as_uint(rcp_approx_ftz(448.0f)); }
+
+template <int BITS>
+int launch_quant_rows(const void* x, int64_t rows, int64_t total_rows, int64_t k, int64_t xs, const void* up,
+                      int64_t us, const void* lut, int mode, void* q, float* scales, int true_division,
+                      cudaStream_t st) {
+  const int kpad = static_cast<int>(round_up(k, 128));
+  const int vec_ok = aligned16(x) && xs % 8 == 0 && (mode != RK_ACT_LUT_MUL || (aligned16(up) && us % 8 == 0));
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  auto ub = static_cast<const __nv_bfloat16*>(up);
+  auto lb = static_cast<const __nv_bfloat16*>(lut);
+  auto qb = static_cast<uint8_t*>(q);
+  const dim3 grid(static_cast<unsigned>(total_rows));
+  switch (mode) {
+    case RK_ACT_PLAIN:
+      quant_rows_kernel<BITS, RK_ACT_PLAIN><<<grid, kRowThreads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
+                                                                          static_cast<int>(rows), qb, scales,
+                                                                          true_division, vec_ok);
+      break;
+    case RK_ACT_LUT_MUL:
+      quant_rows_kernel<BITS, RK_ACT_LUT_MUL><<<grid, kRowThreads, 0, st>>>(
+          xb, xs, ub, us, lb, static_cast<int>(k), kpad, static_cast<int>(rows), qb, scales, true_division, vec_ok);
+      break;
+    default:
+      quant_rows_kernel<BITS, RK_ACT_LUT><<<grid, kRowThreads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
+                                                                        static_cast<int>(rows), qb, scales,
+                                                                        true_division, vec_ok);
+  }
+  return check_launch("quant_rows");
+}
+
+}  // namespace
+}  // namespace rk
+
+using namespace rk;
+
+extern "C" int rk_quant_rows(const void* x, int64_t rows, int64_t k, int64_t x_stride, const void* up,
+                             int64_t up_stride, const void* lut, int mode, int bits, void* q, float* scales,
+                             void* stream) {
+  if (!x || !q || !scales) return fail(RK_EINVAL, "rk_quant_rows: null pointer");
+  if (bits != 4 && bits != 8) return fail(RK_EINVAL, "rk_quant_rows: bits must be 4 or 8");
+  if (rows < 1 || k < 1 || k > 65536) return fail(RK_EINVAL, "rk_quant_rows: unsupported activation dimensions");
+  if (mode < 0 || mode > 2) return fail(RK_EINVAL, "rk_quant_rows: unknown mode");
+  if (mode != RK_ACT_PLAIN && !lut) return fail(RK_EINVAL, "rk_quant_rows: table required");
+  if (mode == RK_ACT_LUT_MUL && !up) return fail(RK_EINVAL, "rk_quant_rows: gated mode needs `up`");
+  if (x_stride < k || (mode == RK_ACT_LUT_MUL && up_stride < k)) return fail(RK_EINVAL, "rk_quant_rows: row stride < k");
+  return bits == 8 ? launch_quant_rows<8>(x, rows, rows, k, x_stride, up, up_stride, lut, mode, q, scales, 0,
+                                          as_stream(stream))
+                   : launch_quant_rows<4>(x, rows, rows, k, x_stride, up, up_stride, lut, mode, q, scales, 0,
+                                          as_stream(stream));
+}
+
+extern "C" int rk_quant_weight_int(const void* w, int64_t n, int64_t k, int bits, void* q, float* scales,
+                                   void* stream) {
+  if (!w || !q || !scales) return fail(RK_EINVAL, "rk_quant_weight_int: null pointer");
+  if (bits != 4 && bits != 8) return fail(RK_EINVAL, "rk_quant_weight_int: bits must be 4 or 8");
+  if (n < 1 || k < 1 || k > 65536) return fail(RK_EINVAL, "rk_quant_weight_int: unsupported weight dimensions");
+  const int64_t npad = round_up(n, 8);
+  return bits == 8 ? launch_quant_rows<8>(w, n, npad, k, k, nullptr, 0, nullptr, RK_ACT_PLAIN, q, scales, 1,
+                                          as_stream(stream))
+                   : launch_quant_rows<4>(w, n, npad, k, k, nullptr, 0, nullptr, RK_ACT_PLAIN, q, scales, 1,
+                                          as_stream(stream));
+}
+
+extern "C" int rk_quant_rows_modulated(const void* x, const void* scale, const void* shift, int64_t rows, int64_t k,
+                                       int64_t tokens, int layer_norm, float eps, const void* y, const void* gate,
+                                       void* residual_out, int bits, void* q, float* scales, void* stream) {
+  if (!x || !scale || !shift || !q || !scales) return fail(RK_EINVAL, "rk_quant_rows_modulated: null pointer");
+  if (bits != 4 && bits != 8) return fail(RK_EINVAL, "rk_quant_rows_modulated: bits must be 4 or 8");
+  if (rows < 1 || k < 1 || tokens < 1 || rows % tokens != 0)
+    return fail(RK_EINVAL, "rk_quant_rows_modulated: rows must be a positive multiple of tokens");
+  if (k > kCachedK) return fail(RK_EUNSUPPORTED, "rk_quant_rows_modulated: k > %d", kCachedK);
+  if ((y == nullptr) != (gate == nullptr) || (y != nullptr && residual_out == nullptr))
+    return fail(RK_EINVAL, "rk_quant_rows_modulated: y, gate and residual_out go together");
+  if (!aligned16(x) || !aligned16(scale) || !aligned16(shift) || (y && (!aligned16(y) || !aligned16(gate))))
+    return fail(RK_EINVAL, "rk_quant_rows_modulated: pointers must be 16-byte aligned");
+  const int kpad = static_cast<int>(round_up(k, 128));
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  if (bits == 8)
+    quant_rows_modulated_kernel<8><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+        b(x), b(scale), b(shift), static_cast<int>(k), kpad, static_cast<int>(tokens), layer_norm, eps, b(y), b(gate),
+        static_cast<__nv_bfloat16*>(residual_out), static_cast<uint8_t*>(q), scales);
+  else
+    quant_rows_modulated_kernel<4><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+        b(x), b(scale), b(shift), static_cast<int>(k), kpad, static_cast<int>(tokens), layer_norm, eps, b(y), b(gate),
+        static_cast<__nv_bfloat16*>(residual_out), static_cast<uint8_t*>(q), scales);
+  return check_launch("quant_rows_modulated");
+}
+
+extern "C" int rk_rmsnorm_quant_rows(const void* x, const void* residual, const void* scale, const void* shift,
+                                     int64_t tokens, int64_t rows, int64_t k, float eps, int bits, void* sum_out,
+                                     void* norm_out, void* q, float* scales, void* stream) {
+  if (!x || !scale || !q || !scales) return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: null pointer");
+  if (bits != 4 && bits != 8) return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: bits must be 4 or 8");
+  if (rows < 1 || k < 1 || tokens < 0 || (tokens > 0 && rows % tokens != 0))
+    return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: bad row / token counts");
+  if (k > kCachedK) return fail(RK_EUNSUPPORTED, "rk_rmsnorm_quant_rows: k > %d", kCachedK);
+  if (!aligned16(x) || !aligned16(scale) || (residual && !aligned16(residual)) || (shift && !aligned16(shift)))
+    return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: pointers must be 16-byte aligned");
+  const int kpad = static_cast<int>(round_up(k, 128));
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  if (bits == 8)
+    rmsnorm_quant_rows_kernel<8><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+        b(x), b(residual), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
+        static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), static_cast<uint8_t*>(q), scales);
+  else
+    rmsnorm_quant_rows_kernel<4><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+        b(x), b(residual), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
+        static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), static_cast<uint8_t*>(q), scales);
+  return check_launch("rmsnorm_quant_rows");
+}
+
+extern "C" int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, void* stream) {
+  if (!w || !q || !scales) return fail(RK_EINVAL, "rk_pack_w4_g128: null pointer");
+  if (n < 1 || k < 128 || k % 128 != 0) return fail(RK_EINVAL, "rk_pack_w4_g128: k must be a positive multiple of 128");
+  if (!aligned16(w)) return fail(RK_EINVAL, "rk_pack_w4_g128: w must be 16-byte aligned");
+  const long long warps = static_cast<long long>(n) * (k / 128);
+  const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
+  pack_w4_g128_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(w), static_cast<int>(n),
+                                                             static_cast<int>(k), static_cast<uint8_t*>(q),
+                                                             static_cast<__nv_bfloat16*>(scales));
+  return check_launch("pack_w4_g128");
+}
+
+namespace {
+int tensor_amax_scale(const void* x, int64_t elements, float divisor, float* scale_out, void* workspace,
+                      size_t workspace_bytes, cudaStream_t st, const char* who) {
+  if (!x || !scale_out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
+  if (elements < 1 || !aligned16(x)) return fail(RK_EINVAL, "%s: bad size or alignment", who);
+  unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
+  long long blocks = (elements + 2047) / 2048;
+  if (blocks > 1184) blocks = 1184;  // 148 SMs x 8 CTAs
+  amax_finite_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), elements,
+                                                                    staging);
+  finalize_scale_kernel<<<1, 1, 0, st>>>(staging, divisor, scale_out);
+  return check_launch(who);
+}
+}  // namespace
+
+extern "C" int rk_quant_tensor_fp8_with_scale(const void* x, int64_t elements, const float* scale, void* q,
+                                              void* stream) {
+  if (!x || !scale || !q) return fail(RK_EINVAL, "rk_quant_tensor_fp8_with_scale: null pointer");
+  if (elements < 1 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7u))
+    return fail(RK_EINVAL, "rk_quant_tensor_fp8_with_scale: bad size or alignment");
+  long long blocks = (elements + 2047) / 2048;
+  if (blocks > 2368) blocks = 2368;
+  to_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                              elements, scale, static_cast<uint8_t*>(q));
+  return check_launch("to_fp8");
+}
+
+extern "C" int rk_quant_tensor_fp8(const void* x, int64_t elements, void* q, float* scale_out, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  int rc = tensor_amax_scale(x, elements, 448.0f, scale_out, workspace, workspace_bytes, as_stream(stream),
+                             "rk_quant_tensor_fp8");
+  if (rc != RK_OK) return rc;
+  return rk_quant_tensor_fp8_with_scale(x, elements, scale_out, q, stream);
+}
+
+extern "C" int rk_nvfp4_global_scale(const void* x, int64_t elements, float* scale_out, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  return tensor_amax_scale(x, elements, 6.0f * 448.0f, scale_out, workspace, workspace_bytes, as_stream(stream),
+                           "rk_nvfp4_global_scale");
+}
+
+extern "C" size_t rk_sf_bytes(int64_t rows, int64_t groups) {
+  if (rows < 1 || groups < 1) return 0;
+  return static_cast<size_t>(((rows + 127) / 128) * ((groups + 3) / 4) * 512);
+}
+
+extern "C" int rk_pack_mxfp8(const void* x, int64_t rows, int64_t k, void* q, void* sf, void* stream) {
+  if (!x || !q || !sf) return fail(RK_EINVAL, "rk_pack_mxfp8: null pointer");
+  if (rows < 1 || k < 32 || k % 32 != 0) return fail(RK_EINVAL, "rk_pack_mxfp8: k must be a positive multiple of 32");
+  if (!aligned16(x) || !aligned16(q)) return fail(RK_EINVAL, "rk_pack_mxfp8: pointers must be 16-byte aligned");
+  const long long blocks32 = ((rows + 127) / 128 * 128) * ((k + 127) / 128 * 4);
+  const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
+  pack_mxfp8_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k,
+                                                         static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
+  return check_launch("pack_mxfp8");
+}
+
+extern "C" int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float* global_scale, void* q, void* sf,
+                             void* stream) {
+  if (!x || !q || !sf) return fail(RK_EINVAL, "rk_pack_nvfp4: null pointer");
+  if (rows < 1 || k < 32 || k % 32 != 0) return fail(RK_EINVAL, "rk_pack_nvfp4: k must be a positive multiple of 32");
+  if (!aligned16(x) || !aligned16(q)) return fail(RK_EINVAL, "rk_pack_nvfp4: pointers must be 16-byte aligned");
+  const long long threads = ((rows + 127) / 128 * 128) * ((k / 16 + 3) / 4 * 4);
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  pack_nvfp4_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k, global_scale,
+                                                         static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
+  return check_launch("pack_nvfp4");
+}
+
+extern "C" int rk_probe_rcp_approx_448(uint32_t* bits) {
+  if (!bits) return fail(RK_EINVAL, "rk_probe_rcp_approx_448: null pointer");
+  uint32_t* d = nullptr;
+  if (cudaMalloc(&d, 4) != cudaSuccess) return fail(RK_ECUDA, "rk_probe_rcp_approx_448: cudaMalloc failed");
+  probe_rcp_kernel<<<1, 1>>>(d);
+  cudaError_t e = cudaMemcpy(bits, d, 4, cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  if (e != cudaSuccess) return fail(RK_ECUDA, "rk_probe_rcp_approx_448: %s", cudaGetErrorString(e));
+  return RK_OK;
+}

@@ -1,0 +1,151 @@
+"""ctypes binding of ``librk_b200.so`` (the C ABI declared in ``include/rk_b200.h``).
+
+The library is the only compute path: if it is missing or a call fails, the wrappers raise.
+There is no PyTorch or CPU fallback behind these calls.
+"""
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+RK_OK = 0
+RK_EINVAL = -1
+RK_EUNSUPPORTED = -2
+RK_ECUDA = -3
+RK_EWORKSPACE = -4
+RK_EDEVICE = -5
+
+ACT_PLAIN, ACT_LUT_MUL, ACT_LUT = 0, 1, 2
+OP_W8A8, OP_W4A4, OP_W4A16, OP_FP8, OP_MXFP8, OP_NVFP4 = range(6)
+WORKSPACE_HEADER = 256
+
+_vp, _i64, _int, _sz, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t, ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/rk_b200.h one to one
+SIGNATURES = {
+    "rk_version": (_int, []),
+    "rk_last_error_string": (ctypes.c_char_p, []),
+    "rk_supports_device": (_int, [_int, _int]),
+    "rk_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
+    "rk_sf_bytes": (_sz, [_i64, _i64]),
+    "rk_read_status": (_int, [_vp, ctypes.POINTER(_int), _vp]),
+    "rk_probe_rcp_approx_448": (_int, [ctypes.POINTER(ctypes.c_uint32)]),
+    "rk_quant_rows": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _int, _int, _vp, _vp, _vp]),
+    "rk_quant_weight_int": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "rk_quant_rows_modulated": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _f32, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
+    "rk_rmsnorm_quant_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _vp, _vp, _vp, _vp]),
+    "rk_gemm_int": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
+    "rk_gemm_int_acc": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
+    "rk_pack_w4_g128": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_gemm_w4a16_g128": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "rk_quant_tensor_fp8": (_int, [_vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "rk_quant_tensor_fp8_with_scale": (_int, [_vp, _i64, _vp, _vp, _vp]),
+    "rk_gemm_fp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "rk_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "rk_pack_nvfp4": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "rk_nvfp4_global_scale": (_int, [_vp, _i64, _vp, _vp, _sz, _vp]),
+    "rk_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def library_path():
+    """Location of the shared library: ``RK_B200_SO`` if set, else next to this file."""
+    override = os.environ.get("RK_B200_SO")
+    return Path(override) if override else Path(__file__).resolve().parent / "librk_b200.so"
+
+
+def load():
+    """Load the library once and declare every signature.  Raises RuntimeError when it is missing."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not path.exists():
+            raise RuntimeError(
+                f"{path} does not exist: build it with robotics-the-speedup-paradox_b200/build.py "
+                "(there is no fallback implementation)"
+            )
+        lib = ctypes.CDLL(str(path))
+        missing = [name for name in SIGNATURES if not hasattr(lib, name)]
+        if missing:
+            raise RuntimeError(f"{path} lacks entry points {missing}")
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+        return lib
+
+
+def backend_status():
+    """(available, error) without raising, in the manner of the reference's extension loaders
+    (src/robotics_kernels/blackwell/extension_loader.py:19-64)."""
+    try:
+        load()
+    except (OSError, RuntimeError) as error:
+        return False, str(error)
+    return True, None
+
+
+def last_error():
+    return load().rk_last_error_string().decode()
+
+
+def check(code, what):
+    """Translate a return code into the exception type the reference surface raises."""
+    if code == RK_OK:
+        return
+    message = f"{what}: {last_error()} (code {code})"
+    if code == RK_EINVAL:
+        raise ValueError(message)
+    raise RuntimeError(message)
+
+
+def ptr(tensor):
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+def stream_ptr(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+# ---- per (device, stream) scratch buffers ---------------------------------------------------
+_workspaces = {}
+
+
+def workspace(device, nbytes):
+    """Zero-initialised scratch tensor for the current stream of `device`, at least `nbytes` long.
+
+    Kernels keep the buffer zero-filled between calls, so it is cleared only when (re)allocated.
+    Growing replaces the buffer; callers that captured the old one in a CUDA graph keep it alive
+    through their own reference.
+    """
+    device = torch.device(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def gemm_workspace(op, device, m, n, k):
+    need = load().rk_workspace_bytes(op, m, n, k)
+    return workspace(device, need)
+
+
+def read_status(buf):
+    code = ctypes.c_int(0)
+    rc = load().rk_read_status(ptr(buf), ctypes.byref(code), stream_ptr(buf.device))
+    check(rc, "rk_read_status")
+    return code.value
