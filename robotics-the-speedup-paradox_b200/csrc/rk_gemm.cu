@@ -91,25 +91,15 @@ int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dtype, in
 }
 
 // ------------------------------------------------------------------ workspace layout
-// [0, 256) status area (word 0 = status, word 16 = amax staging) | counters | partial sums
-constexpr size_t kMaxCounters = 8192;
-constexpr size_t kCounterBytes = kMaxCounters * sizeof(unsigned);
-
+// [0, 256) status area (word 0 = status, word 16 = amax staging) | op-specific scratch
 struct Workspace {
   int* status;
-  unsigned* counters;
-  int* partial;
-  size_t partial_bytes;
 };
 
 int carve_workspace(void* ws, size_t bytes, Workspace* out, const char* who) {
-  if (!ws || bytes < RK_WORKSPACE_HEADER + kCounterBytes) return fail(RK_EWORKSPACE, "%s: workspace missing or too small", who);
+  if (!ws || bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace missing or too small", who);
   if (!aligned16(ws)) return fail(RK_EWORKSPACE, "%s: workspace must be 16-byte aligned", who);
-  uint8_t* p = static_cast<uint8_t*>(ws);
-  out->status = reinterpret_cast<int*>(p);
-  out->counters = reinterpret_cast<unsigned*>(p + RK_WORKSPACE_HEADER);
-  out->partial = reinterpret_cast<int*>(p + RK_WORKSPACE_HEADER + kCounterBytes);
-  out->partial_bytes = bytes - RK_WORKSPACE_HEADER - kCounterBytes;
+  out->status = reinterpret_cast<int*>(ws);
   return RK_OK;
 }
 
@@ -121,12 +111,12 @@ int pow2_at_least(int v, int lo) {
 
 // ------------------------------------------------------------------ tile selection
 struct Plan {
-  int swap, bn, tiles_a, tiles_b, splits, stages, tmem_cols, smem_bytes;
+  int swap, bn, tiles_a, tiles_b, splits, stages, tmem_cols, acc_stride, acc_bufs, out_bufs, smem_bytes, grid_x;
 };
 
 // `tactic` only nudges the shape of the decomposition (it can never change integer results and
 // only reorders fp32 partial sums): bit 0 forbids swap, bit 1 forbids split-K, bit 2 halves bn.
-Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic, size_t partial_bytes) {
+Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   Plan pl{};
   const bool block_scaled = kind == KIND_MXF8 || kind == KIND_NVF4;
   // Weights on the 128-lane axis whenever the activation row count fits one or a few
@@ -135,40 +125,58 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic, size_t p
   // only one must start on a multiple of 128 rows: they swap only when one tile covers m.
   pl.swap = (m <= (block_scaled ? 256 : 1024) && !(tactic & 1)) ? 1 : 0;
   if (pl.swap) {
-    // smallest number of <=256-row chunks, rows per chunk rounded up to 16 (block-scaled: 32)
+    // fewest <=256-row chunks; a lone chunk may be any multiple of 16 rows (32 when block-scaled),
+    // several chunks must be multiples of 32 rows (the TMA store works on 32-row boxes)
     const int chunks = static_cast<int>((m + 255) / 256);
-    const int q = block_scaled ? 32 : 16;
+    const int q = (block_scaled || chunks > 1) ? 32 : 16;
     int bn = static_cast<int>(round_up((m + chunks - 1) / chunks, q));
-    if ((tactic & 4) && bn >= 2 * q) bn = static_cast<int>(round_up(bn / 2, q));
+    if ((tactic & 4) && bn >= 64 && !block_scaled) bn = static_cast<int>(round_up(bn / 2, 32));
     pl.bn = bn;
     pl.tiles_a = static_cast<int>((n + 127) / 128);
     pl.tiles_b = static_cast<int>((m + bn - 1) / bn);
   } else {
+    // the TMA store of this layout works on 64-column boxes: bn is a multiple of 64
     pl.bn = (tactic & 4) ? 128 : 256;
-    if (n < pl.bn) pl.bn = static_cast<int>(round_up(n, block_scaled ? 32 : 16));
+    if (n < pl.bn) pl.bn = static_cast<int>(round_up(n, 64));
     pl.tiles_a = static_cast<int>((m + 127) / 128);
     pl.tiles_b = static_cast<int>((n + pl.bn - 1) / pl.bn);
   }
-  const int stage = gemm_stage_bytes(kind, pl.bn);
-  pl.stages = kSmemBudget / stage;
-  if (pl.stages > kMaxStages) pl.stages = kMaxStages;
-  if (pl.stages > kblocks) pl.stages = kblocks < 2 ? 2 : kblocks;
-  pl.smem_bytes = pl.stages * stage + 1024;
-  pl.tmem_cols = block_scaled ? 512 : pow2_at_least(pl.bn, 32);
-  // split-K: fill the machine when the output has few tiles; keep >= 2 K blocks per split
-  pl.splits = 1;
+  // TMEM: accumulator buffers (+ 48 scale-factor columns for the block-scaled kinds)
+  pl.acc_stride = static_cast<int>(round_up(pl.bn, 32));
+  const int sf_cols = block_scaled ? 48 : 0;
+  pl.acc_bufs = (2 * pl.acc_stride + sf_cols <= 512) ? 2 : 1;
+  pl.tmem_cols = pow2_at_least(pl.acc_bufs * pl.acc_stride + sf_cols, 32);
+  // split-K across a cluster when the tiles cannot occupy the machine; >= 2 K blocks per CTA
   const long long tiles = static_cast<long long>(pl.tiles_a) * pl.tiles_b;
-  if (!(tactic & 2) && tiles < kNumSms && tiles <= static_cast<long long>(kMaxCounters)) {
-    int s = static_cast<int>((kNumSms + tiles - 1) / tiles);
+  pl.splits = 1;
+  if (!(tactic & 2) && tiles * 2 <= kNumSms) {
+    int s = static_cast<int>(kNumSms / tiles);
+    if (s > 8) s = 8;
     if (s > kblocks / 2) s = kblocks / 2;
-    if (static_cast<size_t>(m) * n * 4 > partial_bytes) s = 1;
     if (s > 1) pl.splits = s;
   }
+  // shared memory: pipeline stages + output staging + per-tile vectors
+  const int stage = gemm_stage_bytes(kind, pl.bn);
+  pl.out_bufs = 2;
+  int budget = kSmemBudget - kVecBytes - pl.out_bufs * kOutBufBytes;
+  if (budget / stage < 4 && (kSmemBudget - kVecBytes - kOutBufBytes) / stage >= 4) {
+    pl.out_bufs = 1;  // one more pipeline stage is worth more than a second staging buffer
+    budget = kSmemBudget - kVecBytes - kOutBufBytes;
+  }
+  pl.stages = budget / stage;
+  if (pl.stages > kMaxStages) pl.stages = kMaxStages;
+  const int kb_per_cta = (kblocks + pl.splits - 1) / pl.splits;
+  if (pl.stages > kb_per_cta) pl.stages = kb_per_cta < 2 ? 2 : kb_per_cta;
+  // the split-K exchange parks a bn x 128 x 4-byte tile in the stage memory
+  while (pl.splits > 1 && pl.stages * stage < pl.bn * 512) ++pl.stages;
+  pl.smem_bytes = pl.stages * stage + pl.out_bufs * kOutBufBytes + kVecBytes + 1024;
+  pl.grid_x = pl.splits > 1 ? static_cast<int>(tiles) : static_cast<int>(tiles < kNumSms ? tiles : kNumSms);
   return pl;
 }
 
 template <int KIND>
-int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmParams& p, const Plan& pl, cudaStream_t st) {
+int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out, const GemmParams& p,
+              const Plan& pl, cudaStream_t st) {
   static bool configured_dev[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -179,9 +187,24 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmParams
     if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  const dim3 grid(pl.tiles_a, pl.tiles_b, pl.splits);
-  rk_gemm_tc_kernel<KIND><<<grid, kGemmThreads, pl.smem_bytes, st>>>(tm_a, tm_b, p);
-  return check_launch("rk_gemm_tc_kernel");
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.grid_x, 1, pl.splits);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = pl.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_kernel<KIND>, tm_a, tm_b, tm_out, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_gemm_tc_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
 }
 
 struct TcArgs {
@@ -214,9 +237,9 @@ int run_tc(const TcArgs& a) {
   int rc = carve_workspace(a.workspace, a.workspace_bytes, &ws, a.who);
   if (rc != RK_OK) return rc;
   const int kblocks = static_cast<int>((a.k_bytes + kStageKBytes - 1) / kStageKBytes);
-  const Plan pl = make_plan(a.kind, a.m, a.n, kblocks, a.tactic, ws.partial_bytes);
+  const Plan pl = make_plan(a.kind, a.m, a.n, kblocks, a.tactic);
 
-  CUtensorMap tm_act, tm_wgt;
+  CUtensorMap tm_act, tm_wgt, tm_out;
   const uint32_t box_act = pl.swap ? pl.bn : kTileA;
   const uint32_t box_wgt = pl.swap ? kTileA : pl.bn;
   rc = make_map_2d(&tm_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, box_act,
@@ -225,6 +248,18 @@ int run_tc(const TcArgs& a) {
   rc = make_map_2d(&tm_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.n, a.k_bytes, kStageKBytes, box_wgt,
                    CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
+  if (a.out != nullptr && a.acc_out == nullptr) {
+    // output tiles leave through TMA: 32 rows x 128 channels (swap) or 128 rows x 64 channels
+    if (pl.swap)
+      rc = make_map_2d(&tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 128, 32,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+    else
+      rc = make_map_2d(&tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 64, 128,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != RK_OK) return rc;
+  } else {
+    tm_out = tm_act;  // unused by the raw-accumulator variant
+  }
 
   GemmParams p{};
   p.m = static_cast<int>(a.m);
@@ -237,6 +272,11 @@ int run_tc(const TcArgs& a) {
   p.splits = pl.splits;
   p.stages = pl.stages;
   p.tmem_cols = pl.tmem_cols;
+  p.acc_stride = pl.acc_stride;
+  p.acc_bufs = pl.acc_bufs;
+  p.out_bufs = pl.out_bufs;
+  p.tiles_a = pl.tiles_a;
+  p.tiles_b = pl.tiles_b;
   p.ldo = a.n;
   p.scale_act = a.scale_act;
   p.scale_wgt = a.scale_wgt;
@@ -247,32 +287,57 @@ int run_tc(const TcArgs& a) {
   p.sf_wgt = a.sf_wgt;
   p.sf_kt = a.sf_kt;
   p.status = ws.status;
-  p.counters = ws.counters;
-  p.partial = ws.partial;
   const CUtensorMap& tm_a = pl.swap ? tm_wgt : tm_act;
   const CUtensorMap& tm_b = pl.swap ? tm_act : tm_wgt;
   switch (a.kind) {
-    case KIND_I8: return launch_tc<KIND_I8>(tm_a, tm_b, p, pl, a.stream);
-    case KIND_F8: return launch_tc<KIND_F8>(tm_a, tm_b, p, pl, a.stream);
-    case KIND_MXF8: return launch_tc<KIND_MXF8>(tm_a, tm_b, p, pl, a.stream);
-    default: return launch_tc<KIND_NVF4>(tm_a, tm_b, p, pl, a.stream);
+    case KIND_I8: return launch_tc<KIND_I8>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_F8: return launch_tc<KIND_F8>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_MXF8: return launch_tc<KIND_MXF8>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    default: return launch_tc<KIND_NVF4>(tm_a, tm_b, tm_out, p, pl, a.stream);
   }
 }
 
-template <int BN>
-int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const W4Params& p, int tiles_n, int tiles_m, int smem,
-              cudaStream_t st) {
+// Two's-complement nibbles (low nibble = even k) -> int8, 16 packed bytes per thread.
+__global__ void __launch_bounds__(256) unpack_int4_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                          long long vectors) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= vectors) return;
+  const uint4 v = in[i];
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // per-byte sign extension of the even and odd nibbles: (u ^ 8) - 8
+    const uint32_t even = __vsub4((w[j] & 0x0F0F0F0Fu) ^ 0x08080808u, 0x08080808u);
+    const uint32_t odd = __vsub4(((w[j] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u, 0x08080808u);
+    o[2 * j] = __byte_perm(even, odd, 0x5140);      // e0 o0 e1 o1
+    o[2 * j + 1] = __byte_perm(even, odd, 0x7362);  // e2 o2 e3 o3
+  }
+  out[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+  out[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+int unpack_int4(const void* in, void* out, long long packed_bytes, cudaStream_t st) {
+  const long long vectors = packed_bytes / 16;
+  unpack_int4_kernel<<<static_cast<unsigned>((vectors + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint4*>(in), static_cast<uint4*>(out), vectors);
+  return check_launch("unpack_int4_kernel");
+}
+
+template <int BN, int UW>
+int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const W4Params& p, int tiles_n,
+              int tiles_m, int smem, cudaStream_t st) {
   static bool configured_dev[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   bool& configured = configured_dev[dev & 63];
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(rk_gemm_w4a16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(rk_gemm_w4a16_kernel<BN, UW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBudget + 1024);
     if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  rk_gemm_w4a16_kernel<BN><<<dim3(tiles_n, tiles_m), kW4Threads, smem, st>>>(tm_w, tm_x, p);
+  rk_gemm_w4a16_kernel<BN, UW><<<dim3(tiles_n, tiles_m), w4_threads(UW), smem, st>>>(tm_w, tm_x, tm_s, p);
   return check_launch("rk_gemm_w4a16_kernel");
 }
 
@@ -282,10 +347,9 @@ int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const W4Params& 
 using namespace rk;
 
 extern "C" size_t rk_workspace_bytes(int op, int64_t m, int64_t n, int64_t k) {
-  (void)k;
   if (m < 1 || n < 1) return 0;
-  size_t bytes = RK_WORKSPACE_HEADER + kCounterBytes;
-  if (op != RK_OP_W4A16) bytes += static_cast<size_t>(m) * static_cast<size_t>(n) * 4;  // split-K partial sums
+  size_t bytes = RK_WORKSPACE_HEADER;
+  if (op == RK_OP_W4A4) bytes += static_cast<size_t>(round_up(m + n, 16)) * static_cast<size_t>(round_up(k, 128));  // int8 copies
   return (bytes + 255) / 256 * 256;
 }
 
@@ -307,10 +371,32 @@ extern "C" int rk_read_status(void* workspace, int* code, void* stream) {
 static int gemm_int_common(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
                            int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits, int tactic, void* workspace,
                            size_t workspace_bytes, void* stream, const char* who) {
-  if (bits != 8) return fail(RK_EUNSUPPORTED, "%s: bits=%d has no kernel in this build", who, bits);
+  if (bits != 8 && bits != 4) return fail(RK_EINVAL, "%s: bits must be 4 or 8", who);
   if (kpad < 128 || kpad % 128 != 0) return fail(RK_EINVAL, "%s: kpad must be a positive multiple of 128", who);
   if (tactic < 0 || tactic > 7) return fail(RK_EINVAL, "%s: tactic must be 0..7", who);
   if (!acc && (!sa || !sb)) return fail(RK_EINVAL, "%s: null scale pointer", who);
+  if (!a || !b) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (m < 1 || n < 1 || m > (1 << 24) || n > (1 << 24) || kpad > (1 << 24)) return fail(RK_EINVAL, "%s: bad dimensions", who);
+  uint8_t* copies = nullptr;
+  size_t copies_bytes = 0;
+  if (bits == 4) {
+    // tcgen05 has no 4-bit integer kind: widen both operands to int8 in the scratch buffer (the
+    // products and the int32 sums are identical), then run the int8 kernel on the copies.
+    if (!aligned16(a) || !aligned16(b)) return fail(RK_EINVAL, "%s: operands must be 16-byte aligned", who);
+    const size_t need = rk_workspace_bytes(RK_OP_W4A4, m, n, kpad);
+    if (!workspace || workspace_bytes < need) return fail(RK_EWORKSPACE, "%s: workspace too small for the int8 copies", who);
+    uint8_t* a8 = static_cast<uint8_t*>(workspace) + need - static_cast<size_t>(round_up(m + n, 16)) * kpad;
+    uint8_t* b8 = a8 + static_cast<size_t>(m) * kpad;
+    int rc = unpack_int4(a, a8, m * kpad / 2, as_stream(stream));
+    if (rc != RK_OK) return rc;
+    rc = unpack_int4(b, b8, n * kpad / 2, as_stream(stream));
+    if (rc != RK_OK) return rc;
+    a = a8;
+    b = b8;
+    copies = a8;
+    copies_bytes = static_cast<size_t>(round_up(m + n, 16)) * kpad;
+    workspace_bytes = need - static_cast<size_t>(round_up(m + n, 16)) * kpad;
+  }
   TcArgs t{};
   t.kind = KIND_I8;
   t.act = a;
@@ -329,7 +415,13 @@ static int gemm_int_common(const void* a, const float* sa, const void* b, const 
   t.workspace_bytes = workspace_bytes;
   t.stream = as_stream(stream);
   t.who = who;
-  return run_tc(t);
+  int rc = run_tc(t);
+  if (rc == RK_OK && copies != nullptr) {
+    // leave the whole scratch buffer zero-filled, as every entry point promises
+    if (cudaMemsetAsync(copies, 0, copies_bytes, as_stream(stream)) != cudaSuccess)
+      return fail(RK_ECUDA, "%s: cudaMemsetAsync failed", who);
+  }
+  return rc;
 }
 
 extern "C" int rk_gemm_int(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
@@ -447,32 +539,43 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   if ((tactic & 4) && bn > 16) bn /= 2;
   const int tiles_n = static_cast<int>((n + 127) / 128);
   const int tiles_m = static_cast<int>((m + bn - 1) / bn);
-  const int stage = kW4RawBytes + 2 * bn * 128;
   W4Params p{};
   p.m = static_cast<int>(m);
   p.n = static_cast<int>(n);
   p.groups = static_cast<int>(k / 128);
-  p.xf_stages = bn >= 128 ? 2 : 3;
-  int stages = (kSmemBudget - p.xf_stages * kW4XfBytes) / stage;
-  if (stages > kW4MaxStages) stages = kW4MaxStages;
-  if (stages > p.groups) stages = p.groups < 2 ? 2 : p.groups;
-  p.stages = stages;
+  const int scales_bytes = static_cast<int>(round_up((k / 128) * 256, 1024));  // [groups][128] bf16 in shared memory
+  if (scales_bytes > 64 * 1024) return fail(RK_EUNSUPPORTED, "%s: k > 32768", who);
+  // ring depths: unpacked tiles (32 KB each) and activation tiles first, the rest goes to the
+  // raw-weight ring, whose depth is what keeps enough HBM requests in flight
+  const int x_bytes = 2 * bn * 128;
+  p.xf_stages = bn == 16 ? 4 : (bn == 128 ? 2 : 3);
+  p.x_stages = bn == 16 ? 4 : (bn == 128 ? 2 : 3);
+  if (p.x_stages > p.groups) p.x_stages = p.groups;
+  int w_stages = (kSmemBudget - scales_bytes - p.xf_stages * kW4XfBytes - p.x_stages * x_bytes) / kW4RawBytes;
+  if (w_stages > kW4MaxW) w_stages = kW4MaxW;
+  if (w_stages > p.groups) w_stages = p.groups;
+  if (w_stages < 2) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
+  p.w_stages = w_stages;
   p.ldo = n;
-  p.scales = static_cast<const __nv_bfloat16*>(scales);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = ws.status;
-  const int smem = stages * stage + p.xf_stages * kW4XfBytes + 1024;
-  CUtensorMap tm_w, tm_x;
+  const int smem = p.xf_stages * kW4XfBytes + p.x_stages * x_bytes + w_stages * kW4RawBytes + scales_bytes + 1024;
+  if (!aligned16(scales)) return fail(RK_EINVAL, "%s: scales must be 16-byte aligned", who);
+  CUtensorMap tm_w, tm_x, tm_s;
+  const uint32_t group_box = static_cast<uint32_t>(p.groups < 256 ? p.groups : 256);
+  rc = make_map_2d(&tm_s, scales, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k / 128, n * 2, 128, group_box,
+                   CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != RK_OK) return rc;
   rc = make_map_2d(&tm_w, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k / 2, n, k / 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_64B);
   if (rc != RK_OK) return rc;
   rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
   cudaStream_t st = as_stream(stream);
   switch (bn) {
-    case 16: return launch_w4<16>(tm_w, tm_x, p, tiles_n, tiles_m, smem, st);
-    case 32: return launch_w4<32>(tm_w, tm_x, p, tiles_n, tiles_m, smem, st);
-    case 64: return launch_w4<64>(tm_w, tm_x, p, tiles_n, tiles_m, smem, st);
-    default: return launch_w4<128>(tm_w, tm_x, p, tiles_n, tiles_m, smem, st);
+    case 16: return launch_w4<16, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+    case 32: return launch_w4<32, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+    case 64: return launch_w4<64, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+    default: return launch_w4<128, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
   }
 }

@@ -3,12 +3,20 @@
 //
 //   D[rowsA, rowsB] = A[rowsA, K] . B[rowsB, K]^T        (both operands K-major)
 //
-// One CTA computes one 128 x bn accumulator tile that lives in TMEM.  The "A role" (128 rows on
-// the MMA M axis, one TMEM lane per row) is taken by the weights when `swap` is set, so that a
-// ragged, small activation row count lands on the MMA N axis (any multiple of 16 up to 256)
-// instead of being padded to 128.  Split-K (grid.z) spreads weight streaming over all SMs for
-// small outputs; partial sums are combined in a zero-initialised scratch buffer by the CTA that
-// arrives last on a per-tile counter (no spinning), which also restores the scratch to zero.
+// A CTA computes 128 x bn accumulator tiles that live in TMEM.  The "A role" (128 rows on the MMA
+// M axis, one TMEM lane per row) is taken by the weights when `swap` is set, so that a ragged,
+// small activation row count lands on the MMA N axis (any multiple of 16 up to 256) instead of
+// being padded to 128.
+//
+// Two schedules:
+//   * persistent (splits == 1): grid = min(tiles, SMs); each CTA walks tiles t, t + grid, ...;
+//     the accumulator is double-buffered in TMEM so the epilogue of one tile overlaps the MMAs
+//     of the next; output goes through a shared-memory staging tile and a TMA store.
+//   * split-K (splits > 1): a thread-block cluster of `splits` CTAs shares one output tile, each
+//     CTA reducing a slice of K; partial accumulators are exchanged through distributed shared
+//     memory (no global scratch, no atomics, fixed summation order) and each CTA finishes and
+//     stores a slice of the tile's columns.  Used when the output has too few tiles to put
+//     every SM to work streaming weights.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4) .. +31).
@@ -26,6 +34,8 @@ constexpr int kGemmThreads = 192;
 constexpr int kTileA = 128;        // rows of the A-role tile (MMA M)
 constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage (one 128-byte swizzle atom)
 constexpr int kMaxStages = 8;
+constexpr int kOutBufBytes = 16 * 1024;    // one output staging buffer (one or two are carved)
+constexpr int kVecBytes = 2 * 1024;        // per-tile B-role scale and bias vectors, 256 f32 entries each
 
 struct GemmParams {
   int m;        // activation rows (output rows)
@@ -34,12 +44,16 @@ struct GemmParams {
   int k_valid_mmas_last;  // MMAs (32 bytes of K each) to issue in the last K block (1..4)
   int bn;       // rows of the B-role tile (MMA N): multiple of 16, <= 256
   int swap;     // 1: A role = weights, B role = activations
-  int splits;   // split-K factor (grid.z)
+  int splits;   // split-K factor == cluster size along z (1 = persistent schedule)
   int stages;   // pipeline depth
   int tmem_cols;
+  int acc_stride;  // TMEM columns between the accumulator buffers
+  int acc_bufs;    // 1 or 2 accumulator buffers in TMEM
+  int out_bufs;    // 1 or 2 output staging buffers in shared memory
+  int tiles_a, tiles_b;
   long long ldo;  // output row stride (elements)
-  const float* scale_act;   // KIND_I8: [m] row scales.  KIND_F8: pointer to one scalar.  block-scaled: optional scalar
-  const float* scale_wgt;   // KIND_I8: [n] channel scales.  KIND_F8: pointer to one scalar.  block-scaled: optional scalar
+  const float* scale_act;   // KIND_I8: [m] row scales.  other kinds: optional pointer to one scalar
+  const float* scale_wgt;   // KIND_I8: [n] channel scales.  other kinds: optional pointer to one scalar
   const __nv_bfloat16* bias;  // [n] or null
   __nv_bfloat16* out;         // [m, ldo]
   int* acc_out;               // optional raw accumulators [m, n] (s32 or f32 bits), written instead of `out`
@@ -47,8 +61,6 @@ struct GemmParams {
   const uint8_t* sf_wgt;
   int sf_kt;                  // 512-byte scale chunks per 128-row block along K
   int* status;                // device status word
-  unsigned* counters;         // split-K: one arrival counter per output tile (zero between calls)
-  int* partial;               // split-K: [m, n] 32-bit partial sums (zero between calls)
 };
 
 template <int KIND>
@@ -100,47 +112,84 @@ __device__ __forceinline__ float finish_value(uint32_t acc_bits, float s_act, fl
   }
 }
 
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most `N` of this thread's store groups still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t dsmem_ld_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
   using T = KindTraits<KIND>;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
-  __shared__ __align__(8) uint64_t bar_acc;
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int is_last_cta;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* const smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));  // generic pointer to smem_base
   const int stage_bytes = gemm_stage_bytes(KIND, p.bn);
   const int rb_b = (p.bn + 127) / 128;  // 128-row scale blocks in the B tile
+  // shared memory map: [pipeline stages][output staging, 1 or 2 x 16 KB][B-role scale + bias vectors]
+  const uint32_t out_stage_off = p.stages * stage_bytes;
+  const uint32_t vec_off = out_stage_off + p.out_bufs * kOutBufBytes;
 
-  const int tile_a = blockIdx.x;  // 128-row tile index along the A role
-  const int tile_b = blockIdx.y;  // bn-row tile index along the B role
-  const int split = blockIdx.z;
+  const bool split_mode = p.splits > 1;
+  const int num_tiles = p.tiles_a * p.tiles_b;
+  const int tile_first = split_mode ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int tile_step = split_mode ? num_tiles : static_cast<int>(gridDim.x);  // split mode: exactly one tile
+  const int split = split_mode ? static_cast<int>(blockIdx.z) : 0;
   const int kb_begin = static_cast<int>((static_cast<long long>(p.kblocks) * split) / p.splits);
   const int kb_end = static_cast<int>((static_cast<long long>(p.kblocks) * (split + 1)) / p.splits);
   const int nkb = kb_end - kb_begin;
-  const int row_a0 = tile_a * kTileA;
-  const int row_b0 = tile_b * p.bn;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    mbar_init(smem_u32(&bar_acc), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_acc_full[b]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 128);
+    }
     abort_flag = 0;
-    is_last_cta = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_out);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), static_cast<uint32_t>(p.tmem_cols));
@@ -150,9 +199,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  // TMEM columns: [0, bn) accumulator; block-scaled kinds keep scale factors after it.
-  const uint32_t tmem_sfa = tmem_base + 256;
-  const uint32_t tmem_sfb = tmem_base + 256 + 16;
+  // TMEM columns: two accumulator buffers, then (block-scaled kinds) the scale factors.
+  const uint32_t tmem_sfa = tmem_base + p.acc_bufs * p.acc_stride;
+  const uint32_t tmem_sfb = tmem_sfa + 16;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -164,38 +213,47 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint64_t pol_b = p.swap ? pol_x : pol_w;
       const uint8_t* sf_a = p.swap ? p.sf_wgt : p.sf_act;
       const uint8_t* sf_b = p.swap ? p.sf_act : p.sf_wgt;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % p.stages;
-        const uint32_t ph = (i / p.stages) & 1;
-        if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) break;
-        const uint32_t full = smem_u32(&bar_full[s]);
-        const uint32_t sa = smem_base + s * stage_bytes;
-        const uint32_t sb = sa + kTileA * kStageKBytes;
-        const int kb = kb_begin + i;
-        uint32_t tx = (kTileA + p.bn) * kStageKBytes;
-        // scale chunks present in this K block (the last block of a ragged K holds fewer)
-        int cs = 0;
-        if constexpr (T::kBlockScaled) {
-          cs = min(T::kSfChunksPerStage, p.sf_kt - kb * T::kSfChunksPerStage);
-          tx += cs * 512 * (1 + rb_b);
-        }
-        mbar_arrive_expect_tx(full, tx);
-        tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a);
-        tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b);
-        if constexpr (T::kBlockScaled) {
-          // Scale factors: contiguous 512-byte chunks in the 128-row swizzled global layout.
-          const uint32_t ssf = sb + p.bn * kStageKBytes;
-          const int c = T::kSfChunksPerStage;
-          const long long chunk0 = static_cast<long long>(kb) * c;
-          const uint8_t* src_a = sf_a + (static_cast<long long>(row_a0 / 128) * p.sf_kt + chunk0) * 512;
-          asm volatile(
-              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-              ::"r"(ssf), "l"(src_a), "r"(cs * 512), "r"(full) : "memory");
-          for (int rb = 0; rb < rb_b; ++rb) {
-            const uint8_t* src_b = sf_b + (static_cast<long long>(row_b0 / 128 + rb) * p.sf_kt + chunk0) * 512;
+      int it = 0;
+      bool alive = true;
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
+        const int row_a0 = (tile / p.tiles_b) * kTileA;
+        const int row_b0 = (tile % p.tiles_b) * p.bn;
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
+            alive = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t sa = smem_base + s * stage_bytes;
+          const uint32_t sb = sa + kTileA * kStageKBytes;
+          const int kb = kb_begin + i;
+          uint32_t tx = (kTileA + p.bn) * kStageKBytes;
+          // scale chunks present in this K block (the last block of a ragged K holds fewer)
+          int cs = 0;
+          if constexpr (T::kBlockScaled) {
+            cs = min(T::kSfChunksPerStage, p.sf_kt - kb * T::kSfChunksPerStage);
+            tx += cs * 512 * (1 + rb_b);
+          }
+          mbar_arrive_expect_tx(full, tx);
+          tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a);
+          tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b);
+          if constexpr (T::kBlockScaled) {
+            // Scale factors: contiguous 512-byte chunks in the 128-row swizzled global layout.
+            const uint32_t ssf = sb + p.bn * kStageKBytes;
+            const int c = T::kSfChunksPerStage;
+            const long long chunk0 = static_cast<long long>(kb) * c;
+            const uint8_t* src_a = sf_a + (static_cast<long long>(row_a0 / 128) * p.sf_kt + chunk0) * 512;
             asm volatile(
                 "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                ::"r"(ssf + (1 + rb) * c * 512), "l"(src_b), "r"(cs * 512), "r"(full) : "memory");
+                ::"r"(ssf), "l"(src_a), "r"(cs * 512), "r"(full) : "memory");
+            for (int rb = 0; rb < rb_b; ++rb) {
+              const uint8_t* src_b = sf_b + (static_cast<long long>(row_b0 / 128 + rb) * p.sf_kt + chunk0) * 512;
+              asm volatile(
+                  "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                  ::"r"(ssf + (1 + rb) * c * 512), "l"(src_b), "r"(cs * 512), "r"(full) : "memory");
+            }
           }
         }
       }
@@ -203,171 +261,308 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % p.stages;
-        const uint32_t ph = (i / p.stages) & 1;
-        if (!mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) break;
+      int it = 0, tcount = 0;
+      bool alive = true;
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step, ++tcount) {
+        const int ab = tcount % p.acc_bufs;
+        // the epilogue must have drained this accumulator buffer (its previous use)
+        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[ab]), ((tcount / p.acc_bufs) & 1) ^ 1, &abort_flag, p.status,
+                               RK_DEV_TIMEOUT_ACC_FREE)) break;
         tc_fence_after();
-        const uint32_t sa = smem_base + s * stage_bytes;
-        const uint32_t sb = sa + kTileA * kStageKBytes;
-        const uint64_t adesc = umma_desc_k128(sa);
-        const uint64_t bdesc = umma_desc_k128(sb);
-        const int nmma = (kb_begin + i == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
-        if constexpr (T::kBlockScaled) {
-          const uint32_t ssf = sb + p.bn * kStageKBytes;
-          const int c = T::kSfChunksPerStage;
-          // chunk (row block r, k chunk j) of the stage -> 4 TMEM columns
-          const int cs = min(c, p.sf_kt - (kb_begin + i) * c);
-          for (int j = 0; j < cs; ++j) {
-            tmem_cp_32x128b_warpx4(tmem_sfa + j * 4, umma_desc_noswizzle(ssf + j * 512, 16, 128));
-            for (int rb = 0; rb < rb_b; ++rb)
-              tmem_cp_32x128b_warpx4(tmem_sfb + (j * rb_b + rb) * 4,
-                                     umma_desc_noswizzle(ssf + ((1 + rb) * c + j) * 512, 16, 128));
+        const uint32_t d_tmem = tmem_base + ab * p.acc_stride;
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
+            alive = false;
+            break;
           }
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (k < nmma) {
-            const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
-            // 32 bytes of K per MMA: advance the descriptor start address by 32 >> 4.
-            const uint64_t ad = adesc + static_cast<uint64_t>(k * 2);
-            const uint64_t bd = bdesc + static_cast<uint64_t>(k * 2);
-            if constexpr (KIND == KIND_I8) {
-              mma_i8(tmem_base, ad, bd, umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn), accumulate);
-            } else if constexpr (KIND == KIND_F8) {
-              mma_f8f6f4(tmem_base, ad, bd, umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn), accumulate);
-            } else if constexpr (KIND == KIND_MXF8) {
-              // four MMAs share one set of scale columns; byte k of each 32-bit column is theirs
-              mma_mxf8(tmem_base, ad, bd, umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, k, k), tmem_sfa,
-                       tmem_sfb, accumulate);
-            } else {
-              mma_nvf4(tmem_base, ad, bd, umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 128, p.bn, 0, 0, 0),
-                       tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate);
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * stage_bytes;
+          const uint32_t sb = sa + kTileA * kStageKBytes;
+          const uint64_t adesc = umma_desc_k128(sa);
+          const uint64_t bdesc = umma_desc_k128(sb);
+          const int nmma = (kb_begin + i == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
+          if constexpr (T::kBlockScaled) {
+            const uint32_t ssf = sb + p.bn * kStageKBytes;
+            const int c = T::kSfChunksPerStage;
+            // chunk (row block r, k chunk j) of the stage -> 4 TMEM columns
+            const int cs = min(c, p.sf_kt - (kb_begin + i) * c);
+            for (int j = 0; j < cs; ++j) {
+              tmem_cp_32x128b_warpx4(tmem_sfa + j * 4, umma_desc_noswizzle(ssf + j * 512, 16, 128));
+              for (int rb = 0; rb < rb_b; ++rb)
+                tmem_cp_32x128b_warpx4(tmem_sfb + (j * rb_b + rb) * 4,
+                                       umma_desc_noswizzle(ssf + ((1 + rb) * c + j) * 512, 16, 128));
             }
           }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (k < nmma) {
+              const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
+              // 32 bytes of K per MMA: advance the descriptor start address by 32 >> 4.
+              const uint64_t ad = adesc + static_cast<uint64_t>(k * 2);
+              const uint64_t bd = bdesc + static_cast<uint64_t>(k * 2);
+              if constexpr (KIND == KIND_I8) {
+                mma_i8(d_tmem, ad, bd, umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn), accumulate);
+              } else if constexpr (KIND == KIND_F8) {
+                mma_f8f6f4(d_tmem, ad, bd, umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn), accumulate);
+              } else if constexpr (KIND == KIND_MXF8) {
+                // four MMAs share one set of scale columns; byte k of each 32-bit column is theirs
+                mma_mxf8(d_tmem, ad, bd, umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, k, k), tmem_sfa, tmem_sfb,
+                         accumulate);
+              } else {
+                mma_nvf4(d_tmem, ad, bd, umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 128, p.bn, 0, 0, 0),
+                         tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate);
+              }
+            }
+          }
+          tc_commit(smem_u32(&bar_empty[s]));  // stage reusable once these MMAs have read it
         }
-        tc_commit(smem_u32(&bar_empty[s]));  // stage reusable once these MMAs have read it
+        if (alive) tc_commit(smem_u32(&bar_acc_full[ab]));  // accumulator complete
       }
-      tc_commit(smem_u32(&bar_acc));  // accumulator complete
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;
-    const bool ok = mbar_wait_bounded(smem_u32(&bar_acc), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
-    tc_fence_after();
-    const int ra = row_a0 + quad * 32 + lane;  // this thread's row along the A role
+    const int et = quad * 32 + lane;  // 0..127: TMEM lane == row of the A-role tile
     const int lim_a = p.swap ? p.n : p.m;
     const int lim_b = p.swap ? p.m : p.n;
-    const bool ra_ok = ok && ra < lim_a;
-    const bool direct = (p.splits == 1);
-    // per-thread constants of the A-role row
-    float row_scale = 1.0f, row_bias = 0.0f;
-    const bool has_bias = p.bias != nullptr;
-    // (the raw-accumulator variant passes no scales at all)
-    if constexpr (KIND == KIND_I8) {
-      if (ra_ok && p.acc_out == nullptr) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
-    }
-    if (p.swap && has_bias && ra_ok && p.acc_out == nullptr) row_bias = __bfloat162float(p.bias[ra]);
+    const bool has_bias = p.bias != nullptr && p.acc_out == nullptr;
+    float* const vec_scale = reinterpret_cast<float*>(smem_gen + vec_off);  // [256] B-role scales
+    float* const vec_bias = vec_scale + 256;                                // [256] B-role bias (non-swap)
     float s_act_scalar = 1.0f, s_wgt_scalar = 1.0f;
     if constexpr (KIND != KIND_I8) {
       if (p.scale_act) s_act_scalar = *p.scale_act;
       if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
     }
-    for (int c0 = 0; c0 < p.bn; c0 += 16) {
-      uint32_t r[16];
-      __syncwarp();  // the collective TMEM load needs the whole warp, whatever the lanes skipped above
-      tmem_ld_16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
-      tc_wait_ld();
-      if (!ra_ok) continue;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int rbj = row_b0 + c0 + j;  // row along the B role
-        if (rbj >= lim_b) continue;
-        const int om = p.swap ? rbj : ra;
-        const int on = p.swap ? ra : rbj;
-        if (!direct) {
-          int* dst = p.partial + static_cast<long long>(om) * p.n + on;
-          if constexpr (KIND == KIND_I8) {
-            atomicAdd(dst, static_cast<int>(r[j]));
-          } else {
-            atomicAdd(reinterpret_cast<float*>(dst), __uint_as_float(r[j]));
-          }
-          continue;
-        }
-        if (p.acc_out) {
-          p.acc_out[static_cast<long long>(om) * p.n + on] = static_cast<int>(r[j]);
-          continue;
-        }
-        float sa_v, sw_v, bias_v;
+    int tcount = 0;
+    int pending_store = 0;  // epilogue thread 0: a TMA store may still be reading a staging buffer
+    int obuf = 0;
+    for (int tile = tile_first; tile < num_tiles; tile += tile_step, ++tcount) {
+      const int ab = tcount % p.acc_bufs;
+      const int row_a0 = (tile / p.tiles_b) * kTileA;
+      const int row_b0 = (tile % p.tiles_b) * p.bn;
+      const int ra = row_a0 + et;
+      const bool ra_ok = ra < lim_a;
+      // per-thread constants of the A-role row, and the B-role vectors of this tile into shared memory
+      float row_scale = 1.0f, row_bias = 0.0f;
+      if (p.acc_out == nullptr) {
         if constexpr (KIND == KIND_I8) {
-          sa_v = p.swap ? p.scale_act[om] : row_scale;
-          sw_v = p.swap ? row_scale : p.scale_wgt[on];
-        } else {
-          sa_v = s_act_scalar;
-          sw_v = s_wgt_scalar;
+          if (ra_ok) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
         }
-        bias_v = p.swap ? row_bias : (has_bias ? __bfloat162float(p.bias[on]) : 0.0f);
-        const float v = finish_value<KIND>(r[j], sa_v, sw_v, has_bias, bias_v);
-        p.out[static_cast<long long>(om) * p.ldo + on] = __float2bfloat16_rn(v);
+        if (p.swap && has_bias && ra_ok) row_bias = __bfloat162float(p.bias[ra]);
+        epi_bar_sync();  // previous tile's readers of the vectors are done
+        for (int j = et; j < p.bn; j += 128) {
+          const int rb = row_b0 + j;
+          float sv = 1.0f, bv = 0.0f;
+          if (rb < lim_b) {
+            if constexpr (KIND == KIND_I8) sv = p.swap ? p.scale_act[rb] : p.scale_wgt[rb];
+            if (!p.swap && has_bias) bv = __bfloat162float(p.bias[rb]);
+          }
+          vec_scale[j] = sv;
+          vec_bias[j] = bv;
+        }
+        epi_bar_sync();
+      }
+      const bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[ab]), (tcount / p.acc_bufs) & 1, &abort_flag, p.status,
+                                        RK_DEV_TIMEOUT_ACC);
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + ab * p.acc_stride + (static_cast<uint32_t>(quad * 32) << 16);
+
+      if (split_mode) {
+        // ---- split-K: park the raw partial accumulators in shared memory, column-major [bn][128]
+        uint32_t* const part = reinterpret_cast<uint32_t*>(smem_gen);
+        for (int c0 = 0; c0 < p.bn; c0 += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + c0, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(c0 + j) * 128 + et] = ok ? r[j] : 0u;
+        }
+        continue;  // reduction happens after the cluster barrier below
+      }
+
+      if (p.acc_out != nullptr) {
+        // ---- raw accumulator dump (parity aid): plain stores
+        for (int c0 = 0; c0 < p.bn; c0 += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + c0, r);
+          tc_wait_ld();
+          if (ra_ok && ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int rbj = row_b0 + c0 + j;
+              if (rbj < lim_b) {
+                const long long om = p.swap ? rbj : ra, on = p.swap ? ra : rbj;
+                p.acc_out[om * p.n + on] = static_cast<int>(r[j]);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+        continue;
+      }
+
+      // ---- finish values, stage them in shared memory, store with TMA (clipped at the matrix edge)
+      // swap:     chunk = 32 activation rows x 128 channels, row-major [32][128] bf16 (8 KB)
+      // non-swap: chunk = 128 activation rows x 64 channels, 128-byte-swizzled rows (16 KB)
+      const int chunk_cols = p.swap ? 32 : 64;
+      for (int cc = 0; cc < p.bn; cc += chunk_cols, obuf = (p.out_bufs == 2) ? (obuf ^ 1) : 0) {
+        uint8_t* const stage = smem_gen + out_stage_off + obuf * kOutBufBytes;
+        // the staging buffer was handed to TMA earlier: wait until that store has read it
+        if (et == 0 && pending_store) {
+          if (p.out_bufs == 2) tma_store_wait_read<1>();
+          else tma_store_wait_read<0>();
+        }
+        epi_bar_sync();
+        const int ncols = min(chunk_cols, p.bn - cc);
+        for (int c0 = 0; c0 < ncols; c0 += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + cc + c0, r);
+          tc_wait_ld();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float sv = vec_scale[cc + c0 + j];
+            if constexpr (KIND == KIND_I8) {
+              v[j] = p.swap ? finish_value<KIND>(r[j], sv, row_scale, has_bias, row_bias)
+                            : finish_value<KIND>(r[j], row_scale, sv, has_bias, vec_bias[cc + c0 + j]);
+            } else {
+              v[j] = finish_value<KIND>(r[j], s_act_scalar, s_wgt_scalar, has_bias,
+                                        p.swap ? row_bias : vec_bias[cc + c0 + j]);
+            }
+          }
+          if (p.swap) {
+            __nv_bfloat16* const srow = reinterpret_cast<__nv_bfloat16*>(stage);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) srow[(c0 + j) * 128 + et] = __float2bfloat16_rn(v[j]);
+          } else {
+            // 16 values = two 16-byte chunks (index c0/8, c0/8+1) of this thread's 128-byte row
+            uint4 lo = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                  pack_bf16x2(v[6], v[7]));
+            uint4 hi = make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]),
+                                  pack_bf16x2(v[14], v[15]));
+            const int ch = c0 >> 3;
+            *reinterpret_cast<uint4*>(stage + et * 128 + (((ch) ^ (et & 7)) << 4)) = lo;
+            *reinterpret_cast<uint4*>(stage + et * 128 + (((ch + 1) ^ (et & 7)) << 4)) = hi;
+          }
+        }
+        if (cc + chunk_cols >= p.bn) {
+          // last TMEM read of this tile is done: hand the accumulator buffer back to the MMA warp
+          tc_fence_before();
+          mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (et == 0) {
+          if (ok) {
+            if (p.swap) tma_store_2d(&tm_out, smem_u32(stage), row_a0, row_b0 + cc);
+            else tma_store_2d(&tm_out, smem_u32(stage), row_b0 + cc, row_a0);
+          }
+          tma_store_commit();
+          pending_store = 1;
+        }
       }
     }
+    if (et == 0) tma_store_wait_all();
   }
 
-  // ---------------------------------------------------------------- split-K fix-up (last arriver)
-  if (p.splits > 1) {
-    __threadfence();
+  // ---------------------------------------------------------------- split-K: reduce across the cluster
+  if (split_mode) {
     __syncthreads();
-    if (threadIdx.x == 0) {
-      const unsigned tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-      const unsigned prev = atomicAdd(&p.counters[tile_id], 1u);
-      is_last_cta = (prev == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
-      if (is_last_cta) p.counters[tile_id] = 0;  // restore for the next call
-    }
-    __syncthreads();
-    if (is_last_cta && !abort_flag) {
-      __threadfence();
+    cluster_sync_all();  // every CTA's partial tile is in its shared memory
+    if (warp >= 2) {
+      const int quad = warp & 3;
+      const int et = quad * 32 + lane;
+      const int tile = tile_first;
+      const int row_a0 = (tile / p.tiles_b) * kTileA;
+      const int row_b0 = (tile % p.tiles_b) * p.bn;
       const int lim_a = p.swap ? p.n : p.m;
       const int lim_b = p.swap ? p.m : p.n;
-      const bool has_bias = p.bias != nullptr;
+      const int ra = row_a0 + et;
+      const bool has_bias = p.bias != nullptr && p.acc_out == nullptr;
       float s_act_scalar = 1.0f, s_wgt_scalar = 1.0f;
       if constexpr (KIND != KIND_I8) {
         if (p.scale_act) s_act_scalar = *p.scale_act;
         if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
       }
-      // Walk the tile so that consecutive threads touch consecutive output columns.
-      const int span_n = p.swap ? kTileA : p.bn;   // tile extent along output columns
-      const int span_m = p.swap ? p.bn : kTileA;   // tile extent along output rows
-      const int m0 = p.swap ? row_b0 : row_a0;
-      const int n0 = p.swap ? row_a0 : row_b0;
-      const int lim_m = p.swap ? lim_b : lim_a;
-      const int lim_n = p.swap ? lim_a : lim_b;
-      for (int idx = threadIdx.x; idx < span_n * span_m; idx += kGemmThreads) {
-        const int om = m0 + idx / span_n;
-        const int on = n0 + idx % span_n;
-        if (om >= lim_m || on >= lim_n) continue;
-        int* src = p.partial + static_cast<long long>(om) * p.n + on;
-        const uint32_t bits = static_cast<uint32_t>(__ldcg(src));
-        *src = 0;  // restore for the next call
-        if (p.acc_out) {
-          p.acc_out[static_cast<long long>(om) * p.n + on] = static_cast<int>(bits);
-          continue;
+      // this CTA finishes columns [c_lo, c_hi) of the tile
+      const int per = (p.bn + p.splits - 1) / p.splits;
+      const int c_lo = static_cast<int>(cluster_ctarank()) * per;
+      const int c_hi = min(p.bn, c_lo + per);
+      float row_scale = 1.0f, row_bias = 0.0f;
+      if (ra < lim_a && p.acc_out == nullptr) {
+        if constexpr (KIND == KIND_I8) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
+        if (p.swap && has_bias) row_bias = __bfloat162float(p.bias[ra]);
+      }
+      // shared::cluster base address of every peer's partial tile
+      uint32_t peer[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        peer[q] = 0;
+        if (q < p.splits)
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[q]) : "r"(smem_base), "r"(q));
+      }
+      for (int c4 = c_lo; c4 < c_hi; c4 += 4) {
+        // issue the loads of four columns from every peer back to back, then add in rank order
+        uint32_t v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            v[u][q] = 0u;
+            if (q < p.splits && c4 + u < c_hi)
+              asm volatile("ld.shared::cluster.u32 %0, [%1];"
+                           : "=r"(v[u][q])
+                           : "r"(peer[q] + static_cast<uint32_t>((c4 + u) * 128 + et) * 4u)
+                           : "memory");
+          }
         }
-        float sa_v = s_act_scalar, sw_v = s_wgt_scalar;
-        if constexpr (KIND == KIND_I8) {
-          sa_v = p.scale_act[om];
-          sw_v = p.scale_wgt[on];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c4 + u;
+          if (c >= c_hi) continue;
+          uint32_t total = 0;
+          float ftotal = 0.0f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {  // fixed order: rank 0, 1, ... (absent ranks contribute zero)
+            if constexpr (KIND == KIND_I8) total += v[u][q];
+            else ftotal += __uint_as_float(v[u][q]);
+          }
+          if constexpr (KIND != KIND_I8) total = __float_as_uint(ftotal);
+          const int rbj = row_b0 + c;
+          if (ra >= lim_a || rbj >= lim_b || abort_flag) continue;
+          const long long om = p.swap ? rbj : ra, on = p.swap ? ra : rbj;
+          if (p.acc_out != nullptr) {
+            p.acc_out[om * p.n + on] = static_cast<int>(total);
+            continue;
+          }
+          float val;
+          const float bias_v = p.swap ? row_bias : (has_bias ? __bfloat162float(p.bias[rbj]) : 0.0f);
+          if constexpr (KIND == KIND_I8) {
+            const float other = p.swap ? p.scale_act[rbj] : p.scale_wgt[rbj];
+            val = p.swap ? finish_value<KIND>(total, other, row_scale, has_bias, bias_v)
+                         : finish_value<KIND>(total, row_scale, other, has_bias, bias_v);
+          } else {
+            val = finish_value<KIND>(total, s_act_scalar, s_wgt_scalar, has_bias, bias_v);
+          }
+          p.out[om * p.ldo + on] = __float2bfloat16_rn(val);
         }
-        const float bias_v = has_bias ? __bfloat162float(p.bias[on]) : 0.0f;
-        const float v = finish_value<KIND>(bits, sa_v, sw_v, has_bias, bias_v);
-        p.out[static_cast<long long>(om) * p.ldo + on] = __float2bfloat16_rn(v);
       }
     }
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }

@@ -1,0 +1,109 @@
+"""GPU parity of the W4A16 int4 group-128 path: packed nibbles and bf16 group scales bit-exact,
+GEMM within 1e-2 relative Frobenius error of dequantize -> fp32 matmul (the stated tolerance)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as F
+from oracle import w4a16 as OW
+from rk_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def H():
+    import gpu_helpers
+
+    return gpu_helpers
+
+
+def run_gemm(H, x, q, s, bias, m, n, k, tactic=0):
+    buf = torch.full((m + 2, n), 7.0, dtype=torch.bfloat16, device=H.DEVICE)
+    out = buf[1:m + 1]
+    ws = _lib.gemm_workspace(_lib.OP_W4A16, H.DEVICE, m, n, k)
+    H.call("rk_gemm_w4a16_g128", _lib.ptr(x), _lib.ptr(q), _lib.ptr(s), _lib.ptr(bias), _lib.ptr(out), m, n, k,
+           tactic, _lib.ptr(ws), ws.numel(), H.stream())
+    assert _lib.read_status(ws) == 0
+    assert (buf[0] == 7.0).all() and (buf[m + 1] == 7.0).all()
+    return out
+
+
+def pack(H, w):
+    n, k = w.shape
+    q = torch.empty((n, k // 2), dtype=torch.uint8, device=H.DEVICE)
+    s = torch.empty((k // 128, n), dtype=torch.bfloat16, device=H.DEVICE)
+    H.call("rk_pack_w4_g128", _lib.ptr(w), n, k, _lib.ptr(q), _lib.ptr(s), H.stream())
+    return q, s
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (1000, 384), (16384, 2048)])
+def test_pack_codes_and_scales_bit_exact(H, shape):
+    w = H.randn_bf16(shape, 0.02, 6)
+    w[5, :128] = 0  # an all-zero group: scale 1.0, codes 0
+    q, s = pack(H, w.to(H.DEVICE))
+    ep, es, _ = OW.pack_weight(H.to_np(w))
+    assert np.array_equal(q.cpu().numpy(), ep)
+    assert np.array_equal(H.bits(s), F.bf16_bits(es))
+    assert H.to_np(s)[0, 5] == 1.0
+
+
+@pytest.mark.parametrize("m", [1, 8, 50, 256])
+def test_cfg2_gemm_within_tolerance(H, m):
+    """BASELINE config 2: N=16384, K=2048, M in {1, 8, 50, 256}."""
+    n, k = 16384, 2048
+    x = H.randn_bf16((m, k), 1.0, 5)
+    w = H.randn_bf16((n, k), 0.02, 6)
+    q, s = pack(H, w.to(H.DEVICE))
+    out = run_gemm(H, x.to(H.DEVICE), q, s, None, m, n, k)
+    ep, es, _ = OW.pack_weight(H.to_np(w))
+    _, want = OW.gemm(H.to_np(x), ep, es)
+    assert H.rel_frobenius(H.to_np(out), want) < TOL
+    # element-wise: the only rounding beyond fp32 accumulation order is the bf16 output cast
+    assert np.abs(H.to_np(out) - want).max() <= 2.0 ** -8 * np.abs(want).max() + 1e-6
+
+
+@pytest.mark.parametrize("shape", [(8, 128, 128), (16, 256, 512), (100, 1000, 384), (130, 136, 256), (300, 256, 128)])
+@pytest.mark.parametrize("tactic", [0, 4])
+def test_ragged_shapes_and_bias(H, shape, tactic):
+    m, n, k = shape
+    x = H.randn_bf16((m, k), 1.0, 7)
+    w = H.randn_bf16((n, k), 0.02, 8)
+    bias = H.randn_bf16((n,), 0.5, 9)
+    q, s = pack(H, w.to(H.DEVICE))
+    out = run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, tactic)
+    ep, es, _ = OW.pack_weight(H.to_np(w))
+    _, want = OW.gemm(H.to_np(x), ep, es, H.to_np(bias))
+    assert H.rel_frobenius(H.to_np(out), want) < TOL
+
+
+def test_linearity_at_full_size(H):
+    """Size-independent property: the GEMM is linear in the activations (exact powers of two)."""
+    n, k, m = 16384, 2048, 50
+    x = H.randn_bf16((m, k), 1.0, 10).to(H.DEVICE)
+    w = H.randn_bf16((n, k), 0.02, 11).to(H.DEVICE)
+    q, s = pack(H, w)
+    y1 = run_gemm(H, x, q, s, None, m, n, k)
+    y4 = run_gemm(H, (x * 4).contiguous(), q, s, None, m, n, k)
+    assert torch.equal(y4, y1 * 4)
+    assert torch.equal(run_gemm(H, x, q, s, None, m, n, k), y1)  # deterministic
+
+
+def test_module_surface(H):
+    from rk_b200.w4a16_linear import W4A16Linear
+
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(256, 136, device="cuda", dtype=torch.bfloat16).eval()
+    layer = W4A16Linear.from_linear(lin)
+    x = torch.randn(2, 5, 256, device="cuda", dtype=torch.bfloat16)
+    y = layer(x)
+    assert y.shape == (2, 5, 136)
+    ep, es, _ = OW.pack_weight(H.to_np(lin.weight))
+    _, want = OW.gemm(H.to_np(x.reshape(10, 256)), ep, es, H.to_np(lin.bias))
+    assert H.rel_frobenius(H.to_np(y).reshape(10, 136), want) < TOL
+    with pytest.raises(ValueError):
+        layer(torch.zeros(2, 128, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        W4A16Linear.from_linear(torch.nn.Linear(256, 136, dtype=torch.bfloat16))

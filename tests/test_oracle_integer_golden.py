@@ -63,7 +63,7 @@ def test_known_answer_formula(golden, case, bits):
     formula_scales = (np.abs(x).max(axis=1) / limit).astype(np.float32)
     same = kernel_scales == formula_scales
     assert np.array_equal(F.bf16_bits(out)[same], want[same])
-    np.testing.assert_allclose(out[~same], bf16_from_bits(want)[~same], rtol=0.05, atol=0.02)
+    np.testing.assert_allclose(out[~same], bf16_from_bits(want)[~same], rtol=0.05, atol=0.02 if bits == 8 else 0.3)
 
 
 @pytest.mark.parametrize("case", range(2))
