@@ -77,6 +77,49 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return false;
 }
 
+// Ring position: stage index plus the phase parity of that stage's barriers.  Advancing costs an
+// add, a compare and a select; the single-thread roles (TMA producer, MMA issuer) are latency
+// bound, so integer division by a run-time ring depth in their loops would dominate them.
+struct Ring {
+  int stage;
+  uint32_t phase;
+  __device__ __forceinline__ void advance(int depth) {
+    if (++stage == depth) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+// Warp-wide bounded wait: lane 0 polls, the verdict is broadcast.  Thirty-two lanes polling one
+// barrier word would flood the shared-memory pipe that the TMA-issuing and MMA-issuing threads of
+// the same SM also need; one polling lane per warp, backing off with short sleeps after the
+// first few misses, keeps that pipe free.  Every lane of the warp must call this.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code, uint32_t sleep_ns = 32) {
+  int ok = 0;
+  if ((threadIdx.x & 31) == 0) {
+    ok = 1;
+    uint32_t it = 0;
+    while (!mbar_try_wait(bar, parity)) {
+      if (++it > 4) {
+        if (*abort_flag) {
+          ok = 0;
+          break;
+        }
+        __nanosleep(sleep_ns);
+      }
+      if (it > kWaitSpinMax) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        ok = 0;
+        break;
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---------------------------------------------------------------- TMA (bulk tensor copy, one CTA, no multicast)
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -239,6 +282,17 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream is still running.  `pdl_launch_dependents` lets the successor's CTAs
+// be scheduled as soon as resources free up; `pdl_wait` blocks until the predecessor grid has
+// completed and its memory is visible.  Everything before `pdl_wait` must touch on-chip state
+// only (barrier init, TMEM allocation, descriptor prefetch).  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------- small numeric helpers
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }

@@ -3,6 +3,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -16,6 +17,16 @@ namespace {
 
 constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic shared memory we ask for at most (static barriers excluded)
 constexpr int kNumSms = 148;
+
+// Programmatic dependent launch lets a GEMM's on-chip set-up overlap the tail of the kernel before
+// it in the stream.  RK_B200_PDL=0 in the environment turns it off.
+bool use_pdl() {
+  static const bool on = [] {
+    const char* v = std::getenv("RK_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
 
 // ------------------------------------------------------------------ tensor maps
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -192,13 +203,15 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = pl.splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = use_pdl() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_kernel<KIND>, tm_a, tm_b, tm_out, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -337,8 +350,22 @@ int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMa
     if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  rk_gemm_w4a16_kernel<BN, UW><<<dim3(tiles_n, tiles_m), w4_threads(UW), smem, st>>>(tm_w, tm_x, tm_s, p);
-  return check_launch("rk_gemm_w4a16_kernel");
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(tiles_n, tiles_m, 1);
+  cfg.blockDim = dim3(w4_threads(UW));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_kernel<BN, UW>, tm_w, tm_x, tm_s, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_gemm_w4a16_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
 }
 
 }  // namespace
@@ -554,7 +581,7 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   int w_stages = (kSmemBudget - scales_bytes - p.xf_stages * kW4XfBytes - p.x_stages * x_bytes) / kW4RawBytes;
   if (w_stages > kW4MaxW) w_stages = kW4MaxW;
   if (w_stages > p.groups) w_stages = p.groups;
-  if (w_stages < 2) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
+  if (w_stages < 1) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
   p.w_stages = w_stages;
   p.ldo = n;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -579,3 +606,11 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
     default: return launch_w4<128, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
   }
 }
+
+#ifdef RK_TRACE
+// Developer aid (trace builds only): copies the W4A16 role timestamps of CTA (0,0) to the host.
+extern "C" int rk_trace_read(long long* host, int count) {
+  if (count > 16 * 64) count = 16 * 64;
+  return cudaMemcpyFromSymbol(host, rk::rk_trace_buf, sizeof(long long) * count) == cudaSuccess ? 0 : -3;
+}
+#endif

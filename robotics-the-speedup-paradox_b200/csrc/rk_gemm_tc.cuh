@@ -174,6 +174,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int kb_end = static_cast<int>((static_cast<long long>(p.kblocks) * (split + 1)) / p.splits);
   const int nkb = kb_end - kb_begin;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
@@ -198,6 +199,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // from here on global memory is read and written
   const uint32_t tmem_base = tmem_base_slot;
   // TMEM columns: two accumulator buffers, then (block-scaled kinds) the scale factors.
   const uint32_t tmem_sfa = tmem_base + p.acc_bufs * p.acc_stride;
@@ -213,14 +215,15 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint64_t pol_b = p.swap ? pol_x : pol_w;
       const uint8_t* sf_a = p.swap ? p.sf_wgt : p.sf_act;
       const uint8_t* sf_b = p.swap ? p.sf_act : p.sf_wgt;
-      int it = 0;
+      Ring ring{0, 0};
       bool alive = true;
+      const uint32_t tx_data = (kTileA + p.bn) * kStageKBytes;
       for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
         const int row_a0 = (tile / p.tiles_b) * kTileA;
         const int row_b0 = (tile % p.tiles_b) * p.bn;
-        for (int i = 0; i < nkb; ++i, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1;
+        for (int i = 0; i < nkb; ++i, ring.advance(p.stages)) {
+          const int s = ring.stage;
+          const uint32_t ph = ring.phase;
           if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
             alive = false;
             break;
@@ -229,7 +232,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint32_t sa = smem_base + s * stage_bytes;
           const uint32_t sb = sa + kTileA * kStageKBytes;
           const int kb = kb_begin + i;
-          uint32_t tx = (kTileA + p.bn) * kStageKBytes;
+          uint32_t tx = tx_data;
           // scale chunks present in this K block (the last block of a ragged K holds fewer)
           int cs = 0;
           if constexpr (T::kBlockScaled) {
@@ -261,18 +264,27 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      int it = 0, tcount = 0;
+      Ring ring{0, 0}, racc{0, 0};
       bool alive = true;
-      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step, ++tcount) {
-        const int ab = tcount % p.acc_bufs;
+      // instruction descriptor(s) and the descriptor of stage 0 are loop invariants
+      uint32_t idesc = 0;
+      if constexpr (KIND == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn);
+      else if constexpr (KIND == KIND_F8) idesc = umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn);
+      else if constexpr (KIND == KIND_MXF8) idesc = umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, 0, 0);
+      else idesc = umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 128, p.bn, 0, 0, 0);
+      const uint64_t adesc0 = umma_desc_k128(smem_base);
+      const uint64_t bdesc0 = umma_desc_k128(smem_base + kTileA * kStageKBytes);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step, racc.advance(p.acc_bufs)) {
+        const int ab = racc.stage;
         // the epilogue must have drained this accumulator buffer (its previous use)
-        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[ab]), ((tcount / p.acc_bufs) & 1) ^ 1, &abort_flag, p.status,
+        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[ab]), racc.phase ^ 1, &abort_flag, p.status,
                                RK_DEV_TIMEOUT_ACC_FREE)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * p.acc_stride;
-        for (int i = 0; i < nkb; ++i, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1;
+        for (int i = 0; i < nkb; ++i, ring.advance(p.stages)) {
+          const int s = ring.stage;
+          const uint32_t ph = ring.phase;
           if (!mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
             alive = false;
             break;
@@ -280,8 +292,8 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           tc_fence_after();
           const uint32_t sa = smem_base + s * stage_bytes;
           const uint32_t sb = sa + kTileA * kStageKBytes;
-          const uint64_t adesc = umma_desc_k128(sa);
-          const uint64_t bdesc = umma_desc_k128(sb);
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
           const int nmma = (kb_begin + i == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
           if constexpr (T::kBlockScaled) {
             const uint32_t ssf = sb + p.bn * kStageKBytes;
@@ -303,16 +315,16 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               const uint64_t ad = adesc + static_cast<uint64_t>(k * 2);
               const uint64_t bd = bdesc + static_cast<uint64_t>(k * 2);
               if constexpr (KIND == KIND_I8) {
-                mma_i8(d_tmem, ad, bd, umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn), accumulate);
+                mma_i8(d_tmem, ad, bd, idesc, accumulate);
               } else if constexpr (KIND == KIND_F8) {
-                mma_f8f6f4(d_tmem, ad, bd, umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn), accumulate);
+                mma_f8f6f4(d_tmem, ad, bd, idesc, accumulate);
               } else if constexpr (KIND == KIND_MXF8) {
                 // four MMAs share one set of scale columns; byte k of each 32-bit column is theirs
-                mma_mxf8(d_tmem, ad, bd, umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, k, k), tmem_sfa, tmem_sfb,
-                         accumulate);
+                // (scale-factor ids: bits [4,6) for B, [29,31) for A)
+                mma_mxf8(d_tmem, ad, bd, idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29),
+                         tmem_sfa, tmem_sfb, accumulate);
               } else {
-                mma_nvf4(d_tmem, ad, bd, umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 128, p.bn, 0, 0, 0),
-                         tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate);
+                mma_nvf4(d_tmem, ad, bd, idesc, tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate);
               }
             }
           }
@@ -335,11 +347,11 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (p.scale_act) s_act_scalar = *p.scale_act;
       if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
     }
-    int tcount = 0;
+    Ring racc{0, 0};
     int pending_store = 0;  // epilogue thread 0: a TMA store may still be reading a staging buffer
     int obuf = 0;
-    for (int tile = tile_first; tile < num_tiles; tile += tile_step, ++tcount) {
-      const int ab = tcount % p.acc_bufs;
+    for (int tile = tile_first; tile < num_tiles; tile += tile_step, racc.advance(p.acc_bufs)) {
+      const int ab = racc.stage;
       const int row_a0 = (tile / p.tiles_b) * kTileA;
       const int row_b0 = (tile % p.tiles_b) * p.bn;
       const int ra = row_a0 + et;
@@ -364,9 +376,8 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         epi_bar_sync();
       }
-      const bool ok = mbar_wait_bounded(smem_u32(&bar_acc_full[ab]), (tcount / p.acc_bufs) & 1, &abort_flag, p.status,
-                                        RK_DEV_TIMEOUT_ACC);
-      __syncwarp();
+      const bool ok = mbar_wait_warp(smem_u32(&bar_acc_full[ab]), racc.phase, &abort_flag, p.status,
+                                     RK_DEV_TIMEOUT_ACC, 64);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ab * p.acc_stride + (static_cast<uint32_t>(quad * 32) << 16);
 
@@ -500,6 +511,8 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if constexpr (KIND == KIND_I8) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
         if (p.swap && has_bias) row_bias = __bfloat162float(p.bias[ra]);
       }
+      const float* const vec_scale_r = reinterpret_cast<const float*>(smem_gen + vec_off);
+      const float* const vec_bias_r = vec_scale_r + 256;
       // shared::cluster base address of every peer's partial tile
       uint32_t peer[8];
 #pragma unroll
@@ -543,9 +556,10 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             continue;
           }
           float val;
-          const float bias_v = p.swap ? row_bias : (has_bias ? __bfloat162float(p.bias[rbj]) : 0.0f);
+          // B-role scale and bias of this column were staged in shared memory by the epilogue prologue
+          const float bias_v = p.swap ? row_bias : vec_bias_r[c];
           if constexpr (KIND == KIND_I8) {
-            const float other = p.swap ? p.scale_act[rbj] : p.scale_wgt[rbj];
+            const float other = vec_scale_r[c];
             val = p.swap ? finish_value<KIND>(total, other, row_scale, has_bias, bias_v)
                          : finish_value<KIND>(total, row_scale, other, has_bias, bias_v);
           } else {

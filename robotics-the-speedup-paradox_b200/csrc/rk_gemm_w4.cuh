@@ -21,6 +21,18 @@
 
 namespace rk {
 
+// Developer aid, compiled out unless RK_TRACE is defined: CTA (0,0) records SM-clock timestamps of
+// each role's progress per K group into a device array that rk_trace_read() copies back.
+#ifdef RK_TRACE
+__device__ long long rk_trace_buf[16 * 64];
+#define RK_TRACE_REC(slot, g)                                                        \
+  do {                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (g) < 64) rk_trace_buf[(slot) * 64 + (g)] = clock64(); \
+  } while (0)
+#else
+#define RK_TRACE_REC(slot, g) do { } while (0)
+#endif
+
 constexpr int kW4Group = 128;                // K elements per scale group == K elements per pipeline step
 constexpr int kW4RawBytes = 128 * 64;        // packed 128 x 128 int4 tile
 constexpr int kW4AtomBytes = 128 * 128;      // one 128-row x 64-element bf16 swizzle atom
@@ -102,6 +114,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   const int m0 = blockIdx.y * BN;
   const int G = p.groups;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.w_stages; ++s) {
       mbar_init(smem_u32(&bar_w_full[s]), 1);
@@ -135,7 +148,9 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // from here on global memory is read and written
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) RK_TRACE_REC(9, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer: two rings, weights run ahead
@@ -145,28 +160,35 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       mbar_arrive_expect_tx(smem_u32(&bar_scales), static_cast<uint32_t>(G) * 256u);
       tma_load_2d_hint(smem_base + scales_off, &tm_s, n0, 0, smem_u32(&bar_scales), pol_w);
       int gw = 0, gx = 0;
+      Ring rw{0, 0}, rx{0, 0};
       uint32_t idle = 0;
       while ((gw < G || gx < G) && !*reinterpret_cast<volatile int*>(&abort_flag)) {
         bool progressed = false;
         if (gw < G) {
-          const int s = gw % p.w_stages;
-          if (mbar_try_wait(smem_u32(&bar_w_empty[s]), ((gw / p.w_stages) & 1) ^ 1)) {
+          const int s = rw.stage;
+          if (mbar_try_wait(smem_u32(&bar_w_empty[s]), rw.phase ^ 1)) {
             const uint32_t full = smem_u32(&bar_w_full[s]);
+            RK_TRACE_REC(14, gw);
             mbar_arrive_expect_tx(full, kW4RawBytes);
+            RK_TRACE_REC(15, gw);
             tma_load_2d_hint(smem_base + w_off + s * kW4RawBytes, &tm_w, gw * 64, n0, full, pol_w);
+            RK_TRACE_REC(0, gw);
             ++gw;
+            rw.advance(p.w_stages);
             progressed = true;
           }
         }
         if (gx < G) {
-          const int s = gx % p.x_stages;
-          if (mbar_try_wait(smem_u32(&bar_x_empty[s]), ((gx / p.x_stages) & 1) ^ 1)) {
+          const int s = rx.stage;
+          if (mbar_try_wait(smem_u32(&bar_x_empty[s]), rx.phase ^ 1)) {
             const uint32_t full = smem_u32(&bar_x_full[s]);
             const uint32_t xs = smem_base + x_off + s * kXBytes;
             mbar_arrive_expect_tx(full, kXBytes);
             tma_load_2d_hint(xs, &tm_x, gx * 128, m0, full, pol_x);                  // k 0..63 of the group
             tma_load_2d_hint(xs + BN * 128, &tm_x, gx * 128 + 64, m0, full, pol_x);  // k 64..127
+            RK_TRACE_REC(1, gx);
             ++gx;
+            rx.advance(p.x_stages);
             progressed = true;
           }
         }
@@ -175,8 +197,8 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         } else if (++idle > kWaitSpinMax) {
           abort_flag = 1;
           atomicCAS(p.status, 0, RK_DEV_TIMEOUT_EMPTY);
-        } else if (idle > kWaitSpinFast) {
-          __nanosleep(256);
+        } else if (idle > 2) {
+          __nanosleep(idle > kWaitSpinFast ? 256 : 32);
         }
       }
     }
@@ -184,29 +206,38 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 128, BN);
-      for (int g = 0; g < G; ++g) {
-        const int sx = g % p.x_stages;
-        const int t = g % p.xf_stages;
-        const int b = g % kAcc;
-        if (!mbar_wait_bounded(smem_u32(&bar_x_full[sx]), (g / p.x_stages) & 1, &abort_flag, p.status,
-                               RK_DEV_TIMEOUT_FULL)) break;
-        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[b]), ((g / kAcc) & 1) ^ 1, &abort_flag, p.status,
+      const uint64_t desc_w0 = umma_desc_k128(smem_base + xf_off);
+      const uint64_t desc_x0 = umma_desc_k128(smem_base + x_off);
+      Ring rx{0, 0}, rt{0, 0}, rb{0, 0};
+      for (int g = 0; g < G; ++g, rx.advance(p.x_stages), rt.advance(p.xf_stages), rb.advance(kAcc)) {
+        const int sx = rx.stage;
+        const int t = rt.stage;
+        const int b = rb.stage;
+        if (!mbar_wait_bounded(smem_u32(&bar_x_full[sx]), rx.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) break;
+        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[b]), rb.phase ^ 1, &abort_flag, p.status,
                                RK_DEV_TIMEOUT_ACC_FREE)) break;
-        if (!mbar_wait_bounded(smem_u32(&bar_xf_full[t]), (g / p.xf_stages) & 1, &abort_flag, p.status,
-                               RK_DEV_TIMEOUT_XFORM)) break;
+        if (!mbar_wait_bounded(smem_u32(&bar_xf_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
         tc_fence_after();
-        const uint32_t xs = smem_base + x_off + sx * kXBytes;
-        const uint32_t ws = smem_base + xf_off + t * kW4XfBytes;
+        RK_TRACE_REC(5, g);
+        // descriptors of the stage: the start-address field advances by bytes >> 4
+        const uint64_t ad0 = desc_w0 + static_cast<uint64_t>((t * kW4XfBytes) >> 4);
+        const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((sx * kXBytes) >> 4);
+        const uint32_t d_tmem = tmem_base + b * BN;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // 16 bf16 (32 bytes) of K per MMA; four MMAs per 64-element atom.
-          const uint64_t ad = umma_desc_k128(ws + (k >> 2) * kW4AtomBytes) + static_cast<uint64_t>((k & 3) * 2);
-          const uint64_t bd = umma_desc_k128(xs + (k >> 2) * (BN * 128)) + static_cast<uint64_t>((k & 3) * 2);
-          mma_f16(tmem_base + b * BN, ad, bd, idesc, k > 0 ? 1u : 0u);
+          const uint64_t ad = ad0 + static_cast<uint64_t>(((k >> 2) * kW4AtomBytes + (k & 3) * 32) >> 4);
+          const uint64_t bd = bd0 + static_cast<uint64_t>(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
+          mma_f16(d_tmem, ad, bd, idesc, k > 0 ? 1u : 0u);
+          if (k == 0) RK_TRACE_REC(10, g);
+          if (k == 3) RK_TRACE_REC(11, g);
         }
+        RK_TRACE_REC(12, g);
         tc_commit(smem_u32(&bar_x_empty[sx]));
+        RK_TRACE_REC(13, g);
         tc_commit(smem_u32(&bar_xf_empty[t]));
         tc_commit(smem_u32(&bar_acc_full[b]));
+        RK_TRACE_REC(6, g);
       }
     }
   } else if (warp < kEpiWarp0) {
@@ -218,11 +249,12 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     constexpr int kRawChunks = 4 / kPerRow;  // 16-byte raw chunks per thread
     const int r = ut / kPerRow;
     const int h = ut % kPerRow;
-    for (int g = 0; g < G; ++g) {
-      const int sw = g % p.w_stages;
-      const int t = g % p.xf_stages;
-      if (!mbar_wait_bounded(smem_u32(&bar_w_full[sw]), (g / p.w_stages) & 1, &abort_flag, p.status,
-                             RK_DEV_TIMEOUT_RAW)) break;
+    Ring rw{0, 0}, rt{0, 0};
+    for (int g = 0; g < G; ++g, rw.advance(p.w_stages), rt.advance(p.xf_stages)) {
+      const int sw = rw.stage;
+      const int t = rt.stage;
+      if (!mbar_wait_warp(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW)) break;
+      if (ut == 0) RK_TRACE_REC(2, g);
       const uint8_t* raw = smem_gen + w_off + sw * kW4RawBytes;
       uint4 pk[kRawChunks];
 #pragma unroll
@@ -233,8 +265,8 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_w_empty[sw]));  // raw bytes are in registers: slot reusable
-      if (!mbar_wait_bounded(smem_u32(&bar_xf_empty[t]), ((g / p.xf_stages) & 1) ^ 1, &abort_flag, p.status,
-                             RK_DEV_TIMEOUT_XFORM)) break;
+      if (!mbar_wait_warp(smem_u32(&bar_xf_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
+      if (ut == 0) RK_TRACE_REC(3, g);
       uint8_t* dst = smem_gen + xf_off + t * kW4XfBytes;
 #pragma unroll
       for (int i = 0; i < kRawChunks; ++i) {
@@ -253,6 +285,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       fence_proxy_async_smem();  // make these generic-proxy writes visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_xf_full[t]));
+      if (ut == 0) RK_TRACE_REC(4, g);
     }
   } else {
     // ------------------------------------------------------------ epilogue: scale each group, accumulate, store
@@ -262,14 +295,15 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     float acc[BN];
 #pragma unroll
     for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
-    bool alive = mbar_wait_bounded(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL);
+    bool alive = mbar_wait_warp(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL, 64);
     const __nv_bfloat16* my_scales = reinterpret_cast<const __nv_bfloat16*>(smem_gen + scales_off) + quad * 32 + lane;
-    for (int g = 0; g < G && alive; ++g) {
-      const int b = g % kAcc;
+    Ring rb{0, 0};
+    for (int g = 0; g < G && alive; ++g, rb.advance(kAcc)) {
+      const int b = rb.stage;
       const float sc = __bfloat162float(my_scales[g * 128]);
-      alive = mbar_wait_bounded(smem_u32(&bar_acc_full[b]), (g / kAcc) & 1, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
-      __syncwarp();
+      alive = mbar_wait_warp(smem_u32(&bar_acc_full[b]), rb.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
       tc_fence_after();
+      if (quad == 0 && lane == 0) RK_TRACE_REC(7, g);
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16];
@@ -281,6 +315,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[b]));
+      if (quad == 0 && lane == 0) RK_TRACE_REC(8, g);
     }
     if (alive && n_ok) {
       const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.0f;

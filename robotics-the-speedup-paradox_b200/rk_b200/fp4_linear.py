@@ -1,0 +1,139 @@
+"""NVFP4 Linear on the B200 tcgen05 kernels (E2M1 codes, one UE4M3 scale per 16 k,
+``kind::mxf4nvf4.block_scale.scale_vec::4X``), activations quantized on the fly.
+
+Host-side mirror of the reference's ``src/robotics_kernels/blackwell/fp4_linear.py``
+(``Fp4CutlassLinear``: ``from_linear(linear, role, target_name)``, ``pack_input``,
+``forward_packed``, ``forward``, ``fp4_backend``, status helpers).  ``global_scale=False``
+reproduces the reference's format exactly (no per-tensor scale, alpha = 1:
+blackwell/csrc/fp4_cutlass_linear.cu:1358); ``global_scale=True`` adds the fp32 per-tensor scale
+``amax / (6 * 448)`` on weights and activations that the benchmark configuration asks for.
+The reference's other activation modes map to other modules of this package: ``bf16`` (W4A16) to
+``W4A16Linear``.
+"""
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+
+@dataclass
+class Fp4BackendStatus:
+    available: bool
+    error: str | None
+    backend: str = "b200_tcgen05_nvfp4"
+
+    def to_dict(self):
+        return {"available": self.available, "error": self.error, "backend": self.backend}
+
+
+def fp4_backend_status(device=None):
+    ok, error = _lib.backend_status()
+    if ok and torch.cuda.is_available():
+        major, minor = torch.cuda.get_device_capability(device)
+        if not _lib.load().rk_supports_device(major, minor):
+            ok, error = False, f"compute capability {major}.{minor} is not supported (sm_100 only)"
+    elif ok:
+        ok, error = False, "CUDA is not available"
+    return Fp4BackendStatus(ok, error)
+
+
+def require_fp4_backend(device=None):
+    status = fp4_backend_status(device)
+    if not status.available:
+        raise RuntimeError(f"FP4 backend unavailable: {status.to_dict()}")
+
+
+def tensor_global_scale(x):
+    """float32[1] = max(amax / (6 * 448), 1e-12)."""
+    scale = torch.empty(1, device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        ws = _lib.workspace(x.device, _lib.WORKSPACE_HEADER)
+        code = _lib.load().rk_nvfp4_global_scale(_lib.ptr(x), x.numel(), _lib.ptr(scale), _lib.ptr(ws), ws.numel(),
+                                                 _lib.stream_ptr(x.device))
+    _lib.check(code, "tensor_global_scale")
+    return scale
+
+
+def pack_nvfp4(x, global_scale=None):
+    """bf16 [rows, K] -> (uint8 [rows, K/2] codes, uint8 swizzled UE4M3 scale buffer); K % 32 == 0."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.dim() != 2 or x.shape[1] % 32:
+        raise ValueError("NVFP4 pack requires contiguous CUDA BF16 [M,K] with K divisible by 32")
+    rows, k = x.shape
+    lib = _lib.load()
+    q = torch.empty((rows, k // 2), device=x.device, dtype=torch.uint8)
+    sf = torch.empty(lib.rk_sf_bytes(rows, k // 16), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        code = lib.rk_pack_nvfp4(_lib.ptr(x), rows, k, _lib.ptr(global_scale), _lib.ptr(q), _lib.ptr(sf),
+                                 _lib.stream_ptr(x.device))
+    _lib.check(code, "pack_nvfp4")
+    return q, sf
+
+
+def linear_forward_packed_gemm_bf16(a, sfa, ga, b, sfb, gb, bias, k, tactic=0):
+    m, n = a.shape[0], b.shape[0]
+    out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
+    with torch.cuda.device(a.device):
+        ws = _lib.gemm_workspace(_lib.OP_NVFP4, a.device, m, n, k)
+        code = _lib.load().rk_gemm_nvfp4(_lib.ptr(a), _lib.ptr(sfa), _lib.ptr(ga), _lib.ptr(b), _lib.ptr(sfb),
+                                         _lib.ptr(gb), _lib.ptr(bias), _lib.ptr(out), m, n, k, tactic, _lib.ptr(ws),
+                                         ws.numel(), _lib.stream_ptr(a.device))
+    _lib.check(code, "linear_forward_packed_gemm_bf16")
+    return out
+
+
+class Fp4CutlassLinear(torch.nn.Module):
+    def __init__(self, packed, scales, weight_global, bias, in_features, out_features, role, target_name):
+        super().__init__()
+        self.register_buffer("packed_weight", packed)
+        self.register_buffer("weight_scale", scales)
+        self.register_buffer("weight_global_scale", weight_global)
+        self.register_buffer("bias", bias)
+        self.register_buffer("_weight_descriptor", torch.empty(0, device=packed.device, dtype=torch.bfloat16),
+                             persistent=False)
+        self.in_features = in_features
+        self.out_features = out_features
+        self.role = role
+        self.target_name = target_name
+        self.fp4_backend = "b200_tcgen05_nvfp4" + ("_global" if weight_global is not None else "")
+
+    @classmethod
+    def from_linear(cls, linear, role, target_name, global_scale=False):
+        if not linear.weight.is_cuda or linear.weight.dtype != torch.bfloat16:
+            raise ValueError("Fp4CutlassLinear requires CUDA BF16 weights")
+        require_fp4_backend(linear.weight.device)
+        n, k = linear.weight.shape
+        if n % 8 or k % 64:
+            raise ValueError("Fp4CutlassLinear requires out_features % 8 == 0 and in_features % 64 == 0")
+        w = linear.weight.detach().contiguous()
+        weight_global = tensor_global_scale(w) if global_scale else None
+        packed, scales = pack_nvfp4(w, weight_global)
+        bias = None if linear.bias is None else linear.bias.detach().to(torch.bfloat16).contiguous()
+        return cls(packed, scales, weight_global, bias, k, n, role, target_name)
+
+    @property
+    def weight(self):
+        return self._weight_descriptor
+
+    def pack_input(self, x):
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Wrong input feature count")
+        flat = x.reshape(-1, self.in_features)
+        if not flat.is_contiguous():
+            flat = flat.contiguous()
+        ga = tensor_global_scale(flat) if self.weight_global_scale is not None else None
+        q, sf = pack_nvfp4(flat, ga)
+        return q, sf, ga
+
+    def forward_packed(self, packed, scales, activation_global=None, shape=None):
+        out = linear_forward_packed_gemm_bf16(packed, scales, activation_global, self.packed_weight, self.weight_scale,
+                                              self.weight_global_scale, self.bias, self.in_features)
+        return out if shape is None else out.reshape(*shape, self.out_features)
+
+    def forward(self, x):
+        q, sf, ga = self.pack_input(x)
+        return self.forward_packed(q, sf, ga, x.shape[:-1])
+
+    def extra_repr(self):
+        return f"in_features={self.in_features}, out_features={self.out_features}, role={self.role}"

@@ -1,0 +1,186 @@
+"""FP8 Linear on the B200 tcgen05 kernels: per-tensor E4M3 (``kind::f8f6f4``) and MXFP8
+(E4M3 with one UE8M0 scale per 32 k, ``kind::mxf8f6f4.block_scale``).
+
+Host-side mirror of the reference's ``src/robotics_kernels/blackwell/fp8_linear.py``
+(``Fp8CutlassLinear``: ``from_linear(linear, role, target_name)``, ``pack_input``,
+``forward_packed``, ``forward_mxfp8``, ``forward``, ``fp8_backend``, status helpers) and of
+``mxfp8_linear.py`` (``pack`` / ``linear``).  The reference reaches MXFP8 only for a few prefill
+roles chosen by environment variables (fp8_linear.py:30,565); here it is a mode of the module.
+Arithmetic runs in ``librk_b200.so``; there is no fallback.
+"""
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+FP8_DTYPE = torch.float8_e4m3fn
+
+
+@dataclass
+class Fp8BackendStatus:
+    available: bool
+    error: str | None
+    backend: str = "b200_tcgen05_e4m3"
+
+    def to_dict(self):
+        return {"available": self.available, "error": self.error, "backend": self.backend}
+
+
+def fp8_backend_status(device=None):
+    ok, error = _lib.backend_status()
+    if ok and torch.cuda.is_available():
+        major, minor = torch.cuda.get_device_capability(device)
+        if not _lib.load().rk_supports_device(major, minor):
+            ok, error = False, f"compute capability {major}.{minor} is not supported (sm_100 only)"
+    elif ok:
+        ok, error = False, "CUDA is not available"
+    return Fp8BackendStatus(ok, error)
+
+
+def require_fp8_backend(device=None):
+    status = fp8_backend_status(device)
+    if not status.available:
+        raise RuntimeError(f"FP8 backend unavailable: {status.to_dict()}")
+
+
+def _check_bf16(x, what):
+    if not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError(f"{what} must be a contiguous CUDA BF16 tensor")
+
+
+# ---- per-tensor E4M3 -------------------------------------------------------------------------
+def quantize_bf16(x):
+    """-> (e4m3 tensor of x's shape, float32 scale[1]); scale = max(amax / 448, 1e-12)."""
+    _check_bf16(x, "quantize_bf16 input")
+    q = torch.empty(x.shape, device=x.device, dtype=FP8_DTYPE)
+    scale = torch.empty(1, device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        ws = _lib.workspace(x.device, _lib.WORKSPACE_HEADER)
+        code = _lib.load().rk_quant_tensor_fp8(_lib.ptr(x), x.numel(), _lib.ptr(q), _lib.ptr(scale), _lib.ptr(ws),
+                                               ws.numel(), _lib.stream_ptr(x.device))
+    _lib.check(code, "quantize_bf16")
+    return q, scale
+
+
+def quantize_bf16_with_scale(x, scale):
+    _check_bf16(x, "quantize_bf16_with_scale input")
+    q = torch.empty(x.shape, device=x.device, dtype=FP8_DTYPE)
+    with torch.cuda.device(x.device):
+        code = _lib.load().rk_quant_tensor_fp8_with_scale(_lib.ptr(x), x.numel(), _lib.ptr(scale), _lib.ptr(q),
+                                                          _lib.stream_ptr(x.device))
+    _lib.check(code, "quantize_bf16_with_scale")
+    return q
+
+
+def linear_forward_packed(a, scale_a, b, scale_b, bias=None, tactic=0):
+    """e4m3 [M, K] x e4m3 [N, K]^T -> bf16 [M, N] = bf16(scale_a * scale_b * acc + bias)."""
+    m, k = a.shape
+    n = b.shape[0]
+    out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
+    with torch.cuda.device(a.device):
+        ws = _lib.gemm_workspace(_lib.OP_FP8, a.device, m, n, k)
+        code = _lib.load().rk_gemm_fp8(_lib.ptr(a), _lib.ptr(scale_a), _lib.ptr(b), _lib.ptr(scale_b), _lib.ptr(bias),
+                                       _lib.ptr(out), m, n, k, tactic, _lib.ptr(ws), ws.numel(),
+                                       _lib.stream_ptr(a.device))
+    _lib.check(code, "linear_forward_packed")
+    return out
+
+
+# ---- MXFP8 -----------------------------------------------------------------------------------
+def mxfp8_pack(x):
+    """bf16 [rows, K] -> (e4m3 [rows, K], uint8 swizzled UE8M0 scale buffer); K % 32 == 0."""
+    _check_bf16(x, "mxfp8 pack input")
+    if x.dim() != 2 or x.shape[1] % 32:
+        raise ValueError("MXFP8 pack requires contiguous CUDA BF16 [M,K] with K divisible by 32")
+    rows, k = x.shape
+    lib = _lib.load()
+    q = torch.empty((rows, k), device=x.device, dtype=FP8_DTYPE)
+    sf = torch.empty(lib.rk_sf_bytes(rows, k // 32), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        code = lib.rk_pack_mxfp8(_lib.ptr(x), rows, k, _lib.ptr(q), _lib.ptr(sf), _lib.stream_ptr(x.device))
+    _lib.check(code, "mxfp8 pack")
+    return q, sf
+
+
+def mxfp8_linear(a, sfa, b, sfb, bias=None, tactic=0):
+    m, k = a.shape
+    n = b.shape[0]
+    out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
+    with torch.cuda.device(a.device):
+        ws = _lib.gemm_workspace(_lib.OP_MXFP8, a.device, m, n, k)
+        code = _lib.load().rk_gemm_mxfp8(_lib.ptr(a), _lib.ptr(sfa), _lib.ptr(b), _lib.ptr(sfb), _lib.ptr(bias),
+                                         _lib.ptr(out), m, n, k, tactic, _lib.ptr(ws), ws.numel(),
+                                         _lib.stream_ptr(a.device))
+    _lib.check(code, "mxfp8 linear")
+    return out
+
+
+class Fp8CutlassLinear(torch.nn.Module):
+    """Quantized replacement of a BF16 ``nn.Linear``; ``mode`` is "per_tensor" or "mxfp8"."""
+
+    def __init__(self, weight_q, weight_scale, bias, in_features, out_features, role, target_name, mode):
+        super().__init__()
+        self.register_buffer("packed_weight", weight_q)
+        self.register_buffer("weight_scale", weight_scale)
+        self.register_buffer("bias", bias)
+        self.register_buffer("_weight_descriptor", torch.empty(0, device=weight_q.device, dtype=torch.bfloat16),
+                             persistent=False)
+        self.in_features = in_features
+        self.out_features = out_features
+        self.role = role
+        self.target_name = target_name
+        self.mode = mode
+        self.fp8_backend = "b200_tcgen05_e4m3" if mode == "per_tensor" else "b200_tcgen05_mxfp8_e4m3_ue8m0"
+
+    @classmethod
+    def from_linear(cls, linear, role, target_name, mode="per_tensor"):
+        if mode not in ("per_tensor", "mxfp8"):
+            raise ValueError("mode must be per_tensor or mxfp8")
+        if not linear.weight.is_cuda or linear.weight.dtype != torch.bfloat16:
+            raise ValueError("Fp8CutlassLinear requires CUDA BF16 weights")
+        require_fp8_backend(linear.weight.device)
+        n, k = linear.weight.shape
+        if n % 8 or k % (16 if mode == "per_tensor" else 32):
+            raise ValueError("Fp8CutlassLinear requires out_features % 8 == 0 and in_features % 16 (32 for MXFP8) == 0")
+        w = linear.weight.detach().contiguous()
+        if mode == "per_tensor":
+            weight_q, weight_scale = quantize_bf16(w)
+        else:
+            weight_q, weight_scale = mxfp8_pack(w)
+        bias = None if linear.bias is None else linear.bias.detach().to(torch.bfloat16).contiguous()
+        return cls(weight_q, weight_scale, bias, k, n, role, target_name, mode)
+
+    @property
+    def weight(self):
+        return self._weight_descriptor
+
+    def _rows(self, x):
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Wrong input feature count")
+        flat = x.reshape(-1, self.in_features)
+        return flat if flat.is_contiguous() else flat.contiguous()
+
+    def pack_input(self, x):
+        flat = self._rows(x)
+        return quantize_bf16(flat) if self.mode == "per_tensor" else mxfp8_pack(flat)
+
+    def forward_packed(self, packed, scale, shape=None):
+        if self.mode == "per_tensor":
+            out = linear_forward_packed(packed, scale, self.packed_weight, self.weight_scale, self.bias)
+        else:
+            out = mxfp8_linear(packed, scale, self.packed_weight, self.weight_scale, self.bias)
+        return out if shape is None else out.reshape(*shape, self.out_features)
+
+    def forward_mxfp8(self, x):
+        if self.mode != "mxfp8":
+            raise RuntimeError("This layer was packed per-tensor; build it with mode='mxfp8'")
+        return self.forward(x)
+
+    def forward(self, x):
+        packed, scale = self.pack_input(x)
+        return self.forward_packed(packed, scale, x.shape[:-1])
+
+    def extra_repr(self):
+        return f"in_features={self.in_features}, out_features={self.out_features}, mode={self.mode}, role={self.role}"

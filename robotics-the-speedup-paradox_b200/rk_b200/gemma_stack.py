@@ -1,0 +1,238 @@
+"""Random-init Gemma-architecture stacks that host the quantized linears: the 2B VLM prefix pass
+(18 layers, width 2048, 8 query heads / 1 KV head, head_dim 256, GeGLU MLP 16384) and the
+action-expert flow-matching loop (18 layers, width 1024, MLP 4096, adaptive RMSNorm, chunk 50 x 32,
+10 Euler steps over a cached prefix KV).
+
+This is the caller side of the hot path, kept in plain torch: norms, RoPE, eager fp32-softmax
+attention and residuals follow the reference's owned runtime (models/pi05/modeling_gemma.py:62-106,
+126-128, 185-274, 315-443; models/pi05/modeling_pi05.py:673-720, 793-889).  Every bf16
+``nn.Linear`` is a plain module so that ``quantize_linears`` can swap it; the fp32 adaptive-norm
+``dense`` layers and the fp32 action projections stay unquantized, as in the reference
+(optimizations/quantization.py:108-110).  Weights are random (N(0, 0.02)); there are no
+checkpoints in this package.
+"""
+
+from dataclasses import dataclass
+import math
+
+import torch
+from torch import nn
+import torch.nn.functional as F
+
+
+@dataclass(frozen=True)
+class GemmaConfig:
+    width: int
+    mlp_dim: int
+    depth: int = 18
+    num_heads: int = 8
+    num_kv_heads: int = 1
+    head_dim: int = 256
+    rms_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    adarms_cond_dim: int | None = None
+
+
+def gemma_2b():
+    return GemmaConfig(width=2048, mlp_dim=16384)
+
+
+def gemma_300m():
+    return GemmaConfig(width=1024, mlp_dim=4096, adarms_cond_dim=1024)
+
+
+class GemmaRMSNorm(nn.Module):
+    """fp32 statistics; plain: x * inv * (1 + w); adaptive: x * inv * (1 + scale) + shift, gate."""
+
+    def __init__(self, dim, eps, cond_dim=None):
+        super().__init__()
+        self.eps = eps
+        if cond_dim is None:
+            self.weight = nn.Parameter(torch.zeros(dim, dtype=torch.bfloat16))
+            self.dense = None
+        else:
+            self.dense = nn.Linear(cond_dim, dim * 3, bias=True).float()  # stays fp32: never quantized
+
+    def forward(self, x, cond=None):
+        xf = x.float()
+        normed = xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
+        if self.dense is None:
+            return (normed * (1.0 + self.weight.float())).to(x.dtype), None
+        scale, shift, gate = self.dense(cond.float()).unsqueeze(1).chunk(3, dim=-1)
+        return (normed * (1.0 + scale) + shift).to(x.dtype), gate.to(x.dtype)
+
+
+def rotate_half(x):
+    half = x.shape[-1] // 2
+    return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def rope_tables(positions, head_dim, theta, dtype):
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
+    angles = positions.float()[..., None] * inv_freq
+    emb = torch.cat((angles, angles), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+class GemmaAttention(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.cfg = cfg
+        self.q_proj = nn.Linear(cfg.width, cfg.num_heads * cfg.head_dim, bias=False)
+        self.k_proj = nn.Linear(cfg.width, cfg.num_kv_heads * cfg.head_dim, bias=False)
+        self.v_proj = nn.Linear(cfg.width, cfg.num_kv_heads * cfg.head_dim, bias=False)
+        self.o_proj = nn.Linear(cfg.num_heads * cfg.head_dim, cfg.width, bias=False)
+
+    def forward(self, x, cos, sin, past_kv=None):
+        b, t, _ = x.shape
+        cfg = self.cfg
+        q = self.q_proj(x).view(b, t, cfg.num_heads, cfg.head_dim).transpose(1, 2)
+        k = self.k_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
+        v = self.v_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
+        q = q * cos[:, None] + rotate_half(q) * sin[:, None]
+        k = k * cos[:, None] + rotate_half(k) * sin[:, None]
+        if past_kv is not None:
+            k = torch.cat([past_kv[0], k], dim=2)
+            v = torch.cat([past_kv[1], v], dim=2)
+        present = (k, v)
+        rep = cfg.num_heads // cfg.num_kv_heads
+        kk = k[:, :, None].expand(b, cfg.num_kv_heads, rep, k.shape[2], cfg.head_dim).reshape(b, cfg.num_heads, -1, cfg.head_dim)
+        vv = v[:, :, None].expand(b, cfg.num_kv_heads, rep, v.shape[2], cfg.head_dim).reshape(b, cfg.num_heads, -1, cfg.head_dim)
+        # full (non-causal) visibility: prefix tokens see each other; suffix tokens see the whole
+        # prefix and each other (models/pi05/modeling_pi05.py:649,662,713)
+        weights = torch.matmul(q, kk.transpose(2, 3)) * (cfg.head_dim ** -0.5)
+        weights = F.softmax(weights, dim=-1, dtype=torch.float32).to(q.dtype)
+        out = torch.matmul(weights, vv).transpose(1, 2).reshape(b, t, -1).contiguous()
+        return self.o_proj(out), present
+
+
+class GemmaMLP(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.gate_proj = nn.Linear(cfg.width, cfg.mlp_dim, bias=False)
+        self.up_proj = nn.Linear(cfg.width, cfg.mlp_dim, bias=False)
+        self.down_proj = nn.Linear(cfg.mlp_dim, cfg.width, bias=False)
+
+    def forward(self, x):
+        gate, up = self.gate_proj(x), self.up_proj(x)
+        fused = getattr(self.down_proj, "forward_gelu", None)
+        if fused is not None:  # quantized down_proj: GELU(gate) * up fused into its row quantizer
+            return fused(gate, up)
+        return self.down_proj(F.gelu(gate, approximate="tanh") * up)
+
+
+class GemmaLayer(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.self_attn = GemmaAttention(cfg)
+        self.mlp = GemmaMLP(cfg)
+        self.input_layernorm = GemmaRMSNorm(cfg.width, cfg.rms_eps, cfg.adarms_cond_dim)
+        self.post_attention_layernorm = GemmaRMSNorm(cfg.width, cfg.rms_eps, cfg.adarms_cond_dim)
+
+    def forward(self, x, cos, sin, past_kv=None, cond=None):
+        h, gate = self.input_layernorm(x, cond)
+        h, present = self.self_attn(h, cos, sin, past_kv)
+        x = x + h if gate is None else x + h * gate
+        h, gate = self.post_attention_layernorm(x, cond)
+        h = self.mlp(h)
+        x = x + h if gate is None else x + h * gate
+        return x, present
+
+
+class GemmaStack(nn.Module):
+    """`depth` decoder layers plus the final norm; layer names end in ``layers.<i>.<...>``."""
+
+    def __init__(self, cfg):
+        super().__init__()
+        self.cfg = cfg
+        self.layers = nn.ModuleList([GemmaLayer(cfg) for _ in range(cfg.depth)])
+        self.norm = GemmaRMSNorm(cfg.width, cfg.rms_eps, cfg.adarms_cond_dim)
+
+    @torch.no_grad()
+    def init_random(self, seed=0, std=0.02):
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        for param in self.parameters():
+            if param.dim() >= 2:
+                param.copy_((torch.randn(param.shape, generator=gen) * std).to(param.dtype))
+        return self
+
+    def forward(self, x, positions, past=None, cond=None):
+        cos, sin = rope_tables(positions, self.cfg.head_dim, self.cfg.rope_theta, x.dtype)
+        presents = []
+        for index, layer in enumerate(self.layers):
+            x, present = layer(x, cos, sin, None if past is None else past[index], cond)
+            presents.append(present)
+        x, _ = self.norm(x, cond)
+        return x, presents
+
+
+def build_prefix_model(device, seed=0):
+    """The 2B VLM backbone of the prefix pass: embeddings [B, 816, 2048] in, hidden states and KV out."""
+    model = GemmaStack(gemma_2b()).to(torch.bfloat16).init_random(seed)
+    return model.to(device).eval()
+
+
+def sinusoidal_time_embedding(time, dimension, min_period=4e-3, max_period=4.0):
+    fraction = torch.linspace(0.0, 1.0, dimension // 2, dtype=torch.float64, device=time.device)
+    period = min_period * (max_period / min_period) ** fraction
+    angles = (1.0 / period * 2 * math.pi)[None, :] * time.double()[:, None]
+    return torch.cat([torch.sin(angles), torch.cos(angles)], dim=1)
+
+
+class ActionExpert(nn.Module):
+    """Flow-matching action expert: `steps` Euler steps of an 18-layer Gemma stack over `chunk`
+    action tokens that attend to a cached prefix KV (models/pi05/modeling_pi05.py:793-889)."""
+
+    def __init__(self, cfg=None, chunk=50, action_dim=32, steps=10):
+        super().__init__()
+        self.cfg = cfg or gemma_300m()
+        self.chunk, self.action_dim, self.steps = chunk, action_dim, steps
+        self.stack = GemmaStack(self.cfg).to(torch.bfloat16)
+        for layer in list(self.stack.layers) + [self.stack]:
+            for norm in (getattr(layer, "input_layernorm", None), getattr(layer, "post_attention_layernorm", None),
+                         getattr(layer, "norm", None)):
+                if norm is not None and norm.dense is not None:
+                    norm.dense.float()
+        width = self.cfg.width
+        self.action_in_proj = nn.Linear(action_dim, width).float()
+        self.time_mlp_in = nn.Linear(width, width).float()
+        self.time_mlp_out = nn.Linear(width, width).float()
+        self.action_out_proj = nn.Linear(width, action_dim).float()
+
+    @torch.no_grad()
+    def init_random(self, seed=0, std=0.02):
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        for param in self.parameters():
+            if param.dim() >= 2:
+                param.copy_((torch.randn(param.shape, generator=gen) * std).to(param.dtype))
+        return self
+
+    def denoise_step(self, x_t, time, prefix_kv, prefix_len):
+        b = x_t.shape[0]
+        cond = F.silu(self.time_mlp_out(F.silu(self.time_mlp_in(
+            sinusoidal_time_embedding(time, self.cfg.width).float()))))
+        tokens = self.action_in_proj(x_t).to(torch.bfloat16)
+        positions = prefix_len + torch.arange(self.chunk, device=x_t.device)[None, :].expand(b, -1)
+        hidden, _ = self.stack(tokens, positions, past=prefix_kv, cond=cond)
+        return self.action_out_proj(hidden.float())
+
+    def forward(self, noise, prefix_k, prefix_v):
+        """noise [B, chunk, action_dim] fp32; prefix_k / prefix_v [depth, B, kv_heads, T, head_dim] bf16."""
+        b = noise.shape[0]
+        prefix_len = prefix_k.shape[3]
+        prefix_kv = [(prefix_k[i], prefix_v[i]) for i in range(self.cfg.depth)]
+        dt = -1.0 / self.steps
+        x_t = noise
+        for step in range(self.steps):
+            time = torch.full((b,), 1.0 + step * dt, device=noise.device, dtype=torch.float32)
+            x_t = x_t + dt * self.denoise_step(x_t, time, prefix_kv, prefix_len)
+        return x_t
+
+
+def expert_scope(name):
+    """Selector for `quantize_linears`: the bf16 linears of the decoder layers are "expert"."""
+    return "expert" if ".layers." in name and ".dense" not in name else None
+
+
+def prefix_scope(name):
+    return "text" if name.startswith("layers.") or ".layers." in name else None

@@ -1,0 +1,87 @@
+"""GPU tests of the Gemma-architecture harness around the quantized linears: per-linear parity of
+the W8A8 path inside the action-expert loop, CUDA-graph replay of the whole loop, NVFP4 prefix."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as F
+from oracle import integer as OI
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def H():
+    import gpu_helpers
+
+    return gpu_helpers
+
+
+def small_expert(device):
+    from rk_b200.gemma_stack import ActionExpert, GemmaConfig
+
+    cfg = GemmaConfig(width=256, mlp_dim=512, depth=2, num_heads=2, num_kv_heads=1, head_dim=128, adarms_cond_dim=256)
+    return ActionExpert(cfg, chunk=50, action_dim=32, steps=3).init_random(1).to(device).eval()
+
+
+def test_expert_loop_w8a8_linears_match_oracle_and_graph_replays(H):
+    from rk_b200.gemma_stack import expert_scope
+    from rk_b200.graph import CudaGraphCall
+    from rk_b200.integer import IntegerLinear
+    from rk_b200.optimizations import quantize_linears
+
+    expert = small_expert(H.DEVICE)
+    b, t = 8, 96
+    gen = torch.Generator().manual_seed(3)
+    noise = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+    pk = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    pv = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    with torch.no_grad():
+        reference = expert(noise, pk, pv)
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope) as report:
+            assert len(report["modules"]) == 2 * 7 and not report["skipped"]
+            # every swapped linear reproduces the oracle bit for bit on the activations it sees
+            seen = {}
+            hooks = [m.register_forward_hook(lambda mod, args, out, name=n: seen.__setitem__(name, (args[0], out)))
+                     for n, m in expert.named_modules() if isinstance(m, IntegerLinear)]
+            quantized = expert(noise, pk, pv)
+            for hook in hooks:
+                hook.remove()
+            # down_proj runs through forward_gelu (fused GELU*up pack), which bypasses module hooks
+            assert len(seen) == 12
+            for name, (x, y) in seen.items():
+                if getattr(x, "_robotics_packed_input", False):
+                    continue
+                layer = expert.get_submodule(name)
+                xs = H.to_np(x).reshape(-1, layer.in_features)
+                a, sa, _ = OI.quantize_rows(xs, 8)
+                want, _ = OI.gemm(a, sa, layer.packed_weight.cpu().numpy(), layer.weight_scale.cpu().numpy(), None, 8)
+                assert np.array_equal(H.bits(y).reshape(-1, layer.out_features), F.bf16_bits(want)), name
+            # the whole loop under a captured graph equals eager execution, also after new inputs
+            call = CudaGraphCall(lambda n_, k_, v_: expert(n_, k_, v_))
+            assert torch.equal(call(noise, pk, pv), quantized)
+            noise2 = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+            assert torch.equal(call(noise2, pk, pv), expert(noise2, pk, pv))
+            assert call.captures == 1 and call.replays == 2
+    rel = (quantized - reference).norm() / reference.norm()
+    assert rel < 0.1
+
+
+def test_prefix_stack_nvfp4_close_to_bf16(H):
+    from rk_b200.gemma_stack import GemmaConfig, GemmaStack, prefix_scope
+    from rk_b200.optimizations import quantize_linears
+
+    cfg = GemmaConfig(width=256, mlp_dim=1024, depth=2, num_heads=2, num_kv_heads=1, head_dim=128)
+    model = GemmaStack(cfg).to(torch.bfloat16).init_random(2).to(H.DEVICE).eval()
+    x = H.randn_bf16((1, 816, 256), 1.0, 5).to(H.DEVICE)
+    pos = torch.arange(816, device=H.DEVICE)[None]
+    with torch.no_grad():
+        ref, _ = model(x, pos)
+        for precision, tol in (("fp4", 0.35), ("mxfp8", 0.08), ("fp8", 0.08), ("w4a16", 0.35)):
+            with quantize_linears(model, precision, scopes=("text",), selector=prefix_scope) as report:
+                assert len(report["modules"]) == 14
+                out, kv = model(x, pos)
+            rel = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
+            assert rel < tol, (precision, rel)
+            assert kv[0][0].shape == (1, 1, 816, 128)
