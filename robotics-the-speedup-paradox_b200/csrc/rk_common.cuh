@@ -58,6 +58,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// Non-blocking probe of a phase: never parks the thread, so it does not disturb a thread that is
+// parked on the same barrier with try_wait.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any role has given up, every
 // other wait returns immediately so that the CTA can drain.  Returns false on give-up.
 constexpr uint32_t kWaitSpinFast = 2048;
@@ -102,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     ok = 1;
     uint32_t it = 0;
     while (!mbar_try_wait(bar, parity)) {
-      if (++it > 4) {
+      if (++it > 64) {
         if (*abort_flag) {
           ok = 0;
           break;
@@ -118,6 +132,23 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     }
   }
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// Group-wide bounded wait with ONE polling thread: the hardware parks a single waiter per
+// barrier; further threads polling the same barrier return at once and spin at full issue rate,
+// starving the warps that share their scheduler.  So one thread of the group waits on the
+// mbarrier and a named hardware barrier (`bar.sync id, nthreads`) releases the rest.
+// Every thread of the group must call this; `nthreads` is the group size (multiple of 32).
+// `verdict` points at two shared words owned by the group; `iter` counts the group's calls.  The
+// leader publishes its result in slot iter & 1 before the named barrier, so every thread of the
+// group takes the same decision even if another role raises the abort flag meanwhile (threads
+// leaving a loop at different iterations would strand the others on the hardware barrier).
+__device__ __forceinline__ bool mbar_wait_group(uint32_t bar, uint32_t parity, bool is_leader, int named_id,
+                                                int nthreads, int* abort_flag, int* status, int code,
+                                                volatile int* verdict, uint32_t iter) {
+  if (is_leader) verdict[iter & 1] = mbar_wait_bounded(bar, parity, abort_flag, status, code) ? 1 : 0;
+  asm volatile("bar.sync %0, %1;" ::"r"(named_id), "r"(nthreads) : "memory");
+  return verdict[iter & 1] != 0;
 }
 
 // ---------------------------------------------------------------- TMA (bulk tensor copy, one CTA, no multicast)
@@ -197,6 +228,26 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// 32 lanes x 32 consecutive 32-bit columns, registers -> TMEM (thread t of the warp writes lane base_lane + t)
+__device__ __forceinline__ void tmem_st_32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_8(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3, uint32_t r4,
+                                          uint32_t r5, uint32_t r6, uint32_t r7) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(r4), "r"(r5), "r"(r6), "r"(r7)
+               : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // tcgen05.cp: 32 lanes x 128 bits from shared memory, replicated to the four 32-lane quadrants.
 // Used to place block scale factors where the block-scaled MMA reads them.
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
@@ -265,6 +316,16 @@ RK_DEFINE_MMA(mma_i8, "i8")
 RK_DEFINE_MMA(mma_f16, "f16")
 RK_DEFINE_MMA(mma_f8f6f4, "f8f6f4")
 #undef RK_DEFINE_MMA
+
+// D[tmem] (+)= A[tmem] * B[smem]^T: the A operand is a TMEM tile (one row per lane, K along columns)
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 __device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {

@@ -9,6 +9,7 @@
 #include <unordered_map>
 
 #include "rk_gemm_tc.cuh"
+#include "rk_gemm_tc2.cuh"
 #include "rk_gemm_w4.cuh"
 #include "rk_host.h"
 
@@ -138,7 +139,12 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   if (pl.swap) {
     // fewest <=256-row chunks; a lone chunk may be any multiple of 16 rows (32 when block-scaled),
     // several chunks must be multiples of 32 rows (the TMA store works on 32-row boxes)
-    const int chunks = static_cast<int>((m + 255) / 256);
+    int chunks = static_cast<int>((m + 255) / 256);
+    // When the 128-row weight tiles alone cannot occupy the machine, cut the activation rows
+    // into more (<=128-row) chunks before resorting to split-K: the split-K exchange moves
+    // bn x 128 x 4 bytes per CTA through distributed shared memory, so narrow tiles keep it cheap.
+    const long long wide_tiles = ((n + 127) / 128) * chunks;
+    if (!block_scaled && m > 128 && wide_tiles * 2 <= kNumSms) chunks = static_cast<int>((m + 127) / 128);
     const int q = (block_scaled || chunks > 1) ? 32 : 16;
     int bn = static_cast<int>(round_up((m + chunks - 1) / chunks, q));
     if ((tactic & 4) && bn >= 64 && !block_scaled) bn = static_cast<int>(round_up(bn / 2, 32));
@@ -220,6 +226,54 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
   return RK_OK;
 }
 
+// Two-CTA schedule: RK_B200_TWO_CTA=0 never, =1 whenever the kind allows it, unset = for
+// activation row counts beyond the swap range.
+int two_cta_mode() {
+  static const int mode = [] {
+    const char* v = std::getenv("RK_B200_TWO_CTA");
+    if (!v) return -1;
+    return v[0] == '0' ? 0 : 1;
+  }();
+  return mode;
+}
+
+template <int KIND>
+int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out, const Gemm2Params& p,
+               int smem, cudaStream_t st) {
+  static bool configured_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& configured = configured_dev[dev & 63];
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(rk_gemm_tc2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBudget + 1024);
+    if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int clusters = tiles < kNumSms / 2 ? tiles : kNumSms / 2;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc2_kernel<KIND>, tm_a, tm_b, tm_out, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_gemm_tc2_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
+}
+
 struct TcArgs {
   int kind;
   const void* act;       // [m, k_bytes] bytes
@@ -250,6 +304,43 @@ int run_tc(const TcArgs& a) {
   int rc = carve_workspace(a.workspace, a.workspace_bytes, &ws, a.who);
   if (rc != RK_OK) return rc;
   const int kblocks = static_cast<int>((a.k_bytes + kStageKBytes - 1) / kStageKBytes);
+  const bool two_cta_kind = (a.kind == KIND_I8 || a.kind == KIND_F8) && a.acc_out == nullptr && a.out != nullptr;
+  const int mode = two_cta_mode();
+  if (two_cta_kind && mode != 0 && ((mode == 1 && a.m > 256) || a.m > 1024) && a.n >= 128) {
+    Gemm2Params p2{};
+    p2.m = static_cast<int>(a.m);
+    p2.n = static_cast<int>(a.n);
+    p2.kblocks = kblocks;
+    p2.k_valid_mmas_last = (a.mma_bytes_last + 31) / 32;
+    if (p2.k_valid_mmas_last < 1 || p2.k_valid_mmas_last > 4) p2.k_valid_mmas_last = 4;
+    p2.bn = ((a.tactic & 4) || a.n < 256) ? 128 : 256;
+    p2.tiles_m = static_cast<int>((a.m + 255) / 256);
+    p2.tiles_n = static_cast<int>((a.n + p2.bn - 1) / p2.bn);
+    const int stage = (kTileA + p2.bn / 2) * kStageKBytes;
+    p2.out_bufs = 2;
+    p2.stages = (kSmemBudget - kVecBytes - 2 * kOutBufBytes) / stage;
+    if (p2.stages > kMaxStages) p2.stages = kMaxStages;
+    if (p2.stages > kblocks) p2.stages = kblocks < 2 ? 2 : kblocks;
+    p2.ldo = a.n;
+    p2.scale_act = a.scale_act;
+    p2.scale_wgt = a.scale_wgt;
+    p2.bias = static_cast<const __nv_bfloat16*>(a.bias);
+    p2.out = static_cast<__nv_bfloat16*>(a.out);
+    p2.status = ws.status;
+    CUtensorMap t_act, t_wgt, t_out;
+    rc = make_map_2d(&t_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, kTileA,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != RK_OK) return rc;
+    rc = make_map_2d(&t_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.n, a.k_bytes, kStageKBytes,
+                     static_cast<uint32_t>(p2.bn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != RK_OK) return rc;
+    rc = make_map_2d(&t_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 64, 128,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != RK_OK) return rc;
+    const int smem = p2.stages * stage + 2 * kOutBufBytes + kVecBytes + 1024;
+    return a.kind == KIND_I8 ? launch_tc2<KIND_I8>(t_act, t_wgt, t_out, p2, smem, a.stream)
+                             : launch_tc2<KIND_F8>(t_act, t_wgt, t_out, p2, smem, a.stream);
+  }
   const Plan pl = make_plan(a.kind, a.m, a.n, kblocks, a.tactic);
 
   CUtensorMap tm_act, tm_wgt, tm_out;
@@ -575,10 +666,9 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   // ring depths: unpacked tiles (32 KB each) and activation tiles first, the rest goes to the
   // raw-weight ring, whose depth is what keeps enough HBM requests in flight
   const int x_bytes = 2 * bn * 128;
-  p.xf_stages = bn == 16 ? 4 : (bn == 128 ? 2 : 3);
-  p.x_stages = bn == 16 ? 4 : (bn == 128 ? 2 : 3);
-  if (p.x_stages > p.groups) p.x_stages = p.groups;
-  int w_stages = (kSmemBudget - scales_bytes - p.xf_stages * kW4XfBytes - p.x_stages * x_bytes) / kW4RawBytes;
+  p.xf_stages = w4_xf_depth(bn);  // unpacked weights live in TMEM; the activation ring in shared memory matches
+  p.x_stages = p.xf_stages;       // one commit releases both rings
+  int w_stages = (kSmemBudget - scales_bytes - p.x_stages * x_bytes) / kW4RawBytes;
   if (w_stages > kW4MaxW) w_stages = kW4MaxW;
   if (w_stages > p.groups) w_stages = p.groups;
   if (w_stages < 1) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
@@ -587,7 +677,7 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = ws.status;
-  const int smem = p.xf_stages * kW4XfBytes + p.x_stages * x_bytes + w_stages * kW4RawBytes + scales_bytes + 1024;
+  const int smem = p.x_stages * x_bytes + w_stages * kW4RawBytes + scales_bytes + 1024;
   if (!aligned16(scales)) return fail(RK_EINVAL, "%s: scales must be 16-byte aligned", who);
   CUtensorMap tm_w, tm_x, tm_s;
   const uint32_t group_box = static_cast<uint32_t>(p.groups < 256 ? p.groups : 256);
@@ -599,6 +689,14 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
   cudaStream_t st = as_stream(stream);
+  if (tactic & 1) {  // four unpack warps instead of eight
+    switch (bn) {
+      case 16: return launch_w4<16, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+      case 32: return launch_w4<32, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+      case 64: return launch_w4<64, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+      default: break;
+    }
+  }
   switch (bn) {
     case 16: return launch_w4<16, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
     case 32: return launch_w4<32, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);

@@ -154,6 +154,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int verdict_epi[2];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -348,6 +349,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
     }
     Ring racc{0, 0};
+    uint32_t epi_iter = 0;
     int pending_store = 0;  // epilogue thread 0: a TMA store may still be reading a staging buffer
     int obuf = 0;
     for (int tile = tile_first; tile < num_tiles; tile += tile_step, racc.advance(p.acc_bufs)) {
@@ -376,8 +378,8 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         epi_bar_sync();
       }
-      const bool ok = mbar_wait_warp(smem_u32(&bar_acc_full[ab]), racc.phase, &abort_flag, p.status,
-                                     RK_DEV_TIMEOUT_ACC, 64);
+      const bool ok = mbar_wait_group(smem_u32(&bar_acc_full[ab]), racc.phase, et == 0, 1, 128, &abort_flag, p.status,
+                                      RK_DEV_TIMEOUT_ACC, verdict_epi, epi_iter++);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ab * p.acc_stride + (static_cast<uint32_t>(quad * 32) << 16);
 

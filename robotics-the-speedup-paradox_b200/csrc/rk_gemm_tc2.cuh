@@ -1,0 +1,299 @@
+// Two-CTA tcgen05 GEMM for large activation row counts: int8 x int8 -> s32 (W8A8) and
+// e4m3 x e4m3 -> f32 (per-tensor FP8).
+//
+// A pair of CTAs (a cluster of two SMs) computes one 256 x bn output tile with
+// `tcgen05.mma.cta_group::2`: each CTA holds 128 of the 256 activation rows (its half of the
+// accumulator lives in its own TMEM) and loads only bn/2 of the bn weight rows; the tensor cores
+// of both SMs read both halves of the weight tile through the pair's shared memory.  Compared
+// with two independent 128 x bn tiles this halves the weight traffic from L2 per SM and makes a
+// pipeline stage 32 KB instead of 48 KB, so more stages are in flight.
+//
+// Every TMA load is issued by the CTA that owns the destination shared memory (no multicast);
+// the loads of both CTAs signal the leader CTA's "full" barrier, the leader issues the MMAs, and
+// `tcgen05.commit ... multicast::cluster` releases the stage in both CTAs.
+//
+// Warp roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation (+ MMA issue
+// in the leader), warps 2..5 = epilogue.
+#pragma once
+
+#include <cuda.h>
+
+#include "rk_gemm_tc.cuh"
+
+namespace rk {
+
+struct Gemm2Params {
+  int m, n, kblocks;
+  int k_valid_mmas_last;
+  int bn;        // weight rows per pair tile (128 or 256); each CTA loads bn / 2
+  int stages;
+  int out_bufs;
+  int tiles_m, tiles_n;  // pair tiles: 256 x bn
+  long long ldo;
+  const float* scale_act;
+  const float* scale_wgt;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* out;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// load into this CTA's shared memory, completion counted on a barrier of the pair (cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t bar_cluster,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
+  // arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+#define RK_DEFINE_MMA2(NAME, KIND)                                                                          \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,     \
+                                       uint32_t accumulate) {                                               \
+    asm volatile(                                                                                           \
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                   \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t}"                                 \
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                                  \
+        : "memory");                                                                                        \
+  }
+RK_DEFINE_MMA2(mma2_i8, "i8")
+RK_DEFINE_MMA2(mma2_f8f6f4, "f8f6f4")
+#undef RK_DEFINE_MMA2
+
+template <int KIND>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                   const __grid_constant__ CUtensorMap tm_out, const Gemm2Params p) {
+  static_assert(KIND == KIND_I8 || KIND == KIND_F8, "two-CTA schedule: int8 and per-tensor FP8 only");
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages];    // used in the leader: both CTAs' loads land
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStages];   // per CTA: the MMAs have read this stage
+  __shared__ __align__(8) uint64_t bar_acc_full[2];         // per CTA: accumulator buffer complete
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];        // used in the leader: both epilogues drained it
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int verdict_epi[2];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* const smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+  const int half_bn = p.bn / 2;
+  const int stage_bytes = (kTileA + half_bn) * kStageKBytes;
+  const uint32_t out_stage_off = p.stages * stage_bytes;
+  const uint32_t vec_off = out_stage_off + p.out_bufs * kOutBufBytes;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tile_first = static_cast<int>(blockIdx.x >> 1);
+  const int tile_step = static_cast<int>(gridDim.x >> 1);
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_acc_full[b]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 8);  // four epilogue warps in each CTA of the pair
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_out);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything may signal them
+  tc_fence_after();
+  pdl_wait();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      Ring ring{0, 0};
+      bool alive = true;
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
+        const int row_a0 = (tile / p.tiles_n) * 256 + static_cast<int>(rank) * kTileA;
+        const int row_b0 = (tile % p.tiles_n) * p.bn + static_cast<int>(rank) * half_bn;
+        for (int kb = 0; kb < p.kblocks; ++kb, ring.advance(p.stages)) {
+          const int s = ring.stage;
+          if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ring.phase ^ 1, &abort_flag, p.status,
+                                 RK_DEV_TIMEOUT_EMPTY)) {
+            alive = false;
+            break;
+          }
+          // both CTAs' bytes are counted on the leader's barrier; the leader announces the total
+          const uint32_t full_leader = mapa_u32(smem_u32(&bar_full[s]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * static_cast<uint32_t>(stage_bytes));
+          const uint32_t sa = smem_base + s * stage_bytes;
+          tma_load_2d_pair(sa, &tm_a, kb * kStageKBytes, row_a0, full_leader, pol_x);
+          tma_load_2d_pair(sa + kTileA * kStageKBytes, &tm_b, kb * kStageKBytes, row_b0, full_leader, pol_w);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      Ring ring{0, 0}, racc{0, 0};
+      bool alive = true;
+      const uint32_t idesc = KIND == KIND_I8 ? umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 256, p.bn)
+                                             : umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 256, p.bn);
+      const uint64_t adesc0 = umma_desc_k128(smem_base);
+      const uint64_t bdesc0 = umma_desc_k128(smem_base + kTileA * kStageKBytes);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step, racc.advance(2)) {
+        const int ab = racc.stage;
+        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[ab]), racc.phase ^ 1, &abort_flag, p.status,
+                               RK_DEV_TIMEOUT_ACC_FREE)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * 256;
+        for (int kb = 0; kb < p.kblocks; ++kb, ring.advance(p.stages)) {
+          const int s = ring.stage;
+          if (!mbar_wait_bounded(smem_u32(&bar_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
+          const int nmma = (kb == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (k < nmma) {
+              const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+              if constexpr (KIND == KIND_I8) mma2_i8(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate);
+              else mma2_f8f6f4(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate);
+            }
+          }
+          tc2_commit_both(smem_u32(&bar_empty[s]));
+        }
+        if (alive) tc2_commit_both(smem_u32(&bar_acc_full[ab]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int quad = warp & 3;
+    const int et = quad * 32 + lane;
+    const bool has_bias = p.bias != nullptr;
+    float* const vec_scale = reinterpret_cast<float*>(smem_gen + vec_off);
+    float* const vec_bias = vec_scale + 256;
+    float s_act_scalar = 1.0f, s_wgt_scalar = 1.0f;
+    if constexpr (KIND != KIND_I8) {
+      if (p.scale_act) s_act_scalar = *p.scale_act;
+      if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
+    }
+    const uint32_t acc_empty_leader0 = mapa_u32(smem_u32(&bar_acc_empty[0]), 0);
+    const uint32_t acc_empty_leader1 = mapa_u32(smem_u32(&bar_acc_empty[1]), 0);
+    Ring racc{0, 0};
+    uint32_t epi_iter = 0;
+    int pending_store = 0, obuf = 0;
+    for (int tile = tile_first; tile < num_tiles; tile += tile_step, racc.advance(2)) {
+      const int ab = racc.stage;
+      const int row_a0 = (tile / p.tiles_n) * 256 + static_cast<int>(rank) * kTileA;  // this CTA's 128 rows
+      const int row_b0 = (tile % p.tiles_n) * p.bn;                                    // all bn columns
+      const int ra = row_a0 + et;
+      float row_scale = 1.0f;
+      if constexpr (KIND == KIND_I8) {
+        if (ra < p.m) row_scale = p.scale_act[ra];
+      }
+      epi_bar_sync();
+      for (int j = et; j < p.bn; j += 128) {
+        const int rb = row_b0 + j;
+        float sv = 1.0f, bv = 0.0f;
+        if (rb < p.n) {
+          if constexpr (KIND == KIND_I8) sv = p.scale_wgt[rb];
+          if (has_bias) bv = __bfloat162float(p.bias[rb]);
+        }
+        vec_scale[j] = sv;
+        vec_bias[j] = bv;
+      }
+      epi_bar_sync();
+      const bool ok = mbar_wait_group(smem_u32(&bar_acc_full[ab]), racc.phase, et == 0, 1, 128, &abort_flag, p.status,
+                                      RK_DEV_TIMEOUT_ACC, verdict_epi, epi_iter++);
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + ab * 256 + (static_cast<uint32_t>(quad * 32) << 16);
+      for (int cc = 0; cc < p.bn; cc += 64, obuf = (p.out_bufs == 2) ? (obuf ^ 1) : 0) {
+        uint8_t* const stage = smem_gen + out_stage_off + obuf * kOutBufBytes;
+        if (et == 0 && pending_store) {
+          if (p.out_bufs == 2) tma_store_wait_read<1>();
+          else tma_store_wait_read<0>();
+        }
+        epi_bar_sync();
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + cc + c0, r);
+          tc_wait_ld();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if constexpr (KIND == KIND_I8)
+              v[j] = finish_value<KIND>(r[j], row_scale, vec_scale[cc + c0 + j], has_bias, vec_bias[cc + c0 + j]);
+            else
+              v[j] = finish_value<KIND>(r[j], s_act_scalar, s_wgt_scalar, has_bias, vec_bias[cc + c0 + j]);
+          }
+          const uint4 lo = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                      pack_bf16x2(v[6], v[7]));
+          const uint4 hi = make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]),
+                                      pack_bf16x2(v[14], v[15]));
+          const int ch = c0 >> 3;
+          *reinterpret_cast<uint4*>(stage + et * 128 + ((ch ^ (et & 7)) << 4)) = lo;
+          *reinterpret_cast<uint4*>(stage + et * 128 + (((ch + 1) ^ (et & 7)) << 4)) = hi;
+        }
+        if (cc + 64 >= p.bn) {
+          // accumulator drained: tell the leader's MMA thread (its barrier counts both CTAs' warps)
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(ab == 0 ? acc_empty_leader0 : acc_empty_leader1);
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (et == 0) {
+          if (ok) tma_store_2d(&tm_out, smem_u32(stage), row_b0 + cc, row_a0);
+          tma_store_commit();
+          pending_store = 1;
+        }
+      }
+    }
+    if (et == 0) tma_store_wait_all();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be reading this CTA's shared memory through its MMAs
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+}  // namespace rk
