@@ -129,6 +129,22 @@ int rk_gemm_int(const void* a, const float* sa, const void* b, const float* sb, 
 int rk_gemm_int_acc(const void* a, const void* b, int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits,
                     int tactic, void* workspace, size_t workspace_bytes, void* stream);
 
+/* W4A4 GEMM (the bits = 4 case of rk_gemm_int) for callers that cannot allocate device memory
+ * when they call: code that runs inside a fixed memory plan, or a host thread that must stay out
+ * of the allocator.  It has no counterpart in the reference.  The int8 copies of both operands,
+ * which rk_gemm_int places in the caller's workspace, go to a device array built into the library
+ * (8 MiB + 4 KiB; every GPU that loads the library holds it until the process exits), so there is
+ * no workspace argument and nothing is allocated or freed, here or in any routine it calls.
+ *   Limit: (m + n) * kpad <= 8 MiB, otherwise RK_EUNSUPPORTED (use rk_gemm_int instead).
+ *   The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ *   that first call outside any stream capture.
+ *   All calls on a device share the one array: calls that may overlap on the GPU (different
+ *   streams, or graphs replayed concurrently) race and must be serialised by the caller.
+ *   The head of the array holds the device status word; it is cleared at the start of each call.
+ * Arguments as rk_gemm_int with bits = 4. */
+int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* b, const float* sb, const void* bias,
+                         void* out, int64_t m, int64_t n, int64_t kpad, int tactic, void* stream);
+
 /* ---- W4A16 int4, group 128 -------------------------------------------------------------- */
 
 /* Group-wise symmetric int4 weight packing: per (row, 128 consecutive k): s = bf16(max|w| / 7)

@@ -705,6 +705,55 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   }
 }
 
+// ------------------------------------------------------------------ W4A4 GEMM without caller scratch
+// The int4 GEMM widens both operands to int8 before the tensor-core kernel runs, which normally
+// happens in the caller's workspace.  Callers that cannot obtain device memory at call time -
+// for example code running inside a fixed memory plan, or a host thread that must not enter the
+// allocator - get this variant: the widened copies live in a device array that is part of the
+// library image.  Every GPU that loads the library carries the array until the process exits.
+constexpr size_t kNoAllocScratchBytes = (8u << 20) + 4096;  // 8 MiB of int8 copies + header
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+// The array's name is only a host-side handle; kernels need its device address, which differs
+// per device.  Looked up once per device (with that device current) and kept.
+int noalloc_scratch_address(uint8_t** out) {
+  static std::mutex mu;
+  static uint8_t* per_device[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return rk::fail(RK_ECUDA, "cudaGetDevice failed");
+  std::lock_guard<std::mutex> lock(mu);
+  if (per_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return rk::fail(RK_ECUDA, "cudaGetSymbolAddress(g_noalloc_scratch): %s", cudaGetErrorString(e));
+    per_device[dev] = static_cast<uint8_t*>(ptr);
+  }
+  *out = per_device[dev];
+  return RK_OK;
+}
+}  // namespace
+
+extern "C" int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* b, const float* sb, const void* bias,
+                                    void* out, int64_t m, int64_t n, int64_t kpad, int tactic, void* stream) {
+  const char* who = "rk_gemm_int4_noalloc";
+  if (m < 1 || n < 1 || kpad < 128 || kpad % 128 != 0) return rk::fail(RK_EINVAL, "%s: bad dimensions", who);
+  const size_t need = rk_workspace_bytes(RK_OP_W4A4, m, n, kpad);
+  if (need > kNoAllocScratchBytes)
+    return rk::fail(RK_EUNSUPPORTED,
+                    "%s: (m + n) * kpad = %lld bytes of int8 copies exceed the built-in %zu-byte scratch; "
+                    "use rk_gemm_int with a caller workspace",
+                    who, static_cast<long long>((m + n) * kpad), kNoAllocScratchBytes - 4096);
+  uint8_t* scratch = nullptr;
+  int rc = noalloc_scratch_address(&scratch);
+  if (rc != RK_OK) return rc;
+  // the status word at the head of the scratch must start at zero; the copies are overwritten anyway
+  if (cudaMemsetAsync(scratch, 0, RK_WORKSPACE_HEADER, rk::as_stream(stream)) != cudaSuccess)
+    return rk::fail(RK_ECUDA, "%s: cudaMemsetAsync failed", who);
+  return gemm_int_common(a, sa, b, sb, bias, out, nullptr, m, n, kpad, 4, tactic, scratch, need, stream, who);
+}
+
 #ifdef RK_TRACE
 // Developer aid (trace builds only): copies the W4A16 role timestamps of CTA (0,0) to the host.
 extern "C" int rk_trace_read(long long* host, int count) {
