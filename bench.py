@@ -51,6 +51,11 @@ def algorithmic_bytes(m):
     return N * K // 2 + (K // GROUP) * N * 2 + m * K * 2 + m * N * 2
 
 
+# DRAM bytes (read + write) of one launch, from an ncu capture of this workload's four launches
+# (dram__bytes_read.sum + dram__bytes_write.sum; the outputs stay in L2, so writes were zero).
+NCU_DRAM_TRAFFIC = {1: 17361920, 8: 17390848, 50: 17573632, 256: 18434560}
+
+
 def algorithmic_ops(m):
     return 2 * m * N * K
 
@@ -153,34 +158,42 @@ def time_cpu_baseline(budget_s=12.0):
                       f"{elapsed:.1f} s of CPU time"}, elapsed / passes
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, budget_s=150.0):
+    """CPU arm: the oracle port on the host cores.  A step is one pass over the four activation
+    batches against a SAMPLE of the weight matrix - the first `rows` output channels - sized so that
+    warm-up plus timed steps fit `budget_s`; throughput counts only the operations actually done."""
     if rank != 0:
         return
-    base, _ = time_cpu_baseline(budget_s=4.0)  # warm caches / thread pool
-    steps_t = []
     from oracle import w4a16 as OW
     from oracle.formats import bf16_round
 
+    _, full_pass_s = time_cpu_baseline(budget_s=4.0)  # warms caches and the thread pool, times a full pass
+    total_steps = args.warmup + args.steps
+    frac = min(1.0, budget_s / (total_steps * full_pass_s))
+    rows = int(min(N, max(GROUP, round(N * frac / GROUP) * GROUP)))
     rng = np.random.default_rng(42)
-    w = bf16_round((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    w = bf16_round((rng.standard_normal((rows, K)) * 0.02).astype(np.float32))
     packed, scales, _ = OW.pack_weight(w)
     xs = {m: bf16_round(rng.standard_normal((m, K)).astype(np.float32)) for m in M_LIST}
-    for i in range(args.warmup + args.steps):
+    steps_t = []
+    for i in range(total_steps):
         t0 = time.perf_counter()
         for m in M_LIST:
             cpu_port_once(xs[m], packed, scales)
         if i >= args.warmup:
             steps_t.append(time.perf_counter() - t0)
     total = sum(steps_t)
-    ops = sum(algorithmic_ops(m) for m in M_LIST) * args.steps
+    ops = sum(2 * m * rows * K for m in M_LIST) * args.steps
     value = ops / total / 1e12
+    sample = (f"each step covers the first {rows} of {N} output channels at every M "
+              f"({100.0 * rows / N:.1f}% of the workload's operations), {total:.1f} s of CPU time in {args.steps} steps")
     line = {
         "impl": "reference", "metric": "quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4xbf16->f32",
         "data": "synthetic", "config": workload_config(default_copies()),
         "cpu_baseline": {"value": value, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": "every step is one full pass of the workload on the host cores"},
+                         "sample": sample},
         "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -242,19 +255,23 @@ def workload_config(copies):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=6000)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="cfg2_w4a16_g128", choices=["cfg2_w4a16_g128"])
     parser.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
     parser.add_argument("--skip-chunk", action="store_true", help="omit the action-chunk latency leg")
+    parser.add_argument("--no-graphs", action="store_true",
+                        help="launch the timed steps directly instead of replaying CUDA graphs (for profilers; "
+                             "host launch cost then sits inside the timed region)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    from rk_b200 import replicas
+
+    info = replicas.rank_info()
+    rank, world, local_rank = info.rank, info.world, info.local_rank
 
     if args.impl == "reference":
         run_reference(args, rank)
@@ -262,15 +279,12 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
-    import torch.distributed as dist
-
     from rk_b200 import _lib
     from rk_b200.w4a16_linear import W4A16Linear, linear_w4a16
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    replicas.init(info, device)
 
     copies = default_copies()
     weights, xs = make_inputs(device, copies, seed=42 + rank)
@@ -295,9 +309,7 @@ def main():
             launch(m, (i * len(M_LIST) + j) % copies)
 
     def barrier():
-        if world > 1:
-            dist.barrier(device_ids=[local_rank])
-        torch.cuda.synchronize(device)
+        replicas.barrier(info, device)
 
     def capture(first_step, count):
         """One CUDA graph holding `count` consecutive steps (host launch cost stays out of the timing)."""
@@ -321,21 +333,30 @@ def main():
     barrier()
     # the timed region replays graphs of `copies` steps (one full rotation of the weight copies)
     # plus one graph with the remainder, so that exactly args.steps steps run
-    cycle = capture(0, copies)
     full, rest = divmod(args.steps, copies)
-    tail = capture(0, rest) if rest else None
-    cycle.replay()
+    cycle = tail = None
+    if not args.no_graphs:
+        cycle = capture(0, copies)
+        tail = capture(0, rest) if rest else None
+        cycle.replay()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        deadline = time.perf_counter() + 3.0  # the first sample marks that sampling is live
+        while not sampler.samples and time.perf_counter() < deadline:
+            time.sleep(0.02)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
-    for _ in range(full):
-        cycle.replay()
-    if tail is not None:
-        tail.replay()
+    if args.no_graphs:
+        for i in range(args.steps):
+            step(i)
+    else:
+        for _ in range(full):
+            cycle.replay()
+        if tail is not None:
+            tail.replay()
     stop.record(stream)
     barrier()
     elapsed_ms = start.elapsed_time(stop)
@@ -347,6 +368,16 @@ def main():
     inner = copies * 4
     per_m_ms = {}
     for m in M_LIST:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if args.no_graphs:
+            torch.cuda.synchronize(device)
+            a.record(stream)
+            for c in range(inner):
+                launch(m, c % copies)
+            b.record(stream)
+            torch.cuda.synchronize(device)
+            per_m_ms[m] = a.elapsed_time(b) / inner
+            continue
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream(device)
         side.wait_stream(stream)
@@ -359,7 +390,6 @@ def main():
         stream.wait_stream(side)
         graph.replay()
         torch.cuda.synchronize(device)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
         for _ in range(3):
             graph.replay()
@@ -396,19 +426,15 @@ def main():
     if not args.skip_chunk:
         chunk = chunk_latency(device)
         if world > 1:
-            worst = torch.tensor([chunk["p50_ms"]], device=device, dtype=torch.float64)
-            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-            chunk["p50_ms_max_over_ranks"] = worst.item()
-            chunk["box_chunks_per_s"] = world * chunk["envs"] / (worst.item() * 1e-3)
+            (worst,) = replicas.max_over_ranks([chunk["p50_ms"]], info, device)
+            chunk["p50_ms_max_over_ranks"] = worst
+            chunk["box_chunks_per_s"] = replicas.whole_job_rate(chunk["envs"], info, worst)
 
-    times = torch.tensor([elapsed_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = times.tolist()
+    elapsed_ms, e2e_ms = replicas.max_over_ranks([elapsed_ms, e2e_s * 1e3], info, device)
 
     step_ops = sum(algorithmic_ops(m) for m in M_LIST)
-    value = step_ops * args.steps * world / (elapsed_ms * 1e-3) / 1e12
-    e2e_value = step_ops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+    value = replicas.whole_job_rate(step_ops * args.steps, info, elapsed_ms) / 1e12
+    e2e_value = replicas.whole_job_rate(step_ops * e2e_steps, info, e2e_ms) / 1e12
 
     if rank == 0:
         peaks = load_peaks()
@@ -430,7 +456,7 @@ def main():
             "peak": peaks["hbm_gbs"] if hbm_bound else peaks["bf16_tflops"],
             "unit": "GB/s" if hbm_bound else "TFLOP/s",
             "frac": d["hbm_frac"] if hbm_bound else d["bf16_frac"],
-            "traffic": None,
+            "traffic": NCU_DRAM_TRAFFIC.get(dominant),
             "peak_source": peaks["source"],
             "algorithmic_per_launch": algorithmic_bytes(dominant) if hbm_bound else algorithmic_ops(dominant),
         }
@@ -449,8 +475,7 @@ def main():
             "cpu_baseline": cpu_baseline, "device_status": status, "action_chunk": chunk,
         }
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    replicas.finish()
 
 
 if __name__ == "__main__":

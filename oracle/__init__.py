@@ -13,10 +13,12 @@ Parity status per family (what the restatement is pinned against):
   by running the reference's own Triton kernels (interpreter mode, CPU) and its
   own torch weight-packing code, and by evaluating the known-answer formula of
   ``tests/gpu/test_integer_linear.py:30-37``.
-* number formats (E4M3, UE4M3, UE8M0, E2M1): PINNED against the host
-  conversion routines of the CUTLASS revision vendored by the reference
-  (``oracle/ref_formats.cpp`` compiled into ``oracle/_ref``) and cross-checked
-  against torch's float8 casts.
+* number formats (E4M3, UE4M3, UE8M0, E2M1) and the scale-factor layout: PINNED
+  against the conversion routines the reference itself calls - the host paths
+  of its vendored CUTLASS 4.4.2 types, the toolkit's FP8 conversion, and its own
+  ``scale_offset`` - compiled from the reference checkout by
+  ``oracle/build_ref.py`` (``oracle/ref_formats.cpp`` -> ``oracle/_ref``), and
+  cross-checked against torch's float8 casts.
 * per-tensor FP8, MXFP8, NVFP4 packers and GEMMs: PARITY UNPINNED by any
   reference test or runnable reference code (they are CUDA-only and the
   reference has no numerical test for them); the restatement follows the

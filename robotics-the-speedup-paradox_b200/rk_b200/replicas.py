@@ -1,0 +1,83 @@
+"""Host-side helpers for running the quantized linears as independent replicas, one process per GPU.
+
+The linears of independent environment rollouts never exchange data: every rank owns a full copy
+of the packed weights and its own activations, so there is no data-path collective.  What the ranks
+do share is measurement: a common start line (barrier) and the slowest rank's time (max over
+ranks), from which whole-job throughput is the units all ranks processed divided by that time.
+The same helpers run on CPU ranks (`gloo`) and GPU ranks (`nccl`).
+"""
+
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class RankInfo:
+    rank: int
+    world: int
+    local_rank: int
+
+
+def rank_info(env=None) -> RankInfo:
+    """Reads the launcher's RANK / WORLD_SIZE / LOCAL_RANK (defaults describe a single process)."""
+    env = os.environ if env is None else env
+    rank = int(env.get("RANK", "0"))
+    world = int(env.get("WORLD_SIZE", "1"))
+    local = int(env.get("LOCAL_RANK", "0"))
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"inconsistent launcher environment: RANK={rank} WORLD_SIZE={world}")
+    return RankInfo(rank, world, local)
+
+
+def init(info: RankInfo, device: torch.device) -> None:
+    """Joins the process group when there is more than one rank (nccl on GPUs, gloo on CPU)."""
+    if info.world == 1 or dist.is_initialized():
+        return
+    if device.type == "cuda":
+        dist.init_process_group("nccl", device_id=device)
+    else:
+        dist.init_process_group("gloo")
+
+
+def barrier(info: RankInfo, device: torch.device) -> None:
+    """All ranks arrive, and this rank's device is idle, before anyone continues."""
+    if info.world > 1:
+        if device.type == "cuda":
+            dist.barrier(device_ids=[device.index])
+        else:
+            dist.barrier()
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+
+
+def max_over_ranks(values, info: RankInfo, device: torch.device):
+    """Element-wise maximum of a short list of floats over all ranks (the slowest rank's times)."""
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    if info.world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def shard_range(total_units: int, info: RankInfo):
+    """Contiguous slice [begin, end) of `total_units` independent units owned by this rank; the first
+    `total_units % world` ranks take one extra unit.  Used when a fixed job is split (strong scaling)."""
+    if total_units < 0:
+        raise ValueError("total_units must be non-negative")
+    base, extra = divmod(total_units, info.world)
+    begin = info.rank * base + min(info.rank, extra)
+    return begin, begin + base + (1 if info.rank < extra else 0)
+
+
+def whole_job_rate(units_per_rank: float, info: RankInfo, slowest_ms: float) -> float:
+    """Units per second of the whole job when every rank processed `units_per_rank` (weak scaling)."""
+    if slowest_ms <= 0:
+        raise ValueError("elapsed time must be positive")
+    return units_per_rank * info.world / (slowest_ms * 1e-3)
+
+
+def finish() -> None:
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -1,0 +1,72 @@
+"""Two CPU ranks over gloo exercise the multi-process host logic the benchmark uses on GPUs:
+launcher environment parsing, the common start line, max-over-ranks timing and the whole-job rate."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, results):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    sys.path.insert(0, str(root / "robotics-the-speedup-paradox_b200"))
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from rk_b200 import replicas
+
+    info = replicas.rank_info()
+    device = torch.device("cpu")
+    replicas.init(info, device)
+    replicas.barrier(info, device)
+    # rank r pretends its timed region took 10 + 5 r ms and its end-to-end region 20 - 3 r ms
+    slow = replicas.max_over_ranks([10.0 + 5.0 * rank, 20.0 - 3.0 * rank], info, device)
+    begin, end = replicas.shard_range(7, info)
+    rate = replicas.whole_job_rate(1000.0, info, slow[0])
+    results[rank] = (info.rank, info.world, slow, (begin, end), rate)
+    replicas.barrier(info, device)
+    replicas.finish()
+
+
+@pytest.mark.timeout(120)
+def test_two_gloo_ranks_agree_on_slowest_time_and_job_rate():
+    world = 2
+    port = _free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
+    assert sorted(results.keys()) == [0, 1]
+    for rank in range(world):
+        r, w, slow, shard, rate = results[rank]
+        assert (r, w) == (rank, world)
+        assert slow == [15.0, 20.0]  # element-wise maxima: rank 1's first value, rank 0's second
+        assert rate == pytest.approx(1000.0 * 2 / 15e-3)
+    # the two shards tile [0, 7) without overlap, the first rank taking the extra unit
+    assert results[0][3] == (0, 4) and results[1][3] == (4, 7)
+
+
+def test_single_process_defaults_and_validation():
+    import sys
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "robotics-the-speedup-paradox_b200"))
+    from rk_b200 import replicas
+
+    info = replicas.rank_info({})
+    assert (info.rank, info.world, info.local_rank) == (0, 1, 0)
+    assert replicas.max_over_ranks([3.0, 1.0], info, torch.device("cpu")) == [3.0, 1.0]
+    assert replicas.shard_range(5, info) == (0, 5)
+    with pytest.raises(ValueError):
+        replicas.rank_info({"RANK": "2", "WORLD_SIZE": "2"})
+    with pytest.raises(ValueError):
+        replicas.whole_job_rate(1.0, info, 0.0)
