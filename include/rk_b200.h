@@ -148,9 +148,13 @@ int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* b, const fl
 /* ---- W4A16 int4, group 128 -------------------------------------------------------------- */
 
 /* Group-wise symmetric int4 weight packing: per (row, 128 consecutive k): s = bf16(max|w| / 7)
- * (1.0 when zero), q = clamp(rint(w / s), -7, 7).  q uint8 [n, k/2]; scales bf16 [k/128, n].
- * Conventions follow the reference's int4 packing (ampere_ada/integer.py:250-263) and its mixed
- * scale orientation (blackwell/csrc/fp4_mixed_cutlass_linear.cu:89-90); k % 128 == 0. */
+ * (1.0 when zero), q = clamp(rint(w / s), -7, 7) as a two's-complement nibble.  q uint8 [n, k/2];
+ * scales bf16 [k/128, n].  Quantisation rules follow the reference's int4 packing
+ * (ampere_ada/integer.py:250-263) and its mixed scale orientation
+ * (blackwell/csrc/fp4_mixed_cutlass_linear.cu:89-90); k % 128 == 0.
+ * Nibble order (this format's own, chosen for the GEMM's expansion step): eight consecutive
+ * weights k0..k7 of a row occupy four bytes, byte b = k_b | (k_{b+4} << 4).  The packed buffer is
+ * only meaningful to rk_gemm_w4a16_g128. */
 int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, void* stream);
 /* out[m, n] = bf16( sum_g s[g, n] * sum_{k in g} x[m, k] * q[n, k] (+ bias[n]) ), fp32 accumulation.
  * Stands in for `linear_w4a16` (blackwell/csrc/fp4_mixed_cutlass_linear.cu:190-410) with the

@@ -79,6 +79,11 @@ constexpr uint32_t kWaitSpinMax = 1u << 21;  // with 256 ns sleeps: roughly half
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code) {
+  // In steady state most waits find their phase already complete.  The non-blocking probe answers
+  // that case an order of magnitude faster than the potentially-blocking form (measured: a
+  // try_wait that succeeds at once still costs a few hundred cycles), so probe first and park
+  // only when there is something to wait for.
+  if (mbar_test_wait(bar, parity)) return true;
   for (uint32_t it = 0; it < kWaitSpinMax; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > kWaitSpinFast) {
@@ -89,6 +94,33 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   *abort_flag = 1;
   if (status) atomicCAS(status, 0, code);
   return false;
+}
+
+// Warp-level wait by polling.  Lane 0 probes the barrier with the non-blocking form and sleeps a
+// few tens of nanoseconds between probes, so several warps may watch one barrier without parking on
+// it and without flooding the shared-memory pipe; the verdict reaches the other lanes by shuffle.
+// There is no CTA-wide rendezvous: warps that share a role drift freely and the barrier arrival
+// counts keep them honest.  Every lane of the warp must call this.  Returns false on give-up.
+constexpr uint32_t kPollFast = 64;
+__device__ __forceinline__ bool mbar_poll_lane(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code) {
+  uint32_t it = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (++it > kWaitSpinMax) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+    __nanosleep(it < kPollFast ? 20 : 256);
+  }
+  return true;
+}
+__device__ __forceinline__ bool mbar_poll_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_poll_lane(bar, parity, abort_flag, status, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // Ring position: stage index plus the phase parity of that stage's barriers.  Advancing costs an
@@ -105,34 +137,6 @@ struct Ring {
   }
 };
 
-// Warp-wide bounded wait: lane 0 polls, the verdict is broadcast.  Thirty-two lanes polling one
-// barrier word would flood the shared-memory pipe that the TMA-issuing and MMA-issuing threads of
-// the same SM also need; one polling lane per warp, backing off with short sleeps after the
-// first few misses, keeps that pipe free.  Every lane of the warp must call this.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                               int code, uint32_t sleep_ns = 32) {
-  int ok = 0;
-  if ((threadIdx.x & 31) == 0) {
-    ok = 1;
-    uint32_t it = 0;
-    while (!mbar_try_wait(bar, parity)) {
-      if (++it > 64) {
-        if (*abort_flag) {
-          ok = 0;
-          break;
-        }
-        __nanosleep(sleep_ns);
-      }
-      if (it > kWaitSpinMax) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        ok = 0;
-        break;
-      }
-    }
-  }
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
 
 // Group-wide bounded wait with ONE polling thread: the hardware parks a single waiter per
 // barrier; further threads polling the same barrier return at once and spin at full issue rate,
@@ -169,6 +173,15 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap,
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%3, %4}], [%2], %5;"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+// Three coordinates (innermost first); the x * element-size alignment rule is the same as in 2-D.
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

@@ -11,6 +11,7 @@
 #include "rk_gemm_tc.cuh"
 #include "rk_gemm_tc2.cuh"
 #include "rk_gemm_w4.cuh"
+#include "rk_gemm_w4fold.cuh"
 #include "rk_host.h"
 
 namespace rk {
@@ -49,8 +50,11 @@ EncodeTiledFn encode_fn() {
 struct MapKey {
   const void* ptr;
   uint64_t inner, rows, pitch;
+  uint64_t planes, plane_pitch;  // third dimension (0 for 2-D maps)
   uint32_t box_inner, box_rows;
+  uint32_t box_planes;
   int dtype, swizzle;
+  int pad;
   bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
 struct MapKeyHash {
@@ -96,6 +100,53 @@ int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dtype, in
   CUresult r = fn(out, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(RK_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return RK_OK;
+}
+
+// 3-D view [planes, rows, inner] (elements) of a row-major matrix: `planes` consecutive slices of
+// `inner` elements along each row, `plane_pitch_bytes` apart.  One box {box_inner, box_rows,
+// box_planes} then lands in shared memory as box_planes blocks of box_rows x box_inner, which is how
+// one copy fetches several swizzle-width column blocks of a tile.
+int make_map_3d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dtype, uint64_t inner, uint64_t rows,
+                uint64_t planes, uint64_t pitch_bytes, uint64_t plane_pitch_bytes, uint32_t box_inner,
+                uint32_t box_rows, uint32_t box_planes, CUtensorMapSwizzle swizzle) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.ptr = ptr;
+  key.inner = inner;
+  key.rows = rows;
+  key.pitch = pitch_bytes;
+  key.planes = planes;
+  key.plane_pitch = plane_pitch_bytes;
+  key.box_inner = box_inner;
+  key.box_rows = box_rows;
+  key.box_planes = box_planes;
+  key.dtype = static_cast<int>(dtype);
+  key.swizzle = static_cast<int>(swizzle);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return RK_OK;
+    }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(RK_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (!aligned16(ptr) || pitch_bytes % 16 != 0 || plane_pitch_bytes % 16 != 0)
+    return fail(RK_EINVAL, "matrix base and pitches must be 16-byte aligned");
+  const cuuint64_t dims[3] = {inner, rows, planes};
+  const cuuint64_t strides[2] = {pitch_bytes, plane_pitch_bytes};
+  const cuuint32_t box[3] = {box_inner, box_rows, box_planes};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dtype, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(RK_ECUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", static_cast<int>(r));
   std::lock_guard<std::mutex> lock(mu);
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
@@ -638,6 +689,65 @@ extern "C" int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, co
   return run_tc(t);
 }
 
+template <int BN>
+int launch_w4_fold(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const W4Params& p,
+                   int tiles_n, int tiles_m, int smem, cudaStream_t st) {
+  static bool configured_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& configured = configured_dev[dev & 63];
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(rk_gemm_w4a16_fold_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBudget + 1024);
+    if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(tiles_n, tiles_m, 1);
+  cfg.blockDim = dim3(kW4fThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_fold_kernel<BN>, tm_w, tm_x, tm_s, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_gemm_w4a16_fold_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
+}
+
+// Activation batches above 64 rows: scale folded into the expanded weights, one accumulator for all of K.
+int run_w4_fold(const void* x, const void* q, const void* scales, W4Params p, int64_t m, int64_t n, int64_t k,
+                int scales_bytes, cudaStream_t st, const char* who) {
+  const int bn = m > 128 ? 256 : 128;
+  const int tiles_n = static_cast<int>((n + 127) / 128);
+  const int tiles_m = static_cast<int>((m + bn - 1) / bn);
+  const int x_bytes = bn * 128;
+  const int slots = w4f_slots(bn);
+  const int copies = (p.groups + 1) / 2;
+  int w_stages = (kSmemBudget - scales_bytes - slots * x_bytes) / kW4PairBytes;
+  if (w_stages > kW4MaxW) w_stages = kW4MaxW;
+  if (w_stages > copies) w_stages = copies;
+  if (w_stages < 1) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
+  p.w_stages = w_stages;
+  const int smem = slots * x_bytes + w_stages * kW4PairBytes + scales_bytes + 1024;
+  CUtensorMap tm_w, tm_x, tm_s;
+  const uint32_t group_box = static_cast<uint32_t>(p.groups < 256 ? p.groups : 256);
+  int rc = make_map_2d(&tm_s, scales, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k / 128, n * 2, 128, group_box,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != RK_OK) return rc;
+  rc = make_map_2d(&tm_w, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k / 2, n, k / 2, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != RK_OK) return rc;
+  rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != RK_OK) return rc;
+  return bn == 256 ? launch_w4_fold<256>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st)
+                   : launch_w4_fold<128>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+}
+
 extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scales, const void* bias, void* out,
                                   int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
                                   void* stream) {
@@ -663,30 +773,41 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   p.groups = static_cast<int>(k / 128);
   const int scales_bytes = static_cast<int>(round_up((k / 128) * 256, 1024));  // [groups][128] bf16 in shared memory
   if (scales_bytes > 64 * 1024) return fail(RK_EUNSUPPORTED, "%s: k > 32768", who);
-  // ring depths: unpacked tiles (32 KB each) and activation tiles first, the rest goes to the
-  // raw-weight ring, whose depth is what keeps enough HBM requests in flight
+  if (!aligned16(scales)) return fail(RK_EINVAL, "%s: scales must be 16-byte aligned", who);
+  if (m > 64 && !(tactic & 2)) {  // tactic bit 1 keeps the per-group-accumulator kernel for any m
+    p.ldo = n;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.status = ws.status;
+    return run_w4_fold(x, q, scales, p, m, n, k, scales_bytes, as_stream(stream), who);
+  }
+  // shared memory: the activation tiles of the slot ring first, the rest goes to the raw-weight
+  // ring (group pairs of 16 KB), whose depth is what keeps enough HBM requests in flight
   const int x_bytes = 2 * bn * 128;
-  p.xf_stages = w4_xf_depth(bn);  // unpacked weights live in TMEM; the activation ring in shared memory matches
-  p.x_stages = p.xf_stages;       // one commit releases both rings
-  int w_stages = (kSmemBudget - scales_bytes - p.x_stages * x_bytes) / kW4RawBytes;
+  const int slots = w4_slots(bn);
+  const int pairs = (p.groups + 1) / 2;
+  int w_stages = (kSmemBudget - scales_bytes - slots * x_bytes) / kW4PairBytes;
   if (w_stages > kW4MaxW) w_stages = kW4MaxW;
-  if (w_stages > p.groups) w_stages = p.groups;
+  if (w_stages > pairs) w_stages = pairs;
   if (w_stages < 1) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
   p.w_stages = w_stages;
   p.ldo = n;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = ws.status;
-  const int smem = p.x_stages * x_bytes + w_stages * kW4RawBytes + scales_bytes + 1024;
+  const int smem = slots * x_bytes + w_stages * kW4PairBytes + scales_bytes + 1024;
   if (!aligned16(scales)) return fail(RK_EINVAL, "%s: scales must be 16-byte aligned", who);
   CUtensorMap tm_w, tm_x, tm_s;
   const uint32_t group_box = static_cast<uint32_t>(p.groups < 256 ? p.groups : 256);
   rc = make_map_2d(&tm_s, scales, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k / 128, n * 2, 128, group_box,
                    CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != RK_OK) return rc;
-  rc = make_map_2d(&tm_w, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k / 2, n, k / 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_64B);
+  // raw weights: 128 bytes (two K groups) of 128 rows per copy
+  rc = make_map_2d(&tm_w, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k / 2, n, k / 2, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
-  rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B);
+  // activations as [k / 64][m][64]: one box {64, bn, 2} is both 64-element column blocks of a K group
+  rc = make_map_3d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 64, m, k / 64, k * 2, 128, 64, bn, 2,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
   cudaStream_t st = as_stream(stream);
   if (tactic & 1) {  // four unpack warps instead of eight
@@ -757,7 +878,7 @@ extern "C" int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* 
 #ifdef RK_TRACE
 // Developer aid (trace builds only): copies the W4A16 role timestamps of CTA (0,0) to the host.
 extern "C" int rk_trace_read(long long* host, int count) {
-  if (count > 16 * 64) count = 16 * 64;
+  if (count > 32 * 64) count = 32 * 64;
   return cudaMemcpyFromSymbol(host, rk::rk_trace_buf, sizeof(long long) * count) == cudaSuccess ? 0 : -3;
 }
 #endif

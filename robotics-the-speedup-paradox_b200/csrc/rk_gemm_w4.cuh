@@ -1,18 +1,25 @@
 // W4A16 group-wise int4 GEMM: bf16 activations x signed-int4 weights (group 128 along K,
 // bf16 group scales), fp32 accumulation, bf16 output.
 //
-// Packed weights stream from HBM by TMA as raw bytes through a deep ring (the weight stream is
-// what must saturate HBM); the small activation tile of each K group rides a second, shallow ring
-// (it comes from L2).  "Unpack" warps expand each 128 x 128 group tile to bf16 integers (exact) and
-// store them straight into TENSOR MEMORY with tcgen05.st (one output channel per TMEM lane, two
-// bf16 per 32-bit column) - writing the four-times-larger bf16 tile to shared memory instead costs
-// more shared-memory store bandwidth than the whole kernel may spend.  One thread issues tcgen05
-// kind::f16 MMAs whose A operand is that TMEM tile and whose B operand is the activation tile in
-// shared memory; each K group's *unscaled* partial sum lands in a ring of TMEM accumulators; four
-// epilogue warps drain each group's partial sum, multiply by that group's scale in fp32 and keep
-// the running total in registers.  The weights sit on the MMA M axis (one TMEM lane per output
-// channel) so the group scale is a per-thread scalar; the group scales of the CTA's 128 channels
-// are fetched once into shared memory.
+// Packed weights stream from HBM by TMA as raw bytes through a deep ring, two K groups (128 bytes
+// of every row) per copy; the weight stream is what must saturate HBM.  Everything else moves
+// through ONE ring of "slots".  A slot holds what one K group needs on chip: the activation tile
+// of the group in shared memory (one 3-D TMA copy, it comes from L2), the group's 128 x 128
+// weight tile expanded to bf16 in TENSOR MEMORY, and a TMEM accumulator for the group's partial
+// sum.  "Unpack" warps expand the raw tile to bf16 integers (exact) and store them straight into
+// tensor memory with tcgen05.st (one output channel per TMEM lane, two bf16 per 32-bit column) -
+// writing the four-times-larger bf16 tile to shared memory instead costs more shared-memory store
+// bandwidth than the whole kernel may spend.  One thread issues tcgen05 kind::f16 MMAs whose A
+// operand is that TMEM tile and whose B operand is the activation tile; the group's *unscaled*
+// partial sum lands in the slot's accumulator; four epilogue warps drain it, multiply by the
+// group's scale in fp32 and keep the running total in registers, then hand the whole slot back.
+// The weights sit on the MMA M axis (one TMEM lane per output channel) so the group scale is a
+// per-thread scalar; the group scales of the CTA's 128 channels are fetched once into shared memory.
+//
+// Barriers per slot: `slot_full` (unpack warps + the activation copy -> MMA thread), `acc_full`
+// (MMA commit -> epilogue), `slot_empty` (epilogue -> unpack warps and producer).  The MMA thread
+// is a single thread sharing its scheduler with busy unpack warps, so every instruction it issues
+// is slow; it therefore waits on exactly one barrier and commits exactly once per group.
 //
 // Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2 .. 2+UW-1 = unpack,
 // last four = epilogue.
@@ -27,7 +34,7 @@ namespace rk {
 // Developer aid, compiled out unless RK_TRACE is defined: CTA (0,0) records SM-clock timestamps of
 // each role's progress per K group into a device array that rk_trace_read() copies back.
 #ifdef RK_TRACE
-__device__ long long rk_trace_buf[16 * 64];
+__device__ long long rk_trace_buf[32 * 64];
 #define RK_TRACE_REC(slot, g)                                                        \
   do {                                                                               \
     if (blockIdx.x == 0 && blockIdx.y == 0 && (g) < 64) rk_trace_buf[(slot) * 64 + (g)] = clock64(); \
@@ -37,18 +44,14 @@ __device__ long long rk_trace_buf[16 * 64];
 #endif
 
 constexpr int kW4Group = 128;                // K elements per scale group == K elements per pipeline step
-constexpr int kW4RawBytes = 128 * 64;        // packed 128 x 128 int4 tile
+constexpr int kW4PairBytes = 128 * 128;      // packed weights of two K groups: 128 rows x 128 bytes
 constexpr int kW4ACols = 64;                 // TMEM columns of one unpacked 128 x 128 bf16 tile (2 per column)
-constexpr int kW4MaxW = 16;                  // raw-weight ring depth limit
-constexpr int kW4MaxX = 4;                   // activation ring depth limit
-constexpr int kW4MaxXf = 4;                  // unpacked-weight ring depth limit
-constexpr int kW4MaxAcc = 8;                 // TMEM accumulator ring depth limit
+constexpr int kW4MaxW = 8;                   // raw-weight ring depth limit (group pairs)
+constexpr int kW4MaxSlots = 6;               // slot ring depth limit
 
 struct W4Params {
   int m, n, groups;  // activation rows, weight rows, K / 128
-  int w_stages;      // raw-weight ring depth
-  int x_stages;      // activation ring depth
-  int xf_stages;     // unpacked-weight (TMEM) ring depth == activation ring depth
+  int w_stages;      // raw-weight ring depth, in group pairs
   long long ldo;
   const __nv_bfloat16* bias;    // [n] or null
   __nv_bfloat16* out;           // [m, ldo]
@@ -56,27 +59,28 @@ struct W4Params {
 };
 
 __host__ __device__ constexpr int w4_threads(int unpack_warps) { return 32 * (2 + unpack_warps + 4); }
-// TMEM budget (512 columns): `xf` unpacked-weight tiles of 64 columns, the rest accumulators.
-__host__ __device__ constexpr int w4_xf_depth(int bn) { return bn == 128 ? 2 : 4; }
-__host__ __device__ constexpr int w4_acc_depth(int bn) {
-  return (512 - w4_xf_depth(bn) * kW4ACols) / bn < kW4MaxAcc ? (512 - w4_xf_depth(bn) * kW4ACols) / bn : kW4MaxAcc;
+// TMEM budget (512 columns): every slot takes 64 columns of unpacked weights and `bn` accumulator columns.
+__host__ __device__ constexpr int w4_slots(int bn) {
+  return 512 / (kW4ACols + bn) < kW4MaxSlots ? 512 / (kW4ACols + bn) : kW4MaxSlots;
 }
 
-// Eight two's-complement nibbles (k ascending from the low nibble) -> eight bf16 integers.
-// Per pair of weights: one byte permute puts byte j of `w` (even k) in byte 0 and byte j of
-// `w >> 4` (odd k) in byte 2, one logic op keeps the low nibbles and ORs in the bf16 pattern of
-// 128 (0x4300 | u == 128 + u exactly), one packed subtract of 136 gives the signed value.
+// One packed word = eight two's-complement nibbles; byte b holds weight k_b (low nibble) and
+// k_{b+4} (high nibble).  Two logic ops isolate the low and the high nibbles as offset-binary bytes
+// (n + 8, 0..15); one byte permute per output register then interleaves two of those bytes with
+// the constant 0x43 (0x4300 | u is the bf16 value 128 + u exactly), and a packed subtract of 136
+// gives the signed values.  Output register j holds the bf16 pair (k_2j, k_2j+1).
 __device__ __forceinline__ uint4 w4_unpack8(uint32_t w) {
-  w ^= 0x88888888u;  // n -> n + 8 (offset binary, 0..15)
-  const uint32_t wh = w >> 4;
+  const uint32_t lo = (w ^ 0x88888888u) & 0x0F0F0F0Fu;         // bytes: k0 k1 k2 k3 (+8)
+  const uint32_t hi = ((w >> 4) ^ 0x08080808u) & 0x0F0F0F0Fu;  // bytes: k4 k5 k6 k7 (+8)
+  const uint32_t c43 = 0x43434343u;
+  const uint32_t c136 = 0x43084308u;  // bf16 136.0 twice
+  uint32_t v[4] = {__byte_perm(lo, c43, 0x4140u), __byte_perm(lo, c43, 0x4342u), __byte_perm(hi, c43, 0x4140u),
+                   __byte_perm(hi, c43, 0x4342u)};
   uint32_t o[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const uint32_t x = __byte_perm(w, wh, 0x0400u + j * 0x0101u);  // bytes: w[j], w[0], wh[j], w[0]
-    const uint32_t v = (x & 0x000F000Fu) | 0x43004300u;
-    const uint32_t c = 0x43084308u;  // bf16 136.0 twice
-    __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v),
-                               *reinterpret_cast<const __nv_bfloat162*>(&c));
+    __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v[j]),
+                               *reinterpret_cast<const __nv_bfloat162*>(&c136));
     o[j] = *reinterpret_cast<uint32_t*>(&d);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
@@ -88,35 +92,30 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                      const __grid_constant__ CUtensorMap tm_s, const W4Params p) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 128, "activation tile must be 16..128 rows");
   static_assert(UW == 4 || UW == 8, "four or eight unpack warps");
-  constexpr int kXBytes = 2 * BN * 128;  // two 64-element atoms of BN rows
-  constexpr int kAcc = w4_acc_depth(BN);
-  constexpr int kXf = w4_xf_depth(BN);
-  constexpr int kAccCols = BN;             // TMEM columns of one accumulator slot
-  constexpr uint32_t kTmemCols = 512;      // [0, kXf*64): unpacked weights; then kAcc accumulator slots
-  constexpr uint32_t kAccBase = kXf * kW4ACols;
+  constexpr int kXBytes = 2 * BN * 128;  // two 64-element column blocks of BN rows
+  constexpr int kSlots = w4_slots(BN);
+  constexpr uint32_t kTmemCols = 512;      // [0, kSlots*64): unpacked weights; then kSlots accumulators of BN columns
+  constexpr uint32_t kAccBase = kSlots * kW4ACols;
   constexpr int kEpiWarp0 = 2 + UW;
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_w_full[kW4MaxW];
   __shared__ __align__(8) uint64_t bar_w_empty[kW4MaxW];
-  __shared__ __align__(8) uint64_t bar_x_full[kW4MaxX];
-  __shared__ __align__(8) uint64_t bar_xf_full[kW4MaxXf];
-  __shared__ __align__(8) uint64_t bar_xf_empty[kW4MaxXf];
-  __shared__ __align__(8) uint64_t bar_acc_full[kW4MaxAcc];
-  __shared__ __align__(8) uint64_t bar_acc_empty[kW4MaxAcc];
+  __shared__ __align__(8) uint64_t bar_slot_full[kW4MaxSlots];
+  __shared__ __align__(8) uint64_t bar_slot_empty[kW4MaxSlots];
+  __shared__ __align__(8) uint64_t bar_acc_full[kW4MaxSlots];
   __shared__ __align__(8) uint64_t bar_scales;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int verdict_unpack[2], verdict_epi[2];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* const smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
-  // shared memory map: [activation ring][raw ring][group scales]
+  // shared memory map: [activation tiles of the slots][raw ring][group scales]
   const uint32_t x_off = 0;
-  const uint32_t w_off = x_off + p.x_stages * kXBytes;
-  const uint32_t scales_off = w_off + p.w_stages * kW4RawBytes;
+  const uint32_t w_off = x_off + kSlots * kXBytes;
+  const uint32_t scales_off = w_off + p.w_stages * kW4PairBytes;
   const int n0 = blockIdx.x * 128;
   const int m0 = blockIdx.y * BN;
   const int G = p.groups;
@@ -127,16 +126,10 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       mbar_init(smem_u32(&bar_w_full[s]), 1);
       mbar_init(smem_u32(&bar_w_empty[s]), UW);
     }
-    for (int s = 0; s < p.x_stages; ++s) {
-      mbar_init(smem_u32(&bar_x_full[s]), 1);
-    }
-    for (int s = 0; s < p.xf_stages; ++s) {
-      mbar_init(smem_u32(&bar_xf_full[s]), UW);
-      mbar_init(smem_u32(&bar_xf_empty[s]), 1);
-    }
-    for (int b = 0; b < kAcc; ++b) {
-      mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[b]), 4);
+    for (int t = 0; t < kSlots; ++t) {
+      mbar_init(smem_u32(&bar_slot_full[t]), UW + 1);  // unpack warps + the activation copy
+      mbar_init(smem_u32(&bar_slot_empty[t]), 4);      // epilogue warps
+      mbar_init(smem_u32(&bar_acc_full[t]), 1);
     }
     mbar_init(smem_u32(&bar_scales), 1);
     abort_flag = 0;
@@ -159,25 +152,24 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   if (threadIdx.x == 0) RK_TRACE_REC(9, 0);
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer: two rings, weights run ahead
+    // ------------------------------------------------------------ TMA producer: weights run ahead of the slots
     if (lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
       mbar_arrive_expect_tx(smem_u32(&bar_scales), static_cast<uint32_t>(G) * 256u);
       tma_load_2d_hint(smem_base + scales_off, &tm_s, n0, 0, smem_u32(&bar_scales), pol_w);
+      const int P = (G + 1) >> 1;  // group pairs; an odd last pair reads zeros beyond K
       int gw = 0, gx = 0;
       Ring rw{0, 0}, rx{0, 0};
       uint32_t idle = 0;
-      while ((gw < G || gx < G) && !*reinterpret_cast<volatile int*>(&abort_flag)) {
+      while ((gw < P || gx < G) && !*reinterpret_cast<volatile int*>(&abort_flag)) {
         bool progressed = false;
-        if (gw < G) {
+        if (gw < P) {
           const int s = rw.stage;
           if (mbar_test_wait(smem_u32(&bar_w_empty[s]), rw.phase ^ 1)) {
             const uint32_t full = smem_u32(&bar_w_full[s]);
-            RK_TRACE_REC(14, gw);
-            mbar_arrive_expect_tx(full, kW4RawBytes);
-            RK_TRACE_REC(15, gw);
-            tma_load_2d_hint(smem_base + w_off + s * kW4RawBytes, &tm_w, gw * 64, n0, full, pol_w);
+            mbar_arrive_expect_tx(full, kW4PairBytes);
+            tma_load_2d_hint(smem_base + w_off + s * kW4PairBytes, &tm_w, gw * 128, n0, full, pol_w);
             RK_TRACE_REC(0, gw);
             ++gw;
             rw.advance(p.w_stages);
@@ -185,18 +177,16 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
           }
         }
         if (gx < G) {
-          const int s = rx.stage;
-          // the activation ring is as deep as the unpacked ring and is released by the same commit;
-          // the unpack leader parks on that barrier, so the producer only probes it
-          if (mbar_test_wait(smem_u32(&bar_xf_empty[s]), rx.phase ^ 1)) {
-            const uint32_t full = smem_u32(&bar_x_full[s]);
-            const uint32_t xs = smem_base + x_off + s * kXBytes;
+          const int t = rx.stage;
+          // nobody parks on this barrier: unpack warps and producer all probe it
+          if (mbar_test_wait(smem_u32(&bar_slot_empty[t]), rx.phase ^ 1)) {
+            const uint32_t full = smem_u32(&bar_slot_full[t]);
             mbar_arrive_expect_tx(full, kXBytes);
-            tma_load_2d_hint(xs, &tm_x, gx * 128, m0, full, pol_x);                  // k 0..63 of the group
-            tma_load_2d_hint(xs + BN * 128, &tm_x, gx * 128 + 64, m0, full, pol_x);  // k 64..127
+            // one copy brings both 64-element column blocks of the group: box {64, BN, 2}
+            tma_load_3d_hint(smem_base + x_off + t * kXBytes, &tm_x, 0, m0, gx * 2, full, pol_x);
             RK_TRACE_REC(1, gx);
             ++gx;
-            rx.advance(p.x_stages);
+            rx.advance(kSlots);
             progressed = true;
           }
         }
@@ -206,42 +196,34 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
           abort_flag = 1;
           atomicCAS(p.status, 0, RK_DEV_TIMEOUT_EMPTY);
         } else if (idle > 2) {
-          __nanosleep(idle > kWaitSpinFast ? 256 : 32);
+          __nanosleep(idle > kWaitSpinFast ? 256 : 64);
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ MMA issuer: one wait, eight MMAs, one commit per group
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 128, BN);
       const uint64_t desc_x0 = umma_desc_k128(smem_base + x_off);
-      Ring rx{0, 0}, rt{0, 0}, rb{0, 0};
-      for (int g = 0; g < G; ++g, rx.advance(p.x_stages), rt.advance(p.xf_stages), rb.advance(kAcc)) {
-        const int sx = rx.stage;
+      Ring rt{0, 0};
+      for (int g = 0; g < G; ++g, rt.advance(kSlots)) {
         const int t = rt.stage;
-        const int b = rb.stage;
-        if (!mbar_wait_bounded(smem_u32(&bar_x_full[sx]), rx.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) break;
-        if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[b]), rb.phase ^ 1, &abort_flag, p.status,
-                               RK_DEV_TIMEOUT_ACC_FREE)) break;
-        if (!mbar_wait_bounded(smem_u32(&bar_xf_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
+        RK_TRACE_REC(26, g);
+        if (!mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
         tc_fence_after();
         RK_TRACE_REC(5, g);
-        // descriptors of the stage: the start-address field advances by bytes >> 4
-        const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((sx * kXBytes) >> 4);
+        // descriptors of the slot: the start-address field advances by bytes >> 4
+        const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((t * kXBytes) >> 4);
         const uint32_t a_tmem = tmem_base + t * kW4ACols;
-        const uint32_t d_tmem = tmem_base + kAccBase + b * kAccCols;
+        const uint32_t d_tmem = tmem_base + kAccBase + t * BN;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          // 16 bf16 of K per MMA: 8 TMEM columns of A, 32 bytes of the activation atom
+          // 16 bf16 of K per MMA: 8 TMEM columns of A, 32 bytes of the activation column block
           const uint64_t bd = bd0 + static_cast<uint64_t>(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
           mma_f16_ts(d_tmem, a_tmem + k * 8, bd, idesc, k > 0 ? 1u : 0u);
-          if (k == 0) RK_TRACE_REC(10, g);
-          if (k == 3) RK_TRACE_REC(11, g);
         }
         RK_TRACE_REC(12, g);
-        RK_TRACE_REC(13, g);
-        tc_commit(smem_u32(&bar_xf_empty[t]));  // frees the unpacked tile and the activation tile
-        tc_commit(smem_u32(&bar_acc_full[b]));
+        tc_commit(smem_u32(&bar_acc_full[t]));
         RK_TRACE_REC(6, g);
       }
     }
@@ -250,36 +232,48 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     // A warp can only write the TMEM lanes of its quadrant (warp % 4), so the thread <-> row map
     // follows it: row = 32 * (warp % 4) + lane.  UW == 4: a thread converts its whole row of the
     // group (64 raw bytes -> 64 columns).  UW == 8: warps w and w + 4 share a quadrant and take
-    // the two halves of K (32 raw bytes -> 32 columns each).
+    // the two halves of the group's K (32 raw bytes -> 32 columns each).
     constexpr int kHalves = UW / 4;          // threads per row
     constexpr int kRawChunks = 4 / kHalves;  // 16-byte raw chunks per thread
     const int uw = warp - 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int h = (kHalves == 2) ? (uw >> 2) : 0;
+    const bool leader = (uw == 0 && lane == 0);
     Ring rw{0, 0}, rt{0, 0};
-    for (int g = 0; g < G; ++g, rw.advance(p.w_stages), rt.advance(p.xf_stages)) {
+    // Barrier probes cost a shared-memory round trip each.  The probes for group g + 1 are issued
+    // right after group g's loads and consumed one loop trip later, so their latency hides behind
+    // the conversion work; only when such an early probe says "not yet" does the warp stop to poll.
+    uint32_t ready = 0;
+    for (int g = 0; g < G; ++g, rt.advance(kSlots)) {
       const int sw = rw.stage;
       const int t = rt.stage;
-      // one rendezvous per group: the leader waits for the raw tile AND for the TMEM slot
-      const bool leader = (uw == 0 && lane == 0);
-      if (leader)
-        verdict_unpack[g & 1] =
-            (mbar_wait_bounded(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW) &&
-             mbar_wait_bounded(smem_u32(&bar_xf_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM))
-                ? 1 : 0;
-      asm volatile("bar.sync 2, %0;" ::"r"(UW * 32) : "memory");
-      if (*reinterpret_cast<volatile int*>(&verdict_unpack[g & 1]) == 0) break;
-      if (uw == 0 && lane == 0) RK_TRACE_REC(2, g);
-      const uint8_t* raw = smem_gen + w_off + sw * kW4RawBytes;
+      const int odd = g & 1;
+      if (!__all_sync(0xffffffffu, ready != 0)) {
+        bool ok = true;
+        if (!odd) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
+        ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      if (leader) RK_TRACE_REC(2, g);
+      // The raw pair was written with the 128-byte swizzle: 16-byte chunk c of row r sits at c ^ (r & 7);
+      // chunks 0..3 belong to the even group of the pair, 4..7 to the odd one.
+      const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
       uint4 pk[kRawChunks];
 #pragma unroll
       for (int i = 0; i < kRawChunks; ++i) {
-        const int c4 = h * kRawChunks + i;
-        // The raw tile was written with the 64-byte swizzle: 16-byte chunk c of row r sits at c ^ ((r >> 1) & 3).
-        pk[i] = *reinterpret_cast<const uint4*>(raw + r * 64 + ((c4 ^ ((r >> 1) & 3)) << 4));
+        const int c = odd * 4 + h * kRawChunks + i;
+        pk[i] = *reinterpret_cast<const uint4*>(raw + ((c ^ (r & 7)) << 4));
       }
-      if (uw == 0 && lane == 0) RK_TRACE_REC(3, g);
+      const bool pair_done = odd || g == G - 1;
+      ready = 0;
+      if (g + 1 < G) {
+        Ring rt2 = rt, rw2 = rw;
+        rt2.advance(kSlots);
+        if (pair_done) rw2.advance(p.w_stages);
+        ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
+        if (odd) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);  // group g + 1 opens a new pair
+      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4ACols + h * 32;
 #pragma unroll
@@ -298,10 +292,12 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(smem_u32(&bar_w_empty[sw]));  // raw slot reusable
-        mbar_arrive(smem_u32(&bar_xf_full[t]));   // unpacked tile ready for the MMA thread
+        mbar_arrive(smem_u32(&bar_slot_full[t]));                    // unpacked tile ready for the MMA thread
+        if (pair_done) mbar_arrive(smem_u32(&bar_w_empty[sw]));      // raw slot reusable
       }
-      if (uw == 0 && lane == 0) RK_TRACE_REC(4, g);
+      if (pair_done) rw.advance(p.w_stages);
+      if (leader) RK_TRACE_REC(4, g);
+      if (lane == 0) RK_TRACE_REC(18 + uw, g);
     }
   } else {
     // ------------------------------------------------------------ epilogue: scale each group, accumulate, store
@@ -311,29 +307,28 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     float acc[BN];
 #pragma unroll
     for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
-    const bool epi_leader = (warp == kEpiWarp0 && lane == 0);
-    bool alive = mbar_wait_group(smem_u32(&bar_scales), 0, epi_leader, 1, 128, &abort_flag, p.status,
-                                 RK_DEV_TIMEOUT_FULL, verdict_epi, 1u);
+    bool alive = mbar_poll_warp(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL);
     const __nv_bfloat16* my_scales = reinterpret_cast<const __nv_bfloat16*>(smem_gen + scales_off) + quad * 32 + lane;
-    Ring rb{0, 0};
-    for (int g = 0; g < G && alive; ++g, rb.advance(kAcc)) {
-      const int b = rb.stage;
+    Ring rt{0, 0};
+    for (int g = 0; g < G && alive; ++g, rt.advance(kSlots)) {
+      const int t = rt.stage;
       const float sc = __bfloat162float(my_scales[g * 128]);
-      alive = mbar_wait_group(smem_u32(&bar_acc_full[b]), rb.phase, epi_leader, 1, 128, &abort_flag, p.status,
-                              RK_DEV_TIMEOUT_ACC, verdict_epi, static_cast<uint32_t>(g));
+      alive = mbar_poll_warp(smem_u32(&bar_acc_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
       tc_fence_after();
       if (quad == 0 && lane == 0) RK_TRACE_REC(7, g);
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16];
-        tmem_ld_16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kAccBase + b * kAccCols + c0, r);
+        tmem_ld_16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kAccBase + t * BN + c0, r);
         tc_wait_ld();
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[c0 + j] = fmaf(__uint_as_float(r[j]), sc, acc[c0 + j]);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[b]));
+      // the MMAs of the group have completed (their commit was observed), so the slot's weight tile,
+      // activation tile and - now drained - accumulator are all free
+      if (lane == 0) mbar_arrive(smem_u32(&bar_slot_empty[t]));
       if (quad == 0 && lane == 0) RK_TRACE_REC(8, g);
     }
     if (alive && n_ok) {

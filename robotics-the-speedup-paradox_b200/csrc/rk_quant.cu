@@ -341,11 +341,16 @@ pack_w4_g128_kernel(const __nv_bfloat16* __restrict__ w, int n, int k, uint8_t* 
   if (!(__bfloat162float(sb) > 0.0f)) sb = __float2bfloat16_rn(1.0f);  // amax / 7 flushed to zero in bf16
   const float s = __bfloat162float(sb);
   if (lane == 0) scales[static_cast<long long>(g) * n + row] = sb;
-  uint32_t packed = 0;
+  // Eight consecutive weights k0..k7 share one 32-bit word whose byte b holds k_b in its low nibble
+  // and k_{b+4} in its high nibble (the order the GEMM's expansion step consumes cheapest).  An
+  // even lane owns k0..k3, its odd neighbour k4..k7.
+  uint32_t spread = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) packed |= static_cast<uint32_t>(quant_code(v[i], s, 7.0f) & 15) << (4 * i);
-  *reinterpret_cast<uint16_t*>(q + static_cast<long long>(row) * (k / 2) + g * 64 + lane * 2) =
-      static_cast<uint16_t>(packed);
+  for (int i = 0; i < 4; ++i) spread |= static_cast<uint32_t>(quant_code(v[i], s, 7.0f) & 15) << (8 * i);
+  const uint32_t upper = __shfl_xor_sync(0xffffffffu, spread, 1);
+  if (!(lane & 1))
+    *reinterpret_cast<uint32_t*>(q + static_cast<long long>(row) * (k / 2) + g * 64 + (lane >> 1) * 4) =
+        spread | (upper << 4);
 }
 
 // ------------------------------------------------------------------ per-tensor FP8

@@ -79,6 +79,32 @@ def test_ragged_shapes_and_bias(H, shape, tactic):
     assert H.rel_frobenius(H.to_np(out), want) < TOL
 
 
+@pytest.mark.parametrize("shape", [(65, 256, 256), (128, 136, 384), (129, 1000, 128), (256, 512, 1024), (300, 256, 640),
+                                   (816, 384, 256)])
+def test_wide_batches_fold_the_scale_into_bf16_weights(H, shape):
+    """Above 64 activation rows the group scale is folded into the expanded weights (one bf16
+    rounding per weight).  The result must (a) stay inside the stated tolerance of the exact
+    definition, (b) match the restatement that folds the same way to within fp32 summation order,
+    and (c) agree with the per-group-accumulator kernel (tactic bit 1) to the same tolerance."""
+    m, n, k = shape
+    x = H.randn_bf16((m, k), 1.0, 17)
+    w = H.randn_bf16((n, k), 0.02, 18)
+    bias = H.randn_bf16((n,), 0.5, 19)
+    q, s = pack(H, w.to(H.DEVICE))
+    out = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 0))
+    exact_kernel = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 2))
+    ep, es, _ = OW.pack_weight(H.to_np(w))
+    _, want = OW.gemm(H.to_np(x), ep, es, H.to_np(bias))
+    folded_bf16, folded = OW.gemm_folded(H.to_np(x), ep, es, H.to_np(bias))
+    assert H.rel_frobenius(out, want) < TOL
+    assert H.rel_frobenius(exact_kernel, want) < TOL
+    assert H.rel_frobenius(out, exact_kernel) < TOL
+    # (b): same values up to the last bf16 digit, and almost everywhere identical
+    assert np.abs(out - folded).max() <= 2.0 ** -8 * np.abs(folded).max() + 1e-6
+    assert (out != folded_bf16).mean() < 0.02
+    assert H.rel_frobenius(out, folded) < H.rel_frobenius(out, want) + 1e-4
+
+
 def test_linearity_at_full_size(H):
     """Size-independent property: the GEMM is linear in the activations (exact powers of two)."""
     n, k, m = 16384, 2048, 50
