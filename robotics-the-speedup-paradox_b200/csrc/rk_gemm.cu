@@ -480,8 +480,8 @@ int unpack_int4(const void* in, void* out, long long packed_bytes, cudaStream_t 
 }
 
 template <int BN, int UW>
-int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const W4Params& p, int tiles_n,
-              int tiles_m, int smem, cudaStream_t st) {
+int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const CUtensorMap& tm_o,
+              const W4Params& p, int tiles_n, int tiles_m, int smem, cudaStream_t st) {
   static bool configured_dev[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -502,7 +502,7 @@ int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMa
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl() ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_kernel<BN, UW>, tm_w, tm_x, tm_s, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_kernel<BN, UW>, tm_w, tm_x, tm_s, tm_o, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(RK_ECUDA, "rk_gemm_w4a16_kernel launch: %s", cudaGetErrorString(e));
@@ -690,8 +690,8 @@ extern "C" int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, co
 }
 
 template <int BN>
-int launch_w4_fold(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const W4Params& p,
-                   int tiles_n, int tiles_m, int smem, cudaStream_t st) {
+int launch_w4_fold(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const CUtensorMap& tm_o,
+                   const W4Params& p, int tiles_n, int tiles_m, int smem, cudaStream_t st) {
   static bool configured_dev[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -712,7 +712,7 @@ int launch_w4_fold(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUten
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl() ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_fold_kernel<BN>, tm_w, tm_x, tm_s, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_fold_kernel<BN>, tm_w, tm_x, tm_s, tm_o, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(RK_ECUDA, "rk_gemm_w4a16_fold_kernel launch: %s", cudaGetErrorString(e));
@@ -735,7 +735,7 @@ int run_w4_fold(const void* x, const void* q, const void* scales, W4Params p, in
   if (w_stages < 1) return fail(RK_EUNSUPPORTED, "%s: shared memory budget exceeded", who);
   p.w_stages = w_stages;
   const int smem = slots * x_bytes + w_stages * kW4PairBytes + scales_bytes + 1024;
-  CUtensorMap tm_w, tm_x, tm_s;
+  CUtensorMap tm_w, tm_x, tm_s, tm_o;
   const uint32_t group_box = static_cast<uint32_t>(p.groups < 256 ? p.groups : 256);
   int rc = make_map_2d(&tm_s, scales, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k / 128, n * 2, 128, group_box,
                        CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -744,8 +744,11 @@ int run_w4_fold(const void* x, const void* q, const void* scales, W4Params p, in
   if (rc != RK_OK) return rc;
   rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
-  return bn == 256 ? launch_w4_fold<256>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st)
-                   : launch_w4_fold<128>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+  // output tiles leave through TMA: 32 rows x 128 channels per store, clipped at the matrix edges
+  rc = make_map_2d(&tm_o, p.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, m, n * 2, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != RK_OK) return rc;
+  return bn == 256 ? launch_w4_fold<256>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st)
+                   : launch_w4_fold<128>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
 }
 
 extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scales, const void* bias, void* out,
@@ -809,20 +812,25 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   rc = make_map_3d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 64, m, k / 64, k * 2, 128, 64, bn, 2,
                    CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
+  // output rows leave through TMA stores of up to 32 rows x 128 channels, clipped at the matrix edges
+  CUtensorMap tm_o;
+  rc = make_map_2d(&tm_o, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, m, n * 2, 128, static_cast<uint32_t>(bn < 32 ? bn : 32),
+                   CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != RK_OK) return rc;
   cudaStream_t st = as_stream(stream);
   if (tactic & 1) {  // four unpack warps instead of eight
     switch (bn) {
-      case 16: return launch_w4<16, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
-      case 32: return launch_w4<32, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
-      case 64: return launch_w4<64, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+      case 16: return launch_w4<16, 4>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+      case 32: return launch_w4<32, 4>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+      case 64: return launch_w4<64, 4>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
       default: break;
     }
   }
   switch (bn) {
-    case 16: return launch_w4<16, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
-    case 32: return launch_w4<32, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
-    case 64: return launch_w4<64, 8>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
-    default: return launch_w4<128, 4>(tm_w, tm_x, tm_s, p, tiles_n, tiles_m, smem, st);
+    case 16: return launch_w4<16, 8>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+    case 32: return launch_w4<32, 8>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+    case 64: return launch_w4<64, 8>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+    default: return launch_w4<128, 4>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
   }
 }
 

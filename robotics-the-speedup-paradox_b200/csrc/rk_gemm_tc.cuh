@@ -114,19 +114,6 @@ __device__ __forceinline__ float finish_value(uint32_t acc_bits, float s_act, fl
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Wait until at most `N` of this thread's store groups still read their shared-memory source.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -218,17 +205,22 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint8_t* sf_b = p.swap ? p.sf_act : p.sf_wgt;
       Ring ring{0, 0};
       bool alive = true;
+      // a barrier probe costs a shared-memory round trip: the probe of the NEXT stage is issued before
+      // this stage's copies and read one trip later, so a stage that is already free costs no wait
+      uint32_t ready = 0;
       const uint32_t tx_data = (kTileA + p.bn) * kStageKBytes;
       for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
         const int row_a0 = (tile / p.tiles_b) * kTileA;
         const int row_b0 = (tile % p.tiles_b) * p.bn;
-        for (int i = 0; i < nkb; ++i, ring.advance(p.stages)) {
+        for (int i = 0; i < nkb; ++i) {
           const int s = ring.stage;
           const uint32_t ph = ring.phase;
-          if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
+          if (!ready && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
             alive = false;
             break;
           }
+          ring.advance(p.stages);
+          ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t sa = smem_base + s * stage_bytes;
           const uint32_t sb = sa + kTileA * kStageKBytes;
@@ -267,6 +259,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (lane == 0) {
       Ring ring{0, 0}, racc{0, 0};
       bool alive = true;
+      uint32_t ready = 0;  // answer of the early probe of the next stage's "full" barrier
       // instruction descriptor(s) and the descriptor of stage 0 are loop invariants
       uint32_t idesc = 0;
       if constexpr (KIND == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn);
@@ -283,14 +276,16 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                RK_DEV_TIMEOUT_ACC_FREE)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * p.acc_stride;
-        for (int i = 0; i < nkb; ++i, ring.advance(p.stages)) {
+        for (int i = 0; i < nkb; ++i) {
           const int s = ring.stage;
           const uint32_t ph = ring.phase;
-          if (!mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
+          if (!ready && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
             alive = false;
             break;
           }
           tc_fence_after();
+          ring.advance(p.stages);  // probe the next stage now, read the answer after this stage's MMAs
+          ready = mbar_test_wait(smem_u32(&bar_full[ring.stage]), ring.phase);
           const uint32_t sa = smem_base + s * stage_bytes;
           const uint32_t sb = sa + kTileA * kStageKBytes;
           const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);

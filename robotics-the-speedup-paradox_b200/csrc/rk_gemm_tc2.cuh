@@ -138,16 +138,21 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       const uint64_t pol_x = l2_policy_evict_last();
       Ring ring{0, 0};
       bool alive = true;
+      // a barrier probe costs a shared-memory round trip: the probe of the NEXT stage is issued before
+      // this stage's copies and read one trip later, so a stage that is already free costs no wait
+      uint32_t ready = 0;
       for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
         const int row_a0 = (tile / p.tiles_n) * 256 + static_cast<int>(rank) * kTileA;
         const int row_b0 = (tile % p.tiles_n) * p.bn + static_cast<int>(rank) * half_bn;
-        for (int kb = 0; kb < p.kblocks; ++kb, ring.advance(p.stages)) {
+        for (int kb = 0; kb < p.kblocks; ++kb) {
           const int s = ring.stage;
-          if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ring.phase ^ 1, &abort_flag, p.status,
-                                 RK_DEV_TIMEOUT_EMPTY)) {
+          if (!ready && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ring.phase ^ 1, &abort_flag, p.status,
+                                           RK_DEV_TIMEOUT_EMPTY)) {
             alive = false;
             break;
           }
+          ring.advance(p.stages);
+          ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           // both CTAs' bytes are counted on the leader's barrier; the leader announces the total
           const uint32_t full_leader = mapa_u32(smem_u32(&bar_full[s]), 0);
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * static_cast<uint32_t>(stage_bytes));
@@ -162,6 +167,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     if (lane == 0 && rank == 0) {
       Ring ring{0, 0}, racc{0, 0};
       bool alive = true;
+      uint32_t ready = 0;
       const uint32_t idesc = KIND == KIND_I8 ? umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 256, p.bn)
                                              : umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 256, p.bn);
       const uint64_t adesc0 = umma_desc_k128(smem_base);
@@ -173,13 +179,15 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                                RK_DEV_TIMEOUT_ACC_FREE)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * 256;
-        for (int kb = 0; kb < p.kblocks; ++kb, ring.advance(p.stages)) {
+        for (int kb = 0; kb < p.kblocks; ++kb) {
           const int s = ring.stage;
-          if (!mbar_wait_bounded(smem_u32(&bar_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
+          if (!ready && !mbar_wait_bounded(smem_u32(&bar_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
             alive = false;
             break;
           }
           tc_fence_after();
+          ring.advance(p.stages);  // probe the next stage now, read the answer after this stage's MMAs
+          ready = mbar_test_wait(smem_u32(&bar_full[ring.stage]), ring.phase);
           const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
           const int nmma = (kb == p.kblocks - 1) ? p.k_valid_mmas_last : 4;

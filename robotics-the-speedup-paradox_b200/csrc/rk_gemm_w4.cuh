@@ -21,8 +21,8 @@
 // is a single thread sharing its scheduler with busy unpack warps, so every instruction it issues
 // is slow; it therefore waits on exactly one barrier and commits exactly once per group.
 //
-// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2 .. 2+UW-1 = unpack,
-// last four = epilogue.
+// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer (even groups), 2 .. 2+UW-1 = unpack,
+// next four = epilogue, last = MMA issuer (odd groups).
 #pragma once
 
 #include <cuda.h>
@@ -58,7 +58,7 @@ struct W4Params {
   int* status;
 };
 
-__host__ __device__ constexpr int w4_threads(int unpack_warps) { return 32 * (2 + unpack_warps + 4); }
+__host__ __device__ constexpr int w4_threads(int unpack_warps) { return 32 * (2 + unpack_warps + 4 + 1); }
 // TMEM budget (512 columns): every slot takes 64 columns of unpacked weights and `bn` accumulator columns.
 __host__ __device__ constexpr int w4_slots(int bn) {
   return 512 / (kW4ACols + bn) < kW4MaxSlots ? 512 / (kW4ACols + bn) : kW4MaxSlots;
@@ -89,7 +89,8 @@ __device__ __forceinline__ uint4 w4_unpack8(uint32_t w) {
 template <int BN, int UW>
 __global__ void __launch_bounds__(w4_threads(UW), 1)
 rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                     const __grid_constant__ CUtensorMap tm_s, const W4Params p) {
+                     const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_o,
+                     const W4Params p) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 128, "activation tile must be 16..128 rows");
   static_assert(UW == 4 || UW == 8, "four or eight unpack warps");
   constexpr int kXBytes = 2 * BN * 128;  // two 64-element column blocks of BN rows
@@ -97,6 +98,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   constexpr uint32_t kTmemCols = 512;      // [0, kSlots*64): unpacked weights; then kSlots accumulators of BN columns
   constexpr uint32_t kAccBase = kSlots * kW4ACols;
   constexpr int kEpiWarp0 = 2 + UW;
+  constexpr int kMmaWarpB = kEpiWarp0 + 4;  // second MMA-issuing warp
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_w_full[kW4MaxW];
@@ -107,6 +109,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   __shared__ __align__(8) uint64_t bar_scales;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int epi_dead;  // set by an epilogue warp that gave up, so that all four skip the store together
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -127,18 +130,20 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       mbar_init(smem_u32(&bar_w_empty[s]), UW);
     }
     for (int t = 0; t < kSlots; ++t) {
-      mbar_init(smem_u32(&bar_slot_full[t]), UW + 1);  // unpack warps + the activation copy
+      mbar_init(smem_u32(&bar_slot_full[t]), 4 + 1);   // the four unpack warps of the group + the activation copy
       mbar_init(smem_u32(&bar_slot_empty[t]), 4);      // epilogue warps
       mbar_init(smem_u32(&bar_acc_full[t]), 1);
     }
     mbar_init(smem_u32(&bar_scales), 1);
     abort_flag = 0;
+    epi_dead = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_s);
+    tma_prefetch_desc(&tm_o);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -200,18 +205,32 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer: one wait, eight MMAs, one commit per group
+  } else if (warp == 1 || warp == kMmaWarpB) {
+    // ------------------------------------------------------------ MMA issuers: one wait, eight MMAs, one commit per group
+    // Two single threads in different warps share the issue work: one takes the even groups, the
+    // other the odd ones.  Every group has its own accumulator, so their MMAs are independent; the
+    // tensor pipe runs them back to back while each thread's waits, commits and loop overhead
+    // (several hundred cycles per group for a lone thread) overlap with the other thread's MMAs.
     if (lane == 0) {
+      const int parity = warp == 1 ? 0 : 1;
       const uint32_t idesc = umma_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 128, BN);
       const uint64_t desc_x0 = umma_desc_k128(smem_base + x_off);
-      Ring rt{0, 0};
-      for (int g = 0; g < G; ++g, rt.advance(kSlots)) {
+      Ring rt{parity % kSlots, static_cast<uint32_t>(parity / kSlots)};
+      // the probe of this thread's NEXT slot is issued before the group's MMAs and read one trip
+      // later, so a slot that is already full costs no wait
+      uint32_t ready = 0;
+      for (int g = parity; g < G; g += 2) {
         const int t = rt.stage;
-        RK_TRACE_REC(26, g);
-        if (!mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
+        if (parity == 0) RK_TRACE_REC(26, g);
+        if (!ready && !mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
         tc_fence_after();
-        RK_TRACE_REC(5, g);
+        if (parity == 0) RK_TRACE_REC(5, g);
+        rt.stage += 2;
+        while (rt.stage >= kSlots) {
+          rt.stage -= kSlots;
+          rt.phase ^= 1u;
+        }
+        ready = (g + 2 < G) ? mbar_test_wait(smem_u32(&bar_slot_full[rt.stage]), rt.phase) : 0u;
         // descriptors of the slot: the start-address field advances by bytes >> 4
         const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((t * kXBytes) >> 4);
         const uint32_t a_tmem = tmem_base + t * kW4ACols;
@@ -222,36 +241,39 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
           const uint64_t bd = bd0 + static_cast<uint64_t>(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
           mma_f16_ts(d_tmem, a_tmem + k * 8, bd, idesc, k > 0 ? 1u : 0u);
         }
-        RK_TRACE_REC(12, g);
+        if (parity == 0) RK_TRACE_REC(12, g);
         tc_commit(smem_u32(&bar_acc_full[t]));
-        RK_TRACE_REC(6, g);
+        if (parity == 0) RK_TRACE_REC(6, g);
       }
     }
   } else if (warp < kEpiWarp0) {
     // ------------------------------------------------------------ unpack int4 -> bf16 into TMEM
     // A warp can only write the TMEM lanes of its quadrant (warp % 4), so the thread <-> row map
-    // follows it: row = 32 * (warp % 4) + lane.  UW == 4: a thread converts its whole row of the
-    // group (64 raw bytes -> 64 columns).  UW == 8: warps w and w + 4 share a quadrant and take
-    // the two halves of the group's K (32 raw bytes -> 32 columns each).
-    constexpr int kHalves = UW / 4;          // threads per row
-    constexpr int kRawChunks = 4 / kHalves;  // 16-byte raw chunks per thread
+    // follows it: row = 32 * (warp % 4) + lane, and a thread expands its whole row of a group (64
+    // raw bytes -> 64 columns).  UW == 4: every warp takes every group.  UW == 8: warps w and w + 4
+    // share a quadrant and take the even and the odd group of each raw pair, so that one barrier
+    // probe, one arrival and one loop trip cover 128 weights per thread.
+    constexpr int kStride = UW / 4;  // groups between two trips of one warp
     const int uw = warp - 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
-    const int h = (kHalves == 2) ? (uw >> 2) : 0;
+    const int h = uw >> 2;  // 0 for UW == 4
     const bool leader = (uw == 0 && lane == 0);
-    Ring rw{0, 0}, rt{0, 0};
-    // Barrier probes cost a shared-memory round trip each.  The probes for group g + 1 are issued
-    // right after group g's loads and consumed one loop trip later, so their latency hides behind
-    // the conversion work; only when such an early probe says "not yet" does the warp stop to poll.
+    Ring rw{0, 0};
+    Ring rt{h, 0};  // slot of group g = h
+    // Barrier probes cost a shared-memory round trip each.  The probes for the next trip are issued
+    // right after this trip's loads and consumed one trip later, so their latency hides behind the
+    // conversion work; only when such an early probe says "not yet" does the warp stop to poll.
     uint32_t ready = 0;
-    for (int g = 0; g < G; ++g, rt.advance(kSlots)) {
+    for (int g = h; g < G; g += kStride) {
       const int sw = rw.stage;
       const int t = rt.stage;
       const int odd = g & 1;
+      const bool new_pair = (kStride == 2) || !odd;                 // this trip reads a raw pair for the first time
+      const bool pair_done = (kStride == 2) || odd || g == G - 1;   // ... and for the last time
       if (!__all_sync(0xffffffffu, ready != 0)) {
         bool ok = true;
-        if (!odd) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
+        if (new_pair) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
         ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
         if (!__all_sync(0xffffffffu, ok)) break;
       }
@@ -259,25 +281,26 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       // The raw pair was written with the 128-byte swizzle: 16-byte chunk c of row r sits at c ^ (r & 7);
       // chunks 0..3 belong to the even group of the pair, 4..7 to the odd one.
       const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
-      uint4 pk[kRawChunks];
+      uint4 pk[4];
 #pragma unroll
-      for (int i = 0; i < kRawChunks; ++i) {
-        const int c = odd * 4 + h * kRawChunks + i;
-        pk[i] = *reinterpret_cast<const uint4*>(raw + ((c ^ (r & 7)) << 4));
+      for (int i = 0; i < 4; ++i) pk[i] = *reinterpret_cast<const uint4*>(raw + (((odd * 4 + i) ^ (r & 7)) << 4));
+      // next trip of this warp: its slot, and - when that trip opens a new raw pair - the pair
+      Ring rt2 = rt, rw2 = rw;
+      rt2.stage += kStride;
+      if (rt2.stage >= kSlots) {
+        rt2.stage -= kSlots;
+        rt2.phase ^= 1u;
       }
-      const bool pair_done = odd || g == G - 1;
+      if (pair_done) rw2.advance(p.w_stages);
       ready = 0;
-      if (g + 1 < G) {
-        Ring rt2 = rt, rw2 = rw;
-        rt2.advance(kSlots);
-        if (pair_done) rw2.advance(p.w_stages);
+      if (g + kStride < G) {
         ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
-        if (odd) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);  // group g + 1 opens a new pair
+        if (pair_done) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4ACols + h * 32;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4ACols;
 #pragma unroll
-      for (int i = 0; i < kRawChunks; ++i) {
+      for (int i = 0; i < 4; ++i) {
         // one raw chunk = 4 words = 32 weights = 16 columns, stored as two 8-column pieces as soon
         // as they are converted so that the TMEM stores overlap the remaining conversions
         const uint32_t words[4] = {pk[i].x, pk[i].y, pk[i].z, pk[i].w};
@@ -295,11 +318,12 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         mbar_arrive(smem_u32(&bar_slot_full[t]));                    // unpacked tile ready for the MMA thread
         if (pair_done) mbar_arrive(smem_u32(&bar_w_empty[sw]));      // raw slot reusable
       }
-      if (pair_done) rw.advance(p.w_stages);
+      rt = rt2;
+      rw = rw2;
       if (leader) RK_TRACE_REC(4, g);
       if (lane == 0) RK_TRACE_REC(18 + uw, g);
     }
-  } else {
+  } else if (warp < kMmaWarpB) {
     // ------------------------------------------------------------ epilogue: scale each group, accumulate, store
     const int quad = warp & 3;
     const int n = n0 + quad * 32 + lane;
@@ -331,12 +355,26 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       if (lane == 0) mbar_arrive(smem_u32(&bar_slot_empty[t]));
       if (quad == 0 && lane == 0) RK_TRACE_REC(8, g);
     }
-    if (alive && n_ok) {
-      const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.0f;
+    // every epilogue warp reaches this rendezvous, whether it completed or gave up
+    if (!alive) *reinterpret_cast<volatile int*>(&epi_dead) = 1;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*reinterpret_cast<volatile int*>(&epi_dead) == 0) {
+      // The running totals hold one output channel per lane while the output is [m][n] with n
+      // contiguous: transpose through shared memory (the activation tiles are free once the last
+      // group's MMAs have completed) and let TMA stores write the rows, clipping ragged edges.
+      const float bias = (p.bias && n_ok) ? __bfloat162float(p.bias[n]) : 0.0f;
+      __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem_gen + x_off);
+      const int nl = quad * 32 + lane;
 #pragma unroll
-      for (int j = 0; j < BN; ++j) {
-        const int m = m0 + j;
-        if (m < p.m) p.out[static_cast<long long>(m) * p.ldo + n] = __float2bfloat16_rn(acc[j] + bias);
+      for (int j = 0; j < BN; ++j) stage[j * 128 + nl] = __float2bfloat16_rn(acc[j] + bias);
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == kEpiWarp0 && lane == 0) {
+        constexpr int kBoxRows = BN < 32 ? BN : 32;
+        const int rows = p.m - m0 < BN ? p.m - m0 : BN;
+        for (int r0 = 0; r0 < rows; r0 += kBoxRows) tma_store_2d(&tm_o, smem_u32(stage + r0 * 128), n0, m0 + r0);
+        tma_store_commit();
+        tma_store_wait_all();
       }
     }
   }

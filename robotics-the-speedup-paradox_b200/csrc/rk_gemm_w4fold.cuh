@@ -37,7 +37,8 @@ __host__ __device__ constexpr int w4f_slots(int bn) { return bn > 128 ? 5 : 8; }
 template <int BN>
 __global__ void __launch_bounds__(kW4fThreads, 1)
 rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                          const __grid_constant__ CUtensorMap tm_s, const W4Params p) {
+                          const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_o,
+                          const W4Params p) {
   static_assert(BN == 128 || BN == 256, "activation tile of 128 or 256 rows");
   constexpr int UW = kW4fUnpackWarps;
   constexpr int kXBytes = BN * 128;  // one 64-element column block of BN rows
@@ -55,6 +56,7 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   __shared__ __align__(8) uint64_t bar_scales;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int epi_dead;  // set by an epilogue warp that gave up, so that all four skip the store together
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -83,18 +85,20 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       mbar_init(smem_u32(&bar_w_empty[s]), UW);
     }
     for (int t = 0; t < kSlots; ++t) {
-      mbar_init(smem_u32(&bar_slot_full[t]), UW + 1);  // unpack warps + the activation copy
+      mbar_init(smem_u32(&bar_slot_full[t]), UW / 2 + 1);  // the four unpack warps of the step + the activation copy
       mbar_init(smem_u32(&bar_slot_empty[t]), 1);      // MMA commit
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
     mbar_init(smem_u32(&bar_scales), 1);
     abort_flag = 0;
+    epi_dead = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_s);
+    tma_prefetch_desc(&tm_o);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -105,6 +109,7 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   tc_fence_after();
   pdl_wait();  // from here on global memory is read and written
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) RK_TRACE_REC(9, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -125,6 +130,7 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
             const uint32_t full = smem_u32(&bar_w_full[s]);
             mbar_arrive_expect_tx(full, kW4PairBytes);
             tma_load_2d_hint(smem_base + w_off + s * kW4PairBytes, &tm_w, kw * 128, n0, full, pol_w);
+            RK_TRACE_REC(0, gw);
             if (++kw == P) kw = 0;
             ++gw;
             rw.advance(p.w_stages);
@@ -137,6 +143,7 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
             const uint32_t full = smem_u32(&bar_slot_full[t]);
             mbar_arrive_expect_tx(full, kXBytes);
             tma_load_2d_hint(smem_base + x_off + t * kXBytes, &tm_x, kx * 64, m0, full, pol_x);
+            RK_TRACE_REC(1, sx);
             if (++kx == S) kx = 0;
             ++sx;
             rx.advance(kSlots);
@@ -161,66 +168,88 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       const uint32_t d_tmem = tmem_base + kW4fAccCol;
       Ring rt{0, 0};
       bool alive = true;
-      for (int s = 0; s < S; ++s, rt.advance(kSlots)) {
+      // The thread's own instructions, not the tensor pipe, set the pace of this loop unless it stays
+      // under the 4 x 128 cycles the pipe needs per step: the probe of the NEXT slot is issued before
+      // this step's MMAs and read one trip later, so a slot that is already full costs no wait.
+      uint32_t ready = 0;
+      for (int s = 0; s < S; ++s) {
         const int t = rt.stage;
-        if (!mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) {
+        RK_TRACE_REC(26, s);
+        if (!ready && !mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) {
           alive = false;
           break;
         }
         tc_fence_after();
+        RK_TRACE_REC(5, s);
+        rt.advance(kSlots);
+        ready = (s + 1 < S) ? mbar_test_wait(smem_u32(&bar_slot_full[rt.stage]), rt.phase) : 0u;
         const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((t * kXBytes) >> 4);
         const uint32_t a_tmem = tmem_base + t * kW4fStepCols;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           mma_f16_ts(d_tmem, a_tmem + k * 8, bd0 + static_cast<uint64_t>((k * 32) >> 4), idesc, (s | k) ? 1u : 0u);
+        RK_TRACE_REC(12, s);
         tc_commit(smem_u32(&bar_slot_empty[t]));  // frees the expanded weights and the activation tile
+        RK_TRACE_REC(6, s);
       }
       if (alive) tc_commit(smem_u32(&bar_acc_full));
     }
   } else if (warp < kEpiWarp0) {
     // ------------------------------------------------------------ unpack: int4 -> bf16(q * scale) into TMEM
-    // row = 32 * (warp % 4) + lane (a warp writes only the TMEM lanes of its quadrant); warps w and
-    // w + 4 take the two 16-byte halves of the step's 32 raw bytes of that row.
+    // row = 32 * (warp % 4) + lane (a warp writes only the TMEM lanes of its quadrant).  One loop
+    // trip covers a scale group, i.e. two steps: warps 0..3 expand the group's first step, warps
+    // 4..7 its second, each into its own slot - 64 weights per thread and one barrier probe, one
+    // arrival and one scale fetch per trip.
     const int uw = warp - 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int h = uw >> 2;
     bool alive = mbar_poll_warp(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL);
     const __nv_bfloat16* my_scales = reinterpret_cast<const __nv_bfloat16*>(smem_gen + scales_off) + r;
-    Ring rw{0, 0}, rt{0, 0};
-    int ks = rot_steps;  // rotated position of step s along K
-    // the barrier probes for step s + 1 are issued right after step s's load and consumed one loop
+    Ring rw{0, 0};
+    Ring rt{h % kSlots, 0};  // slot of step 2 g + h
+    int kg = rot_copies * 2;  // rotated group index along K
+    // the barrier probes for the next trip are issued right after this trip's loads and consumed one
     // trip later (their latency hides behind the conversion); a warp stops to poll only on "not yet"
     uint32_t ready = 0;
-    for (int s = 0; s < S && alive; ++s, rt.advance(kSlots)) {
+    for (int g = 0; g < G && alive; ++g) {
       const int sw = rw.stage;
       const int t = rt.stage;
-      const int sub = s & 3;  // position of the step inside the raw copy
+      const int odd = g & 1;  // second group of the raw copy
       if (!__all_sync(0xffffffffu, ready != 0)) {
         bool ok = true;
-        if (sub == 0) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
+        if (!odd) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
         ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
         if (!__all_sync(0xffffffffu, ok)) break;
       }
-      // 128-byte swizzle of the raw copy: 16-byte chunk c of row r sits at c ^ (r & 7)
-      const int c = sub * 2 + h;
-      const uint4 pk = *reinterpret_cast<const uint4*>(smem_gen + w_off + sw * kW4PairBytes + r * 128 + ((c ^ (r & 7)) << 4));
-      const bool raw_done = sub == 3 || s == S - 1;
-      ready = 0;
-      if (s + 1 < S) {
-        Ring rt2 = rt, rw2 = rw;
-        rt2.advance(kSlots);
-        if (raw_done) rw2.advance(p.w_stages);
-        ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
-        if (sub == 3) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);  // step s + 1 opens a new raw copy
+      if (uw == 0 && lane == 0) RK_TRACE_REC(2, g);
+      // 128-byte swizzle of the raw copy: 16-byte chunk c of row r sits at c ^ (r & 7); the step of
+      // this warp owns chunks 4 * odd + 2 * h and the next one
+      const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
+      const int c = odd * 4 + h * 2;
+      const uint4 pk0 = *reinterpret_cast<const uint4*>(raw + ((c ^ (r & 7)) << 4));
+      const uint4 pk1 = *reinterpret_cast<const uint4*>(raw + (((c + 1) ^ (r & 7)) << 4));
+      const __nv_bfloat162 ss = __bfloat162bfloat162(my_scales[kg * 128]);
+      if (++kg == G) kg = 0;
+      const bool raw_done = odd || g == G - 1;
+      // next trip: this warp's slot two steps on, and - when it opens a new raw copy - that copy
+      Ring rt2 = rt, rw2 = rw;
+      rt2.stage += 2;
+      if (rt2.stage >= kSlots) {
+        rt2.stage -= kSlots;
+        rt2.phase ^= 1u;
       }
-      const __nv_bfloat162 ss = __bfloat162bfloat162(my_scales[(ks >> 1) * 128]);
-      if (++ks == S) ks = 0;
+      if (raw_done) rw2.advance(p.w_stages);
+      ready = 0;
+      if (g + 1 < G) {
+        ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
+        if (odd) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);
+      }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4fStepCols + h * 16;
-      const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4fStepCols;
+      const uint32_t words[8] = {pk0.x, pk0.y, pk0.z, pk0.w, pk1.x, pk1.y, pk1.z, pk1.w};
 #pragma unroll
-      for (int w = 0; w < 4; w += 2) {
+      for (int w = 0; w < 8; w += 2) {
         uint4 u0 = w4_unpack8(words[w]);
         uint4 u1 = w4_unpack8(words[w + 1]);
         uint32_t* v0 = reinterpret_cast<uint32_t*>(&u0);
@@ -241,31 +270,47 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
         mbar_arrive(smem_u32(&bar_slot_full[t]));
         if (raw_done) mbar_arrive(smem_u32(&bar_w_empty[sw]));
       }
-      if (raw_done) rw.advance(p.w_stages);
+      rt = rt2;
+      rw = rw2;
+      if (uw == 0 && lane == 0) RK_TRACE_REC(4, g);
+      if (lane == 0) RK_TRACE_REC(18 + uw, g);
     }
   } else {
     // ------------------------------------------------------------ epilogue: one pass after the last step
+    // The accumulator holds one output channel per lane; the output is [m][n] with n contiguous.
+    // Storing it straight from registers would be one 2-byte store per element.  Instead the tile
+    // is transposed through shared memory (the activation slots are free by now) as [m][128 n]
+    // rows and leaves by TMA stores of 32 rows each, which also clip the ragged edges.
     const int quad = warp & 3;
-    const int n = n0 + quad * 32 + lane;
-    const bool n_ok = n < p.n;
+    const int nl = quad * 32 + lane;
+    const int n = n0 + nl;
     const bool alive = mbar_poll_warp(smem_u32(&bar_acc_full), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
     tc_fence_after();
-    if (alive) {
-      const float bias = (p.bias && n_ok) ? __bfloat162float(p.bias[n]) : 0.0f;
+    if (quad == 0 && lane == 0) RK_TRACE_REC(7, 0);
+    // every epilogue warp reaches this rendezvous, whether it saw the accumulator complete or gave up
+    if (!alive) *reinterpret_cast<volatile int*>(&epi_dead) = 1;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*reinterpret_cast<volatile int*>(&epi_dead) == 0) {
+      const float bias = (p.bias && n < p.n) ? __bfloat162float(p.bias[n]) : 0.0f;
       const int rows = p.m - m0 < BN ? p.m - m0 : BN;
+      __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem_gen + x_off);
       for (int c0 = 0; c0 < rows; c0 += 16) {  // warp-uniform bound: tcgen05.ld is a warp-wide instruction
         uint32_t v[16];
         tmem_ld_16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kW4fAccCol + c0, v);
         tc_wait_ld();
-        if (n_ok) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < p.m) p.out[static_cast<long long>(m) * p.ldo + n] = __float2bfloat16_rn(__uint_as_float(v[j]) + bias);
-          }
-        }
+        for (int j = 0; j < 16; ++j) stage[(c0 + j) * 128 + nl] = __float2bfloat16_rn(__uint_as_float(v[j]) + bias);
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == kEpiWarp0 && lane == 0) {
+        for (int r0 = 0; r0 < rows; r0 += 32)
+          tma_store_2d(&tm_o, smem_u32(stage + r0 * 128), n0, m0 + r0);
+        tma_store_commit();
+        tma_store_wait_all();
       }
     }
+    if (quad == 0 && lane == 0) RK_TRACE_REC(8, 0);
   }
 
   tc_fence_before();
