@@ -450,7 +450,7 @@ def main():
         d = per_case[f"M{dominant}"]
         hbm_bound = d["hbm_frac"] >= d["bf16_frac"]
         roofline = {
-            "kernel": f"rk_gemm_w4a16_kernel (M={dominant})",
+            "kernel": f"{'rk_gemm_w4a16_fold_kernel' if dominant > 64 else 'rk_gemm_w4a16_kernel'} (M={dominant})",
             "bound": "hbm" if hbm_bound else "tensor",
             "achieved": d["gbs"] if hbm_bound else d["tops"],
             "peak": peaks["hbm_gbs"] if hbm_bound else peaks["bf16_tflops"],

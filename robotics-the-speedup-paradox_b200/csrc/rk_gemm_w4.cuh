@@ -109,6 +109,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   __shared__ __align__(8) uint64_t bar_scales;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int verdict_epi[2];
   __shared__ int epi_dead;  // set by an epilogue warp that gave up, so that all four skip the store together
 
   const int warp = threadIdx.x >> 5;
@@ -197,11 +198,16 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         }
         if (progressed) {
           idle = 0;
+        } else if (gw == P && gx < G) {
+          // only activation copies remain: park on the slot's barrier instead of spinning, so that
+          // this thread stops taking issue slots from the unpack warps of its scheduler
+          if (!mbar_wait_bounded(smem_u32(&bar_slot_empty[rx.stage]), rx.phase ^ 1, &abort_flag, p.status,
+                                 RK_DEV_TIMEOUT_EMPTY)) break;
         } else if (++idle > kWaitSpinMax) {
           abort_flag = 1;
           atomicCAS(p.status, 0, RK_DEV_TIMEOUT_EMPTY);
-        } else if (idle > 2) {
-          __nanosleep(idle > kWaitSpinFast ? 256 : 64);
+        } else {
+          __nanosleep(idle > kWaitSpinFast ? 256 : 128);
         }
       }
     }
@@ -299,18 +305,26 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4ACols;
+      // Convert the whole row first, then store: with the stores (ordered, volatile) out of the way
+      // the compiler interleaves the sixteen independent word conversions, which hides the
+      // latency of each word's short dependent chain (the warp was stalling on exactly that).
+      uint32_t o[64];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        // one raw chunk = 4 words = 32 weights = 16 columns, stored as two 8-column pieces as soon
-        // as they are converted so that the TMEM stores overlap the remaining conversions
         const uint32_t words[4] = {pk[i].x, pk[i].y, pk[i].z, pk[i].w};
 #pragma unroll
-        for (int w = 0; w < 4; w += 2) {
-          const uint4 u0 = w4_unpack8(words[w]);
-          const uint4 u1 = w4_unpack8(words[w + 1]);
-          tmem_st_8(taddr + i * 16 + w * 4, u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w);
+        for (int w = 0; w < 4; ++w) {
+          const uint4 u = w4_unpack8(words[w]);
+          o[(i * 4 + w) * 4 + 0] = u.x;
+          o[(i * 4 + w) * 4 + 1] = u.y;
+          o[(i * 4 + w) * 4 + 2] = u.z;
+          o[(i * 4 + w) * 4 + 3] = u.w;
         }
       }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        tmem_st_8(taddr + j * 8, o[j * 8 + 0], o[j * 8 + 1], o[j * 8 + 2], o[j * 8 + 3], o[j * 8 + 4], o[j * 8 + 5],
+                  o[j * 8 + 6], o[j * 8 + 7]);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -331,13 +345,17 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     float acc[BN];
 #pragma unroll
     for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+    const bool epi_leader = (warp == kEpiWarp0 && lane == 0);
     bool alive = mbar_poll_warp(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL);
     const __nv_bfloat16* my_scales = reinterpret_cast<const __nv_bfloat16*>(smem_gen + scales_off) + quad * 32 + lane;
     Ring rt{0, 0};
     for (int g = 0; g < G && alive; ++g, rt.advance(kSlots)) {
       const int t = rt.stage;
       const float sc = __bfloat162float(my_scales[g * 128]);
-      alive = mbar_poll_warp(smem_u32(&bar_acc_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
+      // one thread parks on the barrier, the other 127 wait at a hardware barrier: a waiting epilogue
+      // costs no issue slots (polling here took a third of all instructions the SM executed)
+      alive = mbar_wait_group(smem_u32(&bar_acc_full[t]), rt.phase, epi_leader, 1, 128, &abort_flag, p.status,
+                              RK_DEV_TIMEOUT_ACC, verdict_epi, static_cast<uint32_t>(g));
       tc_fence_after();
       if (quad == 0 && lane == 0) RK_TRACE_REC(7, g);
 #pragma unroll

@@ -152,11 +152,16 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
         }
         if (progressed) {
           idle = 0;
+        } else if (gw == P && sx < S) {
+          // only activation copies remain: park on the slot's barrier instead of spinning, so that
+          // this thread stops taking issue slots from the unpack warps of its scheduler
+          if (!mbar_wait_bounded(smem_u32(&bar_slot_empty[rx.stage]), rx.phase ^ 1, &abort_flag, p.status,
+                                 RK_DEV_TIMEOUT_EMPTY)) break;
         } else if (++idle > kWaitSpinMax) {
           abort_flag = 1;
           atomicCAS(p.status, 0, RK_DEV_TIMEOUT_EMPTY);
-        } else if (idle > 2) {
-          __nanosleep(idle > kWaitSpinFast ? 256 : 64);
+        } else {
+          __nanosleep(idle > kWaitSpinFast ? 256 : 128);
         }
       }
     }

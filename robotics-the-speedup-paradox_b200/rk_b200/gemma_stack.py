@@ -95,14 +95,12 @@ class GemmaAttention(nn.Module):
             k = torch.cat([past_kv[0], k], dim=2)
             v = torch.cat([past_kv[1], v], dim=2)
         present = (k, v)
-        rep = cfg.num_heads // cfg.num_kv_heads
-        kk = k[:, :, None].expand(b, cfg.num_kv_heads, rep, k.shape[2], cfg.head_dim).reshape(b, cfg.num_heads, -1, cfg.head_dim)
-        vv = v[:, :, None].expand(b, cfg.num_kv_heads, rep, v.shape[2], cfg.head_dim).reshape(b, cfg.num_heads, -1, cfg.head_dim)
         # full (non-causal) visibility: prefix tokens see each other; suffix tokens see the whole
-        # prefix and each other (models/pi05/modeling_pi05.py:649,662,713)
-        weights = torch.matmul(q, kk.transpose(2, 3)) * (cfg.head_dim ** -0.5)
-        weights = F.softmax(weights, dim=-1, dtype=torch.float32).to(q.dtype)
-        out = torch.matmul(weights, vv).transpose(1, 2).reshape(b, t, -1).contiguous()
+        # prefix and each other (models/pi05/modeling_pi05.py:649,662,713).  Grouped-query attention
+        # goes through the fused kernel, which reads each key/value head once instead of
+        # materialising one copy per query head.
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=False, enable_gqa=True)
+        out = out.transpose(1, 2).reshape(b, t, -1).contiguous()
         return self.o_proj(out), present
 
 

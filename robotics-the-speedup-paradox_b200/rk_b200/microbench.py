@@ -1,0 +1,210 @@
+#!/usr/bin/env python3
+"""Per-shape timing of the quantized GEMM and quantizer entry points, through the C ABI.
+
+    python robotics-the-speedup-paradox_b200/rk_b200/microbench.py [w4a16] [w8a8] [fp8] [mxfp8] [nvfp4] [quant]
+    python robotics-the-speedup-paradox_b200/build.py --trace && \
+        RK_B200_SO=robotics-the-speedup-paradox_b200/rk_b200/librk_b200_trace.so \
+        python robotics-the-speedup-paradox_b200/rk_b200/microbench.py trace
+
+Each shape is timed as a CUDA graph of back-to-back launches that rotate through enough independent
+weight copies to exceed the 126 MB L2 (so a launch streams its weights from HBM), between two CUDA
+events on the launching stream.  Shapes are the ones the reference's benchmark configurations name:
+the Gemma-2B MLP gate/up GEMM at decode batch sizes (W4A16), the Cosmos cross-attention projection
+(W8A8, M = 64), the action-expert and prefix linears of the pi0.5 stack (W8A8, M = 400 / 1764) and
+the 816-token prefix GEMMs (FP8 / MXFP8 / NVFP4).  One line per shape: time, algorithmic GB/s and
+its share of the measured copy bandwidth, T(FL)OPS, and the device status word (0 = no wait gave up).
+"""
+
+import json
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent))
+
+import torch
+
+from rk_b200 import _lib as L
+
+
+def _hbm_peak():
+    path = HERE.parent.parent / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text())["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+class Bench:
+    def __init__(self):
+        if not torch.cuda.is_available():
+            raise SystemExit("microbench needs a CUDA device")
+        self.lib = L.load()
+        self.dev = torch.device("cuda:0")
+        torch.cuda.set_device(0)
+        self.hbm, self.hbm_src = _hbm_peak()
+
+    def time_us(self, calls, reps=3):
+        """calls: one callable(stream_ptr) per rotating copy; average microseconds per launch."""
+        stream = torch.cuda.current_stream()
+        for f in calls:
+            f(L.stream_ptr(self.dev))
+        torch.cuda.synchronize()
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        side.wait_stream(stream)
+        inner = len(calls) * 3
+        with torch.cuda.graph(graph, stream=side):
+            sp = L.stream_ptr(self.dev)
+            for i in range(inner):
+                calls[i % len(calls)](sp)
+        stream.wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (reps * inner) * 1e3
+
+    @staticmethod
+    def copies(nbytes):
+        return max(2, int(300e6 // nbytes) + 1)
+
+    def report(self, name, m, n, k, tactic, us, nbytes, ops, unit, ws):
+        print(f"{name:6s} m{m:5d} n{n:6d} k{k:6d} t{tactic}: {us:8.2f} us  {nbytes / us / 1e3:8.1f} GB/s "
+              f"({nbytes / us / 1e3 / self.hbm * 100:5.1f}% of {self.hbm_src} copy bw)  {ops / us / 1e6:8.1f} {unit}  "
+              f"status={L.read_status(ws)}", flush=True)
+
+    def w8a8(self, m, n, k, tactic=0):
+        dev, lib = self.dev, self.lib
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+        sa, sb = torch.rand(m, device=dev), torch.rand(n, device=dev)
+        bs = [torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev) for _ in range(self.copies(n * k))]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        ws = L.gemm_workspace(L.OP_W8A8, dev, m, n, k)
+        calls = [(lambda sp, b=b: lib.rk_gemm_int(L.ptr(a), L.ptr(sa), L.ptr(b), L.ptr(sb), None, L.ptr(out), m, n, k, 8,
+                                                  tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+        self.report("w8a8", m, n, k, tactic, self.time_us(calls), m * k + n * k + 2 * m * n + 4 * (m + n), 2 * m * n * k,
+                    "TOPS", ws)
+
+    def float8(self, kind, m, n, k, tactic=0):
+        dev, lib = self.dev, self.lib
+        a = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
+        bs = [torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev) for _ in range(self.copies(n * k))]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        one = torch.ones(1, device=dev)
+        if kind == "fp8":
+            ws = L.gemm_workspace(L.OP_FP8, dev, m, n, k)
+            calls = [(lambda sp, b=b: lib.rk_gemm_fp8(L.ptr(a), L.ptr(one), L.ptr(b), L.ptr(one), None, L.ptr(out), m, n, k,
+                                                      tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = m * k + n * k + 2 * m * n
+        elif kind == "mxfp8":
+            ws = L.gemm_workspace(L.OP_MXFP8, dev, m, n, k)
+            sfa = torch.full((lib.rk_sf_bytes(m, k // 32),), 127, dtype=torch.uint8, device=dev)
+            sfb = torch.full((lib.rk_sf_bytes(n, k // 32),), 127, dtype=torch.uint8, device=dev)
+            calls = [(lambda sp, b=b: lib.rk_gemm_mxfp8(L.ptr(a), L.ptr(sfa), L.ptr(b), L.ptr(sfb), None, L.ptr(out), m, n,
+                                                        k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = m * k + n * k + 2 * m * n + (m + n) * k // 32
+        else:
+            ws = L.gemm_workspace(L.OP_NVFP4, dev, m, n, k)
+            a = a[:, :k // 2].contiguous()
+            bs = [b[:, :k // 2].contiguous() for b in bs]
+            sfa = torch.full((lib.rk_sf_bytes(m, k // 16),), 0x38, dtype=torch.uint8, device=dev)
+            sfb = torch.full((lib.rk_sf_bytes(n, k // 16),), 0x38, dtype=torch.uint8, device=dev)
+            calls = [(lambda sp, b=b: lib.rk_gemm_nvfp4(L.ptr(a), L.ptr(sfa), None, L.ptr(b), L.ptr(sfb), None, None,
+                                                        L.ptr(out), m, n, k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = (m * k + n * k) // 2 + 2 * m * n + (m + n) * k // 16
+        self.report(kind, m, n, k, tactic, self.time_us(calls), nbytes, 2 * m * n * k, "TFLOPS", ws)
+
+    def w4a16(self, m, n, k, tactic=0):
+        dev, lib = self.dev, self.lib
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        qs = [torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device=dev) for _ in range(self.copies(n * k // 2))]
+        sc = torch.rand(k // 128, n, device=dev).to(torch.bfloat16)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        ws = L.gemm_workspace(L.OP_W4A16, dev, m, n, k)
+        calls = [(lambda sp, q=q: lib.rk_gemm_w4a16_g128(L.ptr(x), L.ptr(q), L.ptr(sc), None, L.ptr(out), m, n, k, tactic,
+                                                         L.ptr(ws), ws.numel(), sp)) for q in qs]
+        nbytes = n * k // 2 + k // 128 * n * 2 + 2 * m * k + 2 * m * n
+        self.report("w4a16", m, n, k, tactic, self.time_us(calls), nbytes, 2 * m * n * k, "TFLOPS", ws)
+
+    def quant_rows(self, rows, k, bits=8):
+        dev, lib = self.dev, self.lib
+        xs = [torch.randn(rows, k, device=dev).to(torch.bfloat16) for _ in range(self.copies(rows * k * 2))]
+        kp = (k + 127) // 128 * 128
+        q = torch.empty((rows, kp), dtype=torch.uint8, device=dev)
+        s = torch.empty(rows, device=dev)
+        calls = [(lambda sp, x=x: lib.rk_quant_rows(L.ptr(x), rows, k, k, None, 0, None, 0, bits, L.ptr(q), L.ptr(s), sp))
+                 for x in xs]
+        us = self.time_us(calls)
+        nbytes = rows * k * 3
+        print(f"quant  rows{rows:6d} k{k:6d} int{bits}: {us:8.2f} us  {nbytes / us / 1e3:8.1f} GB/s "
+              f"({nbytes / us / 1e3 / self.hbm * 100:5.1f}% of {self.hbm_src} copy bw)", flush=True)
+
+
+def role_trace(bench, m, n=16384, k=2048):
+    """Per-role progress of CTA (0, 0) of one W4A16 launch, in SM clocks since the CTA finished its
+    set-up.  Needs the developer build of the library (`build.py --trace`)."""
+    import ctypes
+
+    import numpy as np
+
+    lib, dev = bench.lib, bench.dev
+    try:
+        reader = lib.rk_trace_read
+    except AttributeError:
+        raise SystemExit("this library was not built with build.py --trace (set RK_B200_SO to the trace build)")
+    reader.restype = ctypes.c_int
+    reader.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    q = torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device=dev)
+    sc = torch.rand(k // 128, n, device=dev).to(torch.bfloat16)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    ws = L.gemm_workspace(L.OP_W4A16, dev, m, n, k)
+    for _ in range(3):
+        lib.rk_gemm_w4a16_g128(L.ptr(x), L.ptr(q), L.ptr(sc), None, L.ptr(out), m, n, k, 0, L.ptr(ws), ws.numel(),
+                               L.stream_ptr(dev))
+    torch.cuda.synchronize()
+    buf = np.zeros(32 * 64, dtype=np.int64)
+    reader(buf.ctypes.data, buf.size)
+    t = buf.reshape(32, 64)
+    t0 = t[9, 0]
+    rows = k // 128 if m <= 64 else k // 64
+    names = ("w_copy", "x_copy", "unpack_start", "unpack_done", "mma_top", "mma_ready", "mma_issued", "commit_done",
+             "epi_full", "epi_done")
+    slots = (0, 1, 2, 4, 26, 5, 12, 6, 7, 8)
+    print(f"--- W4A16 m={m} n={n} k={k}: SM clocks since set-up, one row per pipeline step "
+          f"({'K group' if m <= 64 else '64 elements of K'}); '-' = not recorded for this row")
+    print("step " + " ".join(f"{s:>12s}" for s in names))
+    for g in range(min(rows, 40)):
+        cells = [(t[i, g] - t0) for i in slots]
+        print(f"{g:4d} " + " ".join(f"{c:12d}" if 0 <= c < 10 ** 9 else f"{'-':>12s}" for c in cells))
+
+
+def main(argv):
+    which = argv or ["w4a16", "w8a8", "fp8", "mxfp8", "nvfp4", "quant"]
+    b = Bench()
+    if "trace" in which:
+        for m in (8, 50, 256):
+            role_trace(b, m)
+        return
+    if "w4a16" in which:
+        for m in (1, 8, 50, 128, 256):
+            b.w4a16(m, 16384, 2048)
+    if "w8a8" in which:
+        for shape in ((64, 2048, 2048), (400, 2560, 1024), (400, 1024, 2048), (400, 8192, 1024), (400, 1024, 4096),
+                      (1764, 2048, 2048), (1764, 8192, 2048), (1764, 2048, 8192), (1764, 6144, 2048), (4096, 8192, 8192)):
+            b.w8a8(*shape)
+    for kind in ("fp8", "mxfp8", "nvfp4"):
+        if kind in which:
+            for shape in ((50, 16384, 2048), (256, 16384, 2048), (816, 16384, 2048), (816, 2048, 16384), (816, 2048, 2048),
+                          (4096, 8192, 8192)):
+                b.float8(kind, *shape)
+    if "quant" in which:
+        for rows, k in ((64, 2048), (400, 1024), (400, 4096), (1764, 2048), (1764, 8192), (16384, 2048)):
+            b.quant_rows(rows, k)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
