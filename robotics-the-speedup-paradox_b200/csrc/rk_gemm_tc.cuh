@@ -256,7 +256,10 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (uniform control flow); the tcgen05 instructions execute in one
+    // elected lane.  Every lane takes part in the barrier waits.
+    {
+      const uint32_t on = elect_one();
       Ring ring{0, 0}, racc{0, 0};
       bool alive = true;
       uint32_t ready = 0;  // answer of the early probe of the next stage's "full" barrier
@@ -297,10 +300,10 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             // chunk (row block r, k chunk j) of the stage -> 4 TMEM columns
             const int cs = min(c, p.sf_kt - (kb_begin + i) * c);
             for (int j = 0; j < cs; ++j) {
-              tmem_cp_32x128b_warpx4(tmem_sfa + j * 4, umma_desc_noswizzle(ssf + j * 512, 16, 128));
+              tmem_cp_32x128b_warpx4(tmem_sfa + j * 4, umma_desc_noswizzle(ssf + j * 512, 16, 128), on);
               for (int rb = 0; rb < rb_b; ++rb)
                 tmem_cp_32x128b_warpx4(tmem_sfb + (j * rb_b + rb) * 4,
-                                       umma_desc_noswizzle(ssf + ((1 + rb) * c + j) * 512, 16, 128));
+                                       umma_desc_noswizzle(ssf + ((1 + rb) * c + j) * 512, 16, 128), on);
             }
           }
 #pragma unroll
@@ -311,22 +314,22 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               const uint64_t ad = adesc + static_cast<uint64_t>(k * 2);
               const uint64_t bd = bdesc + static_cast<uint64_t>(k * 2);
               if constexpr (KIND == KIND_I8) {
-                mma_i8(d_tmem, ad, bd, idesc, accumulate);
+                mma_i8(d_tmem, ad, bd, idesc, accumulate, on);
               } else if constexpr (KIND == KIND_F8) {
-                mma_f8f6f4(d_tmem, ad, bd, idesc, accumulate);
+                mma_f8f6f4(d_tmem, ad, bd, idesc, accumulate, on);
               } else if constexpr (KIND == KIND_MXF8) {
                 // four MMAs share one set of scale columns; byte k of each 32-bit column is theirs
                 // (scale-factor ids: bits [4,6) for B, [29,31) for A)
                 mma_mxf8(d_tmem, ad, bd, idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29),
-                         tmem_sfa, tmem_sfb, accumulate);
+                         tmem_sfa, tmem_sfb, accumulate, on);
               } else {
-                mma_nvf4(d_tmem, ad, bd, idesc, tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate);
+                mma_nvf4(d_tmem, ad, bd, idesc, tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate, on);
               }
             }
           }
-          tc_commit(smem_u32(&bar_empty[s]));  // stage reusable once these MMAs have read it
+          tc_commit(smem_u32(&bar_empty[s]), on);  // stage reusable once these MMAs have read it
         }
-        if (alive) tc_commit(smem_u32(&bar_acc_full[ab]));  // accumulator complete
+        if (alive) tc_commit(smem_u32(&bar_acc_full[ab]), on);  // accumulator complete
       }
     }
   } else {
@@ -412,6 +415,53 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         tc_fence_before();
         mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+        continue;
+      }
+
+      // ---- small swapped tiles: stage the whole tile once, then issue all its TMA stores.  The
+      // chunk-by-chunk path below costs two CTA-wide rendezvous per 32 columns; for a CTA that owns
+      // a single tile nothing overlaps that tail, so it is taken in one pass whenever the tile
+      // ([bn][128] bf16) fits the staging area.
+      if (p.swap && p.bn * 256 <= p.out_bufs * kOutBufBytes) {
+        uint8_t* const stage = smem_gen + out_stage_off;
+        if (et == 0 && pending_store) tma_store_wait_read<0>();
+        epi_bar_sync();
+        __nv_bfloat16* const srow = reinterpret_cast<__nv_bfloat16*>(stage);
+        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+          const bool two = c0 + 32 <= p.bn;  // warp-uniform
+          uint32_t r0[16], r1[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + c0, r0);
+          if (two) tmem_ld_16(t_acc + c0 + 16, r1);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float v;
+            if constexpr (KIND == KIND_I8) v = finish_value<KIND>(r0[j], vec_scale[c0 + j], row_scale, has_bias, row_bias);
+            else v = finish_value<KIND>(r0[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
+            srow[(c0 + j) * 128 + et] = __float2bfloat16_rn(v);
+          }
+          if (two) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v;
+              if constexpr (KIND == KIND_I8) v = finish_value<KIND>(r1[j], vec_scale[c0 + 16 + j], row_scale, has_bias, row_bias);
+              else v = finish_value<KIND>(r1[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
+              srow[(c0 + 16 + j) * 128 + et] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (et == 0) {
+          if (ok)
+            for (int r0w = 0; r0w < p.bn; r0w += 32)
+              tma_store_2d(&tm_out, smem_u32(stage + r0w * 256), row_a0, row_b0 + r0w);
+          tma_store_commit();
+          pending_store = 1;
+        }
         continue;
       }
 

@@ -54,20 +54,21 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
-__device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar, uint32_t on = 1u) {
   // arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done
   asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(bar), "h"(static_cast<uint16_t>(3))
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
+      ::"r"(bar), "h"(static_cast<uint16_t>(3)), "r"(on)
       : "memory");
 }
 #define RK_DEFINE_MMA2(NAME, KIND)                                                                          \
   __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,     \
-                                       uint32_t accumulate) {                                               \
+                                       uint32_t accumulate, uint32_t on = 1u) {                             \
     asm volatile(                                                                                           \
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                   \
-        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t}"                                 \
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                                  \
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"                        \
+        "@q tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t}"                              \
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(on)                         \
         : "memory");                                                                                        \
   }
 RK_DEFINE_MMA2(mma2_i8, "i8")
@@ -164,7 +165,9 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
-    if (lane == 0 && rank == 0) {
+    // the whole warp of the leader walks the loop; the tcgen05 instructions execute in one elected lane
+    if (rank == 0) {
+      const uint32_t on = elect_one();
       Ring ring{0, 0}, racc{0, 0};
       bool alive = true;
       uint32_t ready = 0;
@@ -195,13 +198,13 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           for (int k = 0; k < 4; ++k) {
             if (k < nmma) {
               const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-              if constexpr (KIND == KIND_I8) mma2_i8(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate);
-              else mma2_f8f6f4(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate);
+              if constexpr (KIND == KIND_I8) mma2_i8(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate, on);
+              else mma2_f8f6f4(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate, on);
             }
           }
-          tc2_commit_both(smem_u32(&bar_empty[s]));
+          tc2_commit_both(smem_u32(&bar_empty[s]), on);
         }
-        if (alive) tc2_commit_both(smem_u32(&bar_acc_full[ab]));
+        if (alive) tc2_commit_both(smem_u32(&bar_acc_full[ab]), on);
       }
     }
   } else {

@@ -31,18 +31,6 @@
 
 namespace rk {
 
-// Developer aid, compiled out unless RK_TRACE is defined: CTA (0,0) records SM-clock timestamps of
-// each role's progress per K group into a device array that rk_trace_read() copies back.
-#ifdef RK_TRACE
-__device__ long long rk_trace_buf[32 * 64];
-#define RK_TRACE_REC(slot, g)                                                        \
-  do {                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (g) < 64) rk_trace_buf[(slot) * 64 + (g)] = clock64(); \
-  } while (0)
-#else
-#define RK_TRACE_REC(slot, g) do { } while (0)
-#endif
-
 constexpr int kW4Group = 128;                // K elements per scale group == K elements per pipeline step
 constexpr int kW4PairBytes = 128 * 128;      // packed weights of two K groups: 128 rows x 128 bytes
 constexpr int kW4ACols = 64;                 // TMEM columns of one unpacked 128 x 128 bf16 tile (2 per column)
@@ -217,7 +205,10 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     // other the odd ones.  Every group has its own accumulator, so their MMAs are independent; the
     // tensor pipe runs them back to back while each thread's waits, commits and loop overhead
     // (several hundred cycles per group for a lone thread) overlap with the other thread's MMAs.
-    if (lane == 0) {
+    // Each issuing warp walks its loop as a whole (uniform control flow); the tcgen05 instructions
+    // execute in one elected lane and every lane takes part in the barrier waits.
+    {
+      const uint32_t on = elect_one();
       const int parity = warp == 1 ? 0 : 1;
       const uint32_t idesc = umma_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 128, BN);
       const uint64_t desc_x0 = umma_desc_k128(smem_base + x_off);
@@ -227,10 +218,10 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       uint32_t ready = 0;
       for (int g = parity; g < G; g += 2) {
         const int t = rt.stage;
-        if (parity == 0) RK_TRACE_REC(26, g);
+        if (parity == 0 && on) RK_TRACE_REC(26, g);
         if (!ready && !mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
         tc_fence_after();
-        if (parity == 0) RK_TRACE_REC(5, g);
+        if (parity == 0 && on) RK_TRACE_REC(5, g);
         rt.stage += 2;
         while (rt.stage >= kSlots) {
           rt.stage -= kSlots;
@@ -245,11 +236,11 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         for (int k = 0; k < 8; ++k) {
           // 16 bf16 of K per MMA: 8 TMEM columns of A, 32 bytes of the activation column block
           const uint64_t bd = bd0 + static_cast<uint64_t>(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
-          mma_f16_ts(d_tmem, a_tmem + k * 8, bd, idesc, k > 0 ? 1u : 0u);
+          mma_f16_ts(d_tmem, a_tmem + k * 8, bd, idesc, k > 0 ? 1u : 0u, on);
         }
-        if (parity == 0) RK_TRACE_REC(12, g);
-        tc_commit(smem_u32(&bar_acc_full[t]));
-        if (parity == 0) RK_TRACE_REC(6, g);
+        if (parity == 0 && on) RK_TRACE_REC(12, g);
+        tc_commit(smem_u32(&bar_acc_full[t]), on);
+        if (parity == 0 && on) RK_TRACE_REC(6, g);
       }
     }
   } else if (warp < kEpiWarp0) {

@@ -167,7 +167,9 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer: four MMAs of K = 16 per step
-    if (lane == 0) {
+    // the whole warp walks the loop (uniform control flow); the tcgen05 instructions execute in one elected lane
+    {
+      const uint32_t on = elect_one();
       const uint32_t idesc = umma_idesc(DFMT_F32, FMT_BF16, FMT_BF16, 128, BN);
       const uint64_t desc_x0 = umma_desc_k128(smem_base + x_off);
       const uint32_t d_tmem = tmem_base + kW4fAccCol;
@@ -179,25 +181,25 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       uint32_t ready = 0;
       for (int s = 0; s < S; ++s) {
         const int t = rt.stage;
-        RK_TRACE_REC(26, s);
+        if (on) RK_TRACE_REC(26, s);
         if (!ready && !mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) {
           alive = false;
           break;
         }
         tc_fence_after();
-        RK_TRACE_REC(5, s);
+        if (on) RK_TRACE_REC(5, s);
         rt.advance(kSlots);
         ready = (s + 1 < S) ? mbar_test_wait(smem_u32(&bar_slot_full[rt.stage]), rt.phase) : 0u;
         const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((t * kXBytes) >> 4);
         const uint32_t a_tmem = tmem_base + t * kW4fStepCols;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_f16_ts(d_tmem, a_tmem + k * 8, bd0 + static_cast<uint64_t>((k * 32) >> 4), idesc, (s | k) ? 1u : 0u);
-        RK_TRACE_REC(12, s);
-        tc_commit(smem_u32(&bar_slot_empty[t]));  // frees the expanded weights and the activation tile
-        RK_TRACE_REC(6, s);
+          mma_f16_ts(d_tmem, a_tmem + k * 8, bd0 + static_cast<uint64_t>((k * 32) >> 4), idesc, (s | k) ? 1u : 0u, on);
+        if (on) RK_TRACE_REC(12, s);
+        tc_commit(smem_u32(&bar_slot_empty[t]), on);  // frees the expanded weights and the activation tile
+        if (on) RK_TRACE_REC(6, s);
       }
-      if (alive) tc_commit(smem_u32(&bar_acc_full));
+      if (alive) tc_commit(smem_u32(&bar_acc_full), on);
     }
   } else if (warp < kEpiWarp0) {
     // ------------------------------------------------------------ unpack: int4 -> bf16(q * scale) into TMEM

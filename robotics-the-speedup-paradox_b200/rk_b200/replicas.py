@@ -8,6 +8,7 @@ The same helpers run on CPU ranks (`gloo`) and GPU ranks (`nccl`).
 """
 
 import os
+import sys
 from dataclasses import dataclass
 
 import torch
@@ -32,14 +33,36 @@ def rank_info(env=None) -> RankInfo:
     return RankInfo(rank, world, local)
 
 
+class _stdout_to_stderr:
+    """Routes file descriptor 1 to stderr for a while: the communication library announces itself
+    on stdout when its communicator is created, and stdout is reserved for the result line."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+        return False
+
+
 def init(info: RankInfo, device: torch.device) -> None:
-    """Joins the process group when there is more than one rank (nccl on GPUs, gloo on CPU)."""
+    """Joins the process group when there is more than one rank (nccl on GPUs, gloo on CPU) and runs
+    one barrier so that the communicator exists before any timed region."""
     if info.world == 1 or dist.is_initialized():
         return
-    if device.type == "cuda":
-        dist.init_process_group("nccl", device_id=device)
-    else:
-        dist.init_process_group("gloo")
+    with _stdout_to_stderr():
+        if device.type == "cuda":
+            dist.init_process_group("nccl", device_id=device)
+            dist.barrier(device_ids=[device.index])
+            torch.cuda.synchronize(device)
+        else:
+            dist.init_process_group("gloo")
+            dist.barrier()
 
 
 def barrier(info: RankInfo, device: torch.device) -> None:
