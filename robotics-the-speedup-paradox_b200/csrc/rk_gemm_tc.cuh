@@ -195,7 +195,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // the whole warp walks the loop (uniform control flow); the copies are issued by one elected lane
+    {
+      const uint32_t on = elect_one();
       // Weights are read once: let them leave L2 first.  Activations are re-read by every tile.
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
@@ -232,9 +234,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             cs = min(T::kSfChunksPerStage, p.sf_kt - kb * T::kSfChunksPerStage);
             tx += cs * 512 * (1 + rb_b);
           }
-          mbar_arrive_expect_tx(full, tx);
-          tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a);
-          tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b);
+          mbar_arrive_expect_tx(full, tx, on);
+          tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a, on);
+          tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b, on);
           if constexpr (T::kBlockScaled) {
             // Scale factors: contiguous 512-byte chunks in the 128-row swizzled global layout.
             const uint32_t ssf = sb + p.bn * kStageKBytes;
@@ -242,13 +244,15 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const long long chunk0 = static_cast<long long>(kb) * c;
             const uint8_t* src_a = sf_a + (static_cast<long long>(row_a0 / 128) * p.sf_kt + chunk0) * 512;
             asm volatile(
-                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                ::"r"(ssf), "l"(src_a), "r"(cs * 512), "r"(full) : "memory");
+                "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+                "@q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
+                ::"r"(ssf), "l"(src_a), "r"(cs * 512), "r"(full), "r"(on) : "memory");
             for (int rb = 0; rb < rb_b; ++rb) {
               const uint8_t* src_b = sf_b + (static_cast<long long>(row_b0 / 128 + rb) * p.sf_kt + chunk0) * 512;
               asm volatile(
-                  "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                  ::"r"(ssf + (1 + rb) * c * 512), "l"(src_b), "r"(cs * 512), "r"(full) : "memory");
+                  "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+                  "@q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
+                  ::"r"(ssf + (1 + rb) * c * 512), "l"(src_b), "r"(cs * 512), "r"(full), "r"(on) : "memory");
             }
           }
         }

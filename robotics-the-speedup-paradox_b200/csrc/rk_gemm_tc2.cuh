@@ -47,11 +47,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 // load into this CTA's shared memory, completion counted on a barrier of the pair (cluster address)
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t bar_cluster,
-                                                 uint64_t policy) {
+                                                 uint64_t policy, uint32_t on = 1u) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4}], [%2], %5;"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy)
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;\n\t}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy), "r"(on)
       : "memory");
 }
 __device__ __forceinline__ void tc2_commit_both(uint32_t bar, uint32_t on = 1u) {
@@ -134,7 +135,9 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
+    // the whole warp walks the loop (uniform control flow); the copies are issued by one elected lane
+    {
+      const uint32_t on = elect_one();
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
       Ring ring{0, 0};
@@ -156,10 +159,10 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           // both CTAs' bytes are counted on the leader's barrier; the leader announces the total
           const uint32_t full_leader = mapa_u32(smem_u32(&bar_full[s]), 0);
-          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * static_cast<uint32_t>(stage_bytes));
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * static_cast<uint32_t>(stage_bytes), on);
           const uint32_t sa = smem_base + s * stage_bytes;
-          tma_load_2d_pair(sa, &tm_a, kb * kStageKBytes, row_a0, full_leader, pol_x);
-          tma_load_2d_pair(sa + kTileA * kStageKBytes, &tm_b, kb * kStageKBytes, row_b0, full_leader, pol_w);
+          tma_load_2d_pair(sa, &tm_a, kb * kStageKBytes, row_a0, full_leader, pol_x, on);
+          tma_load_2d_pair(sa + kTileA * kStageKBytes, &tm_b, kb * kStageKBytes, row_b0, full_leader, pol_w, on);
         }
       }
     }
