@@ -179,6 +179,24 @@ int rk_gemm_fp8(const void* a, const float* scale_a, const void* b, const float*
                 void* out, int64_t m, int64_t n, int64_t k, int tactic, void* workspace,
                 size_t workspace_bytes, void* stream);
 
+/* (residual add +) RMSNorm in front of the per-tensor quantizer.  s = bf16(x + residual) (s = x
+ * when residual is NULL), r = rsqrt(mean(s^2) + eps), y = bf16( bf16(s * r) * weight[k] ); then
+ * scale and codes as rk_quant_tensor_fp8 over y.  Replaces `add_rms_norm_quantize_bf16`
+ * (blackwell/csrc/fp8_cutlass_linear.cu:145-269, 913-960).
+ *   x, residual bf16 [rows, k]; weight bf16 [k]; sum_out bf16 [rows, k] or NULL (written only
+ *   with a residual); norm_out bf16 [rows, k] (required); q e4m3 [rows, k]; scale_out f32 [1];
+ *   k % 16 == 0, k <= 8192; needs a workspace (header only). */
+int rk_rmsnorm_quant_fp8(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k,
+                         float eps, void* sum_out, void* norm_out, void* q, float* scale_out, void* workspace,
+                         size_t workspace_bytes, void* stream);
+/* SwiGLU in front of the per-tensor quantizer: a = bf16( gate / (1 + exp(-gate)) * up ) in fp32,
+ * gate = gate_up[r, 0:inter], up = gate_up[r, inter:2*inter]; scale = *scale_in when given, else
+ * computed over a and written to scale_out.  Replaces `quantize_swiglu_bf16` and
+ * `quantize_swiglu_bf16_with_scale` (blackwell/csrc/fp8_cutlass_linear.cu:271-389, 962-1009).
+ *   gate_up bf16 [rows, 2*inter]; q e4m3 [rows, inter]; inter % 16 == 0. */
+int rk_swiglu_quant_fp8(const void* gate_up, int64_t rows, int64_t inter, const float* scale_in, void* q,
+                        float* scale_out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- MXFP8 ------------------------------------------------------------------------------ */
 
 /* Per 32 consecutive k: SF = UE8M0 round-up of max|x| * rcp(448) (255 when the block holds a
@@ -201,6 +219,19 @@ int rk_gemm_mxfp8(const void* a, const void* sfa, const void* b, const void* sfb
  * q uint8 [rows, k/2]; sf: rk_sf_bytes(rows, k/16) bytes, fully written. */
 int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float* global_scale, void* q, void* sf,
                   void* stream);
+/* (residual add +) RMSNorm packed straight to NVFP4 (values never leave the chip between the norm
+ * and the packer).  Norm arithmetic as rk_rmsnorm_quant_fp8, block arithmetic as rk_pack_nvfp4
+ * without a per-tensor scale.  Replaces `add_rms_norm_fp4_quant_bf16`
+ * (blackwell/csrc/fp4_cutlass_linear.cu:843-929, 2538-2608).  sum_out, norm_out: bf16 [rows, k] or
+ * NULL; q uint8 [rows, k/2]; sf: rk_sf_bytes(rows, k/16) bytes, fully written; k % 32 == 0, k <= 8192. */
+int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k,
+                          float eps, void* sum_out, void* norm_out, void* q, void* sf, void* stream);
+/* SwiGLU packed straight to NVFP4: a = gate * rcp(1 + exp(-gate)) * up with every step rounded to
+ * bf16 (the reference evaluates it in packed bf16 arithmetic), then blocks as rk_pack_nvfp4.
+ * Replaces the packing half of `linear_forward_swiglu_gemm_bf16`
+ * (blackwell/csrc/fp4_cutlass_linear.cu:997-1143), non-interleaved gate/up layout.
+ *   gate_up bf16 [rows, 2*inter]; q uint8 [rows, inter/2]; sf: rk_sf_bytes(rows, inter/16); inter % 32 == 0. */
+int rk_swiglu_pack_nvfp4(const void* gate_up, int64_t rows, int64_t inter, void* q, void* sf, void* stream);
 /* *scale_out = max(max|x| / (6 * 448), 1e-12): the optional fp32 per-tensor scale of an NVFP4
  * tensor (absent from the reference, where alpha = 1: blackwell/csrc/fp4_cutlass_linear.cu:1358). */
 int rk_nvfp4_global_scale(const void* x, int64_t elements, float* scale_out, void* workspace,

@@ -87,6 +87,34 @@ def pack_nvfp4(x, global_scale=None):
     return packed, sf, swizzle_sf(sf)
 
 
+def swiglu_bf16_steps(gate_up, inter):
+    """SwiGLU with every intermediate rounded to bf16, the way the reference's NVFP4 producer computes
+    it in packed bf16 arithmetic (blackwell/csrc/fp4_cutlass_linear.cu:1029-1033):
+    e = bf16(exp(-g)); d = bf16(1 + e); r = bf16(1 / d); a = bf16(bf16(g * r) * up)."""
+    g = f32(gate_up[:, :inter])
+    u = f32(gate_up[:, inter:2 * inter])
+    with np.errstate(over="ignore"):
+        e = bf16_round(np.exp(-g.astype(np.float64)).astype(np.float32))
+    d = bf16_round((np.float32(1.0) + e).astype(np.float32))
+    with np.errstate(divide="ignore"):
+        r = bf16_round((np.float32(1.0) / d).astype(np.float32))
+    return bf16_round((bf16_round((g * r).astype(np.float32)) * u).astype(np.float32))
+
+
+def swiglu_pack_nvfp4(gate_up, inter):
+    a = swiglu_bf16_steps(gate_up, inter)
+    return pack_nvfp4(a) + (a,)
+
+
+def rms_norm_pack_nvfp4(x, residual, weight, eps):
+    """(residual add +) RMSNorm -> NVFP4 (blackwell/csrc/fp4_cutlass_linear.cu:843-929).
+    Returns (summed, normalized, packed, sf, swizzled sf)."""
+    from .fp8 import rms_norm
+
+    s, y = rms_norm(x, residual, weight, eps)
+    return (s, y) + pack_nvfp4(y)
+
+
 def dequant_nvfp4(packed, sf, global_scale=None):
     p = np.asarray(packed, dtype=np.uint8)
     rows = p.shape[0]

@@ -41,3 +41,45 @@ def gemm(a_codes, scale_a, b_codes, scale_b, bias=None):
     if bias is not None:
         acc = acc + f32(bias).astype(np.float64)[None, :]
     return bf16_round(acc.astype(np.float32)), acc
+
+
+# ---- fused producers (blackwell/csrc/fp8_cutlass_linear.cu:145-389) ------------------------------
+
+def rms_norm(x, residual, weight, eps):
+    """s = bf16(x + residual); r = rsqrt(mean(s^2) + eps); y = bf16(bf16(s * r) * weight).
+    Returns (summed, normalized) as float32 arrays holding bf16 values.  The sum of squares is taken
+    in float64 and rounded once (the kernel's fp32 tree order is not part of the contract); the
+    device rsqrt is approximate, which the bf16 roundings absorb except at rare ties."""
+    s = f32(x)
+    if residual is not None:
+        s = bf16_round((s + f32(residual)).astype(np.float32))
+    k = s.shape[-1]
+    mean = (np.square(s.astype(np.float64)).sum(axis=-1) / k).astype(np.float32)
+    r = (1.0 / np.sqrt((mean + np.float32(eps)).astype(np.float64))).astype(np.float32)
+    y = bf16_round((s * r[..., None]).astype(np.float32))
+    y = bf16_round((y * f32(weight)[None, :]).astype(np.float32))
+    return s, y
+
+
+def add_rms_norm_quantize(x, residual, weight, eps):
+    """Returns (summed, normalized, codes, scale)."""
+    s, y = rms_norm(x, residual, weight, eps)
+    codes, scale = quantize(y)
+    return s, y, codes, scale
+
+
+def swiglu(gate_up, inter):
+    """bf16( gate / (1 + exp(-gate)) * up ) evaluated in fp32 (fp8_cutlass_linear.cu:271-279)."""
+    g = f32(gate_up[:, :inter])
+    u = f32(gate_up[:, inter:2 * inter])
+    with np.errstate(over="ignore"):
+        e = np.exp(-g.astype(np.float64)).astype(np.float32)
+    act = (g / (np.float32(1.0) + e)).astype(np.float32)
+    return bf16_round((act * u).astype(np.float32))
+
+
+def quantize_swiglu(gate_up, inter, scale=None):
+    a = swiglu(gate_up, inter)
+    if scale is None:
+        scale = tensor_scale(a)
+    return quantize_with_scale(a, scale), np.float32(scale), a

@@ -525,6 +525,223 @@ pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long
   sf[sfi] = code;
 }
 
+// ------------------------------------------------------------------ fused producers for the FP8 / NVFP4 GEMMs
+// SwiGLU in fp32, as the reference's per-tensor FP8 producer evaluates it
+// (blackwell/csrc/fp8_cutlass_linear.cu:271-279): bf16( gate / (1 + exp(-gate)) * up ).
+__device__ __forceinline__ float swiglu_f32(float gate, float up) {
+  return round_bf16(__fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up));
+}
+// SwiGLU in bf16 steps, as the reference's NVFP4 producer evaluates it with packed bf16 arithmetic
+// (blackwell/csrc/fp4_cutlass_linear.cu:1029-1033): every intermediate is rounded to bf16.
+__device__ __forceinline__ float swiglu_bf16_steps(float gate, float up) {
+  const float e = round_bf16(expf(-gate));
+  const float d = round_bf16(__fadd_rn(1.0f, e));
+  const float r = round_bf16(__fdiv_rn(1.0f, d));
+  return round_bf16(__fmul_rn(round_bf16(__fmul_rn(gate, r)), up));
+}
+
+// Eight consecutive SwiGLU outputs of row-major gate_up [rows, 2 * inter] (gate first, then up).
+template <bool BF16_STEPS>
+__device__ __forceinline__ void load8_swiglu(const __nv_bfloat16* gate_up, long long inter, long long idx, int valid,
+                                             float (&v)[8]) {
+  const long long row = idx / inter, col = idx - row * inter;
+  const __nv_bfloat16* g = gate_up + row * 2 * inter + col;
+  float gv[8], uv[8];
+  const bool vec = (inter % 8) == 0;
+  load8(g, vec, valid, gv);
+  load8(g + inter, vec, valid, uv);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = i < valid ? (BF16_STEPS ? swiglu_bf16_steps(gv[i], uv[i]) : swiglu_f32(gv[i], uv[i])) : 0.0f;
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_amax_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter,
+                   unsigned* __restrict__ amax_bits) {
+  __shared__ float scratch[8];
+  float local = 0.0f;
+  const long long elements = rows * inter;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; idx < elements;
+       idx += stride) {
+    float v[8];
+    load8_swiglu<false>(gate_up, inter, idx, 8, v);  // inter % 8 == 0: a vector never straddles rows
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float a = fabsf(v[i]);
+      if (a <= 3.4028234664e38f) local = fmaxf(local, a);
+    }
+  }
+  local = warp_max(local);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float r = scratch[0];
+    for (int w = 1; w < 8; ++w) r = fmaxf(r, scratch[w]);
+    atomicMax(amax_bits, __float_as_uint(r));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_to_fp8_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter,
+                     const float* __restrict__ scale, uint8_t* __restrict__ q) {
+  const float inverse = __fdiv_rn(1.0f, *scale);
+  const long long elements = rows * inter;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; idx < elements;
+       idx += stride) {
+    float v[8];
+    load8_swiglu<false>(gate_up, inter, idx, 8, v);
+    uint32_t c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float t = fminf(448.0f, fmaxf(-448.0f, __fmul_rn(v[i], inverse)));
+      c[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3));
+    }
+    uint2 o;
+    o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+    o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+    *reinterpret_cast<uint2*>(q + idx) = o;
+  }
+}
+
+// One 16-element NVFP4 block: UE4M3 scale byte and eight code bytes (two E2M1 codes each, low nibble first).
+// Same arithmetic as pack_nvfp4_kernel (blackwell/csrc/fp4_cutlass_linear.cu:789-841, no per-tensor scale).
+__device__ __forceinline__ unsigned long long nvfp4_block(const float (&v)[16], uint8_t* code_out) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 6.0f) : 1.0f;
+  const uint8_t code = static_cast<uint8_t>(__nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E4M3)) & 0x7F;
+  float deq = __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
+  if (!(deq > 0.0f)) deq = scale;
+  const float reciprocal = __fdiv_rn(1.0f, deq);
+  unsigned long long packed = 0;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const __nv_fp4x2_storage_t pair = __nv_cvt_float2_to_fp4x2(
+        make_float2(__fmul_rn(v[i], reciprocal), __fmul_rn(v[i + 1], reciprocal)), __NV_E2M1, cudaRoundNearest);
+    packed |= static_cast<unsigned long long>(static_cast<uint8_t>(pair)) << (4 * i);
+  }
+  *code_out = code;
+  return packed;
+}
+
+// SwiGLU -> NVFP4: one thread per 16-element block of the [rows, inter] activation.
+__global__ void __launch_bounds__(256)
+swiglu_pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter,
+                         uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  const long long groups = inter / 16;
+  const long long groups_padded = (groups + 3) / 4 * 4;
+  const long long rows_padded = (rows + 127) / 128 * 128;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = idx / groups_padded;
+  const long long group = idx % groups_padded;
+  if (row >= rows_padded) return;
+  const long long sfi = sf_offset(row, group, groups_padded / 4);
+  if (row >= rows || group >= groups) {
+    sf[sfi] = 0;
+    return;
+  }
+  float v[16];
+  load8_swiglu<true>(gate_up, inter, row * inter + group * 16, 8, *reinterpret_cast<float(*)[8]>(&v[0]));
+  load8_swiglu<true>(gate_up, inter, row * inter + group * 16 + 8, 8, *reinterpret_cast<float(*)[8]>(&v[8]));
+  uint8_t code;
+  const unsigned long long packed = nvfp4_block(v, &code);
+  *reinterpret_cast<unsigned long long*>(q + row * (inter / 2) + group * 8) = packed;
+  sf[sfi] = code;
+}
+
+// (residual add +) RMSNorm feeding a per-tensor FP8 quantizer (FMT 0: writes the bf16 results and the
+// tensor's absolute maximum) or an NVFP4 packer (FMT 1: packs straight from registers).  Arithmetic
+// of blackwell/csrc/fp8_cutlass_linear.cu:145-203 and blackwell/csrc/fp4_cutlass_linear.cu:843-929:
+// s = bf16(x + residual); r = rsqrt(mean(s^2) + eps); y = bf16( bf16(s * r) * weight ).
+// One CTA per row (FMT 1: per row of the 128-row padded scale-factor domain), row cached in registers.
+template <int FMT>
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_producer_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                        const __nv_bfloat16* __restrict__ weight, int rows, int k, float eps,
+                        __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ norm_out,
+                        unsigned* __restrict__ amax_bits, uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  __shared__ float scratch[kRowThreads / 32];
+  const int row = blockIdx.x;
+  const int groups = k / 16;
+  const int groups_padded = (groups + 3) / 4 * 4;
+  if (row >= rows) {  // FMT 1 only: padding rows of the scale-factor buffer read as zero
+    for (int g = threadIdx.x; g < groups_padded; g += kRowThreads) sf[sf_offset(row, g, groups_padded / 4)] = 0;
+    return;
+  }
+  const long long xoff = static_cast<long long>(row) * k;
+  float vals[kMaxVec][8];
+  float sq = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vals[it][i] = 0.0f;
+    if (idx < k) {  // k % 16 == 0: whole vectors only
+      load8(x + xoff + idx, true, 8, vals[it]);
+      if (residual != nullptr) {
+        float rv[8];
+        load8(residual + xoff + idx, true, 8, rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vals[it][i] = round_bf16(__fadd_rn(vals[it][i], rv[i]));
+        if (sum_out != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum_out[xoff + idx + i] = __float2bfloat16_rn(vals[it][i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq = fmaf(vals[it][i], vals[it][i], sq);
+    }
+  }
+  const float inv = rsqrtf(__fadd_rn(__fdiv_rn(block_reduce(sq, false, scratch), static_cast<float>(k)), eps));
+  float local_max = 0.0f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+    if (idx < k) {
+      float wv[8];
+      load8(weight + idx, true, 8, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float y = round_bf16(__fmul_rn(round_bf16(__fmul_rn(vals[it][i], inv)), wv[i]));
+        vals[it][i] = y;
+        if (norm_out != nullptr) norm_out[xoff + idx + i] = __float2bfloat16_rn(y);
+        const float a = fabsf(y);
+        if (a <= 3.4028234664e38f) local_max = fmaxf(local_max, a);
+      }
+    }
+  }
+  if (FMT == 0) {
+    const float m = block_reduce(local_max, true, scratch);
+    if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(m));
+    return;
+  }
+  // FMT 1: a 16-element block is held by an even thread (low half) and its odd neighbour (high half)
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int idx = (it * kRowThreads + threadIdx.x) * 8;  // warp-uniform validity: k % 256 handled by the mask below
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, vals[it][i], 1);
+      v[i] = (threadIdx.x & 1) ? other : vals[it][i];
+      v[8 + i] = (threadIdx.x & 1) ? vals[it][i] : other;
+    }
+    if (idx < k) {
+      uint8_t code;
+      const unsigned long long packed = nvfp4_block(v, &code);
+      const int group = idx / 16;
+      // each thread stores the four code bytes of its own eight values
+      const uint32_t mine = static_cast<uint32_t>((threadIdx.x & 1) ? (packed >> 32) : packed);
+      *reinterpret_cast<uint32_t*>(q + static_cast<long long>(row) * (k / 2) + idx / 2) = mine;
+      if (!(threadIdx.x & 1)) sf[sf_offset(row, group, groups_padded / 4)] = code;
+    }
+  }
+  // scale factors of the padded groups of this row
+  for (int g = groups + threadIdx.x; g < groups_padded; g += kRowThreads) sf[sf_offset(row, g, groups_padded / 4)] = 0;
+}
+
 __global__ void probe_rcp_kernel(uint32_t* out) { *out = __float_as_uint(rcp_approx_ftz(448.0f)); }
 
 template <int BITS>
@@ -717,6 +934,79 @@ extern "C" int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float
   pack_nvfp4_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k, global_scale,
                                                          static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   return check_launch("pack_nvfp4");
+}
+
+extern "C" int rk_rmsnorm_quant_fp8(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k,
+                                    float eps, void* sum_out, void* norm_out, void* q, float* scale_out,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "rk_rmsnorm_quant_fp8";
+  if (!x || !weight || !norm_out || !q || !scale_out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
+  if (rows < 1 || k < 16 || k % 16 != 0 || k > rk::kCachedK) return fail(RK_EINVAL, "%s: k must be a multiple of 16, at most %d", who, rk::kCachedK);
+  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(norm_out))
+    return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  cudaStream_t st = as_stream(stream);
+  unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  rk::rmsnorm_producer_kernel<0><<<static_cast<unsigned>(rows), rk::kRowThreads, 0, st>>>(
+      b(x), b(residual), b(weight), static_cast<int>(rows), static_cast<int>(k), eps,
+      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), staging, nullptr, nullptr);
+  rk::finalize_scale_kernel<<<1, 1, 0, st>>>(staging, 448.0f, scale_out);
+  int rc = check_launch(who);
+  if (rc != RK_OK) return rc;
+  return rk_quant_tensor_fp8_with_scale(norm_out, rows * k, scale_out, q, stream);
+}
+
+extern "C" int rk_swiglu_quant_fp8(const void* gate_up, int64_t rows, int64_t inter, const float* scale_in, void* q,
+                                   float* scale_out, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "rk_swiglu_quant_fp8";
+  if (!gate_up || !q || (!scale_in && !scale_out)) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || inter < 16 || inter % 16 != 0) return fail(RK_EINVAL, "%s: the intermediate size must be a multiple of 16", who);
+  if (!aligned16(gate_up) || (reinterpret_cast<uintptr_t>(q) & 7u)) return fail(RK_EINVAL, "%s: bad alignment", who);
+  cudaStream_t st = as_stream(stream);
+  const long long elements = rows * inter;
+  long long blocks = (elements + 2047) / 2048;
+  if (blocks > 2368) blocks = 2368;
+  const float* scale = scale_in;
+  if (scale_in == nullptr) {
+    if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
+    unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
+    rk::swiglu_amax_kernel<<<static_cast<unsigned>(blocks > 1184 ? 1184 : blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(gate_up), rows, inter, staging);
+    rk::finalize_scale_kernel<<<1, 1, 0, st>>>(staging, 448.0f, scale_out);
+    scale = scale_out;
+  }
+  rk::swiglu_to_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up), rows,
+                                                                          inter, scale, static_cast<uint8_t*>(q));
+  return check_launch(who);
+}
+
+extern "C" int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k,
+                                     float eps, void* sum_out, void* norm_out, void* q, void* sf, void* stream) {
+  const char* who = "rk_rmsnorm_pack_nvfp4";
+  if (!x || !weight || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || k < 32 || k % 32 != 0 || k > rk::kCachedK) return fail(RK_EINVAL, "%s: k must be a multiple of 32, at most %d", who, rk::kCachedK);
+  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(q))
+    return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  const unsigned rows_padded = static_cast<unsigned>((rows + 127) / 128 * 128);
+  rk::rmsnorm_producer_kernel<1><<<rows_padded, rk::kRowThreads, 0, as_stream(stream)>>>(
+      b(x), b(residual), b(weight), static_cast<int>(rows), static_cast<int>(k), eps,
+      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), nullptr, static_cast<uint8_t*>(q),
+      static_cast<uint8_t*>(sf));
+  return check_launch(who);
+}
+
+extern "C" int rk_swiglu_pack_nvfp4(const void* gate_up, int64_t rows, int64_t inter, void* q, void* sf, void* stream) {
+  const char* who = "rk_swiglu_pack_nvfp4";
+  if (!gate_up || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || inter < 32 || inter % 32 != 0) return fail(RK_EINVAL, "%s: the intermediate size must be a multiple of 32", who);
+  if (!aligned16(gate_up) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  const long long threads = ((rows + 127) / 128 * 128) * ((inter / 16 + 3) / 4 * 4);
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  rk::swiglu_pack_nvfp4_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+                                                                   static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
+  return check_launch(who);
 }
 
 extern "C" int rk_probe_rcp_approx_448(uint32_t* bits) {

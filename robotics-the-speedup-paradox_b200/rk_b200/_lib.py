@@ -44,10 +44,14 @@ SIGNATURES = {
     "rk_gemm_w4a16_g128": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_quant_tensor_fp8": (_int, [_vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     "rk_quant_tensor_fp8_with_scale": (_int, [_vp, _i64, _vp, _vp, _vp]),
+    "rk_rmsnorm_quant_fp8": (_int, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "rk_swiglu_quant_fp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rk_gemm_fp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
     "rk_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_pack_nvfp4": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "rk_rmsnorm_pack_nvfp4": (_int, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp, _vp, _vp]),
+    "rk_swiglu_pack_nvfp4": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
     "rk_nvfp4_global_scale": (_int, [_vp, _i64, _vp, _vp, _sz, _vp]),
     "rk_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
 }

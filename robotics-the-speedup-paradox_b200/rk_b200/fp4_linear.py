@@ -71,6 +71,47 @@ def pack_nvfp4(x, global_scale=None):
     return q, sf
 
 
+def add_rms_norm_fp4_quant_bf16(x, residual, weight, epsilon, write_normalized=True):
+    """(residual add +) RMSNorm packed straight to NVFP4: -> (summed, normalized or None, codes, scale buffer).
+
+    Mirrors `robotics_cutlass_fp4::add_rms_norm_fp4_quant_bf16` (blackwell/csrc/fp4_cutlass_linear.cu:2538-2608):
+    x, residual bf16 [rows, K] (residual may be None), weight bf16 [K], K % 32 == 0."""
+    for t, what in ((x, "input"), (weight, "weight")) + (((residual, "residual"),) if residual is not None else ()):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError(f"add_rms_norm_fp4_quant_bf16 {what} must be a contiguous CUDA BF16 tensor")
+    if x.dim() != 2 or x.shape[1] % 32 or weight.shape != (x.shape[1],) or (residual is not None and residual.shape != x.shape):
+        raise ValueError("add_rms_norm_fp4_quant_bf16 requires [rows, K] inputs with K divisible by 32 and weight [K]")
+    rows, k = x.shape
+    lib = _lib.load()
+    summed = torch.empty_like(x) if residual is not None else x
+    normalized = torch.empty_like(x) if write_normalized else None
+    q = torch.empty((rows, k // 2), device=x.device, dtype=torch.uint8)
+    sf = torch.empty(lib.rk_sf_bytes(rows, k // 16), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        code = lib.rk_rmsnorm_pack_nvfp4(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), rows, k, float(epsilon),
+                                         _lib.ptr(summed) if residual is not None else None, _lib.ptr(normalized),
+                                         _lib.ptr(q), _lib.ptr(sf), _lib.stream_ptr(x.device))
+    _lib.check(code, "add_rms_norm_fp4_quant_bf16")
+    return summed, normalized, q, sf
+
+
+def pack_swiglu_nvfp4(gate_up, intermediate_size):
+    """SiLU(gate) * up (bf16 arithmetic steps) packed straight to NVFP4: gate_up bf16 [rows, 2 * inter]."""
+    inter = int(intermediate_size)
+    if (not gate_up.is_cuda or gate_up.dtype != torch.bfloat16 or not gate_up.is_contiguous() or gate_up.dim() != 2
+            or gate_up.shape[1] != 2 * inter or inter % 32):
+        raise ValueError("SwiGLU NVFP4 pack requires contiguous CUDA BF16 [rows, 2 * inter] with inter divisible by 32")
+    rows = gate_up.shape[0]
+    lib = _lib.load()
+    q = torch.empty((rows, inter // 2), device=gate_up.device, dtype=torch.uint8)
+    sf = torch.empty(lib.rk_sf_bytes(rows, inter // 16), device=gate_up.device, dtype=torch.uint8)
+    with torch.cuda.device(gate_up.device):
+        code = lib.rk_swiglu_pack_nvfp4(_lib.ptr(gate_up), rows, inter, _lib.ptr(q), _lib.ptr(sf),
+                                        _lib.stream_ptr(gate_up.device))
+    _lib.check(code, "pack_swiglu_nvfp4")
+    return q, sf
+
+
 def linear_forward_packed_gemm_bf16(a, sfa, ga, b, sfb, gb, bias, k, tactic=0):
     m, n = a.shape[0], b.shape[0]
     out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
@@ -134,6 +175,19 @@ class Fp4CutlassLinear(torch.nn.Module):
     def forward(self, x):
         q, sf, ga = self.pack_input(x)
         return self.forward_packed(q, sf, ga, x.shape[:-1])
+
+    def forward_swiglu(self, gate_up, intermediate_size, interleaved=False):
+        """SwiGLU, activation packing and this (down) projection (blackwell/fp4_linear.py:805-848 of the
+        reference); gate_up [..., 2 * intermediate_size], gate first."""
+        if int(intermediate_size) != self.in_features:
+            raise ValueError(f"expected intermediate_size {self.in_features}, got {intermediate_size}")
+        if interleaved:
+            raise ValueError("the interleaved gate/up layout is not supported")
+        if self.weight_global_scale is not None:
+            raise RuntimeError("forward_swiglu packs without a per-tensor scale; build the layer with global_scale=False")
+        flat = gate_up.to(torch.bfloat16).reshape(-1, 2 * self.in_features).contiguous()
+        q, sf = pack_swiglu_nvfp4(flat, self.in_features)
+        return self.forward_packed(q, sf, None, gate_up.shape[:-1])
 
     def extra_repr(self):
         return f"in_features={self.in_features}, out_features={self.out_features}, role={self.role}"

@@ -74,6 +74,60 @@ def quantize_bf16_with_scale(x, scale):
     return q
 
 
+def add_rms_norm_quantize_bf16(x, residual, weight, epsilon):
+    """(residual add +) RMSNorm -> per-tensor E4M3: -> (summed, normalized, e4m3 codes, float32 scale[1]).
+
+    Mirrors `robotics_cutlass_fp8::add_rms_norm_quantize_bf16` (blackwell/csrc/fp8_cutlass_linear.cu:913-960):
+    x, residual bf16 [rows, K] (residual may be None: then `summed` is x itself), weight bf16 [K]."""
+    _check_bf16(x, "add_rms_norm_quantize_bf16 input")
+    if x.dim() != 2 or x.shape[1] % 16:
+        raise ValueError("add_rms_norm_quantize_bf16 requires [rows, K] with K divisible by 16")
+    if residual is not None:
+        _check_bf16(residual, "add_rms_norm_quantize_bf16 residual")
+        if residual.shape != x.shape:
+            raise ValueError("residual must have the shape of the input")
+    _check_bf16(weight, "add_rms_norm_quantize_bf16 weight")
+    if weight.shape != (x.shape[1],):
+        raise ValueError("weight must have one entry per column")
+    rows, k = x.shape
+    summed = torch.empty_like(x) if residual is not None else x
+    normalized = torch.empty_like(x)
+    q = torch.empty(x.shape, device=x.device, dtype=FP8_DTYPE)
+    scale = torch.empty(1, device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        ws = _lib.workspace(x.device, _lib.WORKSPACE_HEADER)
+        code = _lib.load().rk_rmsnorm_quant_fp8(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), rows, k, float(epsilon),
+                                                _lib.ptr(summed) if residual is not None else None, _lib.ptr(normalized),
+                                                _lib.ptr(q), _lib.ptr(scale), _lib.ptr(ws), ws.numel(),
+                                                _lib.stream_ptr(x.device))
+    _lib.check(code, "add_rms_norm_quantize_bf16")
+    return summed, normalized, q, scale
+
+
+def quantize_swiglu_bf16(gate_up, intermediate_size, scale=None):
+    """SiLU(gate) * up -> per-tensor E4M3: gate_up bf16 [rows, 2 * intermediate_size] (gate first).
+    -> (e4m3 [rows, intermediate_size], float32 scale[1]); `scale` given = `quantize_swiglu_bf16_with_scale`
+    (blackwell/csrc/fp8_cutlass_linear.cu:962-1009)."""
+    _check_bf16(gate_up, "quantize_swiglu_bf16 input")
+    inter = int(intermediate_size)
+    if gate_up.dim() != 2 or gate_up.shape[1] != 2 * inter or inter % 16:
+        raise ValueError("quantize_swiglu_bf16 requires [rows, 2 * intermediate_size], intermediate_size divisible by 16")
+    rows = gate_up.shape[0]
+    q = torch.empty((rows, inter), device=gate_up.device, dtype=FP8_DTYPE)
+    out_scale = scale if scale is not None else torch.empty(1, device=gate_up.device, dtype=torch.float32)
+    with torch.cuda.device(gate_up.device):
+        ws = _lib.workspace(gate_up.device, _lib.WORKSPACE_HEADER)
+        code = _lib.load().rk_swiglu_quant_fp8(_lib.ptr(gate_up), rows, inter, _lib.ptr(scale), _lib.ptr(q),
+                                               _lib.ptr(out_scale), _lib.ptr(ws), ws.numel(),
+                                               _lib.stream_ptr(gate_up.device))
+    _lib.check(code, "quantize_swiglu_bf16")
+    return q, out_scale
+
+
+def quantize_swiglu_bf16_with_scale(gate_up, intermediate_size, scale):
+    return quantize_swiglu_bf16(gate_up, intermediate_size, scale)[0]
+
+
 def linear_forward_packed(a, scale_a, b, scale_b, bias=None, tactic=0):
     """e4m3 [M, K] x e4m3 [N, K]^T -> bf16 [M, N] = bf16(scale_a * scale_b * acc + bias)."""
     m, k = a.shape
@@ -132,6 +186,7 @@ class Fp8CutlassLinear(torch.nn.Module):
         self.role = role
         self.target_name = target_name
         self.mode = mode
+        self._unit_scale = None  # lazily created scalar 1.0 for the producer path
         self.fp8_backend = "b200_tcgen05_e4m3" if mode == "per_tensor" else "b200_tcgen05_mxfp8_e4m3_ue8m0"
 
     @classmethod
@@ -172,6 +227,30 @@ class Fp8CutlassLinear(torch.nn.Module):
         else:
             out = mxfp8_linear(packed, scale, self.packed_weight, self.weight_scale, self.bias)
         return out if shape is None else out.reshape(*shape, self.out_features)
+
+    def forward_swiglu(self, gate_up, intermediate_size, leading_shape):
+        """SiLU * up, dynamic E4M3 packing and this (down) projection; gate_up [..., 2 * intermediate_size]
+        (blackwell/fp8_linear.py:679-691 of the reference)."""
+        if self.mode != "per_tensor":
+            raise RuntimeError("forward_swiglu packs per-tensor E4M3; this layer was packed as MXFP8")
+        if int(intermediate_size) != self.in_features:
+            raise ValueError(f"expected intermediate_size {self.in_features}, got {intermediate_size}")
+        flat = gate_up.to(torch.bfloat16).reshape(-1, 2 * self.in_features).contiguous()
+        packed, scale = quantize_swiglu_bf16(flat, self.in_features)
+        return self.forward_packed(packed, scale, leading_shape)
+
+    def forward_producer(self, x):
+        """BF16 activations converted to E4M3 with a unit activation scale, then the GEMM: the semantics of
+        `linear_forward_producer` (blackwell/csrc/fp8_cutlass_linear.cu:727-856, 1268-1315), which the
+        reference uses for small projections to skip the dynamic activation scale.  Here the conversion
+        is a separate launch in front of the GEMM rather than part of its main loop."""
+        if self.mode != "per_tensor":
+            raise RuntimeError("forward_producer is a per-tensor path; this layer was packed as MXFP8")
+        flat = self._rows(x)
+        if self._unit_scale is None or self._unit_scale.device != flat.device:
+            self._unit_scale = torch.ones(1, device=flat.device, dtype=torch.float32)
+        packed = quantize_bf16_with_scale(flat, self._unit_scale)
+        return self.forward_packed(packed, self._unit_scale, x.shape[:-1])
 
     def forward_mxfp8(self, x):
         if self.mode != "mxfp8":

@@ -1,0 +1,163 @@
+"""GPU parity of the fused producers in front of the FP8 and NVFP4 GEMMs: (residual add +) RMSNorm and
+SwiGLU feeding the per-tensor E4M3 quantizer and the NVFP4 packer, checked against the CPU oracle.
+
+The norm and the SiLU contain one transcendental each (`rsqrt`, `exp`) whose device versions are
+not correctly rounded; every result is rounded to bf16 right after, so device and oracle agree
+except where a value sits on a bf16 rounding boundary.  The tests therefore demand bit equality of
+the bf16 intermediates on (almost) all elements, a two-step bound on the rest, and bit equality of
+the codes and scale factors with what the oracle makes of the kernel's own bf16 intermediates."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import blockscale as OB
+from oracle import formats as F
+from oracle import fp8 as OF
+from rk_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+EPS = 1e-6
+
+
+@pytest.fixture(scope="module")
+def H():
+    import gpu_helpers
+
+    return gpu_helpers
+
+
+def _nearly_identical(got, want, max_fraction=2e-3):
+    """bf16 arrays: equal almost everywhere, never further apart than two bf16 steps (a one-step
+    difference after the first of two consecutive roundings can double in the second)."""
+    got, want = np.asarray(got, np.float32), np.asarray(want, np.float32)
+    differ = got != want
+    assert differ.mean() <= max_fraction
+    assert np.all(np.abs(got - want)[differ] <= np.abs(want)[differ] * 2.0 ** -6 + 1e-30)
+    return ~differ.reshape(got.shape[0], -1).any(axis=1)  # rows that agree exactly
+
+
+@pytest.mark.parametrize("shape", [(5, 64), (100, 1024), (816, 2048)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_rmsnorm_to_per_tensor_fp8(H, shape, with_residual):
+    from rk_b200.fp8_linear import add_rms_norm_quantize_bf16
+
+    rows, k = shape
+    x = H.randn_bf16(shape, 1.0, 21)
+    res = H.randn_bf16(shape, 0.5, 22) if with_residual else None
+    w = (H.randn_bf16((k,), 0.1, 23).float() + 1.0).to(torch.bfloat16)
+    summed, normalized, q, scale = add_rms_norm_quantize_bf16(
+        x.to(H.DEVICE), None if res is None else res.to(H.DEVICE), w.to(H.DEVICE), EPS)
+    ws, wn, wq, wscale = OF.add_rms_norm_quantize(H.to_np(x), None if res is None else H.to_np(res), H.to_np(w), EPS)
+    assert np.array_equal(F.bf16_bits(H.to_np(summed)), F.bf16_bits(ws))  # the residual add is exact arithmetic
+    _nearly_identical(H.to_np(normalized), wn)
+    # scale and codes follow from the kernel's own normalized values exactly
+    own_codes, own_scale = OF.quantize(H.to_np(normalized))
+    assert np.float32(scale.item()) == own_scale
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), own_codes)
+    assert abs(float(scale.item()) - float(wscale)) <= float(wscale) * 2.0 ** -7
+
+
+@pytest.mark.parametrize("shape", [(3, 64), (50, 4096), (816, 16384)])
+def test_swiglu_to_per_tensor_fp8(H, shape):
+    from rk_b200.fp8_linear import quantize_swiglu_bf16, quantize_swiglu_bf16_with_scale
+
+    rows, inter = shape
+    gate_up = H.randn_bf16((rows, 2 * inter), 1.5, 31)
+    q, scale = quantize_swiglu_bf16(gate_up.to(H.DEVICE), inter)
+    wq, wscale, act = OF.quantize_swiglu(H.to_np(gate_up), inter)
+    got = q.view(torch.uint8).cpu().numpy()
+    # the activation itself is not an output; compare through the codes: identical scale (the maximum is
+    # far from a rounding boundary with overwhelming probability) and codes equal almost everywhere
+    assert abs(float(scale.item()) - float(wscale)) <= float(wscale) * 2.0 ** -7
+    if np.float32(scale.item()) == wscale:
+        differ = got != wq
+        assert differ.mean() <= 2e-3
+        step = np.abs(F.e4m3_decode(got).astype(np.float64) - F.e4m3_decode(wq).astype(np.float64))
+        assert np.all(step[differ] <= np.abs(F.e4m3_decode(wq))[differ] * 0.13 + 2.0 ** -9)
+    # a caller-supplied scale reproduces the same codes
+    again = quantize_swiglu_bf16_with_scale(gate_up.to(H.DEVICE), inter, scale)
+    assert torch.equal(again.view(torch.uint8), q.view(torch.uint8))
+
+
+@pytest.mark.parametrize("shape", [(5, 64), (130, 1024), (816, 2048)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_rmsnorm_to_nvfp4(H, shape, with_residual):
+    from rk_b200.fp4_linear import add_rms_norm_fp4_quant_bf16
+
+    rows, k = shape
+    x = H.randn_bf16(shape, 1.0, 41)
+    res = H.randn_bf16(shape, 0.5, 42) if with_residual else None
+    w = (H.randn_bf16((k,), 0.1, 43).float() + 1.0).to(torch.bfloat16)
+    summed, normalized, q, sf = add_rms_norm_fp4_quant_bf16(
+        x.to(H.DEVICE), None if res is None else res.to(H.DEVICE), w.to(H.DEVICE), EPS)
+    ws, wn, wq, wsf, wsf_swizzled = OB.rms_norm_pack_nvfp4(H.to_np(x), None if res is None else H.to_np(res), H.to_np(w), EPS)
+    assert np.array_equal(F.bf16_bits(H.to_np(summed)), F.bf16_bits(ws))
+    _nearly_identical(H.to_np(normalized), wn)
+    # codes and scale factors are exactly what the packer makes of the kernel's own normalized values,
+    # padding bytes included
+    own_q, own_sf, own_swizzled = OB.pack_nvfp4(H.to_np(normalized))
+    assert np.array_equal(q.cpu().numpy(), own_q)
+    assert np.array_equal(sf.cpu().numpy(), own_swizzled)
+
+
+@pytest.mark.parametrize("shape", [(3, 64), (50, 4096), (300, 16384)])
+def test_swiglu_to_nvfp4(H, shape):
+    from rk_b200.fp4_linear import pack_swiglu_nvfp4
+
+    rows, inter = shape
+    gate_up = H.randn_bf16((rows, 2 * inter), 1.5, 51)
+    q, sf = pack_swiglu_nvfp4(gate_up.to(H.DEVICE), inter)
+    wq, wsf, wswizzled, act = OB.swiglu_pack_nvfp4(H.to_np(gate_up), inter)
+    got_q, got_sf = q.cpu().numpy(), OB.unswizzle_sf(sf.cpu().numpy(), rows, inter // 16)
+    # a 16-element block is identical unless one of its activations sat on a bf16 rounding boundary
+    same_block = (got_sf == wsf) & (got_q.reshape(rows, inter // 16, 8) == wq.reshape(rows, inter // 16, 8)).all(axis=2)
+    assert same_block.mean() >= 0.98
+    # and the dequantized tensor stays close everywhere
+    got_deq = OB.dequant_nvfp4(got_q, got_sf)
+    assert H.rel_frobenius(got_deq, OB.dequant_nvfp4(wq, wsf)) < 2e-2
+    # padding of the scale-factor buffer is zero
+    full = sf.cpu().numpy().copy()
+    full[OB.sf_offsets(rows, inter // 16)] = 0
+    assert not full.any()
+
+
+def test_swiglu_modules_end_to_end(H):
+    """forward_swiglu of the FP8 and NVFP4 layers against SiLU * up followed by the plain forward."""
+    from rk_b200.fp4_linear import Fp4CutlassLinear
+    from rk_b200.fp8_linear import Fp8CutlassLinear
+
+    torch.manual_seed(5)
+    inter, width = 512, 256
+    lin = torch.nn.Linear(inter, width, bias=False, device="cuda", dtype=torch.bfloat16).eval().requires_grad_(False)
+    gate_up = torch.randn(4, 7, 2 * inter, device="cuda", dtype=torch.bfloat16)
+    reference = torch.nn.functional.silu(gate_up[..., :inter].float()) * gate_up[..., inter:].float()
+    want = (reference @ lin.weight.float().T).cpu().numpy()
+    for layer in (Fp8CutlassLinear.from_linear(lin, "linear", "down"), Fp4CutlassLinear.from_linear(lin, "linear", "down")):
+        if isinstance(layer, Fp8CutlassLinear):
+            got = layer.forward_swiglu(gate_up, inter, gate_up.shape[:-1])
+            tol = 0.05
+        else:
+            got = layer.forward_swiglu(gate_up, inter)
+            tol = 0.15  # four-bit operands on both sides
+        assert got.shape == (4, 7, width)
+        assert H.rel_frobenius(H.to_np(got).reshape(-1, width), want.reshape(-1, width)) < tol
+    with pytest.raises(ValueError):
+        Fp4CutlassLinear.from_linear(lin, "linear", "down").forward_swiglu(gate_up, inter, interleaved=True)
+
+
+def test_fp8_producer_path_uses_a_unit_activation_scale(H):
+    """`forward_producer`: activations go to E4M3 unscaled (saturating at 448), weights keep their scale."""
+    from rk_b200.fp8_linear import Fp8CutlassLinear
+
+    torch.manual_seed(9)
+    lin = torch.nn.Linear(512, 256, bias=True, device="cuda", dtype=torch.bfloat16).eval().requires_grad_(False)
+    x = torch.randn(3, 40, 512, device="cuda", dtype=torch.bfloat16) * 2
+    x[0, 0, 0] = 1000.0  # saturates to 448
+    layer = Fp8CutlassLinear.from_linear(lin, "linear", "k_proj")
+    got = H.to_np(layer.forward_producer(x)).reshape(-1, 256)
+    xa = OF.quantize_with_scale(H.to_np(x).reshape(-1, 512), np.float32(1.0))
+    wb, ws = OF.quantize(H.to_np(lin.weight))
+    want, _ = OF.gemm(xa, np.float32(1.0), wb, ws, H.to_np(lin.bias))
+    assert H.rel_frobenius(got, want) < 1e-2
+    assert F.e4m3_decode(xa)[0, 0] == 448.0
