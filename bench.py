@@ -245,6 +245,47 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
             "timing": "wall clock around CudaGraphCall (input copy, graph replay, output clone), synchronised"}
 
 
+def column_parallel_leg(info, device, reps=30):
+    """Auxiliary multi-GPU figure (only under a multi-rank launch): the widest projection of the
+    prefix pass (FP8, M=816, N=16384, K=2048) split along N over the ranks, each rank computing its
+    [M, N/G] slab, then one NCCL all-gather.  Reported beside the same GEMM on one GPU."""
+    from rk_b200 import replicas
+    from rk_b200.fp8_linear import Fp8CutlassLinear
+
+    m, n, k = 816, 16384, 2048
+    gen = torch.Generator().manual_seed(3)  # the same layer on every rank
+    full = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        full.weight.copy_((torch.randn(n, k, generator=gen) * 0.02).to(torch.bfloat16))
+    full = full.to(device).requires_grad_(False)
+    x = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(device)
+    make = lambda lin: Fp8CutlassLinear.from_linear(lin, "linear", "gate_up")
+    sharded = replicas.ColumnParallelLinear(full, info, make)
+    single = make(full)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        replicas.barrier(info, device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize(device)
+        return a.elapsed_time(b) / reps * 1e3
+
+    with torch.no_grad():
+        us_sharded = timed(lambda: sharded(x))
+        us_single = timed(lambda: single(x))
+        a, b = sharded(x).float(), single(x).float()
+        rel = float((a - b).norm() / b.norm())  # slabs carry their own per-tensor weight scale
+    us_sharded, us_single = replicas.max_over_ranks([us_sharded, us_single], info, device)
+    return {"op": "fp8 linear (dynamic activation scale) M=816 N=16384 K=2048", "ranks": info.world,
+            "us_column_parallel_with_all_gather": us_sharded, "us_one_gpu": us_single,
+            "rel_frobenius_vs_one_gpu": rel, "collective": "nccl all_gather_into_tensor of bf16 slabs"}
+
+
 def workload_config(copies):
     return {"workload": "cfg2_w4a16_g128", "N": N, "K": K, "group": GROUP, "M": list(M_LIST),
             "launches_per_step": len(M_LIST), "timing": "CUDA events around CUDA-graph replays",
@@ -431,6 +472,7 @@ def main():
             chunk["box_chunks_per_s"] = replicas.whole_job_rate(chunk["envs"], info, worst)
 
     elapsed_ms, e2e_ms = replicas.max_over_ranks([elapsed_ms, e2e_s * 1e3], info, device)
+    column_parallel = column_parallel_leg(info, device) if world > 1 else None
 
     step_ops = sum(algorithmic_ops(m) for m in M_LIST)
     value = replicas.whole_job_rate(step_ops * args.steps, info, elapsed_ms) / 1e12
@@ -473,6 +515,7 @@ def main():
                     "d2h_bytes_per_step": sum(m * N * 2 for m in M_LIST), "steps": e2e_steps},
             "gpu_launches": timed_launches, "roofline": roofline, "per_case": per_case,
             "cpu_baseline": cpu_baseline, "device_status": status, "action_chunk": chunk,
+            "column_parallel": column_parallel,
         }
         print(json.dumps(line))
     replicas.finish()

@@ -104,3 +104,43 @@ def whole_job_rate(units_per_rank: float, info: RankInfo, slowest_ms: float) -> 
 def finish() -> None:
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+class ColumnParallelLinear(torch.nn.Module):
+    """One exchange step across GPUs: the widest projections (gate/up, N = 16384) split along N.
+
+    Rank r builds its quantized linear from rows [r * N / G, (r + 1) * N / G) of the weight (and the
+    matching bias entries); activations are replicated; every rank computes its [M, N / G] slab and
+    an all-gather assembles [M, N] on all ranks.  `make_linear(nn.Linear) -> module` is any of the
+    quantized `from_linear` constructors (or the identity, for a bf16 slab)."""
+
+    def __init__(self, linear, info: RankInfo, make_linear=None):
+        super().__init__()
+        n = linear.out_features
+        if n % info.world:
+            raise ValueError(f"out_features {n} does not split evenly over {info.world} ranks")
+        self.info = info
+        self.out_features = n
+        self.in_features = linear.in_features
+        self.slab = n // info.world
+        rows = slice(info.rank * self.slab, (info.rank + 1) * self.slab)
+        shard = torch.nn.Linear(linear.in_features, self.slab, bias=linear.bias is not None,
+                                device=linear.weight.device, dtype=linear.weight.dtype)
+        with torch.no_grad():
+            shard.weight.copy_(linear.weight[rows])
+            if linear.bias is not None:
+                shard.bias.copy_(linear.bias[rows])
+        shard.requires_grad_(False)
+        self.local = make_linear(shard) if make_linear is not None else shard
+
+    def forward(self, x):
+        part = self.local(x)  # [..., N / G]
+        if self.info.world == 1:
+            return part
+        lead = part.shape[:-1]
+        flat = part.reshape(-1, self.slab).contiguous()
+        rows = flat.shape[0]
+        gathered = torch.empty((self.info.world * rows, self.slab), device=flat.device, dtype=flat.dtype)
+        dist.all_gather_into_tensor(gathered, flat)  # rank r's slab lands in rows [r * M, (r + 1) * M)
+        # [G, M, N / G] -> [M, G * N / G]: rank order along N is the order of the weight rows
+        return gathered.view(self.info.world, rows, self.slab).permute(1, 0, 2).reshape(*lead, self.out_features)

@@ -55,6 +55,44 @@ def test_two_gloo_ranks_agree_on_slowest_time_and_job_rate():
     assert results[0][3] == (0, 4) and results[1][3] == (4, 7)
 
 
+def _column_parallel_main(rank, world, port, results):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    sys.path.insert(0, str(root / "robotics-the-speedup-paradox_b200"))
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from rk_b200 import replicas
+
+    info = replicas.rank_info()
+    device = torch.device("cpu")
+    replicas.init(info, device)
+    torch.manual_seed(0)  # same full layer and input on every rank
+    full = torch.nn.Linear(64, 48, bias=True).requires_grad_(False)
+    x = torch.randn(3, 5, 64)
+    layer = replicas.ColumnParallelLinear(full, info)
+    out = layer(x)
+    results[rank] = (tuple(out.shape), bool(torch.equal(out, full(x))), layer.slab,
+                     bool(torch.equal(layer.local.weight, full.weight[rank * 24:(rank + 1) * 24])))
+    replicas.barrier(info, device)
+    replicas.finish()
+
+
+@pytest.mark.timeout(120)
+def test_column_parallel_slabs_gather_to_the_full_output_on_two_gloo_ranks():
+    world = 2
+    port = _free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_column_parallel_main, args=(world, port, results), nprocs=world, join=True)
+    for rank in range(world):
+        shape, same, slab, owns_rows = results[rank]
+        assert shape == (3, 5, 48) and slab == 24
+        assert owns_rows  # rank r holds weight rows [24 r, 24 r + 24)
+        assert same  # a slab of a linear is bit-identical to the same columns of the full linear
+
+
 def test_single_process_defaults_and_validation():
     import sys
     from pathlib import Path
