@@ -199,6 +199,14 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
     const int q = (block_scaled || chunks > 1) ? 32 : 16;
     int bn = static_cast<int>(round_up((m + chunks - 1) / chunks, q));
     if ((tactic & 4) && bn >= 64 && !block_scaled) bn = static_cast<int>(round_up(bn / 2, 32));
+    // A CTA's K loop runs at the pace of its issuing threads (a few hundred cycles per K block whatever
+    // the tile width), so while the machine is not full, narrower activation chunks - more CTAs, each
+    // with the same loop - beat both wide tiles and split-K (whose exchange costs more than it saves
+    // unless the tiles are very few).
+    if (!block_scaled && !(tactic & 4) && bn >= 64) {
+      const int half = static_cast<int>(round_up(bn / 2, 32));
+      if (((n + 127) / 128) * ((m + half - 1) / half) <= kNumSms) bn = half;
+    }
     pl.bn = bn;
     pl.tiles_a = static_cast<int>((n + 127) / 128);
     pl.tiles_b = static_cast<int>((m + bn - 1) / bn);
@@ -217,7 +225,7 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   // split-K across a cluster when the tiles cannot occupy the machine; >= 2 K blocks per CTA
   const long long tiles = static_cast<long long>(pl.tiles_a) * pl.tiles_b;
   pl.splits = 1;
-  if (!(tactic & 2) && tiles * 2 <= kNumSms) {
+  if (!(tactic & 2) && tiles * 4 <= kNumSms) {  // a two-way split does not pay for its exchange
     int s = static_cast<int>(kNumSms / tiles);
     if (s > 8) s = 8;
     if (s > kblocks / 2) s = kblocks / 2;
