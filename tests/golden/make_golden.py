@@ -1,9 +1,10 @@
 #!/usr/bin/env python3
 """Generate golden fixtures for the integer path by running the REFERENCE's own code on the CPU.
 
-Needs the reference checkout (default ``/root/reference``); run once in the build container:
+Needs a checkout of the reference (``--reference``, default: a directory named ``reference`` beside
+this repository); run once where that checkout exists:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference PATH]
 
 What runs:
 
@@ -42,7 +43,7 @@ def bits16(t):
 
 def main():
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=str(Path(__file__).resolve().parents[3] / "reference"))
     parser.add_argument("--output", default=str(Path(__file__).with_name("integer_golden.npz")))
     args = parser.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "src"))
