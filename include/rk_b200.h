@@ -158,7 +158,13 @@ int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* b, const fl
 int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, void* stream);
 /* out[m, n] = bf16( sum_g s[g, n] * sum_{k in g} x[m, k] * q[n, k] (+ bias[n]) ), fp32 accumulation.
  * Stands in for `linear_w4a16` (blackwell/csrc/fp4_mixed_cutlass_linear.cu:190-410) with the
- * int4 / group-128 format.  x bf16 [m, k] contiguous, out bf16 [m, n] contiguous. */
+ * int4 / group-128 format.  x bf16 [m, k] contiguous, out bf16 [m, n] contiguous.
+ *   m <= 64: every group's sum is scaled in fp32 exactly as written above.  m > 64: the scale is
+ *   folded into the expanded weight first, bf16(q * s) - one extra rounding of at most 2^-9 per
+ *   weight, the order of operations of the reference's mixed-input GEMM; still within the 1e-2
+ *   relative Frobenius bound of this operator.  tactic bit 1 (value 2) keeps the m <= 64
+ *   arithmetic for any m; bit 0 selects four instead of eight expansion warps; bit 2 halves the
+ *   activation tile.  k % 128 == 0, n % 8 == 0, out 16-byte aligned. */
 int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scales, const void* bias, void* out,
                        int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
                        void* stream);
