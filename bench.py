@@ -210,7 +210,7 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
     18-layer Gemma-architecture expert (width 1024, MLP 4096), all bf16 linears swapped for W8A8,
     the whole loop replayed from one CUDA graph, `envs` independent environments per GPU attending
     to a cached bf16 prefix KV of `prefix_len` tokens."""
-    from rk_b200.gemma_stack import ActionExpert, expert_scope
+    from rk_b200.gemma_stack import ActionExpert, expert_scope, fuse_norm_quantize, unfuse_norm_quantize
     from rk_b200.graph import CudaGraphCall
     from rk_b200.optimizations import quantize_linears
 
@@ -237,11 +237,15 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
         return float(np.median(samples)), samples
 
     bf16_ms, _ = measure(lambda n, k, v: expert(n, k, v))
-    with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True) as report:
+    with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
+                          grouped=True) as report:
+        norms = fuse_norm_quantize(expert.stack)  # adaRMSNorm + modulation + row quantizer as one kernel
         int8_ms, samples = measure(lambda n, k, v: expert(n, k, v))
+        unfuse_norm_quantize(norms)
         swapped = len(report["modules"])
+        groups = len(report["grouped"])
     return {"p50_ms": int8_ms, "bf16_p50_ms": bf16_ms, "chunks_per_s": envs / (int8_ms * 1e-3), "envs": envs,
-            "steps": expert.steps, "prefix_len": prefix_len, "linears_w8a8": swapped, "reps": reps,
+            "steps": expert.steps, "prefix_len": prefix_len, "linears_w8a8": swapped, "projection_groups": groups, "fused_norm_quantizers": len(norms), "reps": reps,
             "timing": "wall clock around CudaGraphCall (input copy, graph replay, output clone), synchronised"}
 
 

@@ -29,7 +29,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* scrat
   if (lane == 0) scratch[warp] = v;
   __syncthreads();
   float r = scratch[0];
-  for (int w = 1; w < (kRowThreads >> 5); ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+  for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
   return r;
 }
 
@@ -94,7 +94,7 @@ __device__ __forceinline__ void finish_row(float (&vals)[kMaxVec][8], int k, int
   if (threadIdx.x == 0) *scale_out = scale;
 #pragma unroll
   for (int it = 0; it < kMaxVec; ++it) {
-    const int idx = (it * kRowThreads + threadIdx.x) * 8;
+    const int idx = (it * static_cast<int>(blockDim.x) + threadIdx.x) * 8;
     if (idx < kpad) {
       int c[8];
 #pragma unroll
@@ -115,7 +115,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const
   const int qbytes = BITS == 8 ? kpad : kpad / 2;
   uint8_t* qrow = q + static_cast<long long>(row) * qbytes;
   if (row >= n_rows) {  // padding row of a weight matrix: zero codes, unit scale
-    for (int i = threadIdx.x * 4; i < qbytes; i += kRowThreads * 4) *reinterpret_cast<uint32_t*>(qrow + i) = 0;
+    for (int i = threadIdx.x * 4; i < qbytes; i += static_cast<int>(blockDim.x) * 4) *reinterpret_cast<uint32_t*>(qrow + i) = 0;
     if (threadIdx.x == 0) scales[row] = 1.0f;
     return;
   }
@@ -138,11 +138,12 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const
       }
     }
   };
-  if (k <= kCachedK) {
+  const int threads = static_cast<int>(blockDim.x);  // 64, 128 or 256: see launch_quant_rows
+  if (k <= threads * kMaxVec * 8) {
     float vals[kMaxVec][8];
 #pragma unroll
     for (int it = 0; it < kMaxVec; ++it) {
-      const int idx = (it * kRowThreads + threadIdx.x) * 8;
+      const int idx = (it * threads + threadIdx.x) * 8;
       if (idx < k) {
         values_at(idx, vals[it]);
       } else {
@@ -155,7 +156,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const
     // long rows: two passes over global memory (the second one hits L2)
     const float limit = static_cast<float>((1 << (BITS - 1)) - 1);
     float local = 0.0f;
-    for (int idx = threadIdx.x * 8; idx < k; idx += kRowThreads * 8) {
+    for (int idx = threadIdx.x * 8; idx < k; idx += threads * 8) {
       float v[8];
       values_at(idx, v);
 #pragma unroll
@@ -164,7 +165,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const
     const float maximum = block_reduce(local, true, scratch);
     const float scale = row_scale_from_max(maximum, limit, true_division != 0);
     if (threadIdx.x == 0) scales[row] = scale;
-    for (int idx = threadIdx.x * 8; idx < kpad; idx += kRowThreads * 8) {
+    for (int idx = threadIdx.x * 8; idx < kpad; idx += threads * 8) {
       float v[8];
       int c[8];
       if (idx < k) {
@@ -755,18 +756,25 @@ int launch_quant_rows(const void* x, int64_t rows, int64_t total_rows, int64_t k
   auto lb = static_cast<const __nv_bfloat16*>(lut);
   auto qb = static_cast<uint8_t*>(q);
   const dim3 grid(static_cast<unsigned>(total_rows));
+  // One CTA per row.  A thread keeps at most four 16-byte loads in flight, so with 256 threads per
+  // short row an SM holds only 8 rows x 4 KB in flight.  For very tall matrices of short rows, 64 or
+  // 128 threads per row (four vectors per thread, up to 32 resident CTAs per SM) keep more bytes
+  // in flight (measured +14% at 16384 x 2048); below a few thousand rows the extra per-thread
+  // latency costs more than it gains, so those keep the full 256 threads.
+  int threads = kRowThreads;
+  if (total_rows >= 4096) threads = kpad <= 2048 ? 64 : (kpad <= 4096 ? 128 : kRowThreads);
   switch (mode) {
     case RK_ACT_PLAIN:
-      quant_rows_kernel<BITS, RK_ACT_PLAIN><<<grid, kRowThreads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
+      quant_rows_kernel<BITS, RK_ACT_PLAIN><<<grid, threads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
                                                                           static_cast<int>(rows), qb, scales,
                                                                           true_division, vec_ok);
       break;
     case RK_ACT_LUT_MUL:
-      quant_rows_kernel<BITS, RK_ACT_LUT_MUL><<<grid, kRowThreads, 0, st>>>(
+      quant_rows_kernel<BITS, RK_ACT_LUT_MUL><<<grid, threads, 0, st>>>(
           xb, xs, ub, us, lb, static_cast<int>(k), kpad, static_cast<int>(rows), qb, scales, true_division, vec_ok);
       break;
     default:
-      quant_rows_kernel<BITS, RK_ACT_LUT><<<grid, kRowThreads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
+      quant_rows_kernel<BITS, RK_ACT_LUT><<<grid, threads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
                                                                         static_cast<int>(rows), qb, scales,
                                                                         true_division, vec_ok);
   }

@@ -42,11 +42,17 @@ def gemma_300m():
 
 
 class GemmaRMSNorm(nn.Module):
-    """fp32 statistics; plain: x * inv * (1 + w); adaptive: x * inv * (1 + scale) + shift, gate."""
+    """fp32 statistics; plain: x * inv * (1 + w); adaptive: x * inv * (1 + scale) + shift, gate.
+
+    With `fused_bits` set (see `fuse_norm_quantize`) the norm, the modulation and the row quantizer
+    of the integer linears that follow run as ONE kernel and the result is a packed-activation
+    carrier instead of a bf16 tensor (the fusion the reference leaves open for Gemma:
+    models/pi05/modeling_gemma.py:62-106 is a chain of torch ops in front of every quantizer)."""
 
     def __init__(self, dim, eps, cond_dim=None):
         super().__init__()
         self.eps = eps
+        self.fused_bits = None
         if cond_dim is None:
             self.weight = nn.Parameter(torch.zeros(dim, dtype=torch.bfloat16))
             self.dense = None
@@ -54,12 +60,29 @@ class GemmaRMSNorm(nn.Module):
             self.dense = nn.Linear(cond_dim, dim * 3, bias=True).float()  # stays fp32: never quantized
 
     def forward(self, x, cond=None):
+        if self.fused_bits is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            from .modulation import prepare_rmsnorm
+
+            x = x if x.is_contiguous() else x.contiguous()
+            if self.dense is None:
+                return prepare_rmsnorm(x, self.weight.detach(), self.fused_bits, eps=self.eps), None
+            scale, shift, gate = self.dense(cond.float()).chunk(3, dim=-1)  # [B, K] each
+            packed = prepare_rmsnorm(x, scale.to(x.dtype).contiguous(), self.fused_bits, eps=self.eps,
+                                     shift=shift.to(x.dtype).contiguous(), tokens=x.shape[1])
+            return packed, gate.unsqueeze(1).to(x.dtype)
         xf = x.float()
         normed = xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
         if self.dense is None:
             return (normed * (1.0 + self.weight.float())).to(x.dtype), None
         scale, shift, gate = self.dense(cond.float()).unsqueeze(1).chunk(3, dim=-1)
         return (normed * (1.0 + scale) + shift).to(x.dtype), gate.to(x.dtype)
+
+
+def _leading_shape(x):
+    """Shape without the feature axis, for a tensor or a packed-activation carrier."""
+    if getattr(x, "_robotics_packed_input", False):
+        return tuple(next(iter(x.packs.values())).shape)
+    return tuple(x.shape[:-1])
 
 
 def rotate_half(x):
@@ -84,7 +107,7 @@ class GemmaAttention(nn.Module):
         self.o_proj = nn.Linear(cfg.num_heads * cfg.head_dim, cfg.width, bias=False)
 
     def forward(self, x, cos, sin, past_kv=None):
-        b, t, _ = x.shape
+        b, t = _leading_shape(x)
         cfg = self.cfg
         q = self.q_proj(x).view(b, t, cfg.num_heads, cfg.head_dim).transpose(1, 2)
         k = self.k_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
@@ -225,6 +248,32 @@ class ActionExpert(nn.Module):
             time = torch.full((b,), 1.0 + step * dt, device=noise.device, dtype=torch.float32)
             x_t = x_t + dt * self.denoise_step(x_t, time, prefix_kv, prefix_len)
         return x_t
+
+
+def fuse_norm_quantize(stack, bits=8):
+    """Turns on the one-kernel norm -> quantize path for every layer norm whose consumers are all
+    integer linears of `bits` (call it inside the `quantize_linears` context; returns the norms it
+    switched so that the caller can switch them back with `unfuse_norm_quantize`)."""
+    from .integer import IntegerLinear, IntegerProjectionSlice
+
+    def integer(module):
+        return isinstance(module, (IntegerLinear, IntegerProjectionSlice)) and getattr(module, "bits", bits) == bits
+
+    switched = []
+    for layer in stack.layers:
+        attn, mlp = layer.self_attn, layer.mlp
+        if all(integer(m) for m in (attn.q_proj, attn.k_proj, attn.v_proj)):
+            layer.input_layernorm.fused_bits = bits
+            switched.append(layer.input_layernorm)
+        if all(integer(m) for m in (mlp.gate_proj, mlp.up_proj)):
+            layer.post_attention_layernorm.fused_bits = bits
+            switched.append(layer.post_attention_layernorm)
+    return switched
+
+
+def unfuse_norm_quantize(norms):
+    for norm in norms:
+        norm.fused_bits = None
 
 
 def expert_scope(name):

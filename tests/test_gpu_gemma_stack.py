@@ -68,6 +68,35 @@ def test_expert_loop_w8a8_linears_match_oracle_and_graph_replays(H):
     assert rel < 0.1
 
 
+def test_grouped_projections_and_fused_norm_quantizer_keep_the_loop_output(H):
+    """Grouping q/k/v and gate/up into one GEMM each is exact; fusing adaRMSNorm + modulation + row
+    quantizer into one kernel changes only the rounding of the normalized activations."""
+    from rk_b200.gemma_stack import expert_scope, fuse_norm_quantize, unfuse_norm_quantize
+    from rk_b200.optimizations import quantize_linears
+
+    expert = small_expert(H.DEVICE)
+    b, t = 4, 64
+    gen = torch.Generator().manual_seed(5)
+    noise = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+    pk = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    pv = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    with torch.no_grad():
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True) as _:
+            plain = expert(noise, pk, pv)
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
+                              grouped=True) as report:
+            assert len(report["grouped"]) == 2 * 2
+            grouped = expert(noise, pk, pv)
+            norms = fuse_norm_quantize(expert.stack)
+            assert len(norms) == 2 * 2
+            fused = expert(noise, pk, pv)
+            unfuse_norm_quantize(norms)
+            assert torch.equal(expert(noise, pk, pv), grouped)
+    assert torch.equal(grouped, plain)  # same integer arithmetic, one GEMM instead of two or three
+    rel = (fused - grouped).norm() / grouped.norm()
+    assert rel < 2e-2
+
+
 def test_prefix_stack_nvfp4_close_to_bf16(H):
     from rk_b200.gemma_stack import GemmaConfig, GemmaStack, prefix_scope
     from rk_b200.optimizations import quantize_linears
