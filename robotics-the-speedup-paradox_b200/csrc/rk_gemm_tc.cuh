@@ -422,12 +422,17 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         continue;
       }
 
-      // ---- small swapped tiles: stage the whole tile once, then issue all its TMA stores.  The
+      // ---- swapped tiles that fit: stage the whole tile once, then issue all its TMA stores.  The
       // chunk-by-chunk path below costs two CTA-wide rendezvous per 32 columns; for a CTA that owns
       // a single tile nothing overlaps that tail, so it is taken in one pass whenever the tile
       // ([bn][128] bf16) fits the staging area.
-      if (p.swap && p.bn * 256 <= p.out_bufs * kOutBufBytes) {
-        uint8_t* const stage = smem_gen + out_stage_off;
+      // A CTA that owns exactly one tile may also use its pipeline stages as staging memory: once the
+      // accumulator is complete every copy into them has landed and every MMA has read them.
+      const bool one_tile = num_tiles <= static_cast<int>(gridDim.x);
+      const bool fits_out = p.bn * 256 <= p.out_bufs * kOutBufBytes;
+      const bool fits_pipe = one_tile && p.bn * 256 <= p.stages * stage_bytes;
+      if (p.swap && (fits_out || fits_pipe)) {
+        uint8_t* const stage = fits_out ? smem_gen + out_stage_off : smem_gen;
         if (et == 0 && pending_store) tma_store_wait_read<0>();
         epi_bar_sync();
         __nv_bfloat16* const srow = reinterpret_cast<__nv_bfloat16*>(stage);
@@ -436,23 +441,42 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           uint32_t r0[16], r1[16];
           __syncwarp();
           tmem_ld_16(t_acc + c0, r0);
-          if (two) tmem_ld_16(t_acc + c0 + 16, r1);
+          if (two) {
+            tmem_ld_16(t_acc + c0 + 16, r1);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r1[j] = 0u;
+          }
           tc_wait_ld();
+          // the per-column scales are read into registers BEFORE the first store: a shared-memory load
+          // placed between the stores would have to wait for each of them (the two may alias)
+          float sv0[16], sv1[16];
+          if constexpr (KIND == KIND_I8) {
+            const float4* const vs4 = reinterpret_cast<const float4*>(vec_scale + c0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 a = vs4[q];
+              sv0[4 * q] = a.x, sv0[4 * q + 1] = a.y, sv0[4 * q + 2] = a.z, sv0[4 * q + 3] = a.w;
+              const float4 b = two ? vs4[4 + q] : a;
+              sv1[4 * q] = b.x, sv1[4 * q + 1] = b.y, sv1[4 * q + 2] = b.z, sv1[4 * q + 3] = b.w;
+            }
+          }
+          float v0[16], v1[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            float v;
-            if constexpr (KIND == KIND_I8) v = finish_value<KIND>(r0[j], vec_scale[c0 + j], row_scale, has_bias, row_bias);
-            else v = finish_value<KIND>(r0[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
-            srow[(c0 + j) * 128 + et] = __float2bfloat16_rn(v);
+            if constexpr (KIND == KIND_I8) {
+              v0[j] = finish_value<KIND>(r0[j], sv0[j], row_scale, has_bias, row_bias);
+              v1[j] = finish_value<KIND>(r1[j], sv1[j], row_scale, has_bias, row_bias);
+            } else {
+              v0[j] = finish_value<KIND>(r0[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
+              v1[j] = finish_value<KIND>(r1[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
+            }
           }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) srow[(c0 + j) * 128 + et] = __float2bfloat16_rn(v0[j]);
           if (two) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float v;
-              if constexpr (KIND == KIND_I8) v = finish_value<KIND>(r1[j], vec_scale[c0 + 16 + j], row_scale, has_bias, row_bias);
-              else v = finish_value<KIND>(r1[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
-              srow[(c0 + 16 + j) * 128 + et] = __float2bfloat16_rn(v);
-            }
+            for (int j = 0; j < 16; ++j) srow[(c0 + 16 + j) * 128 + et] = __float2bfloat16_rn(v1[j]);
           }
         }
         tc_fence_before();
