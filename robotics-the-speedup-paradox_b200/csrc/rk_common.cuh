@@ -172,6 +172,13 @@ __device__ __forceinline__ bool mbar_wait_group(uint32_t bar, uint32_t parity, b
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
+// Asks L2 to fetch one box of a tiled tensor; nothing is delivered to this kernel.  Used for
+// weights and scales before the dependency wait: they are parameters, not outputs of the kernel
+// that runs before this one, and L2 is the coherence point, so an early fetch can never be stale.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y) : "memory");
+}
 // 2-D tile load global -> shared; completion is signalled on `bar` as transaction bytes.
 // x (innermost coordinate) times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
@@ -210,6 +217,8 @@ template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
+// Full completion (writes performed).  A CTA about to exit only needs tma_store_wait_read<0>(): the
+// grid's completion makes its bulk stores visible to whatever runs next.
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

@@ -12,6 +12,7 @@
 #include "rk_gemm_tc2.cuh"
 #include "rk_gemm_w4.cuh"
 #include "rk_gemm_w4fold.cuh"
+#include "rk_gemm_w4fold2.cuh"
 #include "rk_host.h"
 
 namespace rk {
@@ -728,14 +729,52 @@ int launch_w4_fold(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUten
   return RK_OK;
 }
 
+// The pair kernel: a cluster of two CTAs per 256 channels x 256 activation rows.
+int launch_w4_fold2(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_s, const CUtensorMap& tm_o,
+                    const W4Params& p, int tiles_n, int tiles_m, int smem, cudaStream_t st) {
+  static bool configured_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& configured = configured_dev[dev & 63];
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(rk_gemm_w4a16_fold2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBudget + 1024);
+    if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(tiles_n, tiles_m, 1);
+  cfg.blockDim = dim3(kW4fThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_fold2_kernel, tm_w, tm_x, tm_s, tm_o, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_gemm_w4a16_fold2_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
+}
+
 // Activation batches above 64 rows: scale folded into the expanded weights, one accumulator for all of K.
 int run_w4_fold(const void* x, const void* q, const void* scales, W4Params p, int64_t m, int64_t n, int64_t k,
-                int scales_bytes, cudaStream_t st, const char* who) {
+                int scales_bytes, int tactic, cudaStream_t st, const char* who) {
   const int bn = m > 128 ? 256 : 128;
   const int tiles_n = static_cast<int>((n + 127) / 128);
   const int tiles_m = static_cast<int>((m + bn - 1) / bn);
-  const int x_bytes = bn * 128;
-  const int slots = w4f_slots(bn);
+  // tactic bit 3: 256-row tiles on CTA pairs (each CTA stages half of the activation tile), when
+  // the channel tiles pair up
+  const bool pair = bn == 256 && tiles_n % 2 == 0 && (tactic & 8);
+  const int x_bytes = pair ? kW4f2XBytes : bn * 128;
+  const int slots = pair ? kW4f2Slots : w4f_slots(bn);
   const int copies = (p.groups + 1) / 2;
   int w_stages = (kSmemBudget - scales_bytes - slots * x_bytes) / kW4PairBytes;
   if (w_stages > kW4MaxW) w_stages = kW4MaxW;
@@ -750,11 +789,13 @@ int run_w4_fold(const void* x, const void* q, const void* scales, W4Params p, in
   if (rc != RK_OK) return rc;
   rc = make_map_2d(&tm_w, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k / 2, n, k / 2, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
-  rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, m, k * 2, 64, pair ? 128 : bn,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
   // output tiles leave through TMA: 32 rows x 128 channels per store, clipped at the matrix edges
   rc = make_map_2d(&tm_o, p.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, m, n * 2, 128, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != RK_OK) return rc;
+  if (pair) return launch_w4_fold2(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
   return bn == 256 ? launch_w4_fold<256>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st)
                    : launch_w4_fold<128>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
 }
@@ -790,7 +831,7 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.out = static_cast<__nv_bfloat16*>(out);
     p.status = ws.status;
-    return run_w4_fold(x, q, scales, p, m, n, k, scales_bytes, as_stream(stream), who);
+    return run_w4_fold(x, q, scales, p, m, n, k, scales_bytes, tactic, as_stream(stream), who);
   }
   // shared memory: the activation tiles of the slot ring first, the rest goes to the raw-weight
   // ring (group pairs of 16 KB), whose depth is what keeps enough HBM requests in flight

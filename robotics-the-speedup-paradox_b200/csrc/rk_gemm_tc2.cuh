@@ -296,7 +296,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         }
       }
     }
-    if (et == 0) tma_store_wait_all();
+    if (et == 0) tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
   }
 
   // ---------------------------------------------------------------- teardown

@@ -133,6 +133,11 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_s);
     tma_prefetch_desc(&tm_o);
+    // the first raw copies and the scales start their way from DRAM to L2 while the CTA sets up
+    // and the preceding kernel drains
+    tma_prefetch_l2_2d(&tm_s, n0, 0);
+    const int ahead = min((G + 1) >> 1, kW4MaxW);
+    for (int i = 0; i < ahead; ++i) tma_prefetch_l2_2d(&tm_w, i * 128, n0);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -383,7 +388,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         const int rows = p.m - m0 < BN ? p.m - m0 : BN;
         for (int r0 = 0; r0 < rows; r0 += kBoxRows) tma_store_2d(&tm_o, smem_u32(stage + r0 * 128), n0, m0 + r0);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
       }
     }
   }

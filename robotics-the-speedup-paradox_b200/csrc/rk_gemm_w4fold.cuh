@@ -56,7 +56,7 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   __shared__ __align__(8) uint64_t bar_scales;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int epi_dead;  // set by an epilogue warp that gave up, so that all four skip the store together
+  __shared__ int epi_dead;  // set by a warp that gave up on the accumulator, so that all skip the store together
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -99,6 +99,14 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_s);
     tma_prefetch_desc(&tm_o);
+    // the first raw copies and the scales start their way from DRAM to L2 while the CTA sets up
+    // and the preceding kernel drains
+    tma_prefetch_l2_2d(&tm_s, n0, 0);
+    const int ahead = min(P, kW4MaxW);
+    for (int i = 0, kw = rot_copies; i < ahead; ++i) {
+      tma_prefetch_l2_2d(&tm_w, kw * 128, n0);
+      if (++kw == P) kw = 0;
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -201,107 +209,112 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       }
       if (alive) tc_commit(smem_u32(&bar_acc_full), on);
     }
-  } else if (warp < kEpiWarp0) {
-    // ------------------------------------------------------------ unpack: int4 -> bf16(q * scale) into TMEM
-    // row = 32 * (warp % 4) + lane (a warp writes only the TMEM lanes of its quadrant).  One loop
-    // trip covers a scale group, i.e. two steps: warps 0..3 expand the group's first step, warps
-    // 4..7 its second, each into its own slot - 64 weights per thread and one barrier probe, one
-    // arrival and one scale fetch per trip.
-    const int uw = warp - 2;
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
-    const int h = uw >> 2;
-    bool alive = mbar_poll_warp(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL);
-    const __nv_bfloat16* my_scales = reinterpret_cast<const __nv_bfloat16*>(smem_gen + scales_off) + r;
-    Ring rw{0, 0};
-    Ring rt{h % kSlots, 0};  // slot of step 2 g + h
-    int kg = rot_copies * 2;  // rotated group index along K
-    // the barrier probes for the next trip are issued right after this trip's loads and consumed one
-    // trip later (their latency hides behind the conversion); a warp stops to poll only on "not yet"
-    uint32_t ready = 0;
-    for (int g = 0; g < G && alive; ++g) {
-      const int sw = rw.stage;
-      const int t = rt.stage;
-      const int odd = g & 1;  // second group of the raw copy
-      if (!__all_sync(0xffffffffu, ready != 0)) {
-        bool ok = true;
-        if (!odd) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
-        ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
-        if (!__all_sync(0xffffffffu, ok)) break;
-      }
-      if (uw == 0 && lane == 0) RK_TRACE_REC(2, g);
-      // 128-byte swizzle of the raw copy: 16-byte chunk c of row r sits at c ^ (r & 7); the step of
-      // this warp owns chunks 4 * odd + 2 * h and the next one
-      const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
-      const int c = odd * 4 + h * 2;
-      const uint4 pk0 = *reinterpret_cast<const uint4*>(raw + ((c ^ (r & 7)) << 4));
-      const uint4 pk1 = *reinterpret_cast<const uint4*>(raw + (((c + 1) ^ (r & 7)) << 4));
-      const __nv_bfloat162 ss = __bfloat162bfloat162(my_scales[kg * 128]);
-      if (++kg == G) kg = 0;
-      const bool raw_done = odd || g == G - 1;
-      // next trip: this warp's slot two steps on, and - when it opens a new raw copy - that copy
-      Ring rt2 = rt, rw2 = rw;
-      rt2.stage += 2;
-      if (rt2.stage >= kSlots) {
-        rt2.stage -= kSlots;
-        rt2.phase ^= 1u;
-      }
-      if (raw_done) rw2.advance(p.w_stages);
-      ready = 0;
-      if (g + 1 < G) {
-        ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
-        if (odd) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);
-      }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4fStepCols;
-      const uint32_t words[8] = {pk0.x, pk0.y, pk0.z, pk0.w, pk1.x, pk1.y, pk1.z, pk1.w};
-#pragma unroll
-      for (int w = 0; w < 8; w += 2) {
-        uint4 u0 = w4_unpack8(words[w]);
-        uint4 u1 = w4_unpack8(words[w + 1]);
-        uint32_t* v0 = reinterpret_cast<uint32_t*>(&u0);
-        uint32_t* v1 = reinterpret_cast<uint32_t*>(&u1);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 a = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v0[j]), ss);
-          __nv_bfloat162 b = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v1[j]), ss);
-          v0[j] = *reinterpret_cast<uint32_t*>(&a);
-          v1[j] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        tmem_st_8(taddr + w * 4, u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(&bar_slot_full[t]));
-        if (raw_done) mbar_arrive(smem_u32(&bar_w_empty[sw]));
-      }
-      rt = rt2;
-      rw = rw2;
-      if (uw == 0 && lane == 0) RK_TRACE_REC(4, g);
-      if (lane == 0) RK_TRACE_REC(18 + uw, g);
-    }
   } else {
-    // ------------------------------------------------------------ epilogue: one pass after the last step
+    if (warp < kEpiWarp0) {
+      // ------------------------------------------------------------ unpack: int4 -> bf16(q * scale) into TMEM
+      // row = 32 * (warp % 4) + lane (a warp writes only the TMEM lanes of its quadrant).  One loop
+      // trip covers a scale group, i.e. two steps: warps 0..3 expand the group's first step, warps
+      // 4..7 its second, each into its own slot - 64 weights per thread and one barrier probe, one
+      // arrival and one scale fetch per trip.
+      const int uw = warp - 2;
+      const int quad = warp & 3;
+      const int r = quad * 32 + lane;
+      const int h = uw >> 2;
+      bool alive = mbar_poll_warp(smem_u32(&bar_scales), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL);
+      const __nv_bfloat16* my_scales = reinterpret_cast<const __nv_bfloat16*>(smem_gen + scales_off) + r;
+      Ring rw{0, 0};
+      Ring rt{h % kSlots, 0};  // slot of step 2 g + h
+      int kg = rot_copies * 2;  // rotated group index along K
+      // the barrier probes for the next trip are issued right after this trip's loads and consumed one
+      // trip later (their latency hides behind the conversion); a warp stops to poll only on "not yet"
+      uint32_t ready = 0;
+      for (int g = 0; g < G && alive; ++g) {
+        const int sw = rw.stage;
+        const int t = rt.stage;
+        const int odd = g & 1;  // second group of the raw copy
+        if (!__all_sync(0xffffffffu, ready != 0)) {
+          bool ok = true;
+          if (!odd) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
+          ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
+          if (!__all_sync(0xffffffffu, ok)) break;
+        }
+        if (uw == 0 && lane == 0) RK_TRACE_REC(2, g);
+        // 128-byte swizzle of the raw copy: 16-byte chunk c of row r sits at c ^ (r & 7); the step of
+        // this warp owns chunks 4 * odd + 2 * h and the next one
+        const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
+        const int c = odd * 4 + h * 2;
+        const uint4 pk0 = *reinterpret_cast<const uint4*>(raw + ((c ^ (r & 7)) << 4));
+        const uint4 pk1 = *reinterpret_cast<const uint4*>(raw + (((c + 1) ^ (r & 7)) << 4));
+        const __nv_bfloat162 ss = __bfloat162bfloat162(my_scales[kg * 128]);
+        if (++kg == G) kg = 0;
+        const bool raw_done = odd || g == G - 1;
+        // next trip: this warp's slot two steps on, and - when it opens a new raw copy - that copy
+        Ring rt2 = rt, rw2 = rw;
+        rt2.stage += 2;
+        if (rt2.stage >= kSlots) {
+          rt2.stage -= kSlots;
+          rt2.phase ^= 1u;
+        }
+        if (raw_done) rw2.advance(p.w_stages);
+        ready = 0;
+        if (g + 1 < G) {
+          ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
+          if (odd) ready &= mbar_test_wait(smem_u32(&bar_w_full[rw2.stage]), rw2.phase);
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + t * kW4fStepCols;
+        const uint32_t words[8] = {pk0.x, pk0.y, pk0.z, pk0.w, pk1.x, pk1.y, pk1.z, pk1.w};
+  #pragma unroll
+        for (int w = 0; w < 8; w += 2) {
+          uint4 u0 = w4_unpack8(words[w]);
+          uint4 u1 = w4_unpack8(words[w + 1]);
+          uint32_t* v0 = reinterpret_cast<uint32_t*>(&u0);
+          uint32_t* v1 = reinterpret_cast<uint32_t*>(&u1);
+  #pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 a = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v0[j]), ss);
+            __nv_bfloat162 b = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v1[j]), ss);
+            v0[j] = *reinterpret_cast<uint32_t*>(&a);
+            v1[j] = *reinterpret_cast<uint32_t*>(&b);
+          }
+          tmem_st_8(taddr + w * 4, u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bar_slot_full[t]));
+          if (raw_done) mbar_arrive(smem_u32(&bar_w_empty[sw]));
+        }
+        rt = rt2;
+        rw = rw2;
+        if (uw == 0 && lane == 0) RK_TRACE_REC(4, g);
+        if (lane == 0) RK_TRACE_REC(18 + uw, g);
+      }
+    }
+    // ------------------------------------------------------------ epilogue: all twelve unpack and epilogue warps
     // The accumulator holds one output channel per lane; the output is [m][n] with n contiguous.
     // Storing it straight from registers would be one 2-byte store per element.  Instead the tile
     // is transposed through shared memory (the activation slots are free by now) as [m][128 n]
     // rows and leaves by TMA stores of 32 rows each, which also clip the ragged edges.
+    // The unpack warps have nothing left to do once their last group is written, and a warp may read
+    // any TMEM column of its own lane quadrant: the 16-column chunks of the accumulator are dealt
+    // round-robin to the three warps of each quadrant.
     const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;  // 0, 1: unpack warps; 2: epilogue warps
     const int nl = quad * 32 + lane;
     const int n = n0 + nl;
     const bool alive = mbar_poll_warp(smem_u32(&bar_acc_full), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
     tc_fence_after();
-    if (quad == 0 && lane == 0) RK_TRACE_REC(7, 0);
-    // every epilogue warp reaches this rendezvous, whether it saw the accumulator complete or gave up
+    if (warp == kEpiWarp0 + 2 && lane == 0) RK_TRACE_REC(7, 0);
+    // every one of the twelve warps reaches this rendezvous, whether it saw the accumulator complete or gave up
     if (!alive) *reinterpret_cast<volatile int*>(&epi_dead) = 1;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, 384;" ::: "memory");
     if (*reinterpret_cast<volatile int*>(&epi_dead) == 0) {
       const float bias = (p.bias && n < p.n) ? __bfloat162float(p.bias[n]) : 0.0f;
       const int rows = p.m - m0 < BN ? p.m - m0 : BN;
       __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem_gen + x_off);
-      for (int c0 = 0; c0 < rows; c0 += 16) {  // warp-uniform bound: tcgen05.ld is a warp-wide instruction
+      for (int c0 = part * 16; c0 < rows; c0 += 48) {  // warp-uniform bound: tcgen05.ld is a warp-wide instruction
         uint32_t v[16];
         tmem_ld_16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kW4fAccCol + c0, v);
         tc_wait_ld();
@@ -309,15 +322,15 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
         for (int j = 0; j < 16; ++j) stage[(c0 + j) * 128 + nl] = __float2bfloat16_rn(__uint_as_float(v[j]) + bias);
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 384;" ::: "memory");
       if (warp == kEpiWarp0 && lane == 0) {
         for (int r0 = 0; r0 < rows; r0 += 32)
           tma_store_2d(&tm_o, smem_u32(stage + r0 * 128), n0, m0 + r0);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
       }
     }
-    if (quad == 0 && lane == 0) RK_TRACE_REC(8, 0);
+    if (warp == kEpiWarp0 + 2 && lane == 0) RK_TRACE_REC(8, 0);
   }
 
   tc_fence_before();

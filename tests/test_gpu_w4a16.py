@@ -79,19 +79,21 @@ def test_ragged_shapes_and_bias(H, shape, tactic):
     assert H.rel_frobenius(H.to_np(out), want) < TOL
 
 
-@pytest.mark.parametrize("shape", [(65, 256, 256), (128, 136, 384), (129, 1000, 128), (256, 512, 1024), (300, 256, 640),
-                                   (816, 384, 256)])
-def test_wide_batches_fold_the_scale_into_bf16_weights(H, shape):
+@pytest.mark.parametrize("shape", [(65, 256, 256), (128, 136, 384), (129, 1000, 128), (200, 512, 512), (256, 512, 1024),
+                                   (300, 256, 640), (816, 384, 256), (520, 256, 2048)])
+@pytest.mark.parametrize("tactic", [0, 8])
+def test_wide_batches_fold_the_scale_into_bf16_weights(H, shape, tactic):
     """Above 64 activation rows the group scale is folded into the expanded weights (one bf16
     rounding per weight).  The result must (a) stay inside the stated tolerance of the exact
     definition, (b) match the restatement that folds the same way to within fp32 summation order,
-    and (c) agree with the per-group-accumulator kernel (tactic bit 1) to the same tolerance."""
+    and (c) agree with the per-group-accumulator kernel (tactic bit 1) to the same tolerance.
+    With tactic bit 3, above 128 rows an even number of channel tiles runs on CTA pairs."""
     m, n, k = shape
     x = H.randn_bf16((m, k), 1.0, 17)
     w = H.randn_bf16((n, k), 0.02, 18)
     bias = H.randn_bf16((n,), 0.5, 19)
     q, s = pack(H, w.to(H.DEVICE))
-    out = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 0))
+    out = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, tactic))
     exact_kernel = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 2))
     ep, es, _ = OW.pack_weight(H.to_np(w))
     _, want = OW.gemm(H.to_np(x), ep, es, H.to_np(bias))
