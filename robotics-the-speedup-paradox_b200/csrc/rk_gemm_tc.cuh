@@ -163,6 +163,19 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int nkb = kb_end - kb_begin;
 
   pdl_launch_dependents();
+  if (threadIdx.x == 64) {  // first thing, by a thread that has no part in the set-up
+    // The weight rows of this CTA's first tile start their way from DRAM to L2 during set-up, while
+    // the preceding kernel drains (weights are parameters, never that kernel's output).
+    if (tile_first < num_tiles) {
+      const int row_a0 = (tile_first / p.tiles_b) * kTileA;
+      const int row_b0 = (tile_first % p.tiles_b) * p.bn;
+      const int ahead = min(nkb, p.stages);
+      for (int i = 0; i < ahead; ++i) {
+        if (p.swap) tma_prefetch_l2_2d(&tm_a, (kb_begin + i) * kStageKBytes, row_a0);
+        else tma_prefetch_l2_2d(&tm_b, (kb_begin + i) * kStageKBytes, row_b0);
+      }
+    }
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);

@@ -113,6 +113,13 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   const int G = p.groups;
 
   pdl_launch_dependents();
+  if (threadIdx.x == 64) {
+    // first thing, by a thread that has no part in the set-up: the first raw copies and the scales
+    // start their way from DRAM to L2 while the CTA sets up and the preceding kernel drains
+    tma_prefetch_l2_2d(&tm_s, n0, 0);
+    const int ahead = min((G + 1) >> 1, kW4MaxW);
+    for (int i = 0; i < ahead; ++i) tma_prefetch_l2_2d(&tm_w, i * 128, n0);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.w_stages; ++s) {
       mbar_init(smem_u32(&bar_w_full[s]), 1);
@@ -133,11 +140,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_s);
     tma_prefetch_desc(&tm_o);
-    // the first raw copies and the scales start their way from DRAM to L2 while the CTA sets up
-    // and the preceding kernel drains
-    tma_prefetch_l2_2d(&tm_s, n0, 0);
-    const int ahead = min((G + 1) >> 1, kW4MaxW);
-    for (int i = 0; i < ahead; ++i) tma_prefetch_l2_2d(&tm_w, i * 128, n0);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);

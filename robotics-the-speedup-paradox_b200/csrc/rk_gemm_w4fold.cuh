@@ -79,6 +79,16 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   const int rot_steps = rot_copies * 4;
 
   pdl_launch_dependents();
+  if (threadIdx.x == 64) {
+    // first thing, by a thread that has no part in the set-up: the first raw copies and the scales
+    // start their way from DRAM to L2 while the CTA sets up and the preceding kernel drains
+    tma_prefetch_l2_2d(&tm_s, n0, 0);
+    const int ahead = min(P, kW4MaxW);
+    for (int i = 0, kw = rot_copies; i < ahead; ++i) {
+      tma_prefetch_l2_2d(&tm_w, kw * 128, n0);
+      if (++kw == P) kw = 0;
+    }
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.w_stages; ++s) {
       mbar_init(smem_u32(&bar_w_full[s]), 1);
@@ -99,14 +109,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_s);
     tma_prefetch_desc(&tm_o);
-    // the first raw copies and the scales start their way from DRAM to L2 while the CTA sets up
-    // and the preceding kernel drains
-    tma_prefetch_l2_2d(&tm_s, n0, 0);
-    const int ahead = min(P, kW4MaxW);
-    for (int i = 0, kw = rot_copies; i < ahead; ++i) {
-      tma_prefetch_l2_2d(&tm_w, kw * 128, n0);
-      if (++kw == P) kw = 0;
-    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
