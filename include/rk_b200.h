@@ -165,7 +165,8 @@ int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, 
  *   relative Frobenius bound of this operator.  tactic bit 1 (value 2) keeps the m <= 64
  *   arithmetic for any m; bit 0 selects four instead of eight expansion warps; bit 2 halves the
  *   activation tile; bit 3 (value 8) runs m > 128 on CTA pairs (`cta_group::2`), each CTA staging half of the
- *   activation tile.
+ *   activation tile; for m <= 32 sixteen expansion warps are used when
+ *   k <= 4096: bit 4 (value 16) forces sixteen, bit 5 (value 32) forces eight.
  *   k % 128 == 0, n % 8 == 0, out 16-byte aligned. */
 int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scales, const void* bias, void* out,
                        int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,

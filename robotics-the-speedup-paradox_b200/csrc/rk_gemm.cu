@@ -875,6 +875,18 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
       default: break;
     }
   }
+  // Sixteen unpack warps put four K groups in flight at once, which shortens the ramp at the start of
+  // the K loop; the register file allows them for activation tiles of up to 32 rows.  Chosen by
+  // default for K <= 4096 (the ramp is a smaller share of longer loops, which run a little faster
+  // with eight); tactic bit 4 forces sixteen, bit 5 forces eight.
+  const bool sixteen = (tactic & 16) || (!(tactic & 32) && p.groups <= 32);
+  if (sixteen) {
+    switch (bn) {
+      case 16: return launch_w4<16, 16>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+      case 32: return launch_w4<32, 16>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
+      default: break;
+    }
+  }
   switch (bn) {
     case 16: return launch_w4<16, 8>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);
     case 32: return launch_w4<32, 8>(tm_w, tm_x, tm_s, tm_o, p, tiles_n, tiles_m, smem, st);

@@ -80,7 +80,8 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                      const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_o,
                      const W4Params p) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 128, "activation tile must be 16..128 rows");
-  static_assert(UW == 4 || UW == 8, "four or eight unpack warps");
+  static_assert(UW == 4 || UW == 8 || UW == 16, "four, eight or sixteen unpack warps");
+  static_assert(UW / 4 <= w4_slots(BN), "every concurrently expanded group needs its own slot");
   constexpr int kXBytes = 2 * BN * 128;  // two 64-element column blocks of BN rows
   constexpr int kSlots = w4_slots(BN);
   constexpr uint32_t kTmemCols = 512;      // [0, kSlots*64): unpacked weights; then kSlots accumulators of BN columns
@@ -123,7 +124,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.w_stages; ++s) {
       mbar_init(smem_u32(&bar_w_full[s]), 1);
-      mbar_init(smem_u32(&bar_w_empty[s]), UW);
+      mbar_init(smem_u32(&bar_w_empty[s]), UW < 8 ? UW : 8);  // the warps that read a raw pair: at most two sets of four
     }
     for (int t = 0; t < kSlots; ++t) {
       mbar_init(smem_u32(&bar_slot_full[t]), 4 + 1);   // the four unpack warps of the group + the activation copy
@@ -256,14 +257,19 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     // follows it: row = 32 * (warp % 4) + lane, and a thread expands its whole row of a group (64
     // raw bytes -> 64 columns).  UW == 4: every warp takes every group.  UW == 8: warps w and w + 4
     // share a quadrant and take the even and the odd group of each raw pair, so that one barrier
-    // probe, one arrival and one loop trip cover 128 weights per thread.
+    // probe, one arrival and one loop trip cover 128 weights per thread.  UW == 16: four warps per
+    // quadrant take groups g = 0, 1, 2, 3 (mod 4), i.e. every second raw pair each; the expansion
+    // is a chain of short dependent integer operations, and four warps per scheduler instead of
+    // two keep the pipes busy while a warp waits on its own results.
     constexpr int kStride = UW / 4;  // groups between two trips of one warp
     const int uw = warp - 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int h = uw >> 2;  // 0 for UW == 4
     const bool leader = (uw == 0 && lane == 0);
-    Ring rw{0, 0};
+    // raw pair of this warp's first group, and how many pairs it moves on per trip
+    constexpr int kPairStep = kStride >= 2 ? kStride / 2 : 1;
+    Ring rw{(h >> 1) % p.w_stages, static_cast<uint32_t>(((h >> 1) / p.w_stages) & 1)};
     Ring rt{h, 0};  // slot of group g = h
     // Barrier probes cost a shared-memory round trip each.  The probes for the next trip are issued
     // right after this trip's loads and consumed one trip later, so their latency hides behind the
@@ -273,8 +279,8 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       const int sw = rw.stage;
       const int t = rt.stage;
       const int odd = g & 1;
-      const bool new_pair = (kStride == 2) || !odd;                 // this trip reads a raw pair for the first time
-      const bool pair_done = (kStride == 2) || odd || g == G - 1;   // ... and for the last time
+      const bool new_pair = (kStride >= 2) || !odd;                 // this trip reads a raw pair for the first time
+      const bool pair_done = (kStride >= 2) || odd || g == G - 1;   // ... and for the last time
       if (!__all_sync(0xffffffffu, ready != 0)) {
         bool ok = true;
         if (new_pair) ok = mbar_poll_lane(smem_u32(&bar_w_full[sw]), rw.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW);
@@ -295,7 +301,13 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         rt2.stage -= kSlots;
         rt2.phase ^= 1u;
       }
-      if (pair_done) rw2.advance(p.w_stages);
+      if (pair_done) {
+        rw2.stage += kPairStep;
+        while (rw2.stage >= p.w_stages) {
+          rw2.stage -= p.w_stages;
+          rw2.phase ^= 1u;
+        }
+      }
       ready = 0;
       if (g + kStride < G) {
         ready = mbar_test_wait(smem_u32(&bar_slot_empty[rt2.stage]), rt2.phase ^ 1);
@@ -333,7 +345,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       rt = rt2;
       rw = rw2;
       if (leader) RK_TRACE_REC(4, g);
-      if (lane == 0) RK_TRACE_REC(18 + uw, g);
+      if (lane == 0 && uw < 8) RK_TRACE_REC(18 + uw, g);
     }
   } else if (warp < kMmaWarpB) {
     // ------------------------------------------------------------ epilogue: scale each group, accumulate, store

@@ -66,7 +66,7 @@ def test_cfg2_gemm_within_tolerance(H, m):
 
 
 @pytest.mark.parametrize("shape", [(8, 128, 128), (16, 256, 512), (100, 1000, 384), (130, 136, 256), (300, 256, 128)])
-@pytest.mark.parametrize("tactic", [0, 4])
+@pytest.mark.parametrize("tactic", [0, 4, 16, 32])
 def test_ragged_shapes_and_bias(H, shape, tactic):
     m, n, k = shape
     x = H.randn_bf16((m, k), 1.0, 7)
@@ -105,6 +105,25 @@ def test_wide_batches_fold_the_scale_into_bf16_weights(H, shape, tactic):
     assert np.abs(out - folded).max() <= 2.0 ** -8 * np.abs(folded).max() + 1e-6
     assert (out != folded_bf16).mean() < 0.02
     assert H.rel_frobenius(out, folded) < H.rel_frobenius(out, want) + 1e-4
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 4096), (8, 384, 640), (32, 1000, 2048), (20, 128, 1152)])
+def test_sixteen_expansion_warps_change_nothing(H, shape):
+    """Sixteen expansion warps (four K groups in flight; tactic bit 4 forces them, bit 5 forces eight).  Every
+    group still has its own accumulator and the groups are summed in order, so the output must be
+    bit-identical to the default kernel's, for long K (ring wrap-around) and odd group counts."""
+    m, n, k = shape
+    x = H.randn_bf16((m, k), 1.0, 27)
+    w = H.randn_bf16((n, k), 0.02, 28)
+    bias = H.randn_bf16((n,), 0.5, 29)
+    q, s = pack(H, w.to(H.DEVICE))
+    base = run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 32)
+    wide = run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 16)
+    assert torch.equal(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 0), base)
+    assert torch.equal(base, wide)
+    ep, es, _ = OW.pack_weight(H.to_np(w))
+    _, want = OW.gemm(H.to_np(x), ep, es, H.to_np(bias))
+    assert H.rel_frobenius(H.to_np(wide), want) < TOL
 
 
 def test_linearity_at_full_size(H):
