@@ -73,6 +73,54 @@ __device__ __forceinline__ void store_codes8(uint8_t* qrow, int idx, const int (
   }
 }
 
+// Eight codes at once, bit-identical to quant_code() on every element but without a division, a
+// round instruction and a float -> int conversion per element (those made the row quantizers
+// instruction-bound: ~31 instructions per element at 17% of DRAM bandwidth).
+//   u = v * rcp, rcp = fl(1 / scale), lies within 3 * 2^-24 * |q| <= 2.3e-5 of the correctly rounded
+//   quotient wherever the result is not clamped anyway (|q| <= 127.5); t = u + 1.5 * 2^23 rounds u to
+//   the nearest integer (ties to even) and leaves that integer in the low mantissa bits, so the low
+//   byte of the clamped t IS the two's-complement code.  Only if some u lies within 4e-5 of a tie (or
+//   is not a number) could the exact quotient round the other way; then all eight take the exact
+//   sequence (about one group of eight in a thousand).
+// Elements at and beyond `k` must already be zero in v.
+template <int BITS>
+__device__ __forceinline__ void quantize_store8(uint8_t* qrow, int idx, const float (&v)[8], float scale, float rcp,
+                                                float limit) {
+  const float magic = 12582912.0f;  // 1.5 * 2^23, bits 0x4B400000
+  float t[8];
+  bool near_tie = false;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float u = __fmul_rn(v[i], rcp);
+    t[i] = __fadd_rn(u, magic);
+    const float e = __fsub_rn(u, __fsub_rn(t[i], magic));  // exact: distance of u from the integer it rounded to
+    near_tie |= !(fabsf(e) < 0.49996f);
+  }
+  if (near_tie) {
+    int c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = quant_code(v[i], scale, limit);
+    store_codes8<BITS>(qrow, idx, c);
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t[i] = fminf(fmaxf(t[i], magic - limit), magic + limit);
+  if constexpr (BITS == 8) {
+    uint32_t b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] = __float_as_uint(t[i]);
+    uint2 o;
+    o.x = __byte_perm(__byte_perm(b[0], b[1], 0x0040u), __byte_perm(b[2], b[3], 0x0040u), 0x5410u);
+    o.y = __byte_perm(__byte_perm(b[4], b[5], 0x0040u), __byte_perm(b[6], b[7], 0x0040u), 0x5410u);
+    *reinterpret_cast<uint2*>(qrow + idx) = o;
+  } else {
+    int c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = __float_as_int(t[i]) - 0x4B400000;
+    store_codes8<BITS>(qrow, idx, c);
+  }
+}
+
 __device__ __forceinline__ float row_scale_from_max(float maximum, float limit, bool true_division) {
   if (!(maximum > 0.0f)) return 1.0f;
   // activations: max * fl32(1/limit); weights: max / limit
@@ -92,14 +140,17 @@ __device__ __forceinline__ void finish_row(float (&vals)[kMaxVec][8], int k, int
   const float maximum = block_reduce(local, true, scratch);
   const float scale = row_scale_from_max(maximum, limit, true_division);
   if (threadIdx.x == 0) *scale_out = scale;
+  const float rcp = __frcp_rn(scale);
 #pragma unroll
   for (int it = 0; it < kMaxVec; ++it) {
     const int idx = (it * static_cast<int>(blockDim.x) + threadIdx.x) * 8;
     if (idx < kpad) {
-      int c[8];
+      if (idx + 8 > k) {  // ragged end of the row: codes beyond k are zero
 #pragma unroll
-      for (int i = 0; i < 8; ++i) c[i] = (idx + i < k) ? quant_code(vals[it][i], scale, limit) : 0;
-      store_codes8<BITS>(qrow, idx, c);
+        for (int i = 0; i < 8; ++i)
+          if (idx + i >= k) vals[it][i] = 0.0f;
+      }
+      quantize_store8<BITS>(qrow, idx, vals[it], scale, rcp, limit);
     }
   }
 }
@@ -165,15 +216,16 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const
     const float maximum = block_reduce(local, true, scratch);
     const float scale = row_scale_from_max(maximum, limit, true_division != 0);
     if (threadIdx.x == 0) scales[row] = scale;
+    const float rcp = __frcp_rn(scale);
     for (int idx = threadIdx.x * 8; idx < kpad; idx += threads * 8) {
       float v[8];
-      int c[8];
       if (idx < k) {
         values_at(idx, v);
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) c[i] = (idx + i < k) ? quant_code(v[i], scale, limit) : 0;
-      store_codes8<BITS>(qrow, idx, c);
+      for (int i = 0; i < 8; ++i)
+        if (idx + i >= k) v[i] = 0.0f;
+      quantize_store8<BITS>(qrow, idx, v, scale, rcp, limit);
     }
   }
 }

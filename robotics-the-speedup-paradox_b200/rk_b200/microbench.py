@@ -2,6 +2,7 @@
 """Per-shape timing of the quantized GEMM and quantizer entry points, through the C ABI.
 
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py [w4a16] [w8a8] [fp8] [mxfp8] [nvfp4] [quant]
+    python robotics-the-speedup-paradox_b200/rk_b200/microbench.py w8a8:400x8192x1024 quant:16384x2048   # explicit shapes
     python robotics-the-speedup-paradox_b200/build.py --trace && \
         RK_B200_SO=robotics-the-speedup-paradox_b200/rk_b200/librk_b200_trace.so \
         python robotics-the-speedup-paradox_b200/rk_b200/microbench.py trace
@@ -185,6 +186,19 @@ def role_trace(bench, m, n=16384, k=2048):
 def main(argv):
     which = argv or ["w4a16", "w8a8", "fp8", "mxfp8", "nvfp4", "quant"]
     b = Bench()
+    # one explicit shape: "w8a8:400x8192x1024", "w4a16:8x16384x2048", "fp8:...", "quant:16384x2048"
+    for spec in [a for a in which if ":" in a]:
+        kind, dims = spec.split(":")
+        dims = [int(d) for d in dims.split("x")]
+        if kind == "quant":
+            b.quant_rows(*dims)
+        elif kind == "w4a16":
+            b.w4a16(*dims)
+        elif kind == "w8a8":
+            b.w8a8(*dims)
+        else:
+            b.float8(kind, *dims)
+    which = [a for a in which if ":" not in a]
     if "trace" in which:
         for m in (8, 50, 256):
             role_trace(b, m)
