@@ -807,6 +807,7 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   if (!x || !q || !scales || !out) return fail(RK_EINVAL, "%s: null pointer", who);
   if (m < 1 || n < 1 || k < 128 || k % 128 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 128", who);
   if (n % 8 != 0) return fail(RK_EINVAL, "%s: n must be a multiple of 8", who);
+  if (tactic < 0 || tactic > 63) return fail(RK_EINVAL, "%s: tactic must be 0..63", who);
   if (m > (1 << 24) || n > (1 << 24) || k > (1 << 24)) return fail(RK_EUNSUPPORTED, "%s: dimension too large", who);
   Workspace ws;
   int rc = carve_workspace(workspace, workspace_bytes, &ws, who);

@@ -808,13 +808,14 @@ int launch_quant_rows(const void* x, int64_t rows, int64_t total_rows, int64_t k
   auto lb = static_cast<const __nv_bfloat16*>(lut);
   auto qb = static_cast<uint8_t*>(q);
   const dim3 grid(static_cast<unsigned>(total_rows));
-  // One CTA per row.  A thread keeps at most four 16-byte loads in flight, so with 256 threads per
-  // short row an SM holds only 8 rows x 4 KB in flight.  For very tall matrices of short rows, 64 or
-  // 128 threads per row (four vectors per thread, up to 32 resident CTAs per SM) keep more bytes
-  // in flight (measured +14% at 16384 x 2048); below a few thousand rows the extra per-thread
-  // latency costs more than it gains, so those keep the full 256 threads.
+  // One CTA per row.  With 256 threads a short row is one 16-byte load per thread and eight warps
+  // to reduce over; once there are enough rows to give every SM several CTAs, 64 or 128 threads per
+  // row (four vectors per thread, two or four warps to reduce, up to 32 resident CTAs per SM) are
+  // faster (1764 x 2048: 8.3 -> 6.8 us; 16384 x 2048: 64.5 -> 37.8 us).  With few rows the machine
+  // is not full and the per-thread latency decides, so those keep the full 256 threads
+  // (400 x 4096: 4.5 us with 256 threads, 9.5 us with 64).
   int threads = kRowThreads;
-  if (total_rows >= 4096) threads = kpad <= 2048 ? 64 : (kpad <= 4096 ? 128 : kRowThreads);
+  if (total_rows >= 1024) threads = kpad <= 2048 ? 64 : (kpad <= 4096 ? 128 : kRowThreads);
   switch (mode) {
     case RK_ACT_PLAIN:
       quant_rows_kernel<BITS, RK_ACT_PLAIN><<<grid, threads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,

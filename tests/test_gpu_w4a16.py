@@ -154,3 +154,20 @@ def test_module_surface(H):
         layer(torch.zeros(2, 128, device="cuda", dtype=torch.bfloat16))
     with pytest.raises(ValueError):
         W4A16Linear.from_linear(torch.nn.Linear(256, 136, dtype=torch.bfloat16))
+
+
+def test_invalid_arguments_are_refused_before_any_launch(H):
+    lib = _lib.load()
+    x = torch.zeros(8, 256, dtype=torch.bfloat16, device=H.DEVICE)
+    q = torch.zeros(128, 128, dtype=torch.uint8, device=H.DEVICE)
+    s = torch.ones(2, 128, dtype=torch.bfloat16, device=H.DEVICE)
+    out = torch.full((8, 128), 3.0, dtype=torch.bfloat16, device=H.DEVICE)
+    ws = _lib.gemm_workspace(_lib.OP_W4A16, H.DEVICE, 8, 128, 256)
+    args = lambda m, n, k, tactic: (_lib.ptr(x), _lib.ptr(q), _lib.ptr(s), None, _lib.ptr(out), m, n, k, tactic,
+                                    _lib.ptr(ws), ws.numel(), H.stream())
+    assert lib.rk_gemm_w4a16_g128(*args(8, 128, 200, 0)) == _lib.RK_EINVAL  # k not a multiple of 128
+    assert lib.rk_gemm_w4a16_g128(*args(8, 100, 256, 0)) == _lib.RK_EINVAL  # n not a multiple of 8
+    assert lib.rk_gemm_w4a16_g128(*args(8, 128, 256, 64)) == _lib.RK_EINVAL  # unknown tactic bit
+    assert lib.rk_gemm_w4a16_g128(*args(8, 128, 256, -1)) == _lib.RK_EINVAL
+    torch.cuda.synchronize()
+    assert (out == 3.0).all()
