@@ -53,28 +53,38 @@ class GemmaRMSNorm(nn.Module):
         super().__init__()
         self.eps = eps
         self.fused_bits = None
+        self.projection_cache = None  # a ConstantProjectionCache over `modulation` (see ActionExpert)
         if cond_dim is None:
             self.weight = nn.Parameter(torch.zeros(dim, dtype=torch.bfloat16))
             self.dense = None
         else:
             self.dense = nn.Linear(cond_dim, dim * 3, bias=True).float()  # stays fp32: never quantized
 
+    def modulation(self, cond):
+        """dense(cond) split into everything a forward needs: fp32 (scale, shift) [B, 1, K] for the
+        unfused arithmetic, the bf16 gate [B, 1, K], and contiguous bf16 (scale, shift) [B, K] for
+        the fused norm -> quantize kernel.  A function of `cond` alone, hence cacheable."""
+        scale, shift, gate = self.dense(cond.float()).chunk(3, dim=-1)
+        return (scale.unsqueeze(1), shift.unsqueeze(1), gate.unsqueeze(1).to(torch.bfloat16),
+                scale.to(torch.bfloat16).contiguous(), shift.to(torch.bfloat16).contiguous())
+
     def forward(self, x, cond=None):
-        if self.fused_bits is not None and x.is_cuda and x.dtype == torch.bfloat16:
+        fused = self.fused_bits is not None and x.is_cuda and x.dtype == torch.bfloat16
+        if self.dense is not None:
+            project = self.projection_cache if self.projection_cache is not None else self.modulation
+            scale, shift, gate, scale_bf16, shift_bf16 = project(cond)
+        if fused:
             from .modulation import prepare_rmsnorm
 
             x = x if x.is_contiguous() else x.contiguous()
             if self.dense is None:
                 return prepare_rmsnorm(x, self.weight.detach(), self.fused_bits, eps=self.eps), None
-            scale, shift, gate = self.dense(cond.float()).chunk(3, dim=-1)  # [B, K] each
-            packed = prepare_rmsnorm(x, scale.to(x.dtype).contiguous(), self.fused_bits, eps=self.eps,
-                                     shift=shift.to(x.dtype).contiguous(), tokens=x.shape[1])
-            return packed, gate.unsqueeze(1).to(x.dtype)
+            packed = prepare_rmsnorm(x, scale_bf16, self.fused_bits, eps=self.eps, shift=shift_bf16, tokens=x.shape[1])
+            return packed, gate
         xf = x.float()
         normed = xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
         if self.dense is None:
             return (normed * (1.0 + self.weight.float())).to(x.dtype), None
-        scale, shift, gate = self.dense(cond.float()).unsqueeze(1).chunk(3, dim=-1)
         return (normed * (1.0 + scale) + shift).to(x.dtype), gate.to(x.dtype)
 
 
@@ -114,7 +124,14 @@ class GemmaAttention(nn.Module):
         v = self.v_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
         q = q * cos[:, None] + rotate_half(q) * sin[:, None]
         k = k * cos[:, None] + rotate_half(k) * sin[:, None]
-        if past_kv is not None:
+        if past_kv is not None and len(past_kv) == 3:
+            # preallocated [B, kv_heads, prefix + t, head_dim] buffers whose first `prefix` rows already
+            # hold the cached keys / values: only the t new rows are written (ActionExpert.forward)
+            k_all, v_all, prefix = past_kv
+            k_all[:, :, prefix:prefix + t] = k
+            v_all[:, :, prefix:prefix + t] = v
+            k, v = k_all, v_all
+        elif past_kv is not None:
             k = torch.cat([past_kv[0], k], dim=2)
             v = torch.cat([past_kv[1], v], dim=2)
         present = (k, v)
@@ -219,6 +236,7 @@ class ActionExpert(nn.Module):
         self.time_mlp_in = nn.Linear(width, width).float()
         self.time_mlp_out = nn.Linear(width, width).float()
         self.action_out_proj = nn.Linear(width, action_dim).float()
+        self._conditions = None  # (steps, step, batch, device) -> condition, see enable_condition_caches
 
     @torch.no_grad()
     def init_random(self, seed=0, std=0.02):
@@ -228,10 +246,48 @@ class ActionExpert(nn.Module):
                 param.copy_((torch.randn(param.shape, generator=gen) * std).to(param.dtype))
         return self
 
-    def denoise_step(self, x_t, time, prefix_kv, prefix_len):
-        b = x_t.shape[0]
-        cond = F.silu(self.time_mlp_out(F.silu(self.time_mlp_in(
+    def adaptive_norms(self):
+        return [m for m in self.stack.modules() if isinstance(m, GemmaRMSNorm) and m.dense is not None]
+
+    def enable_condition_caches(self, projections=True):
+        """The reference's `condition_cache` / `condition_projection_cache` switches
+        (optimizations/pi05.py:273-333): the timestep condition of step i of an n-step schedule
+        depends on nothing but (n, i), so it is computed once per (schedule, step, batch, device)
+        and - with `projections` - every adaptive norm's dense(condition) is computed once per such
+        condition.  Later calls, CUDA-graph captures included, read them as constants."""
+        from .optimizations.constant_projection import ConstantProjectionCache
+
+        self._conditions = {}
+        eligible = lambda cond: any(cond is kept for kept in self._conditions.values())
+        for norm in self.adaptive_norms():
+            norm.projection_cache = ConstantProjectionCache(norm.modulation, eligible) if projections else None
+        return self
+
+    def disable_condition_caches(self):
+        self._conditions = None
+        for norm in self.adaptive_norms():
+            norm.projection_cache = None
+
+    def retained_tensors(self):
+        kept = list((self._conditions or {}).values())
+        for norm in self.adaptive_norms():
+            if norm.projection_cache is not None:
+                kept.extend(norm.projection_cache.retained_tensors())
+        return tuple(kept)
+
+    def condition(self, time, step=None):
+        compute = lambda: F.silu(self.time_mlp_out(F.silu(self.time_mlp_in(
             sinusoidal_time_embedding(time, self.cfg.width).float()))))
+        if self._conditions is None or step is None:
+            return compute()
+        key = (self.steps, step, time.shape[0], time.device)
+        if key not in self._conditions:
+            self._conditions[key] = compute()
+        return self._conditions[key]
+
+    def denoise_step(self, x_t, time, prefix_kv, prefix_len, step=None):
+        b = x_t.shape[0]
+        cond = self.condition(time, step)
         tokens = self.action_in_proj(x_t).to(torch.bfloat16)
         positions = prefix_len + torch.arange(self.chunk, device=x_t.device)[None, :].expand(b, -1)
         hidden, _ = self.stack(tokens, positions, past=prefix_kv, cond=cond)
@@ -240,13 +296,21 @@ class ActionExpert(nn.Module):
     def forward(self, noise, prefix_k, prefix_v):
         """noise [B, chunk, action_dim] fp32; prefix_k / prefix_v [depth, B, kv_heads, T, head_dim] bf16."""
         b = noise.shape[0]
-        prefix_len = prefix_k.shape[3]
-        prefix_kv = [(prefix_k[i], prefix_v[i]) for i in range(self.cfg.depth)]
+        depth, _, kv_heads, prefix_len, head_dim = prefix_k.shape
+        # one key and one value buffer per layer for the whole chunk: the prefix rows are copied in
+        # once, every denoise step then overwrites only its `chunk` suffix rows (instead of
+        # concatenating prefix and suffix anew in every layer of every step)
+        shape = (depth, b, kv_heads, prefix_len + self.chunk, head_dim)
+        k_all = torch.empty(shape, dtype=prefix_k.dtype, device=prefix_k.device)
+        v_all = torch.empty(shape, dtype=prefix_v.dtype, device=prefix_v.device)
+        k_all[:, :, :, :prefix_len] = prefix_k
+        v_all[:, :, :, :prefix_len] = prefix_v
+        prefix_kv = [(k_all[i], v_all[i], prefix_len) for i in range(depth)]
         dt = -1.0 / self.steps
         x_t = noise
         for step in range(self.steps):
             time = torch.full((b,), 1.0 + step * dt, device=noise.device, dtype=torch.float32)
-            x_t = x_t + dt * self.denoise_step(x_t, time, prefix_kv, prefix_len)
+            x_t = x_t + dt * self.denoise_step(x_t, time, prefix_kv, prefix_len, step)
         return x_t
 
 

@@ -5,6 +5,7 @@ progressive.py, entry.py); the other hot spots that package tunes (attention, VA
 are accepted as switch names so existing configurations still parse, and are not acted on here.
 """
 
+from .constant_projection import ConstantProjectionCache  # noqa: F401
 from .config import OptimizationConfig, compare_samples, measurement_configurations  # noqa: F401
 from .patching import Patches  # noqa: F401
 from .progressive import cosmos_candidate_sites, cosmos_precision_map, cosmos_tier_variants  # noqa: F401

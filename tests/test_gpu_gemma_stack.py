@@ -97,6 +97,36 @@ def test_grouped_projections_and_fused_norm_quantizer_keep_the_loop_output(H):
     assert rel < 2e-2
 
 
+def test_condition_caches_and_chunk_buffers_under_graph_capture(H):
+    """With the timestep conditions and their projections cached (filled by the eager warm-up
+    calls) the captured loop reads them as constants: same output as the uncached eager loop, for
+    the inputs of the capture and for new ones."""
+    from rk_b200.gemma_stack import expert_scope, fuse_norm_quantize
+    from rk_b200.graph import CudaGraphCall
+    from rk_b200.optimizations import quantize_linears
+
+    expert = small_expert(H.DEVICE)
+    b, t = 4, 64
+    gen = torch.Generator().manual_seed(11)
+    noise = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+    noise2 = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+    pk = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    pv = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    with torch.no_grad():
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
+                              grouped=True) as _:
+            fuse_norm_quantize(expert.stack)
+            want, want2 = expert(noise, pk, pv), expert(noise2, pk, pv)
+            expert.enable_condition_caches()
+            call = CudaGraphCall(lambda n_, k_, v_: expert(n_, k_, v_), retained_tensors=expert.retained_tensors)
+            assert torch.equal(call(noise, pk, pv), want)
+            assert torch.equal(call(noise2, pk, pv), want2)
+            assert call.captures == 1 and len(expert._conditions) == 3
+            assert all(len(n.projection_cache) == 3 for n in expert.adaptive_norms())
+            assert len(call._constants) == len(expert.retained_tensors()) > 0
+            expert.disable_condition_caches()
+
+
 def test_prefix_stack_nvfp4_close_to_bf16(H):
     from rk_b200.gemma_stack import GemmaConfig, GemmaStack, prefix_scope
     from rk_b200.optimizations import quantize_linears

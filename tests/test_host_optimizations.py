@@ -218,3 +218,41 @@ def test_progressive_sweep_variants_from_one_template():
     assert all(c.precision == "int8" and c.tactic == 1 for _, c in rows[2:])
     with pytest.raises(ValueError):
         cosmos_tier_variants(template, [1, 1])
+
+
+def test_condition_caches_leave_the_flow_loop_output_unchanged():
+    """`condition_cache` / `condition_projection_cache` of the reference's pi0.5 optimizations
+    (optimizations/pi05.py:273-333): the per-step timestep condition and every adaptive norm's
+    dense(condition) are constants of the schedule; caching them changes no bit of the result,
+    fills once, and exposes the tensors a CUDA-graph owner has to keep alive."""
+    import torch
+
+    from rk_b200.gemma_stack import ActionExpert, GemmaConfig
+    from rk_b200.optimizations import ConstantProjectionCache
+
+    cfg = GemmaConfig(width=64, mlp_dim=128, depth=2, num_heads=2, num_kv_heads=1, head_dim=32, adarms_cond_dim=64)
+    expert = ActionExpert(cfg, chunk=6, action_dim=8, steps=3).init_random(1).eval()
+    gen = torch.Generator().manual_seed(0)
+    noise = torch.randn(2, 6, 8, generator=gen)
+    pk = torch.randn(2, 2, 1, 10, 32, generator=gen).to(torch.bfloat16)
+    pv = torch.randn(2, 2, 1, 10, 32, generator=gen).to(torch.bfloat16)
+    with torch.no_grad():
+        plain = expert(noise, pk, pv)
+        expert.enable_condition_caches()
+        first = expert(noise, pk, pv)
+        norms = expert.adaptive_norms()
+        assert len(norms) == 2 * 2 + 1  # two per layer and the final norm
+        assert len(expert._conditions) == 3 and all(len(n.projection_cache) == 3 for n in norms)
+        kept = expert.retained_tensors()
+        assert len(kept) == 3 + len(norms) * 3 * 5
+        second = expert(noise * 2, pk, pv)  # other inputs, same schedule: nothing is added
+        assert len(expert._conditions) == 3 and all(len(n.projection_cache) == 3 for n in norms)
+        assert torch.equal(first, plain)
+        expert.disable_condition_caches()
+        assert torch.equal(expert(noise * 2, pk, pv), second)
+        assert all(n.projection_cache is None for n in norms) and expert.retained_tensors() == ()
+    # an input that was not registered is never cached
+    calls = []
+    cache = ConstantProjectionCache(lambda v: (calls.append(1), v + 1)[1], lambda v: False)
+    t = torch.zeros(2)
+    assert torch.equal(cache(t), t + 1) and torch.equal(cache(t), t + 1) and len(calls) == 2 and len(cache) == 0
