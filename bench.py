@@ -210,7 +210,8 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
     18-layer Gemma-architecture expert (width 1024, MLP 4096), all bf16 linears swapped for W8A8,
     the whole loop replayed from one CUDA graph, `envs` independent environments per GPU attending
     to a cached bf16 prefix KV of `prefix_len` tokens."""
-    from rk_b200.gemma_stack import ActionExpert, expert_scope, fuse_norm_quantize, unfuse_norm_quantize
+    from rk_b200.gemma_stack import (ActionExpert, GemmaAttention, expert_scope, fuse_norm_quantize,
+                                     unfuse_norm_quantize)
     from rk_b200.graph import CudaGraphCall
     from rk_b200.optimizations import quantize_linears
 
@@ -219,6 +220,7 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
     # timestep conditions of the fixed 10-step schedule and the adaptive norms' dense(condition)
     # are computed during the eager warm-up calls and are constants of the captured graph
     expert.enable_condition_caches()
+    GemmaAttention.fused_rope = True  # rotary embedding + cache append as one kernel, in both arms
     cfg = expert.cfg
     gen = torch.Generator().manual_seed(7)
     noise = torch.randn(envs, expert.chunk, expert.action_dim, generator=gen).to(device)
@@ -248,9 +250,10 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
         unfuse_norm_quantize(norms)
         swapped = len(report["modules"])
         groups = len(report["grouped"])
+    GemmaAttention.fused_rope = False
     return {"p50_ms": int8_ms, "bf16_p50_ms": bf16_ms, "chunks_per_s": envs / (int8_ms * 1e-3), "envs": envs,
             "steps": expert.steps, "prefix_len": prefix_len, "linears_w8a8": swapped, "projection_groups": groups, "fused_norm_quantizers": len(norms),
-            "cached_conditions": len(expert._conditions),
+            "fused_rope_cache_update": True, "cached_conditions": len(expert._conditions),
             "cached_condition_projections": sum(len(n.projection_cache) for n in expert.adaptive_norms()), "reps": reps,
             "timing": "wall clock around CudaGraphCall (input copy, graph replay, output clone), synchronised"}
 

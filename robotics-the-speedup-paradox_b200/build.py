@@ -26,7 +26,7 @@ CSRC = ROOT / "csrc"
 INCLUDE = ROOT.parent / "include"
 DEFAULT_OUTPUT = ROOT / "rk_b200" / "librk_b200.so"
 BACKENDS = ("all", "integer", "w4a16", "fp8", "mxfp8", "fp4")
-SOURCES = ("rk_api.cu", "rk_quant.cu", "rk_gemm.cu")
+SOURCES = ("rk_api.cu", "rk_quant.cu", "rk_rope.cu", "rk_gemm.cu")
 
 
 def _arch_flags(arch):

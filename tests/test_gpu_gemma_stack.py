@@ -127,6 +127,83 @@ def test_condition_caches_and_chunk_buffers_under_graph_capture(H):
             expert.disable_condition_caches()
 
 
+@pytest.mark.parametrize("shape", [(2, 5, 3, 1, 32, 7), (8, 50, 8, 1, 256, 816), (1, 1, 2, 2, 128, 0), (3, 17, 4, 2, 512, 40)])
+def test_rope_cache_update_kernel_matches_oracle_and_tensor_ops(H, shape):
+    """One launch for rotary embedding + cache append: rotated queries and keys bit-identical to the
+    oracle (and so to the bf16 tensor-op chain), values copied, every other cache row untouched;
+    q, k, v given as slices of one projection output."""
+    from oracle import rope as OR
+    from rk_b200.gemma_stack import rope_cache_update, rope_tables
+
+    b, t, heads, kv, d, prefix = shape
+    gen = torch.Generator().manual_seed(13)
+    width = (heads + 2 * kv) * d
+    qkv = (torch.randn(b, t, width, generator=gen) * 2).to(torch.bfloat16).to(H.DEVICE)
+    q, k, v = qkv[..., :heads * d], qkv[..., heads * d:(heads + kv) * d], qkv[..., (heads + kv) * d:]
+    positions = prefix + torch.arange(t, device=H.DEVICE)[None].expand(b, -1)
+    cos, sin = rope_tables(positions, d, 10000.0, torch.bfloat16)
+    rows = prefix + t + 3
+    k_all = torch.full((b, kv, rows, d), 5.0, dtype=torch.bfloat16, device=H.DEVICE)
+    v_all = torch.full((b, kv, rows, d), 6.0, dtype=torch.bfloat16, device=H.DEVICE)
+    q_out = rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv, d)
+    kc, vc = np.full((b, kv, rows, d), 5.0, np.float32), np.full((b, kv, rows, d), 6.0, np.float32)
+    want_q = OR.cache_update(H.to_np(q).reshape(b, t, heads, d), H.to_np(k).reshape(b, t, kv, d),
+                             H.to_np(v).reshape(b, t, kv, d), H.to_np(cos), H.to_np(sin), kc, vc, prefix)
+    assert np.array_equal(H.bits(q_out), F.bf16_bits(want_q))
+    assert np.array_equal(H.bits(k_all), F.bf16_bits(kc))
+    assert np.array_equal(H.bits(v_all), F.bf16_bits(vc))
+    # and the tensor-op chain the harness runs without the kernel
+    half = d // 2
+    rot = lambda x: torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    q4 = q.reshape(b, t, heads, d).transpose(1, 2)
+    assert torch.equal(q_out, q4 * cos[:, None] + rot(q4) * sin[:, None])
+
+
+def test_rope_cache_update_refuses_bad_arguments(H):
+    from rk_b200 import _lib
+
+    lib = _lib.load()
+    t = torch.zeros(4096, dtype=torch.bfloat16, device=H.DEVICE)
+    p = _lib.ptr(t)
+    call = lambda **kw: lib.rk_rope_cache_update(p, kw.get("qs", 64), p, 32, p, 32, p, p, 1, 2, 2, 1, kw.get("d", 32), p, p, p,
+                                                 kw.get("rows", 8), kw.get("prefix", 0), H.stream())
+    assert call() == 0
+    assert call(d=24) == _lib.RK_EINVAL       # head_dim not a multiple of 16
+    assert call(qs=60) == _lib.RK_EINVAL      # row stride not a multiple of 8 elements
+    assert call(qs=32) == _lib.RK_EINVAL      # row stride shorter than a row of two heads
+    assert call(rows=8, prefix=7) == _lib.RK_EINVAL  # cache too short for prefix + tokens
+    torch.cuda.synchronize()
+
+
+def test_fused_rope_leaves_the_loop_output_unchanged(H):
+    from rk_b200.gemma_stack import GemmaAttention, expert_scope
+    from rk_b200.optimizations import quantize_linears
+
+    expert = small_expert(H.DEVICE)
+    b, t = 4, 64
+    gen = torch.Generator().manual_seed(17)
+    noise = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+    pk = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    pv = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    with torch.no_grad():
+        for grouped in (False, True):
+            with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
+                                  grouped=grouped) as _:
+                want = expert(noise, pk, pv)
+                GemmaAttention.fused_rope = True
+                try:
+                    got = expert(noise, pk, pv)
+                finally:
+                    GemmaAttention.fused_rope = False
+                assert torch.equal(got, want)
+        bf16 = expert(noise, pk, pv)
+        GemmaAttention.fused_rope = True
+        try:
+            assert torch.equal(expert(noise, pk, pv), bf16)
+        finally:
+            GemmaAttention.fused_rope = False
+
+
 def test_prefix_stack_nvfp4_close_to_bf16(H):
     from rk_b200.gemma_stack import GemmaConfig, GemmaStack, prefix_scope
     from rk_b200.optimizations import quantize_linears
