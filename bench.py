@@ -243,8 +243,10 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
         return float(np.median(samples)), samples
 
     bf16_ms, _ = measure(lambda n, k, v: expert(n, k, v))
+    # group_views: the slices of a grouped projection stay views of its output (the rope kernel and
+    # the GELU*up quantizer take row-strided inputs), instead of one copy per slice
     with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
-                          grouped=True) as report:
+                          grouped=True, group_views=True) as report:
         norms = fuse_norm_quantize(expert.stack)  # adaRMSNorm + modulation + row quantizer as one kernel
         int8_ms, samples = measure(lambda n, k, v: expert(n, k, v))
         unfuse_norm_quantize(norms)

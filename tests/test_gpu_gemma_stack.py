@@ -186,9 +186,9 @@ def test_fused_rope_leaves_the_loop_output_unchanged(H):
     pk = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
     pv = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
     with torch.no_grad():
-        for grouped in (False, True):
+        for grouped, views in ((False, False), (True, False), (True, True)):
             with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
-                                  grouped=grouped) as _:
+                                  grouped=grouped, group_views=views) as _:
                 want = expert(noise, pk, pv)
                 GemmaAttention.fused_rope = True
                 try:
