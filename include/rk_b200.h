@@ -117,6 +117,15 @@ int rk_rmsnorm_quant_rows(const void* x, const void* residual, const void* scale
                           int64_t tokens, int64_t rows, int64_t k, float eps, int bits, void* sum_out,
                           void* norm_out, void* q, float* scales, void* stream);
 
+/* The same with the gated residual of the adaptive layers in front (the reference's gated residual,
+ * common/fused.py:47-58, is a kernel of its own, and its residual + norm + modulation + quantize
+ * fusion exists for LayerNorm only: ampere_ada/modulation.py:149-265):
+ *   s = bf16( x + bf16(branch * gate[r / tokens, k]) ), then as rk_rmsnorm_quant_rows.
+ *   branch bf16 [rows, k]; gate bf16 [rows/tokens, k]; tokens >= 1; sum_out receives s. */
+int rk_gated_rmsnorm_quant_rows(const void* x, const void* branch, const void* gate, const void* scale,
+                                const void* shift, int64_t tokens, int64_t rows, int64_t k, float eps, int bits,
+                                void* sum_out, void* norm_out, void* q, float* scales, void* stream);
+
 /* out[m, n] = bf16( (float(sum_k a*b) * sa[m]) * sb[n] (+ bias[n]) ), int32 accumulation.
  * Replaces `robotics_integer::gemm` / `gemm_biasless` (ampere_ada/csrc/integer_gemm.cu:22-195).
  *   bits 8: a int8 [m, kpad], b int8 [n, kpad].  bits 4: packed nibbles [., kpad/2].

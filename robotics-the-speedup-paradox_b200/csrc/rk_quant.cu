@@ -315,6 +315,7 @@ quant_rows_modulated_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
 template <int BITS>
 __global__ void __launch_bounds__(kRowThreads)
 rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                          const __nv_bfloat16* __restrict__ gate,
                           const __nv_bfloat16* __restrict__ a_ptr, const __nv_bfloat16* __restrict__ b_ptr,
                           int tokens, int k, int kpad, float eps, __nv_bfloat16* __restrict__ sum_out,
                           __nv_bfloat16* __restrict__ norm_out, uint8_t* __restrict__ q, float* __restrict__ scales) {
@@ -337,6 +338,12 @@ rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
       if (residual != nullptr) {
         float rv[8];
         load8(residual + xoff + idx, vec, valid, rv);
+        if (gate != nullptr) {  // gated residual: the branch is scaled per (batch entry, channel) first
+          float gv[8];
+          load8(gate + aoff + idx, vec, valid, gv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) rv[i] = round_bf16(__fmul_rn(rv[i], gv[i]));
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) vals[it][i] = round_bf16(__fadd_rn(vals[it][i], rv[i]));
       }
@@ -892,27 +899,47 @@ extern "C" int rk_quant_rows_modulated(const void* x, const void* scale, const v
   return check_launch("quant_rows_modulated");
 }
 
-extern "C" int rk_rmsnorm_quant_rows(const void* x, const void* residual, const void* scale, const void* shift,
-                                     int64_t tokens, int64_t rows, int64_t k, float eps, int bits, void* sum_out,
-                                     void* norm_out, void* q, float* scales, void* stream) {
-  if (!x || !scale || !q || !scales) return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: null pointer");
-  if (bits != 4 && bits != 8) return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: bits must be 4 or 8");
+namespace {
+int launch_rmsnorm_quant_rows(const char* who, const void* x, const void* residual, const void* gate, const void* scale,
+                              const void* shift, int64_t tokens, int64_t rows, int64_t k, float eps, int bits,
+                              void* sum_out, void* norm_out, void* q, float* scales, void* stream) {
+  if (!x || !scale || !q || !scales) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (bits != 4 && bits != 8) return fail(RK_EINVAL, "%s: bits must be 4 or 8", who);
   if (rows < 1 || k < 1 || tokens < 0 || (tokens > 0 && rows % tokens != 0))
-    return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: bad row / token counts");
-  if (k > kCachedK) return fail(RK_EUNSUPPORTED, "rk_rmsnorm_quant_rows: k > %d", kCachedK);
-  if (!aligned16(x) || !aligned16(scale) || (residual && !aligned16(residual)) || (shift && !aligned16(shift)))
-    return fail(RK_EINVAL, "rk_rmsnorm_quant_rows: pointers must be 16-byte aligned");
+    return fail(RK_EINVAL, "%s: bad row / token counts", who);
+  if (gate && (!residual || tokens < 1)) return fail(RK_EINVAL, "%s: a gate needs a residual branch and tokens > 0", who);
+  if (k > kCachedK) return fail(RK_EUNSUPPORTED, "%s: k > %d", who, kCachedK);
+  if (!aligned16(x) || !aligned16(scale) || (residual && !aligned16(residual)) || (shift && !aligned16(shift)) ||
+      (gate && !aligned16(gate)))
+    return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   const int kpad = static_cast<int>(round_up(k, 128));
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
   if (bits == 8)
     rmsnorm_quant_rows_kernel<8><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
-        b(x), b(residual), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
+        b(x), b(residual), b(gate), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
         static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), static_cast<uint8_t*>(q), scales);
   else
     rmsnorm_quant_rows_kernel<4><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
-        b(x), b(residual), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
+        b(x), b(residual), b(gate), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
         static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), static_cast<uint8_t*>(q), scales);
-  return check_launch("rmsnorm_quant_rows");
+  return check_launch(who);
+}
+}  // namespace
+
+extern "C" int rk_rmsnorm_quant_rows(const void* x, const void* residual, const void* scale, const void* shift,
+                                     int64_t tokens, int64_t rows, int64_t k, float eps, int bits, void* sum_out,
+                                     void* norm_out, void* q, float* scales, void* stream) {
+  return launch_rmsnorm_quant_rows("rk_rmsnorm_quant_rows", x, residual, nullptr, scale, shift, tokens, rows, k, eps, bits,
+                                   sum_out, norm_out, q, scales, stream);
+}
+
+extern "C" int rk_gated_rmsnorm_quant_rows(const void* x, const void* branch, const void* gate, const void* scale,
+                                           const void* shift, int64_t tokens, int64_t rows, int64_t k, float eps,
+                                           int bits, void* sum_out, void* norm_out, void* q, float* scales,
+                                           void* stream) {
+  if (!branch || !gate) return fail(RK_EINVAL, "rk_gated_rmsnorm_quant_rows: null pointer");
+  return launch_rmsnorm_quant_rows("rk_gated_rmsnorm_quant_rows", x, branch, gate, scale, shift, tokens, rows, k, eps,
+                                   bits, sum_out, norm_out, q, scales, stream);
 }
 
 extern "C" int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, void* stream) {

@@ -68,24 +68,41 @@ class GemmaRMSNorm(nn.Module):
         return (scale.unsqueeze(1), shift.unsqueeze(1), gate.unsqueeze(1).to(torch.bfloat16),
                 scale.to(torch.bfloat16).contiguous(), shift.to(torch.bfloat16).contiguous())
 
-    def forward(self, x, cond=None):
+    def forward(self, x, cond=None, pending=None):
+        """Returns (normalized, gate, residual stream).  `pending` = (branch, gate) is a residual update
+        that has not been applied yet: the stream becomes x + branch (* gate).  In the fused path the
+        update, the norm, the modulation and the row quantizer are one kernel."""
         fused = self.fused_bits is not None and x.is_cuda and x.dtype == torch.bfloat16
         if self.dense is not None:
             project = self.projection_cache if self.projection_cache is not None else self.modulation
             scale, shift, gate, scale_bf16, shift_bf16 = project(cond)
+        branch, branch_gate = pending if pending is not None else (None, None)
         if fused:
             from .modulation import prepare_rmsnorm
 
             x = x if x.is_contiguous() else x.contiguous()
-            if self.dense is None:
-                return prepare_rmsnorm(x, self.weight.detach(), self.fused_bits, eps=self.eps), None
-            packed = prepare_rmsnorm(x, scale_bf16, self.fused_bits, eps=self.eps, shift=shift_bf16, tokens=x.shape[1])
-            return packed, gate
+            if branch is not None:
+                branch = branch if branch.is_contiguous() else branch.contiguous()
+            tokens = x.shape[1] if self.dense is not None else 0
+            gate_rows = None
+            if branch_gate is not None:
+                if self.dense is None:  # a gate needs per-batch rows; apply it outside the kernel
+                    branch, branch_gate = branch * branch_gate, None
+                else:
+                    gate_rows = branch_gate.reshape(-1, x.shape[-1])
+            weight = self.weight.detach() if self.dense is None else scale_bf16
+            result = prepare_rmsnorm(x, weight, self.fused_bits, eps=self.eps, residual=branch, gate=gate_rows,
+                                     shift=None if self.dense is None else shift_bf16, tokens=tokens,
+                                     return_sum=branch is not None)
+            packed, stream = result if branch is not None else (result, x)
+            return packed, (None if self.dense is None else gate), stream
+        if branch is not None:
+            x = x + branch if branch_gate is None else x + branch * branch_gate
         xf = x.float()
         normed = xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
         if self.dense is None:
-            return (normed * (1.0 + self.weight.float())).to(x.dtype), None
-        return (normed * (1.0 + scale) + shift).to(x.dtype), gate.to(x.dtype)
+            return (normed * (1.0 + self.weight.float())).to(x.dtype), None, x
+        return (normed * (1.0 + scale) + shift).to(x.dtype), gate.to(x.dtype), x
 
 
 def _leading_shape(x):
@@ -199,14 +216,16 @@ class GemmaLayer(nn.Module):
         self.input_layernorm = GemmaRMSNorm(cfg.width, cfg.rms_eps, cfg.adarms_cond_dim)
         self.post_attention_layernorm = GemmaRMSNorm(cfg.width, cfg.rms_eps, cfg.adarms_cond_dim)
 
-    def forward(self, x, cos, sin, past_kv=None, cond=None):
-        h, gate = self.input_layernorm(x, cond)
+    def forward(self, x, cos, sin, past_kv=None, cond=None, pending=None):
+        """`pending`: the previous layer's MLP branch and gate, not yet added to the stream.  Returns the
+        stream BEFORE this layer's own MLP update plus that update as the new `pending`, so that the
+        next norm can apply it inside its kernel (a norm without the fused path applies it eagerly;
+        the arithmetic - bf16(x + bf16(branch * gate)) - is the same either way)."""
+        h, gate, x = self.input_layernorm(x, cond, pending)
         h, present = self.self_attn(h, cos, sin, past_kv)
-        x = x + h if gate is None else x + h * gate
-        h, gate = self.post_attention_layernorm(x, cond)
+        h, gate2, x = self.post_attention_layernorm(x, cond, (h, gate))
         h = self.mlp(h)
-        x = x + h if gate is None else x + h * gate
-        return x, present
+        return x, present, (h, gate2)
 
 
 class GemmaStack(nn.Module):
@@ -229,10 +248,11 @@ class GemmaStack(nn.Module):
     def forward(self, x, positions, past=None, cond=None):
         cos, sin = rope_tables(positions, self.cfg.head_dim, self.cfg.rope_theta, x.dtype)
         presents = []
+        pending = None
         for index, layer in enumerate(self.layers):
-            x, present = layer(x, cos, sin, None if past is None else past[index], cond)
+            x, present, pending = layer(x, cos, sin, None if past is None else past[index], cond, pending)
             presents.append(present)
-        x, _ = self.norm(x, cond)
+        x, _, _ = self.norm(x, cond, pending)
         return x, presents
 
 

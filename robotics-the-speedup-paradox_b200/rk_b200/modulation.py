@@ -78,13 +78,14 @@ def _prepare(x, scale, shift, bits, *, eps=None, residual=None):
     return packed if residual is None else (residual_out, packed)
 
 
-def prepare_rmsnorm(x, weight, bits, *, eps, residual=None, shift=None, tokens=0, return_sum=False,
+def prepare_rmsnorm(x, weight, bits, *, eps, residual=None, gate=None, shift=None, tokens=0, return_sum=False,
                     return_normed=False):
     """Gemma RMSNorm -> integer pack in one pass.
 
     ``weight`` is the learned ``[K]`` vector (plain norm, ``tokens=0``) or the adaptive scale
     ``[rows/tokens, K]`` with ``shift`` of the same shape.  ``residual`` (same shape as ``x``) is
-    added first; ``return_sum`` / ``return_normed`` also return those BF16 tensors.
+    added first - multiplied by ``gate`` ``[rows/tokens, K]`` when one is given (the gated residual
+    of the adaptive layers); ``return_sum`` / ``return_normed`` also return those BF16 tensors.
     """
     if bits not in (4, 8) or not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.ndim < 2:
         raise ValueError("RMSNorm packing requires contiguous CUDA BF16 rows and bits=4 or 8")
@@ -105,12 +106,21 @@ def prepare_rmsnorm(x, weight, bits, *, eps, residual=None, shift=None, tokens=0
     scales = torch.empty(rows, device=x.device, dtype=torch.float32)
     sum_out = torch.empty_like(x) if return_sum else None
     norm_out = torch.empty_like(x) if return_normed else None
+    if gate is not None and (residual is None or tokens < 1 or gate.dtype != x.dtype or gate.numel() != expect):
+        raise ValueError("A gate needs a residual branch, tokens >= 1 and one BF16 row per batch entry")
+    shift = None if shift is None else shift.contiguous()
     with torch.cuda.device(x.device):
-        code = _lib.load().rk_rmsnorm_quant_rows(
-            _lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), _lib.ptr(None if shift is None else shift.contiguous()),
-            tokens, rows, k, eps, bits, _lib.ptr(sum_out), _lib.ptr(norm_out), _lib.ptr(data), _lib.ptr(scales),
-            _lib.stream_ptr(x.device),
-        )
+        if gate is None:
+            code = _lib.load().rk_rmsnorm_quant_rows(
+                _lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), _lib.ptr(shift), tokens, rows, k, eps, bits,
+                _lib.ptr(sum_out), _lib.ptr(norm_out), _lib.ptr(data), _lib.ptr(scales), _lib.stream_ptr(x.device),
+            )
+        else:
+            code = _lib.load().rk_gated_rmsnorm_quant_rows(
+                _lib.ptr(x), _lib.ptr(residual), _lib.ptr(gate.contiguous()), _lib.ptr(weight), _lib.ptr(shift), tokens,
+                rows, k, eps, bits, _lib.ptr(sum_out), _lib.ptr(norm_out), _lib.ptr(data), _lib.ptr(scales),
+                _lib.stream_ptr(x.device),
+            )
     _lib.check(code, "prepare_rmsnorm")
     packed = PackedActivations({bits: PackedActivation(data, scales, tuple(x.shape[:-1]), k, bits)})
     extras = tuple(t for t in (sum_out, norm_out) if t is not None)

@@ -108,7 +108,9 @@ def test_packed_activations_carrier_feeds_integer_linear(H):
 
 
 # ---------------------------------------------------------------- Gemma RMSNorm -> pack
-def _rmsnorm_oracle(x, w, eps, residual=None, shift=None, rows_per=None):
+def _rmsnorm_oracle(x, w, eps, residual=None, shift=None, rows_per=None, gate=None):
+    if gate is not None:  # gated residual (common/fused.py:47-58): bf16(x + bf16(branch * gate))
+        residual = F.bf16_round((residual * gate[np.arange(x.shape[0]) // rows_per]).astype(np.float32))
     s = x if residual is None else F.bf16_round((x + residual).astype(np.float32))
     var = (s.astype(np.float32) ** 2).mean(axis=1, dtype=np.float32)
     inv = (1.0 / np.sqrt(var + np.float32(eps))).astype(np.float32)
@@ -147,6 +149,35 @@ def test_rmsnorm_pack(H, bits, adaptive):
     p = packed.for_bits(bits)
     assert np.array_equal(p.scales.cpu().numpy(), sc)
     assert np.array_equal(p.data.cpu().numpy().view(np.uint8), data.view(np.uint8))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_gated_residual_rmsnorm_pack(H, bits):
+    """x + branch * gate (two bf16 roundings, the gated residual of the adaptive layers) in front of
+    the adaptive RMSNorm and the row quantizer, one kernel: the new residual stream is exact, the
+    pack is the row quantizer applied to the kernel's own normalized values."""
+    from rk_b200.modulation import prepare_rmsnorm
+
+    rows, k, tokens = 150, 1024, 50
+    x, branch = H.randn_bf16((rows, k), 1.0, 11), H.randn_bf16((rows, k), 1.0, 12)
+    w, sh = H.randn_bf16((rows // tokens, k), 0.2, 13), H.randn_bf16((rows // tokens, k), 0.2, 14)
+    gate = H.randn_bf16((rows // tokens, k), 0.5, 15)
+    packed, summed, normed = prepare_rmsnorm(x.to(H.DEVICE), w.to(H.DEVICE), bits, eps=1e-6, residual=branch.to(H.DEVICE),
+                                             gate=gate.to(H.DEVICE), shift=sh.to(H.DEVICE), tokens=tokens,
+                                             return_sum=True, return_normed=True)
+    s, n = _rmsnorm_oracle(H.to_np(x), H.to_np(w), 1e-6, H.to_np(branch), H.to_np(sh), tokens, H.to_np(gate))
+    assert np.array_equal(H.bits(summed), F.bf16_bits(s))
+    want_sum = x.to(H.DEVICE) + branch.to(H.DEVICE) * gate.to(H.DEVICE).repeat_interleave(tokens, 0)
+    assert torch.equal(summed, want_sum)  # the same two roundings as the tensor ops
+    got_n = H.to_np(normed)
+    assert np.abs(got_n - n).max() <= 2.0 ** -7 * np.abs(n).max()
+    data, sc, _ = OI.quantize_rows(got_n, bits)
+    p = packed.for_bits(bits)
+    assert np.array_equal(p.scales.cpu().numpy(), sc)
+    assert np.array_equal(p.data.cpu().numpy().view(np.uint8), data.view(np.uint8))
+    with pytest.raises(ValueError):
+        prepare_rmsnorm(x.to(H.DEVICE), w.to(H.DEVICE), bits, eps=1e-6, gate=gate.to(H.DEVICE), shift=sh.to(H.DEVICE),
+                        tokens=tokens)  # a gate without a branch
 
 
 # ---------------------------------------------------------------- FP8 / MXFP8 / NVFP4 modules
