@@ -3,6 +3,7 @@
 
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py [w4a16] [w8a8] [fp8] [mxfp8] [nvfp4] [quant]
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py w8a8:400x8192x1024 quant:16384x2048   # explicit shapes
+    python robotics-the-speedup-paradox_b200/rk_b200/microbench.py layer    # per-kernel device time of one expert layer
     python robotics-the-speedup-paradox_b200/build.py --trace && \
         RK_B200_SO=robotics-the-speedup-paradox_b200/rk_b200/librk_b200_trace.so \
         python robotics-the-speedup-paradox_b200/rk_b200/microbench.py trace
@@ -183,6 +184,64 @@ def role_trace(bench, m, n=16384, k=2048):
         print(f"{g:4d} " + " ".join(f"{c:12d}" if 0 <= c < 10 ** 9 else f"{'-':>12s}" for c in cells))
 
 
+def layer_breakdown(envs=8, prefix=816, repeats=5):
+    """Device time per kernel of ONE decoder layer of the action expert (width 1024, MLP 4096, 50
+    action tokens x `envs` environments attending to `prefix` cached tokens), eager launches under
+    the torch profiler: the bf16 layer, then the W8A8 layer with every option the benchmark's
+    chunk loop uses (grouped projections as views, fused gated-residual + adaRMSNorm + quantizer,
+    rotary embedding + cache append kernel, cached condition projections)."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from rk_b200.gemma_stack import (ActionExpert, GemmaAttention, expert_scope, fuse_norm_quantize, rope_tables,
+                                     unfuse_norm_quantize)
+    from rk_b200.optimizations import quantize_linears
+
+    dev = torch.device("cuda:0")
+    expert = ActionExpert().init_random(0).to(dev).eval()
+    cfg = expert.cfg
+    gen = torch.Generator().manual_seed(7)
+    x = torch.randn(envs, expert.chunk, cfg.width, generator=gen).to(torch.bfloat16).to(dev)
+    branch = torch.randn(envs, expert.chunk, cfg.width, generator=gen).to(torch.bfloat16).to(dev)
+    cond = torch.randn(envs, cfg.width, generator=gen).to(dev)
+    k_all = torch.randn(envs, cfg.num_kv_heads, prefix + expert.chunk, cfg.head_dim, generator=gen).to(torch.bfloat16).to(dev)
+    v_all = torch.randn(k_all.shape, generator=gen).to(torch.bfloat16).to(dev)
+    positions = prefix + torch.arange(expert.chunk, device=dev)[None].expand(envs, -1)
+    layer = expert.stack.layers[1]
+    expert.enable_condition_caches()
+    expert._conditions[("probe",)] = cond  # registers the condition, so that its projections are cached
+    GemmaAttention.fused_rope = True
+
+    def run(tag):
+        with torch.no_grad():
+            cos, sin = rope_tables(positions, cfg.head_dim, cfg.rope_theta, x.dtype)
+            gate = layer.input_layernorm.modulation(cond)[2]
+            step = lambda: layer(x, cos, sin, (k_all, v_all, prefix), cond, (branch, gate))
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+                for _ in range(repeats):
+                    step()
+                torch.cuda.synchronize()
+        rows = [(e.key, e.count, e.device_time_total) for e in prof.key_averages()
+                if e.device_time_total > 0 and e.device_type == torch.autograd.DeviceType.CUDA]
+        rows.sort(key=lambda r: -r[2])
+        total = sum(r[2] for r in rows)
+        print(f"--- {tag}: {total / repeats:.1f} us of device time per layer ({envs} x {expert.chunk} tokens, prefix {prefix})")
+        for key, count, t in rows:
+            print(f"{t / repeats:8.1f} us  x{count / repeats:4.1f}  {key[:120]}")
+
+    try:
+        run("bf16 linears")
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True, grouped=True,
+                              group_views=True):
+            norms = fuse_norm_quantize(expert.stack)
+            run("W8A8 linears, grouped, fused norm / residual / rope")
+            unfuse_norm_quantize(norms)
+    finally:
+        GemmaAttention.fused_rope = False
+
+
 def main(argv):
     which = argv or ["w4a16", "w8a8", "fp8", "mxfp8", "nvfp4", "quant"]
     b = Bench()
@@ -199,6 +258,9 @@ def main(argv):
         else:
             b.float8(kind, *dims)
     which = [a for a in which if ":" not in a]
+    if "layer" in which:
+        layer_breakdown()
+        return
     if "trace" in which:
         for m in (8, 50, 256):
             role_trace(b, m)
