@@ -411,7 +411,8 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64
 // predecessor in the stream is still running.  `pdl_launch_dependents` lets the successor's CTAs
 // be scheduled as soon as resources free up; `pdl_wait` blocks until the predecessor grid has
 // completed and its memory is visible.  Everything before `pdl_wait` must touch on-chip state
-// only (barrier init, TMEM allocation, descriptor prefetch).  Without the attribute both are no-ops.
+// only (barrier init, TMEM allocation, descriptor prefetch) - with one exception: prefetches of
+// weights into L2 (tma_prefetch_l2_2d), which deliver no data.  Without the attribute both are no-ops.
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

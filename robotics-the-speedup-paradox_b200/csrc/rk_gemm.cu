@@ -13,6 +13,7 @@
 #include "rk_gemm_w4.cuh"
 #include "rk_gemm_w4fold.cuh"
 #include "rk_gemm_w4fold2.cuh"
+#include "rk_gemv_w4.cuh"
 #include "rk_host.h"
 
 namespace rk {
@@ -827,6 +828,38 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
   const int scales_bytes = static_cast<int>(round_up((k / 128) * 256, 1024));  // [groups][128] bf16 in shared memory
   if (scales_bytes > 64 * 1024) return fail(RK_EUNSUPPORTED, "%s: k > 32768", who);
   if (!aligned16(scales)) return fail(RK_EINVAL, "%s: scales must be 16-byte aligned", who);
+  const int64_t gemv_slabs = k / kGemvSlab;
+  const bool gemv_shape = k % kGemvSlab == 0 && (gemv_slabs == 1 || gemv_slabs == 2 || gemv_slabs == 4 || gemv_slabs % 8 == 0);
+  if (m == 1 && tactic == 0 && gemv_shape && aligned16(x) && aligned16(q) && aligned16(out)) {
+    // one activation row: byte-streaming work for the CUDA cores (any tactic bit keeps the tensor-core kernels)
+    GemvParams g{};
+    g.q = static_cast<const uint8_t*>(q);
+    g.scales = static_cast<const __nv_bfloat16*>(scales);
+    g.x = static_cast<const __nv_bfloat16*>(x);
+    g.bias = static_cast<const __nv_bfloat16*>(bias);
+    g.out = static_cast<__nv_bfloat16*>(out);
+    g.n = static_cast<int>(n);
+    g.k = static_cast<int>(k);
+    const int slabs = static_cast<int>(k / kGemvSlab);
+    const int share = slabs < kGemvWarps ? slabs : kGemvWarps;
+    const int batches = static_cast<int>(n / kGemvRows);
+    const int per_cta = kGemvWarps / share;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((batches + per_cta - 1) / per_cta);
+    cfg.blockDim = dim3(kGemvWarps * 32);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemv_w4a16_kernel, g);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(RK_ECUDA, "rk_gemv_w4a16_kernel launch: %s", cudaGetErrorString(e));
+    }
+    return RK_OK;
+  }
   if (m > 64 && !(tactic & 2)) {  // tactic bit 1 keeps the per-group-accumulator kernel for any m
     p.ldo = n;
     p.bias = static_cast<const __nv_bfloat16*>(bias);

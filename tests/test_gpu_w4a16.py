@@ -119,11 +119,45 @@ def test_sixteen_expansion_warps_change_nothing(H, shape):
     q, s = pack(H, w.to(H.DEVICE))
     base = run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 32)
     wide = run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 16)
-    assert torch.equal(run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 0), base)
+    default = run_gemm(H, x.to(H.DEVICE), q, s, bias.to(H.DEVICE), m, n, k, 0)
+    if m == 1 and k in (1024, 2048, 4096):  # one row with no tactic bit set runs on the CUDA cores: other summation order
+        assert H.rel_frobenius(H.to_np(default), H.to_np(base)) < 1e-3
+    else:
+        assert torch.equal(default, base)
     assert torch.equal(base, wide)
     ep, es, _ = OW.pack_weight(H.to_np(w))
     _, want = OW.gemm(H.to_np(x), ep, es, H.to_np(bias))
     assert H.rel_frobenius(H.to_np(wide), want) < TOL
+
+
+@pytest.mark.parametrize("shape", [(256, 1024), (1000, 2048), (16384, 2048), (136, 4096), (264, 8192), (64, 16384),
+                                   (264, 5120)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_single_row_streams_on_cuda_cores(H, shape, with_bias):
+    """m = 1 (tactic 0, k % 1024 == 0) takes the weight-streaming kernel: fp32 sums of exactly
+    recovered x * q products, within the bf16 output rounding of the definition, equal to the
+    tensor-core kernel up to summation order, and exact on integer-valued data."""
+    n, k = shape
+    x = H.randn_bf16((1, k), 1.0, 31)
+    w = H.randn_bf16((n, k), 0.02, 32)
+    bias = H.randn_bf16((n,), 0.5, 33) if with_bias else None
+    q, s = pack(H, w.to(H.DEVICE))
+    dev_bias = None if bias is None else bias.to(H.DEVICE)
+    out = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, dev_bias, 1, n, k, 0))
+    tensor_core = H.to_np(run_gemm(H, x.to(H.DEVICE), q, s, dev_bias, 1, n, k, 2))
+    ep, es, _ = OW.pack_weight(H.to_np(w))
+    _, want = OW.gemm(H.to_np(x), ep, es, None if bias is None else H.to_np(bias))
+    assert H.rel_frobenius(out, want) < 3e-3  # bf16 output rounding alone is ~1.5e-3
+    assert np.abs(out - want).max() <= 2.0 ** -8 * np.abs(want).max() + 1e-6
+    assert H.rel_frobenius(out, tensor_core) < 1e-3
+    # small integers everywhere: every partial sum is an exactly representable integer
+    xi = torch.randint(-3, 4, (1, k)).to(torch.bfloat16)
+    wi = (torch.randint(-7, 8, (n, k)).float()).to(torch.bfloat16)
+    wi[:, ::128] = 7.0  # every group's maximum is 7, so its scale is exactly 1
+    qi, si = pack(H, wi.to(H.DEVICE))
+    got = run_gemm(H, xi.to(H.DEVICE), qi, si, None, 1, n, k, 0)
+    exact = (xi.double() @ wi.double().T)
+    assert torch.equal(got.cpu().double(), exact.to(torch.bfloat16).double())
 
 
 def test_linearity_at_full_size(H):
