@@ -168,6 +168,9 @@ int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, 
 /* out[m, n] = bf16( sum_g s[g, n] * sum_{k in g} x[m, k] * q[n, k] (+ bias[n]) ), fp32 accumulation.
  * Stands in for `linear_w4a16` (blackwell/csrc/fp4_mixed_cutlass_linear.cu:190-410) with the
  * int4 / group-128 format.  x bf16 [m, k] contiguous, out bf16 [m, n] contiguous.
+ *   m == 1 with tactic 0 and k in {1024, 2048, 4096, multiples of 8192}: a weight-streaming kernel
+ *   on the CUDA cores (fp32 sums of exactly recovered x * q products; any tactic bit selects the
+ *   tensor-core kernels instead).
  *   m <= 64: every group's sum is scaled in fp32 exactly as written above.  m > 64: the scale is
  *   folded into the expanded weight first, bf16(q * s) - one extra rounding of at most 2^-9 per
  *   weight, the order of operations of the reference's mixed-input GEMM; still within the 1e-2
