@@ -273,13 +273,15 @@ int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, const void* b
  *   out = bf16( bf16(x * cos) + bf16(r * sin) ), r = -x[j + d/2] (j < d/2) or x[j - d/2].
  *   q bf16 rows [batch*tokens] of heads*head_dim elements, row stride q_stride elements (likewise
  *   k, v with kv_heads); q, k, v may be slices of one projection output.  cos, sin bf16
- *   [batch, tokens, head_dim]; q_out bf16 [batch, heads, tokens, head_dim]; k_cache, v_cache bf16
+ *   [batch, tokens, head_dim]; q_out bf16 [batch, heads, tokens, head_dim], or - q_token_major != 0 -
+ *   [batch, tokens, heads, head_dim] (the layout fused attention kernels read without a copy);
+ *   k_cache, v_cache bf16
  *   [batch, kv_heads, cache_rows, head_dim].  head_dim % 16 == 0, <= 512; strides % 8 == 0; all
  *   pointers 16-byte aligned. */
 int rk_rope_cache_update(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                          int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
-                         int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, void* k_cache,
-                         void* v_cache, int64_t cache_rows, int64_t prefix, void* stream);
+                         int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
+                         void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* stream);
 
 #ifdef __cplusplus
 }

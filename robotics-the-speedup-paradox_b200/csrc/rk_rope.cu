@@ -52,9 +52,9 @@ struct RopeParams {
   const __nv_bfloat16 *q, *k, *v;        // rows of [heads * dim], [kv_heads * dim], [kv_heads * dim]
   long long q_stride, k_stride, v_stride;  // row strides in elements
   const __nv_bfloat16 *cos, *sin;        // [batch, tokens, dim]
-  __nv_bfloat16 *q_out;                  // [batch, heads, tokens, dim]
+  __nv_bfloat16 *q_out;                  // [batch, heads, tokens, dim], or [batch, tokens, heads, dim] (token_major)
   __nv_bfloat16 *k_all, *v_all;          // [batch, kv_heads, cache_rows, dim]
-  int batch, tokens, heads, kv_heads, dim, cache_rows, prefix;
+  int batch, tokens, heads, kv_heads, dim, cache_rows, prefix, token_major;
 };
 
 __global__ void __launch_bounds__(256)
@@ -84,7 +84,8 @@ rope_cache_update_kernel(const RopeParams p) {
       const uint4 s = *reinterpret_cast<const uint4*>(sn + j);
       const uint4 o = rotate8(x, partner, c, s, j < half);
       __nv_bfloat16* dst =
-          is_q ? p.q_out + ((static_cast<long long>(b) * p.heads + head) * p.tokens + token) * p.dim
+          is_q ? p.q_out + (p.token_major ? (row * p.heads + head) * p.dim
+                                          : ((static_cast<long long>(b) * p.heads + head) * p.tokens + token) * p.dim)
                : p.k_all + ((static_cast<long long>(b) * p.kv_heads + head) * p.cache_rows + p.prefix + token) * p.dim;
       *reinterpret_cast<uint4*>(dst + j) = o;
     } else {
@@ -101,8 +102,8 @@ rope_cache_update_kernel(const RopeParams p) {
 
 extern "C" int rk_rope_cache_update(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                                     int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
-                                    int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, void* k_cache,
-                                    void* v_cache, int64_t cache_rows, int64_t prefix, void* stream) {
+                                    int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
+                                    void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* stream) {
   using namespace rk;
   const char* who = "rk_rope_cache_update";
   if (!q || !k || !v || !cos || !sin || !q_out || !k_cache || !v_cache) return fail(RK_EINVAL, "%s: null pointer", who);
@@ -138,6 +139,7 @@ extern "C" int rk_rope_cache_update(const void* q, int64_t q_stride, const void*
   p.dim = static_cast<int>(head_dim);
   p.cache_rows = static_cast<int>(cache_rows);
   p.prefix = static_cast<int>(prefix);
+  p.token_major = q_token_major ? 1 : 0;
   const long long jobs = batch * tokens * (heads + 2 * kv_heads);
   const int warps = 8;
   const unsigned blocks = static_cast<unsigned>((jobs + warps - 1) / warps);

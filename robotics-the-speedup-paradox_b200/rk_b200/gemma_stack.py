@@ -124,11 +124,12 @@ def rope_tables(positions, head_dim, theta, dtype):
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
 
-def rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv_heads, head_dim):
+def rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv_heads, head_dim, token_major=False):
     """One kernel for rotary embedding + cache append (`rk_rope_cache_update`).  q, k, v: bf16
     [B, t, heads * d] / [B, t, kv_heads * d] whose rows are dense (slices of one projection output
     are fine); cos, sin [B, t, d]; k_all, v_all [B, kv_heads, rows, d] already holding `prefix`
-    rows.  Returns the rotated queries as [B, heads, t, d]."""
+    rows.  Returns the rotated queries as [B, heads, t, d]; with `token_major` that tensor is a
+    transposed view of [B, t, heads, d] storage, the layout fused attention reads without a copy."""
     from . import _lib
 
     b, t = q.shape[0], q.shape[1]
@@ -138,13 +139,14 @@ def rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv_heads, 
     cos, sin = cos.contiguous(), sin.contiguous()
     if not (k_all.is_contiguous() and v_all.is_contiguous()):
         raise ValueError("cache buffers must be contiguous")
-    q_out = torch.empty((b, heads, t, head_dim), dtype=torch.bfloat16, device=q.device)
+    shape = (b, t, heads, head_dim) if token_major else (b, heads, t, head_dim)
+    q_out = torch.empty(shape, dtype=torch.bfloat16, device=q.device)
     code = _lib.load().rk_rope_cache_update(
         _lib.ptr(q), q.stride(1), _lib.ptr(k), k.stride(1), _lib.ptr(v), v.stride(1), _lib.ptr(cos), _lib.ptr(sin),
-        b, t, heads, kv_heads, head_dim, _lib.ptr(q_out), _lib.ptr(k_all), _lib.ptr(v_all), k_all.shape[2], prefix,
-        _lib.stream_ptr(q.device))
+        b, t, heads, kv_heads, head_dim, _lib.ptr(q_out), 1 if token_major else 0, _lib.ptr(k_all), _lib.ptr(v_all),
+        k_all.shape[2], prefix, _lib.stream_ptr(q.device))
     _lib.check(code, "rk_rope_cache_update")
-    return q_out
+    return q_out.transpose(1, 2) if token_major else q_out
 
 
 class GemmaAttention(nn.Module):
@@ -164,7 +166,7 @@ class GemmaAttention(nn.Module):
         if self.fused_rope and past_kv is not None and len(past_kv) == 3 and cos.is_cuda:
             k_all, v_all, prefix = past_kv
             q = rope_cache_update(self.q_proj(x), self.k_proj(x), self.v_proj(x), cos, sin, k_all, v_all, prefix,
-                                  cfg.num_heads, cfg.num_kv_heads, cfg.head_dim)
+                                  cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, token_major=True)
             out = F.scaled_dot_product_attention(q, k_all, v_all, is_causal=False, enable_gqa=True)
             out = out.transpose(1, 2).reshape(b, t, -1).contiguous()
             return self.o_proj(out), (k_all, v_all)

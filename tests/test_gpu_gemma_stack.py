@@ -157,6 +157,11 @@ def test_rope_cache_update_kernel_matches_oracle_and_tensor_ops(H, shape):
     rot = lambda x: torch.cat((-x[..., half:], x[..., :half]), dim=-1)
     q4 = q.reshape(b, t, heads, d).transpose(1, 2)
     assert torch.equal(q_out, q4 * cos[:, None] + rot(q4) * sin[:, None])
+    # token-major storage: the same values as a transposed view of [B, t, heads, d]
+    k2, v2 = torch.zeros_like(k_all), torch.zeros_like(v_all)
+    q_tm = rope_cache_update(q, k, v, cos, sin, k2, v2, prefix, heads, kv, d, token_major=True)
+    assert q_tm.shape == q_out.shape and q_tm.transpose(1, 2).is_contiguous() and torch.equal(q_tm, q_out)
+    assert torch.equal(k2[:, :, prefix:prefix + t], k_all[:, :, prefix:prefix + t])
 
 
 def test_rope_cache_update_refuses_bad_arguments(H):
@@ -165,8 +170,8 @@ def test_rope_cache_update_refuses_bad_arguments(H):
     lib = _lib.load()
     t = torch.zeros(4096, dtype=torch.bfloat16, device=H.DEVICE)
     p = _lib.ptr(t)
-    call = lambda **kw: lib.rk_rope_cache_update(p, kw.get("qs", 64), p, 32, p, 32, p, p, 1, 2, 2, 1, kw.get("d", 32), p, p, p,
-                                                 kw.get("rows", 8), kw.get("prefix", 0), H.stream())
+    call = lambda **kw: lib.rk_rope_cache_update(p, kw.get("qs", 64), p, 32, p, 32, p, p, 1, 2, 2, 1, kw.get("d", 32), p, 0, p,
+                                                 p, kw.get("rows", 8), kw.get("prefix", 0), H.stream())
     assert call() == 0
     assert call(d=24) == _lib.RK_EINVAL       # head_dim not a multiple of 16
     assert call(qs=60) == _lib.RK_EINVAL      # row stride not a multiple of 8 elements
