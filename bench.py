@@ -3,18 +3,27 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload ``cfg2_w4a16_g128``: the W4A16 group-wise int4 GEMM of the Gemma-2B MLP gate/up
-shape (N=16384, K=2048, group 128) at M in {1, 8, 50, 256}.  One step = one pass over the four
-activation batches (four GEMM launches).  Weights rotate through enough independent copies that
-the working set exceeds the 126 MB L2, so a launch streams its weights from HBM.
+Workloads (the benchmark configurations of the reference's headline metric, synthetic seeded data):
 
-Prints ONE JSON line (rank 0).  ``value`` is whole-job TOPS with inputs resident in HBM; ``e2e``
-is the same metric through the public Linear module with host activations (H2D copy, GEMM, D2H
-copy inside the timed region); ``roofline`` describes the dominant kernel; ``cpu_baseline`` is
-the CPU oracle port of the same operator timed on the host cores over a bounded sample.
+  cfg2_w4a16_g128   (default, the headline) W4A16 group-wise int4 GEMM of the Gemma-2B MLP gate/up
+                    shape (N=16384, K=2048, group 128) at M in {1, 8, 50, 256}; a step = the four launches
+  cfg1_w8a8         W8A8 linear M=64, N=K=2048 with bias: row quantizer + int8 GEMM + dequant epilogue
+  cfg3_fp8          per-tensor FP8 linear M=816, N=16384, K=2048: tensor quantizer + GEMM
+  cfg3_mxfp8        MXFP8 linear, same shape: block packer + block-scaled GEMM
+  cfg4_nvfp4_prefix NVFP4 prefix pass of a random-init 18-layer Gemma-2B-architecture stack, 816 tokens,
+                    fp32 per-tensor scales on, activations packed on the fly; a step = one pass
+  cfg5_w8a8_expert  W8A8 action-expert loop (18 layers, width 1024, 10 Euler steps, 8 environments, 816
+                    prefix keys) replayed from one CUDA graph; a step = one action chunk
 
-``--impl reference`` times the CPU implementation only (the reference's quantized path has no
-CPU build of its own; the oracle port stands in), on rank 0.
+Weights rotate through enough independent copies that a step's working set exceeds the 126 MB L2.
+Prints ONE JSON line (rank 0).  `value` is whole-job TOPS with inputs resident in HBM (CUDA events
+around CUDA-graph replays); `e2e` is the same metric through the public module API with HOST
+inputs and outputs (copies inside the timed region); `roofline` describes the dominant kernel;
+`cpu_baseline` is the CPU oracle port of the same operator on the host cores over a bounded sample.
+The default line also carries `per_config`: a short device-timed run of every other workload.
+
+`--impl reference` times the CPU implementation only (the reference's quantized path has no CPU
+build of its own; the oracle port stands in), on rank 0.
 """
 
 import argparse
@@ -36,6 +45,7 @@ import torch
 L2_BYTES = 126 * 1024 * 1024
 N, K, GROUP = 16384, 2048, 128
 M_LIST = (1, 8, 50, 256)
+WORKLOADS = ("cfg2_w4a16_g128", "cfg1_w8a8", "cfg3_fp8", "cfg3_mxfp8", "cfg4_nvfp4_prefix", "cfg5_w8a8_expert")
 
 
 def load_peaks():
@@ -51,8 +61,9 @@ def algorithmic_bytes(m):
     return N * K // 2 + (K // GROUP) * N * 2 + m * K * 2 + m * N * 2
 
 
-# DRAM bytes (read + write) of one launch, from an ncu capture of this workload's four launches
-# (dram__bytes_read.sum + dram__bytes_write.sum; the outputs stay in L2, so writes were zero).
+# DRAM bytes (read + write) of one cfg2 launch as ncu measured them (dram__bytes_read.sum +
+# dram__bytes_write.sum; the outputs stay in L2, so writes were zero).  From the capture summarised
+# in profiles/w4a16_cfg2_kernel_metrics.md; not re-measured by this program.
 NCU_DRAM_TRAFFIC = {1: 17330432, 8: 17373952, 50: 17549312, 256: 18384896}
 
 
@@ -82,6 +93,9 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
+        deadline = time.perf_counter() + 3.0  # the first sample marks that sampling is live
+        while not self.samples and time.perf_counter() < deadline:
+            time.sleep(0.02)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -112,6 +126,582 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+# ------------------------------------------------------------------------------------------------
+# Workloads other than the headline.  Each one provides: device-resident steps for the kernel-only
+# figure, steps through the public module API with host buffers for `e2e`, a CPU port on a bounded
+# sample, and its algorithmic operations / bytes per step.
+# ------------------------------------------------------------------------------------------------
+def _seeded(shape, std, seed, device, dtype=torch.bfloat16):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(shape, generator=gen, device=device) * std).to(dtype)
+
+
+def _copies_for(nbytes, extra=2):
+    return max(2, L2_BYTES // max(nbytes, 1) + extra)
+
+
+class LinearWorkload:
+    """One quantized linear: activation quantizer (or packer) + GEMM, weights rotating through copies."""
+
+    kinds = {
+        # name: (m, n, k, weight bytes per element, bound, tensor-peak factor over bf16, dtype string)
+        "cfg1_w8a8": (64, 2048, 2048, 1.0, "hbm", 2, "s8xs8->s32"),
+        "cfg3_fp8": (816, 16384, 2048, 1.0, "tensor", 2, "e4m3xe4m3->f32"),
+        "cfg3_mxfp8": (816, 16384, 2048, 1.0, "tensor", 2, "mxfp8(e4m3,ue8m0/32)->f32"),
+    }
+
+    def __init__(self, name, device, seed):
+        self.name = name
+        self.m, self.n, self.k, wb, self.bound, self.peak_factor, self.dtype = self.kinds[name]
+        self.device = device
+        m, n, k = self.m, self.n, self.k
+        self.copies = _copies_for(int(n * k * wb))
+        self.x = _seeded((m, k), 1.0, seed, device)
+        self.bias = _seeded((n,), 0.01, seed + 1, device) if name == "cfg1_w8a8" else None
+        self.layers = []
+        for c in range(self.copies):
+            lin = torch.nn.Linear(k, n, bias=self.bias is not None, device=device, dtype=torch.bfloat16)
+            with torch.no_grad():
+                lin.weight.copy_(_seeded((n, k), 0.02, seed + 10 + c, device))
+                if self.bias is not None:
+                    lin.bias.copy_(self.bias)
+            lin.requires_grad_(False)
+            self.layers.append(self._make(lin))
+            del lin
+        self.ops_per_step = 2 * m * n * k
+        sf = (m + n) * k // 32 if name == "cfg3_mxfp8" else 4 * (m + n) if name == "cfg1_w8a8" else 8
+        # quantizer: read bf16 activations, write codes; GEMM: read codes + weights (+ scales), write bf16
+        self.bytes_per_step = m * k * 2 + m * k + m * k + int(n * k * wb) + sf + m * n * 2 + (n * 2 if self.bias is not None else 0)
+        self.gemm_bytes = m * k + int(n * k * wb) + sf + m * n * 2
+        self.launches_per_step = {"cfg1_w8a8": 2, "cfg3_fp8": 3, "cfg3_mxfp8": 2}[name]
+        self.kernel = {"cfg1_w8a8": "rk_gemm_tc_kernel<int8> (+ quant_rows_kernel)",
+                       "cfg3_fp8": "rk_gemm_tc_kernel<e4m3> (+ per-tensor quantizer)",
+                       "cfg3_mxfp8": "rk_gemm_tc_kernel<mxfp8> (+ pack_mxfp8_kernel)"}[name]
+        self.h2d_bytes, self.d2h_bytes = m * k * 2, m * n * 2
+        self.host_x = self.x.cpu().pin_memory()
+        self.host_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+        self.dev_x = torch.empty_like(self.x)
+
+    def _make(self, lin):
+        if self.name == "cfg1_w8a8":
+            from rk_b200.integer import IntegerLinear
+
+            return IntegerLinear.from_linear(lin, bits=8)
+        from rk_b200.fp8_linear import Fp8CutlassLinear
+
+        return Fp8CutlassLinear.from_linear(lin, "linear", self.name, mode="per_tensor" if self.name == "cfg3_fp8" else "mxfp8")
+
+    def config(self):
+        return {"workload": self.name, "M": self.m, "N": self.n, "K": self.k, "launches_per_step": self.launches_per_step,
+                "step": "activation quantizer + GEMM of one linear", "timing": "CUDA events around CUDA-graph replays",
+                "l2": f"inputs larger than L2: weights rotate through {self.copies} copies"}
+
+    def device_step(self, i):
+        return self.layers[i % self.copies](self.x)
+
+    def gemm_only_calls(self):
+        """GEMM on a prepared activation (the reference's `prepared_gemm` scope), one callable per copy."""
+        if self.name == "cfg1_w8a8":
+            packed = self.layers[0].pack_input(self.x)
+            return [lambda layer=layer: layer.forward_packed(packed) for layer in self.layers]
+        packed, scale = self.layers[0].pack_input(self.x)
+        return [lambda layer=layer: layer.forward_packed(packed, scale) for layer in self.layers]
+
+    def e2e_step(self, i):
+        self.dev_x.copy_(self.host_x, non_blocking=True)
+        y = self.layers[i % self.copies](self.dev_x)
+        self.host_out.copy_(y, non_blocking=True)
+        torch.cuda.synchronize(self.device)
+
+    # ---- CPU port (oracle) -------------------------------------------------------------------
+    def cpu_setup(self, rows):
+        """Weights of the first `rows` output channels, prepared once (weight preparation is init-time work)."""
+        from oracle.formats import bf16_round
+
+        rng = np.random.default_rng(42)
+        self.cpu_rows = rows
+        x = bf16_round(rng.standard_normal((self.m, self.k)).astype(np.float32))
+        w = bf16_round((rng.standard_normal((rows, self.k)) * 0.02).astype(np.float32))
+        self.cpu_x = x
+        if self.name == "cfg1_w8a8":
+            from oracle import integer as OI
+
+            self.cpu_w = OI.quantize_weight(w, 8)
+            self.cpu_bias = bf16_round((rng.standard_normal(rows) * 0.01).astype(np.float32))
+        elif self.name == "cfg3_fp8":
+            from oracle import fp8 as OF
+            from oracle.formats import e4m3_decode
+
+            codes, scale = OF.quantize(w)
+            self.cpu_w = (torch.from_numpy(e4m3_decode(codes).astype(np.float32)), scale)
+        else:
+            from oracle import blockscale as OB
+
+            codes, sf, _ = OB.pack_mxfp8(w)
+            self.cpu_w = torch.from_numpy(OB.dequant_mxfp8(codes, sf).astype(np.float32))
+
+    def cpu_step(self):
+        """Quantize the activations, multiply; returns the operations done."""
+        if self.name == "cfg1_w8a8":
+            from oracle import integer as OI
+
+            a, sa, _ = OI.quantize_rows(self.cpu_x, 8)
+            b, sb, _ = self.cpu_w
+            OI.gemm(a, sa, b, sb, self.cpu_bias, 8)
+        elif self.name == "cfg3_fp8":
+            from oracle import fp8 as OF
+            from oracle.formats import bf16_round, e4m3_decode
+
+            codes, scale = OF.quantize(self.cpu_x)
+            w, wscale = self.cpu_w
+            acc = torch.from_numpy(e4m3_decode(codes).astype(np.float32)) @ w.T
+            bf16_round((acc.numpy() * np.float32(scale * wscale)).astype(np.float32))
+        else:
+            from oracle import blockscale as OB
+
+            codes, sf, _ = OB.pack_mxfp8(self.cpu_x)
+            (torch.from_numpy(OB.dequant_mxfp8(codes, sf).astype(np.float32)) @ self.cpu_w.T).to(torch.bfloat16)
+        return 2 * self.m * self.cpu_rows * self.k
+
+
+class PrefixWorkload:
+    """cfg4: NVFP4 prefix pass of the 18-layer Gemma-2B-architecture stack over 816 tokens."""
+
+    name = "cfg4_nvfp4_prefix"
+    bound, peak_factor, dtype = "tensor", 4, "nvfp4(e2m1,ue4m3/16,f32 tensor scale)->f32"
+    tokens = 816
+
+    def __init__(self, name, device, seed, depth=18):
+        from rk_b200.gemma_stack import GemmaStack, gemma_2b, prefix_scope
+        from rk_b200.optimizations import quantize_linears
+        from dataclasses import replace
+
+        self.device = device
+        cfg = replace(gemma_2b(), depth=depth)
+        self.cfg = cfg
+        model = GemmaStack(cfg).to(torch.bfloat16).to(device).eval()
+        gen = torch.Generator(device=device).manual_seed(seed)
+        with torch.no_grad():
+            for param in model.parameters():
+                if param.dim() >= 2:
+                    param.copy_((torch.randn(param.shape, generator=gen, device=device) * 0.02).to(param.dtype))
+        self.model = model
+        self.context = quantize_linears(model, "fp4", scopes=("text",), selector=prefix_scope, fp4_global_scale=True)
+        self.report = self.context.__enter__()
+        for p_ in model.parameters():  # the bf16 originals are not needed while the benchmark runs
+            p_.requires_grad_(False)
+        self.x = _seeded((1, self.tokens, cfg.width), 1.0, seed + 1, device)
+        self.pos = torch.arange(self.tokens, device=device)[None]
+        t, w, mlp, qd, kvd = self.tokens, cfg.width, cfg.mlp_dim, cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        per_layer = 2 * t * (w * qd + 2 * w * kvd + qd * w + 2 * w * mlp + mlp * w)
+        attn = 4 * t * t * cfg.num_heads * cfg.head_dim
+        self.linear_ops = per_layer * depth
+        self.ops_per_step = (per_layer + attn) * depth
+        weights = (w * qd + 2 * w * kvd + qd * w + 3 * w * mlp) * depth
+        self.bytes_per_step = weights // 2 + weights // 16  # packed codes + block scales (activations stay in L2)
+        self.launches_per_step = None
+        self.kernel = "rk_gemm_tc_kernel<nvfp4> (+ pack_nvfp4_kernel, global-scale reduction, bf16 attention)"
+        self.h2d_bytes, self.d2h_bytes = self.x.numel() * 2, self.x.numel() * 2
+        self.host_x = self.x.cpu().pin_memory()
+        self.host_out = torch.empty(self.x.shape, dtype=torch.bfloat16).pin_memory()
+        self.dev_x = torch.empty_like(self.x)
+        self.copies = 1
+
+    def close(self):
+        self.context.__exit__(None, None, None)
+
+    def config(self):
+        c = self.cfg
+        return {"workload": self.name, "layers": c.depth, "width": c.width, "mlp": c.mlp_dim, "heads": c.num_heads,
+                "kv_heads": c.num_kv_heads, "head_dim": c.head_dim, "tokens": self.tokens, "batch": 1,
+                "linears_nvfp4": len(self.report["modules"]), "per_tensor_scale": True,
+                "step": "one prefix pass (all linears NVFP4, activations packed on the fly, bf16 attention)",
+                "timing": "CUDA events around CUDA-graph replays",
+                "l2": "inputs larger than L2: 1.1 GB of packed weights per pass"}
+
+    def device_step(self, i):
+        with torch.no_grad():
+            return self.model(self.x, self.pos)[0]
+
+    def gemm_only_calls(self):
+        return None
+
+    def e2e_step(self, i):
+        self.dev_x.copy_(self.host_x, non_blocking=True)
+        with torch.no_grad():
+            y = self.model(self.dev_x, self.pos)[0]
+        self.host_out.copy_(y, non_blocking=True)
+        torch.cuda.synchronize(self.device)
+
+    def cpu_setup(self, rows):
+        """The seven linears of ONE layer (1/18 of the linear work of a pass), weights prepared once."""
+        from oracle import blockscale as OB
+        from oracle.formats import bf16_round
+
+        c = self.cfg
+        rng = np.random.default_rng(42)
+        shapes = [(c.num_heads * c.head_dim, c.width), (c.num_kv_heads * c.head_dim, c.width),
+                  (c.num_kv_heads * c.head_dim, c.width), (c.width, c.num_heads * c.head_dim),
+                  (c.mlp_dim, c.width), (c.mlp_dim, c.width), (c.width, c.mlp_dim)]
+        self.cpu_layers = []
+        for n_, k_ in shapes:
+            w = bf16_round((rng.standard_normal((n_, k_)) * 0.02).astype(np.float32))
+            packed, sf, _ = OB.pack_nvfp4(w)
+            self.cpu_layers.append((torch.from_numpy(OB.dequant_nvfp4(packed, sf).astype(np.float32)),
+                                    bf16_round(rng.standard_normal((self.tokens, k_)).astype(np.float32))))
+
+    def cpu_step(self):
+        from oracle import blockscale as OB
+
+        ops = 0
+        for w, x in self.cpu_layers:
+            packed, sf, _ = OB.pack_nvfp4(x)
+            (torch.from_numpy(OB.dequant_nvfp4(packed, sf).astype(np.float32)) @ w.T).to(torch.bfloat16)
+            ops += 2 * x.shape[0] * w.shape[0] * w.shape[1]
+        return ops
+
+
+class ExpertWorkload:
+    """cfg5: the W8A8 action-expert loop replayed from one CUDA graph; a step = one action chunk."""
+
+    name = "cfg5_w8a8_expert"
+    bound, peak_factor, dtype = "tensor", 2, "s8xs8->s32"
+
+    def __init__(self, name, device, seed, envs=8, prefix_len=816):
+        from rk_b200.gemma_stack import ActionExpert, GemmaAttention, expert_scope, fuse_norm_quantize
+        from rk_b200.graph import CudaGraphCall
+        from rk_b200.optimizations import quantize_linears
+
+        self.device, self.envs, self.prefix_len = device, envs, prefix_len
+        expert = ActionExpert().init_random(0).to(device).eval()
+        expert.enable_condition_caches()
+        self.expert = expert
+        cfg = expert.cfg
+        gen = torch.Generator().manual_seed(seed)
+        self.noise = torch.randn(envs, expert.chunk, expert.action_dim, generator=gen).to(device)
+        shape = (cfg.depth, envs, cfg.num_kv_heads, prefix_len, cfg.head_dim)
+        self.pk = torch.randn(shape, generator=gen).to(torch.bfloat16).to(device)
+        self.pv = torch.randn(shape, generator=gen).to(torch.bfloat16).to(device)
+        self.flags = (GemmaAttention.fused_rope, GemmaAttention.fused_attention)
+        GemmaAttention.fused_rope = True
+        GemmaAttention.fused_attention = True
+        self.context = quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
+                                        grouped=True, group_views=True)
+        self.report = self.context.__enter__()
+        self.norms = fuse_norm_quantize(expert.stack)
+        self.call = CudaGraphCall(lambda n, k, v: expert(n, k, v), retained_tensors=expert.retained_tensors)
+        m = envs * expert.chunk
+        w, mlp, qd, kvd = cfg.width, cfg.mlp_dim, cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        per_layer = 2 * m * (w * qd + 2 * w * kvd + qd * w + 2 * w * mlp + mlp * w)
+        self.ops_per_step = per_layer * cfg.depth * expert.steps
+        self.bytes_per_step = (w * qd + 2 * w * kvd + qd * w + 3 * w * mlp) * cfg.depth * expert.steps  # int8 weights per chunk
+        self.launches_per_step = None
+        self.kernel = "rk_gemm_tc_kernel<int8> (+ fused norm/quantizers, rk_attn_prefix_kernel)"
+        self.h2d_bytes, self.d2h_bytes = self.noise.numel() * 4, self.noise.numel() * 4
+        self.host_noise = self.noise.cpu().pin_memory()
+        self.host_out = torch.empty(self.noise.shape, dtype=torch.float32).pin_memory()
+        self.dev_noise = torch.empty_like(self.noise)
+        self.copies = 1
+
+    def close(self):
+        from rk_b200.gemma_stack import GemmaAttention, unfuse_norm_quantize
+
+        unfuse_norm_quantize(self.norms)
+        self.context.__exit__(None, None, None)
+        GemmaAttention.fused_rope, GemmaAttention.fused_attention = self.flags
+
+    def config(self):
+        e = self.expert
+        return {"workload": self.name, "layers": e.cfg.depth, "width": e.cfg.width, "mlp": e.cfg.mlp_dim,
+                "chunk": e.chunk, "action_dim": e.action_dim, "euler_steps": e.steps, "envs": self.envs,
+                "prefix_len": self.prefix_len, "linears_w8a8": len(self.report["modules"]),
+                "projection_groups": len(self.report["grouped"]), "fused_norm_quantizers": len(self.norms),
+                "attention": "rk_attn_prefix_kernel (eager fp32-softmax arithmetic)",
+                "step": "one action chunk = 10 denoise steps x 18 layers, one CUDA graph",
+                "timing": "CUDA events around CUDA-graph replays",
+                "l2": "inputs larger than L2: 311 MB of int8 weights per denoise step"}
+
+    def device_step(self, i):
+        with torch.no_grad():
+            return self.expert(self.noise, self.pk, self.pv)
+
+    def gemm_only_calls(self):
+        return None
+
+    def e2e_step(self, i):
+        self.dev_noise.copy_(self.host_noise, non_blocking=True)
+        with torch.no_grad():
+            y = self.call(self.dev_noise, self.pk, self.pv)
+        self.host_out.copy_(y, non_blocking=True)
+        torch.cuda.synchronize(self.device)
+
+    def cpu_setup(self, rows):
+        """The W8A8 linears of ONE layer at one denoise step (1/180 of a chunk's linear work)."""
+        from oracle import integer as OI
+        from oracle.formats import bf16_round
+
+        c = self.expert.cfg
+        m = self.envs * self.expert.chunk
+        rng = np.random.default_rng(42)
+        qd, kvd = c.num_heads * c.head_dim, c.num_kv_heads * c.head_dim
+        shapes = [(qd + 2 * kvd, c.width), (c.width, qd), (2 * c.mlp_dim, c.width), (c.width, c.mlp_dim)]
+        self.cpu_layers = []
+        for n_, k_ in shapes:
+            w = bf16_round((rng.standard_normal((n_, k_)) * 0.02).astype(np.float32))
+            self.cpu_layers.append((OI.quantize_weight(w, 8), bf16_round(rng.standard_normal((m, k_)).astype(np.float32))))
+
+    def cpu_step(self):
+        from oracle import integer as OI
+
+        ops = 0
+        for (b, sb, _), x in self.cpu_layers:
+            a, sa, _ = OI.quantize_rows(x, 8)
+            OI.gemm(a, sa, b, sb, None, 8)
+            ops += 2 * x.shape[0] * (b.shape[0]) * x.shape[1]
+        return ops
+
+
+def make_workload(name, device, seed):
+    if name in LinearWorkload.kinds:
+        return LinearWorkload(name, device, seed)
+    if name == "cfg4_nvfp4_prefix":
+        return PrefixWorkload(name, device, seed)
+    if name == "cfg5_w8a8_expert":
+        return ExpertWorkload(name, device, seed)
+    raise ValueError(name)
+
+
+def graph_of(fn, count, device, stream):
+    """A CUDA graph of `count` consecutive steps fn(0) .. fn(count - 1)."""
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device)
+    side.wait_stream(stream)
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(count):
+            fn(i)
+    stream.wait_stream(side)
+    return graph
+
+
+def time_steps(fn, steps, cycle, device, info=None):
+    """Milliseconds for exactly `steps` steps: CUDA events around replays of a graph holding `cycle`
+    steps (plus one graph with the remainder)."""
+    from rk_b200 import replicas
+
+    stream = torch.cuda.current_stream(device)
+    full, rest = divmod(steps, cycle)
+    main = graph_of(fn, cycle, device, stream) if full else None
+    tail = graph_of(fn, rest, device, stream) if rest else None
+    (main or tail).replay()
+    torch.cuda.synchronize(device)
+    if info is not None:
+        replicas.barrier(info, device)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(full):
+        main.replay()
+    if tail is not None:
+        tail.replay()
+    b.record(stream)
+    if info is not None:
+        replicas.barrier(info, device)
+    torch.cuda.synchronize(device)
+    return a.elapsed_time(b)
+
+
+def roofline_of(work, us_per_step, peaks, gemm_us=None):
+    """Fractions of the measured peaks for one step (and for the GEMM alone when it was timed)."""
+    t = us_per_step * 1e-6
+    tensor_peak = peaks["bf16_tflops"] * work.peak_factor
+    entry = {
+        "us_per_step": us_per_step, "tops": work.ops_per_step / t / 1e12, "gbs": work.bytes_per_step / t / 1e9,
+        "bound": work.bound, "hbm_frac": work.bytes_per_step / t / 1e9 / peaks["hbm_gbs"],
+        "tensor_frac": work.ops_per_step / t / 1e12 / tensor_peak,
+        "tensor_peak": f"{work.peak_factor} x measured bf16 ({tensor_peak:.0f} T/s)", "dtype": work.dtype,
+    }
+    if gemm_us is not None:
+        g = gemm_us * 1e-6
+        entry["gemm_only_us"] = gemm_us
+        entry["gemm_only_tops"] = work.ops_per_step / g / 1e12
+        entry["gemm_only_tensor_frac"] = work.ops_per_step / g / 1e12 / tensor_peak
+        entry["gemm_only_hbm_frac"] = work.gemm_bytes / g / 1e9 / peaks["hbm_gbs"]
+    entry["frac"] = entry["hbm_frac"] if work.bound == "hbm" else entry["tensor_frac"]
+    return entry
+
+
+def quick_leg(name, device, peaks, steps):
+    """Short device-timed run of one workload for the `per_config` block of the default line."""
+    try:
+        work = make_workload(name, device, seed=142)
+    except Exception as error:  # noqa: BLE001 - a leg that cannot be set up is reported, not fatal
+        return {"error": f"{type(error).__name__}: {error}"[:300]}
+    try:
+        for i in range(3):
+            work.device_step(i)
+        torch.cuda.synchronize(device)
+        ms = time_steps(work.device_step, steps, work.copies, device)
+        gemm_us = None
+        calls = work.gemm_only_calls()
+        if calls:
+            for c in calls:
+                c()
+            ms_g = time_steps(lambda i: calls[i % len(calls)](), steps, len(calls), device)
+            gemm_us = ms_g / steps * 1e3
+        entry = roofline_of(work, ms / steps * 1e3, peaks, gemm_us)
+        entry["steps"] = steps
+        entry["config"] = work.config()
+        return entry
+    except Exception as error:  # noqa: BLE001
+        return {"error": f"{type(error).__name__}: {error}"[:300]}
+    finally:
+        if hasattr(work, "close"):
+            work.close()
+        del work
+        torch.cuda.empty_cache()
+
+
+def cpu_sample(work, budget_s, rows=None):
+    """CPU port of a workload on a bounded sample; returns the cpu_baseline object."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows = rows or getattr(work, "n", 0)
+    if isinstance(work, LinearWorkload) and work.n > 4096:
+        rows = 4096  # a quarter of the output channels per pass
+    work.cpu_setup(rows)
+    work.cpu_step()  # warm-up
+    ops, elapsed, passes = 0, 0.0, 0
+    while elapsed < budget_s and passes < 50:
+        t0 = time.perf_counter()
+        ops += work.cpu_step()
+        elapsed += time.perf_counter() - t0
+        passes += 1
+    share = ops / passes / work.ops_per_step
+    return {"value": ops / elapsed / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{passes} passes over {100 * share:.2f}% of a step's operations each (activation quantizer + "
+                      f"dequantize/matmul of the oracle; weights prepared once), {elapsed:.1f} s of CPU time"}
+
+
+def run_generic(args, info, device):
+    """Full benchmark line for a workload other than the headline one."""
+    from rk_b200 import _lib, replicas
+
+    rank, world = info.rank, info.world
+    peaks = load_peaks()
+    work = make_workload(args.workload, device, seed=42 + rank)
+    for i in range(args.warmup):
+        work.device_step(i)
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(info.local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_steps(work.device_step, args.steps, work.copies, device, info)
+    gemm_us = None
+    calls = work.gemm_only_calls()
+    if calls:
+        for c in calls:
+            c()
+        inner = max(len(calls), min(args.steps, 200))
+        gemm_us = time_steps(lambda i: calls[i % len(calls)](), inner, len(calls), device) / inner * 1e3
+    e2e_steps = max(5, min(args.steps, 50))
+    for i in range(3):
+        work.e2e_step(i)
+    replicas.barrier(info, device)
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        work.e2e_step(i)
+    replicas.barrier(info, device)
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    ws = _lib.workspace(device, _lib.WORKSPACE_HEADER)
+    status = _lib.read_status(ws)
+    ms, e2e_ms = replicas.max_over_ranks([ms, e2e_s * 1e3], info, device)
+    value = replicas.whole_job_rate(work.ops_per_step * args.steps, info, ms) / 1e12
+    e2e_value = replicas.whole_job_rate(work.ops_per_step * e2e_steps, info, e2e_ms) / 1e12
+    if rank == 0:
+        entry = roofline_of(work, ms / args.steps * 1e3, peaks, gemm_us)
+        hbm = work.bound == "hbm"
+        roofline = {"kernel": work.kernel, "bound": work.bound,
+                    "achieved": entry["gbs"] if hbm else entry["tops"],
+                    "peak": peaks["hbm_gbs"] if hbm else peaks["bf16_tflops"] * work.peak_factor,
+                    "unit": "GB/s" if hbm else "TFLOP/s", "frac": entry["frac"], "traffic": None,
+                    "peak_source": peaks["source"] + ("" if hbm else f" bf16 x {work.peak_factor}"),
+                    "algorithmic_per_launch": work.bytes_per_step if hbm else work.ops_per_step, "detail": entry}
+        cpu_baseline = None if args.skip_cpu else cpu_sample(work, 12.0)
+        line = {"metric": "quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": work.dtype, "data": "synthetic", "config": work.config(), "clocks": clocks,
+                "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": work.h2d_bytes,
+                        "d2h_bytes_per_step": work.d2h_bytes, "steps": e2e_steps},
+                "gpu_launches": (work.launches_per_step or 0) * args.steps or "one CUDA graph per step",
+                "roofline": roofline, "cpu_baseline": cpu_baseline, "device_status": status}
+        if isinstance(work, ExpertWorkload):
+            line["action_chunk"] = {"ms_device": ms / args.steps, "chunks_per_s": work.envs * world / (ms / args.steps * 1e-3),
+                                    "envs": work.envs}
+        print(json.dumps(line))
+    if hasattr(work, "close"):
+        work.close()
+
+
+def run_reference_generic(args, rank):
+    """CPU arm of a non-headline workload: the oracle port, bounded per step."""
+    if rank != 0:
+        return
+    name = args.workload
+    # the CPU port needs the shapes only: the workload objects are built without their CUDA set-up
+    if name in LinearWorkload.kinds:
+        work = LinearWorkload.__new__(LinearWorkload)
+        work.name = name
+        work.m, work.n, work.k, _, work.bound, work.peak_factor, work.dtype = LinearWorkload.kinds[name]
+        work.ops_per_step = 2 * work.m * work.n * work.k
+        rows = work.n if work.n <= 4096 else 4096
+        config = {"workload": name, "M": work.m, "N": work.n, "K": work.k}
+    elif name == "cfg4_nvfp4_prefix":
+        from rk_b200.gemma_stack import gemma_2b
+
+        work = PrefixWorkload.__new__(PrefixWorkload)
+        work.cfg = gemma_2b()
+        c = work.cfg
+        qd, kvd = c.num_heads * c.head_dim, c.num_kv_heads * c.head_dim
+        work.ops_per_step = 2 * 816 * (c.width * qd + 2 * c.width * kvd + qd * c.width + 3 * c.width * c.mlp_dim) * c.depth
+        rows, config = None, {"workload": name, "layers": c.depth, "tokens": 816}
+    else:
+        from rk_b200.gemma_stack import gemma_300m
+
+        work = ExpertWorkload.__new__(ExpertWorkload)
+        work.envs = 8
+        work.expert = type("E", (), {"cfg": gemma_300m(), "chunk": 50, "steps": 10})()
+        c = work.expert.cfg
+        qd, kvd = c.num_heads * c.head_dim, c.num_kv_heads * c.head_dim
+        work.ops_per_step = 2 * 400 * (c.width * qd + 2 * c.width * kvd + qd * c.width + 3 * c.width * c.mlp_dim) * c.depth * 10
+        rows, config = None, {"workload": name, "layers": c.depth, "envs": 8}
+    torch.set_num_threads(os.cpu_count() or 1)
+    work.cpu_setup(rows)
+    work.cpu_step()
+    times, ops = [], 0
+    budget = 150.0 / max(1, args.warmup + args.steps)
+    for i in range(args.warmup + args.steps):
+        t0, done = time.perf_counter(), 0
+        while True:
+            done += work.cpu_step()
+            if time.perf_counter() - t0 >= min(budget, 2.0):
+                break
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+            ops += done
+    total = sum(times)
+    value = ops / total / 1e12
+    sample = (f"each step repeats the oracle port (activation quantizer + dequantize/matmul, weights prepared once) over "
+              f"a bounded part of the workload for {min(budget, 2.0):.1f} s; {total:.1f} s of CPU time in {args.steps} steps")
+    print(json.dumps({
+        "impl": "reference", "metric": "quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": work.dtype, "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
+# ------------------------------------------------------------------------------------------------
+# The headline workload (cfg2)
+# ------------------------------------------------------------------------------------------------
 def make_inputs(device, copies, seed):
     """Seeded synthetic weights (N(0, 0.02)) and activations (N(0, 1)); weights packed on the GPU."""
     from rk_b200.w4a16_linear import pack_weight
@@ -126,16 +716,10 @@ def make_inputs(device, copies, seed):
     return weights, xs
 
 
-def cpu_port_once(x, packed, scales):
-    """The oracle port on host cores: dequantize (int4 codes x bf16 group scales) then fp32 matmul."""
-    from oracle import w4a16 as OW
-
-    w = torch.from_numpy(OW.dequantize(packed, scales))
-    return (torch.from_numpy(x) @ w.T).to(torch.bfloat16)
-
-
 def time_cpu_baseline(budget_s=12.0):
-    """Bounded sample: full-size weights, every M of the workload, as many passes as fit the budget."""
+    """Bounded sample: full-size weights, every M of the workload, as many passes as fit the budget.
+    The port dequantizes (int4 codes x bf16 group scales -> fp32, single-threaded numpy) and then
+    multiplies in fp32 on all cores, per launch, as a stateless operator would; both parts are timed."""
     from oracle import w4a16 as OW
     from oracle.formats import bf16_round
 
@@ -144,18 +728,33 @@ def time_cpu_baseline(budget_s=12.0):
     w = bf16_round((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
     packed, scales, _ = OW.pack_weight(w)
     xs = {m: bf16_round(rng.standard_normal((m, K)).astype(np.float32)) for m in M_LIST}
-    cpu_port_once(xs[1], packed, scales)  # warm-up
-    ops, elapsed, passes = 0, 0.0, 0
-    while elapsed < budget_s and passes < 8:
-        t0 = time.perf_counter()
+    OW.dequantize(packed, scales)  # warm-up
+    ops, t_deq, t_mm, passes = 0, 0.0, 0.0, 0
+    while t_deq + t_mm < budget_s and passes < 8:
         for m in M_LIST:
-            cpu_port_once(xs[m], packed, scales)
-        elapsed += time.perf_counter() - t0
+            t0 = time.perf_counter()
+            wd = torch.from_numpy(OW.dequantize(packed, scales))
+            t1 = time.perf_counter()
+            (torch.from_numpy(xs[m]) @ wd.T).to(torch.bfloat16)
+            t2 = time.perf_counter()
+            t_deq += t1 - t0
+            t_mm += t2 - t1
         ops += sum(algorithmic_ops(m) for m in M_LIST)
         passes += 1
+    elapsed = t_deq + t_mm
     return {"value": ops / elapsed / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{passes} full passes of the workload (dequantize + fp32 matmul per launch), "
-                      f"{elapsed:.1f} s of CPU time"}, elapsed / passes
+            "matmul_only_value": ops / t_mm / 1e12,
+            "sample": f"{passes} full passes of the workload, {elapsed:.1f} s of CPU time: {100 * t_deq / elapsed:.0f}% in the "
+                      f"per-launch int4 -> fp32 dequantize (single-threaded numpy), {100 * t_mm / elapsed:.0f}% in the fp32 "
+                      f"matmul on all cores; `matmul_only_value` counts the matmul time alone"}, elapsed / passes
+
+
+def cpu_port_once(x, packed, scales):
+    """The oracle port on host cores: dequantize (int4 codes x bf16 group scales) then fp32 matmul."""
+    from oracle import w4a16 as OW
+
+    w = torch.from_numpy(OW.dequantize(packed, scales))
+    return (torch.from_numpy(x) @ w.T).to(torch.bfloat16)
 
 
 def run_reference(args, rank, budget_s=150.0):
@@ -186,7 +785,8 @@ def run_reference(args, rank, budget_s=150.0):
     ops = sum(2 * m * rows * K for m in M_LIST) * args.steps
     value = ops / total / 1e12
     sample = (f"each step covers the first {rows} of {N} output channels at every M "
-              f"({100.0 * rows / N:.1f}% of the workload's operations), {total:.1f} s of CPU time in {args.steps} steps")
+              f"({100.0 * rows / N:.1f}% of the workload's operations; dequantize + fp32 matmul per launch), "
+              f"{total:.1f} s of CPU time in {args.steps} steps")
     line = {
         "impl": "reference", "metric": "quantized_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
@@ -248,14 +848,21 @@ def chunk_latency(device, reps=13, warmups=5, envs=8, prefix_len=816):
     with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True,
                           grouped=True, group_views=True) as report:
         norms = fuse_norm_quantize(expert.stack)  # adaRMSNorm + modulation + row quantizer as one kernel
-        int8_ms, samples = measure(lambda n, k, v: expert(n, k, v))
+        sdpa_ms, _ = measure(lambda n, k, v: expert(n, k, v))
+        GemmaAttention.fused_attention = True  # attention as one tcgen05 kernel with the eager arithmetic
+        try:
+            int8_ms, samples = measure(lambda n, k, v: expert(n, k, v))
+        finally:
+            GemmaAttention.fused_attention = False
         unfuse_norm_quantize(norms)
         swapped = len(report["modules"])
         groups = len(report["grouped"])
     GemmaAttention.fused_rope = False
-    return {"p50_ms": int8_ms, "bf16_p50_ms": bf16_ms, "chunks_per_s": envs / (int8_ms * 1e-3), "envs": envs,
+    return {"p50_ms": int8_ms, "bf16_p50_ms": bf16_ms, "w8a8_with_torch_sdpa_p50_ms": sdpa_ms,
+            "chunks_per_s": envs / (int8_ms * 1e-3), "envs": envs,
             "steps": expert.steps, "prefix_len": prefix_len, "linears_w8a8": swapped, "projection_groups": groups, "fused_norm_quantizers": len(norms),
-            "fused_rope_cache_update": True, "cached_conditions": len(expert._conditions),
+            "fused_rope_cache_update": True, "attention": "rk_attn_prefix_kernel (bf16 arm: torch SDPA)",
+            "cached_conditions": len(expert._conditions),
             "cached_condition_projections": sum(len(n.projection_cache) for n in expert.adaptive_norms()), "reps": reps,
             "timing": "wall clock around CudaGraphCall (input copy, graph replay, output clone), synchronised"}
 
@@ -275,8 +882,8 @@ def column_parallel_leg(info, device, reps=30):
     full = full.to(device).requires_grad_(False)
     x = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(device)
     make = lambda lin: Fp8CutlassLinear.from_linear(lin, "linear", "gate_up")
-    sharded = replicas.ColumnParallelLinear(full, info, make)
     single = make(full)
+    sharded = replicas.ColumnParallelLinear(single, info)
 
     def timed(fn):
         for _ in range(3):
@@ -294,7 +901,7 @@ def column_parallel_leg(info, device, reps=30):
         us_sharded = timed(lambda: sharded(x))
         us_single = timed(lambda: single(x))
         a, b = sharded(x).float(), single(x).float()
-        rel = float((a - b).norm() / b.norm())  # slabs carry their own per-tensor weight scale
+        rel = float((a - b).norm() / b.norm())  # the slabs share the one-GPU codes and scale: exactly 0
     us_sharded, us_single = replicas.max_over_ranks([us_sharded, us_single], info, device)
     return {"op": "fp8 linear (dynamic activation scale) M=816 N=16384 K=2048", "ranks": info.world,
             "us_column_parallel_with_all_gather": us_sharded, "us_one_gpu": us_single,
@@ -311,16 +918,24 @@ def workload_config(copies):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=6000)
-    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=None)
+    parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="cfg2_w4a16_g128", choices=["cfg2_w4a16_g128"])
+    parser.add_argument("--workload", default="cfg2_w4a16_g128", choices=WORKLOADS)
     parser.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
     parser.add_argument("--skip-chunk", action="store_true", help="omit the action-chunk latency leg")
+    parser.add_argument("--skip-per-config", action="store_true", help="omit the short runs of the other workloads")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch the timed steps directly instead of replaying CUDA graphs (for profilers; "
                              "host launch cost then sits inside the timed region)")
     args = parser.parse_args()
+    headline = args.workload == "cfg2_w4a16_g128"
+    defaults = {"cfg2_w4a16_g128": (6000, 20), "cfg1_w8a8": (4000, 20), "cfg3_fp8": (500, 10), "cfg3_mxfp8": (500, 10),
+                "cfg4_nvfp4_prefix": (20, 3), "cfg5_w8a8_expert": (13, 5)}[args.workload]
+    if args.steps is None:
+        args.steps = defaults[0]
+    if args.warmup is None:
+        args.warmup = defaults[1]
     if args.warmup < 3:
         args.warmup = 3
 
@@ -330,17 +945,24 @@ def main():
     rank, world, local_rank = info.rank, info.world, info.local_rank
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        if headline:
+            run_reference(args, rank)
+        else:
+            run_reference_generic(args, rank)
         return
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
     from rk_b200 import _lib
-    from rk_b200.w4a16_linear import W4A16Linear, linear_w4a16
+    from rk_b200.w4a16_linear import W4A16Linear
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     replicas.init(info, device)
+    if not headline:
+        run_generic(args, info, device)
+        replicas.finish()
+        return
 
     copies = default_copies()
     weights, xs = make_inputs(device, copies, seed=42 + rank)
@@ -399,9 +1021,6 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        deadline = time.perf_counter() + 3.0  # the first sample marks that sampling is live
-        while not sampler.samples and time.perf_counter() < deadline:
-            time.sleep(0.02)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
@@ -476,6 +1095,8 @@ def main():
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
+    del layers, weights
+    torch.cuda.empty_cache()
 
     # second half of the headline metric: p50 action-chunk latency of the W8A8 expert loop
     chunk = None
@@ -493,8 +1114,17 @@ def main():
     value = replicas.whole_job_rate(step_ops * args.steps, info, elapsed_ms) / 1e12
     e2e_value = replicas.whole_job_rate(step_ops * e2e_steps, info, e2e_ms) / 1e12
 
+    # the other benchmark configurations, device-timed over a short run each (single-GPU runs only)
+    peaks = load_peaks()
+    per_config = None
+    if world == 1 and not args.skip_per_config:
+        torch.cuda.empty_cache()
+        per_config = {}
+        for name, steps in (("cfg1_w8a8", 400), ("cfg3_fp8", 60), ("cfg3_mxfp8", 60), ("cfg4_nvfp4_prefix", 5),
+                            ("cfg5_w8a8_expert", 5)):
+            per_config[name] = quick_leg(name, device, peaks, steps)
+
     if rank == 0:
-        peaks = load_peaks()
         dominant = max(M_LIST, key=lambda m: per_m_ms[m])
         per_case = {}
         for m in M_LIST:
@@ -506,6 +1136,9 @@ def main():
             }
         d = per_case[f"M{dominant}"]
         hbm_bound = d["hbm_frac"] >= d["bf16_frac"]
+        # the HBM-class launches (M = 1, 8, 50) together, time-weighted: the other view of the same step
+        small = [m for m in M_LIST if m <= 64]
+        t_small = sum(per_m_ms[m] for m in small) * 1e-3
         roofline = {
             "kernel": f"{'rk_gemm_w4a16_fold_kernel' if dominant > 64 else 'rk_gemm_w4a16_kernel'} (M={dominant})",
             "bound": "hbm" if hbm_bound else "tensor",
@@ -514,8 +1147,12 @@ def main():
             "unit": "GB/s" if hbm_bound else "TFLOP/s",
             "frac": d["hbm_frac"] if hbm_bound else d["bf16_frac"],
             "traffic": NCU_DRAM_TRAFFIC.get(dominant),
+            "traffic_source": "ncu capture summarised in profiles/w4a16_cfg2_kernel_metrics.md (not re-measured here)",
             "peak_source": peaks["source"],
             "algorithmic_per_launch": algorithmic_bytes(dominant) if hbm_bound else algorithmic_ops(dominant),
+            "hbm_class_launches": {"M": small, "share_of_step_time": t_small / (sum(per_m_ms.values()) * 1e-3),
+                                   "gbs": sum(algorithmic_bytes(m) for m in small) / t_small / 1e9,
+                                   "hbm_frac": sum(algorithmic_bytes(m) for m in small) / t_small / 1e9 / peaks["hbm_gbs"]},
         }
         cpu_baseline = None
         if not args.skip_cpu:
@@ -530,7 +1167,7 @@ def main():
                     "d2h_bytes_per_step": sum(m * N * 2 for m in M_LIST), "steps": e2e_steps},
             "gpu_launches": timed_launches, "roofline": roofline, "per_case": per_case,
             "cpu_baseline": cpu_baseline, "device_status": status, "action_chunk": chunk,
-            "column_parallel": column_parallel,
+            "per_config": per_config, "column_parallel": column_parallel,
         }
         print(json.dumps(line))
     replicas.finish()

@@ -5,7 +5,9 @@
  *   - takes plain device pointers, sizes and a CUDA stream (a cudaStream_t passed as void*),
  *   - launches on that stream and returns without synchronising,
  *   - never allocates, frees or synchronises device memory (the caller owns every buffer,
- *     including the scratch "workspace"), so calls can be captured in a CUDA graph,
+ *     including the scratch "workspace"), so calls can be captured in a CUDA graph.  Two
+ *     exceptions, both test aids: rk_read_status synchronises the stream and copies one word
+ *     back; rk_probe_rcp_approx_448 allocates one word, runs on the default stream and synchronises,
  *   - returns RK_OK (0) or a negative RK_E* code; rk_last_error_string() describes the last
  *     failure on the calling thread.
  * There is no CPU fallback: unsupported shapes are errors.
@@ -71,8 +73,17 @@ size_t rk_workspace_bytes(int op, int64_t m, int64_t n, int64_t k);
  * Reference: `scale_storage_size`, blackwell/csrc/mxfp8_common.cuh:14-16. */
 size_t rk_sf_bytes(int64_t rows, int64_t groups);
 /* Reads (synchronously, after synchronising `stream`) and clears the device status word at the
- * start of `workspace`.  Returns RK_OK or RK_EDEVICE; *code receives the raw device code. */
+ * start of `workspace`; workspace == NULL reads the status word of the scratch array built into the
+ * library (rk_gemm_int4_noalloc) on the current device.  Returns RK_OK or RK_EDEVICE; *code
+ * receives the raw device code. */
 int rk_read_status(void* workspace, int* code, void* stream);
+/* Test aid for the give-up path of the kernels' bounded waits (no reference counterpart).  While
+ * `on` is non-zero, the tensor-core GEMM entry points rk_gemm_int / _fp8 / _mxfp8 / _nvfp4 launch
+ * with every wait limited to `spin_limit` polls (64..2^21) and with a first pipeline stage that is
+ * announced larger than what is copied, so its wait runs out: the kernel records a code in the
+ * status word, drains and returns normally (nothing traps; the context stays usable), and
+ * rk_read_status returns RK_EDEVICE.  Process-wide; switch it off again with on = 0. */
+int rk_debug_wait_expiry(int on, int spin_limit);
 /* Bit pattern of rcp.approx.ftz.f32(448.0f) on the current device (synchronous; test aid for the
  * MXFP8 block-scale formula, blackwell/csrc/mxfp8_common.cuh:25). */
 int rk_probe_rcp_approx_448(uint32_t* bits);
@@ -144,12 +155,14 @@ int rk_gemm_int_acc(const void* a, const void* b, int32_t* acc, int64_t m, int64
  * which rk_gemm_int places in the caller's workspace, go to a device array built into the library
  * (8 MiB + 4 KiB; every GPU that loads the library holds it until the process exits), so there is
  * no workspace argument and nothing is allocated or freed, here or in any routine it calls.
- *   Limit: (m + n) * kpad <= 8 MiB, otherwise RK_EUNSUPPORTED (use rk_gemm_int instead).
+ *   Limit: rk_workspace_bytes(RK_OP_W4A4, m, n, kpad) = 256 + round_up(m + n, 16) * kpad, rounded up
+ *   to 256, must not exceed 8 MiB + 4 KiB; otherwise RK_EUNSUPPORTED (use rk_gemm_int instead).
  *   The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
  *   that first call outside any stream capture.
  *   All calls on a device share the one array: calls that may overlap on the GPU (different
  *   streams, or graphs replayed concurrently) race and must be serialised by the caller.
- *   The head of the array holds the device status word; it is cleared at the start of each call.
+ *   The head of the array holds the device status word; it is cleared at the start of each call
+ *   and read with rk_read_status(NULL, ...).
  * Arguments as rk_gemm_int with bits = 4. */
 int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* b, const float* sb, const void* bias,
                          void* out, int64_t m, int64_t n, int64_t kpad, int tactic, void* stream);
@@ -259,7 +272,7 @@ int rk_nvfp4_global_scale(const void* x, int64_t elements, float* scale_out, voi
                           size_t workspace_bytes, void* stream);
 /* out = bf16( alpha * sum over blocks (sfa * sfb * sum_k a*b) (+ bias[n]) ), alpha = *ga * *gb
  * (each NULL = 1).  Replaces `linear_forward_packed_gemm_bf16` / `gemm_bf16::run`
- * (blackwell/csrc/fp4_cutlass_linear.cu:1199-1447, 1751-1848).  k % 32 == 0, n % 8 == 0. */
+ * (blackwell/csrc/fp4_cutlass_linear.cu:1199-1447, 1751-1848).  k % 64 == 0, n % 8 == 0. */
 int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, const void* b, const void* sfb,
                   const float* gb, const void* bias, void* out, int64_t m, int64_t n, int64_t k, int tactic,
                   void* workspace, size_t workspace_bytes, void* stream);
@@ -282,6 +295,32 @@ int rk_rope_cache_update(const void* q, int64_t q_stride, const void* k, int64_t
                          int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
                          int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
                          void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* stream);
+
+/* The same, additionally writing the fresh value rows into a TRANSPOSED value cache
+ * vt_cache bf16 [batch, kv_heads, head_dim, vt_pitch] (column prefix + token), which is the layout
+ * rk_attention_prefix reads.  vt_pitch >= prefix + tokens. */
+int rk_rope_cache_update_vt(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                            int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
+                            int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
+                            void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* vt_cache,
+                            int64_t vt_pitch, void* stream);
+
+/* Attention of `tokens` fresh query tokens per sequence over kv_len cached keys / values (all keys
+ * visible to all queries), grouped-query.  Stands in for the eager attention of the action expert
+ * (models/pi05/modeling_gemma.py:247-274) with its arithmetic: scores = bf16(q . k) * scaling in
+ * bf16, softmax in fp32 over all keys, probabilities rounded to bf16, output = bf16 of the fp32 sum
+ * of p * v.  One launch: QK^T and PV on the tensor cores, keys split over a thread-block cluster
+ * whose CTAs exchange the softmax statistics and sum their partial outputs on chip.
+ *   q bf16 [batch, tokens, heads, 256] (the token-major output of rk_rope_cache_update);
+ *   k_cache bf16 [batch, kv_heads, cache_rows, 256]; vt_cache bf16 [batch, kv_heads, 256, vt_pitch]
+ *   (values transposed; columns at and beyond kv_len must hold finite numbers, e.g. zeros);
+ *   out bf16 [batch, tokens, heads, 256].  head_dim == 256; tokens <= 128; kv_len <= 2048,
+ *   kv_len <= cache_rows, kv_len <= vt_pitch, vt_pitch % 8 == 0; heads % kv_heads == 0;
+ *   needs a workspace (header only). */
+int rk_attention_prefix(const void* q, const void* k_cache, const void* vt_cache, void* out, int64_t batch,
+                        int64_t tokens, int64_t heads, int64_t kv_heads, int64_t head_dim, int64_t cache_rows,
+                        int64_t vt_pitch, int64_t kv_len, float scaling, void* workspace, size_t workspace_bytes,
+                        void* stream);
 
 #ifdef __cplusplus
 }

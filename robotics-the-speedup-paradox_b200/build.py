@@ -50,11 +50,8 @@ def _digest(paths, flags):
     return h.hexdigest()
 
 
-def build(arch="10.0a", build_dir=None, output=DEFAULT_OUTPUT, verbose=False, force=False, trace=False):
-    """Compile every translation unit and link the shared library.  Returns the library path.
-
-    `trace=True` builds the developer variant whose W4A16 kernels record per-role clock stamps
-    (`-DRK_TRACE`, read back through `rk_trace_read`); give it its own `output` and `build_dir`."""
+def build(arch="10.0a", build_dir=None, output=DEFAULT_OUTPUT, verbose=False, force=False):
+    """Compile every translation unit and link the shared library.  Returns the library path."""
     nvcc = _nvcc()
     build_dir = Path(build_dir) if build_dir else ROOT / "build"
     build_dir.mkdir(parents=True, exist_ok=True)
@@ -62,8 +59,6 @@ def build(arch="10.0a", build_dir=None, output=DEFAULT_OUTPUT, verbose=False, fo
     sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
     deps = sorted(CSRC.glob("*.cu*")) + sorted(CSRC.glob("*.h")) + sorted(INCLUDE.glob("*.h"))
     flags = _arch_flags(arch) + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-    if trace:
-        flags.append("-DRK_TRACE")
     stamp = build_dir / "librk_b200.sha256"
     digest = _digest(deps, flags)
     if not force and output.exists() and stamp.exists() and stamp.read_text() == digest:
@@ -98,19 +93,11 @@ def main():
     parser.add_argument("--build-dir", type=Path)
     parser.add_argument("--output", type=Path, default=DEFAULT_OUTPUT)
     parser.add_argument("--force", action="store_true")
-    parser.add_argument("--trace", action="store_true",
-                        help="developer build with per-role clock stamps in the W4A16 kernels; writes "
-                             "rk_b200/librk_b200_trace.so unless --output is given")
     parser.add_argument("--verbose", action="store_true")
     args = parser.parse_args()
     if args.arch != "10.0a":
         parser.error("these kernels use tcgen05 / TMEM and build for 10.0a only")
-    if args.trace:
-        if args.output == DEFAULT_OUTPUT:
-            args.output = DEFAULT_OUTPUT.with_name("librk_b200_trace.so")
-        if args.build_dir is None:
-            args.build_dir = ROOT / "build" / "trace"
-    print(build(args.arch, args.build_dir, args.output, args.verbose, args.force, args.trace))
+    print(build(args.arch, args.build_dir, args.output, args.verbose, args.force))
 
 
 if __name__ == "__main__":

@@ -30,18 +30,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
-// Developer aid, compiled out unless RK_TRACE is defined: CTA (0,0) records SM-clock timestamps of
-// each role's progress per pipeline step into a device array that rk_trace_read() copies back.
-#ifdef RK_TRACE
-__device__ long long rk_trace_buf[32 * 64];
-#define RK_TRACE_REC(slot, g)                                                        \
-  do {                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (g) < 64) rk_trace_buf[(slot) * 64 + (g)] = clock64(); \
-  } while (0)
-#else
-#define RK_TRACE_REC(slot, g) do { } while (0)
-#endif
-
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -91,13 +79,13 @@ constexpr uint32_t kWaitSpinFast = 2048;
 constexpr uint32_t kWaitSpinMax = 1u << 21;  // with 256 ns sleeps: roughly half a second
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  int* status, int code) {
+                                                  int* status, int code, uint32_t spin_max = kWaitSpinMax) {
   // In steady state most waits find their phase already complete.  The non-blocking probe answers
   // that case an order of magnitude faster than the potentially-blocking form (measured: a
   // try_wait that succeeds at once still costs a few hundred cycles), so probe first and park
   // only when there is something to wait for.
   if (mbar_test_wait(bar, parity)) return true;
-  for (uint32_t it = 0; it < kWaitSpinMax; ++it) {
+  for (uint32_t it = 0; it < spin_max; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > kWaitSpinFast) {
       if (*abort_flag) return false;
@@ -162,8 +150,9 @@ struct Ring {
 // leaving a loop at different iterations would strand the others on the hardware barrier).
 __device__ __forceinline__ bool mbar_wait_group(uint32_t bar, uint32_t parity, bool is_leader, int named_id,
                                                 int nthreads, int* abort_flag, int* status, int code,
-                                                volatile int* verdict, uint32_t iter) {
-  if (is_leader) verdict[iter & 1] = mbar_wait_bounded(bar, parity, abort_flag, status, code) ? 1 : 0;
+                                                volatile int* verdict, uint32_t iter,
+                                                uint32_t spin_max = kWaitSpinMax) {
+  if (is_leader) verdict[iter & 1] = mbar_wait_bounded(bar, parity, abort_flag, status, code, spin_max) ? 1 : 0;
   asm volatile("bar.sync %0, %1;" ::"r"(named_id), "r"(nthreads) : "memory");
   return verdict[iter & 1] != 0;
 }

@@ -8,6 +8,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "rk_attn.cuh"
 #include "rk_gemm_tc.cuh"
 #include "rk_gemm_tc2.cuh"
 #include "rk_gemm_w4.cuh"
@@ -31,6 +32,11 @@ bool use_pdl() {
   }();
   return on;
 }
+
+// Test aid (rk_debug_wait_expiry): a shortened spin limit and a first pipeline stage whose byte
+// count is never met, so that the bounded waits of the next GEMM launches run out.
+int g_debug_wait_limit = 0;
+int g_debug_stall = 0;
 
 // ------------------------------------------------------------------ tensor maps
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -177,7 +183,29 @@ int pow2_at_least(int v, int lo) {
 // ------------------------------------------------------------------ tile selection
 struct Plan {
   int swap, bn, tiles_a, tiles_b, splits, stages, tmem_cols, acc_stride, acc_bufs, out_bufs, smem_bytes, grid_x;
+  int sfb_blocks;
 };
+
+// Block-scaled kinds, rows on the MMA N axis cut into equal tiles of `bn` rows.  Scale factors live in
+// 128-row blocks with one 32-bit TMEM column per 32 rows; the kernel fetches the (up to two) blocks a
+// tile touches and offsets the scale-factor column address of the MMA.  That offset must be EVEN:
+// tcgen05.mma raised "misaligned address" for a B scale-factor address at an odd column on B200, so
+// tiles start on multiples of 64 rows.  Tiles of at most 192 rows leave room in TMEM for two
+// accumulator buffers next to the scale columns, which lets the epilogue of one tile overlap the
+// MMAs of the next.
+int block_scaled_tile_rows(int64_t rows) {
+  constexpr int align = 64;
+  if (rows <= 192) return static_cast<int>(round_up(rows, 32));
+  int best = 128;
+  double best_cost = 1e30;
+  for (int bn = 192; bn >= 64; bn -= align) {
+    const int64_t tiles = (rows + bn - 1) / bn;
+    // operand traffic from L2 per tile is proportional to (128 + bn); tensor time to bn
+    const double cost = static_cast<double>(tiles) * (0.5 * (128 + bn) + bn);
+    if (cost < best_cost) best_cost = cost, best = bn;
+  }
+  return best;
+}
 
 // `tactic` only nudges the shape of the decomposition (it can never change integer results and
 // only reorders fp32 partial sums): bit 0 forbids swap, bit 1 forbids split-K, bit 2 halves bn.
@@ -186,10 +214,24 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   const bool block_scaled = kind == KIND_MXF8 || kind == KIND_NVF4;
   // Weights on the 128-lane axis whenever the activation row count fits one or a few
   // B-role tiles; otherwise activations take the 128-lane axis and weights use wide tiles.
-  // Block-scaled kinds address scale factors in 128-row blocks, so a B-role tile that is not the
-  // only one must start on a multiple of 128 rows: they swap only when one tile covers m.
-  pl.swap = (m <= (block_scaled ? 256 : 1024) && !(tactic & 1)) ? 1 : 0;
-  if (pl.swap) {
+  pl.swap = (m <= 1024 && !(tactic & 1)) ? 1 : 0;
+  pl.sfb_blocks = 0;
+  if (block_scaled) {
+    // A-role tiles are whole 128-row scale blocks; B-role tiles start on multiples of 64 rows
+    const int64_t rows_b = pl.swap ? m : n;
+    pl.bn = block_scaled_tile_rows(rows_b);
+    if ((tactic & 4) && pl.bn > 128) pl.bn = 128;
+    if (!pl.swap) pl.bn = static_cast<int>(round_up(pl.bn, 64)) > 192 ? 192 : static_cast<int>(round_up(pl.bn, 64));
+    pl.tiles_a = static_cast<int>(((pl.swap ? n : m) + 127) / 128);
+    pl.tiles_b = static_cast<int>((rows_b + pl.bn - 1) / pl.bn);
+    // blocks a tile can touch: worst case over the tile starts j * bn
+    int worst = 1;
+    for (int j = 0; j < pl.tiles_b && j < 8; ++j) {
+      const int first = (j * pl.bn) >> 7, last = (j * pl.bn + pl.bn - 1) >> 7;
+      if (last - first + 1 > worst) worst = last - first + 1;
+    }
+    pl.sfb_blocks = worst;
+  } else if (pl.swap) {
     // fewest <=256-row chunks; a lone chunk may be any multiple of 16 rows (32 when block-scaled),
     // several chunks must be multiples of 32 rows (the TMA store works on 32-row boxes)
     int chunks = static_cast<int>((m + 255) / 256);
@@ -219,9 +261,10 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
     pl.tiles_a = static_cast<int>((m + 127) / 128);
     pl.tiles_b = static_cast<int>((n + pl.bn - 1) / pl.bn);
   }
-  // TMEM: accumulator buffers (+ 48 scale-factor columns for the block-scaled kinds)
+  // TMEM: accumulator buffers (+ scale-factor columns for the block-scaled kinds: 16 for the A
+  // role, then 4 per K chunk and 128-row block of the B role)
   pl.acc_stride = static_cast<int>(round_up(pl.bn, 32));
-  const int sf_cols = block_scaled ? 48 : 0;
+  const int sf_cols = block_scaled ? 16 + 4 * (kind == KIND_NVF4 ? 4 : 1) * pl.sfb_blocks : 0;
   pl.acc_bufs = (2 * pl.acc_stride + sf_cols <= 512) ? 2 : 1;
   pl.tmem_cols = pow2_at_least(pl.acc_bufs * pl.acc_stride + sf_cols, 32);
   // split-K across a cluster when the tiles cannot occupy the machine; >= 2 K blocks per CTA
@@ -234,7 +277,7 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
     if (s > 1) pl.splits = s;
   }
   // shared memory: pipeline stages + output staging + per-tile vectors
-  const int stage = gemm_stage_bytes(kind, pl.bn);
+  const int stage = gemm_stage_bytes(kind, pl.bn, pl.sfb_blocks);
   pl.out_bufs = 2;
   int budget = kSmemBudget - kVecBytes - pl.out_bufs * kOutBufBytes;
   if (budget / stage < 4 && (kSmemBudget - kVecBytes - kOutBufBytes) / stage >= 4) {
@@ -299,8 +342,8 @@ int two_cta_mode() {
 }
 
 template <int KIND>
-int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out, const Gemm2Params& p,
-               int smem, cudaStream_t st) {
+int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out, const CUtensorMap& tm_sfa,
+               const CUtensorMap& tm_sfb, const Gemm2Params& p, int smem, cudaStream_t st) {
   static bool configured_dev[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -327,7 +370,7 @@ int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorM
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc2_kernel<KIND>, tm_a, tm_b, tm_out, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc2_kernel<KIND>, tm_a, tm_b, tm_out, tm_sfa, tm_sfb, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(RK_ECUDA, "rk_gemm_tc2_kernel launch: %s", cudaGetErrorString(e));
@@ -365,19 +408,42 @@ int run_tc(const TcArgs& a) {
   int rc = carve_workspace(a.workspace, a.workspace_bytes, &ws, a.who);
   if (rc != RK_OK) return rc;
   const int kblocks = static_cast<int>((a.k_bytes + kStageKBytes - 1) / kStageKBytes);
-  const bool two_cta_kind = (a.kind == KIND_I8 || a.kind == KIND_F8) && a.acc_out == nullptr && a.out != nullptr;
+  const bool block_scaled = a.kind == KIND_MXF8 || a.kind == KIND_NVF4;
+  const bool two_cta_kind = a.acc_out == nullptr && a.out != nullptr;
   const int mode = two_cta_mode();
-  if (two_cta_kind && mode != 0 && ((mode == 1 && a.m > 256) || a.m > 1024) && a.n >= 128) {
+  // CTA pairs from 512 activation rows on (two 256-row pair tiles): one CTA cannot take operand bytes
+  // from L2 fast enough to keep its tensor pipe busy, a pair halves the weight bytes per SM
+  static const int64_t pair_min_m = [] {
+    const char* v = std::getenv("RK_B200_TWO_CTA_MIN_M");
+    return v ? static_cast<int64_t>(std::atoll(v)) : static_cast<int64_t>(512);
+  }();
+  if (two_cta_kind && mode != 0 && ((mode == 1 && a.m > 256) || a.m >= pair_min_m) && a.n >= 128) {
     Gemm2Params p2{};
     p2.m = static_cast<int>(a.m);
     p2.n = static_cast<int>(a.n);
     p2.kblocks = kblocks;
     p2.k_valid_mmas_last = (a.mma_bytes_last + 31) / 32;
     if (p2.k_valid_mmas_last < 1 || p2.k_valid_mmas_last > 4) p2.k_valid_mmas_last = 4;
-    p2.bn = ((a.tactic & 4) || a.n < 256) ? 128 : 256;
+    static const int bn_env = [] {
+      const char* v = std::getenv("RK_B200_PAIR_BN");
+      return v ? std::atoi(v) : 0;
+    }();
+    if (!block_scaled) {
+      p2.bn = ((a.tactic & 4) || a.n < 256) ? 128 : 256;
+      p2.acc_bufs = 2;
+    } else {
+      // the scale factors need tensor-memory columns of their own: 192-column tiles keep two
+      // accumulator buffers (the epilogue overlaps the next tile's MMAs), 256-column tiles have
+      // one and pay for it with an exposed epilogue, which only long K loops amortise
+      p2.bn = ((a.tactic & 4) || a.n < 192) ? 128 : (kblocks >= 48 ? 256 : 192);
+      if (bn_env == 128 || bn_env == 192 || bn_env == 256) p2.bn = bn_env;
+      p2.acc_bufs = p2.bn == 256 ? 1 : 2;
+    }
+    p2.sfb_blocks = block_scaled ? (p2.bn == 128 ? 1 : 2) : 0;
+    p2.sf_kt = a.sf_kt;
     p2.tiles_m = static_cast<int>((a.m + 255) / 256);
     p2.tiles_n = static_cast<int>((a.n + p2.bn - 1) / p2.bn);
-    const int stage = (kTileA + p2.bn / 2) * kStageKBytes;
+    const int stage = gemm2_stage_bytes(a.kind, p2.bn, p2.sfb_blocks);
     p2.out_bufs = 2;
     p2.stages = (kSmemBudget - kVecBytes - 2 * kOutBufBytes) / stage;
     if (p2.stages > kMaxStages) p2.stages = kMaxStages;
@@ -388,7 +454,7 @@ int run_tc(const TcArgs& a) {
     p2.bias = static_cast<const __nv_bfloat16*>(a.bias);
     p2.out = static_cast<__nv_bfloat16*>(a.out);
     p2.status = ws.status;
-    CUtensorMap t_act, t_wgt, t_out;
+    CUtensorMap t_act, t_wgt, t_out, t_sfa, t_sfb;
     rc = make_map_2d(&t_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, kTileA,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != RK_OK) return rc;
@@ -398,9 +464,25 @@ int run_tc(const TcArgs& a) {
     rc = make_map_2d(&t_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 64, 128,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != RK_OK) return rc;
+    t_sfa = t_act;
+    t_sfb = t_act;
+    if (block_scaled) {
+      // scale buffers as [chunks, 128] 32-bit words; one box = the chunks of one stage and row block
+      const uint32_t chunks = a.kind == KIND_NVF4 ? 4 : 1;
+      rc = make_map_2d(&t_sfa, a.sf_act, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, 128, ((a.m + 127) / 128) * a.sf_kt, 512, 128,
+                       chunks, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc != RK_OK) return rc;
+      rc = make_map_2d(&t_sfb, a.sf_wgt, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, 128, ((a.n + 127) / 128) * a.sf_kt, 512, 128,
+                       chunks, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc != RK_OK) return rc;
+    }
     const int smem = p2.stages * stage + 2 * kOutBufBytes + kVecBytes + 1024;
-    return a.kind == KIND_I8 ? launch_tc2<KIND_I8>(t_act, t_wgt, t_out, p2, smem, a.stream)
-                             : launch_tc2<KIND_F8>(t_act, t_wgt, t_out, p2, smem, a.stream);
+    switch (a.kind) {
+      case KIND_I8: return launch_tc2<KIND_I8>(t_act, t_wgt, t_out, t_sfa, t_sfb, p2, smem, a.stream);
+      case KIND_F8: return launch_tc2<KIND_F8>(t_act, t_wgt, t_out, t_sfa, t_sfb, p2, smem, a.stream);
+      case KIND_MXF8: return launch_tc2<KIND_MXF8>(t_act, t_wgt, t_out, t_sfa, t_sfb, p2, smem, a.stream);
+      default: return launch_tc2<KIND_NVF4>(t_act, t_wgt, t_out, t_sfa, t_sfb, p2, smem, a.stream);
+    }
   }
   const Plan pl = make_plan(a.kind, a.m, a.n, kblocks, a.tactic);
 
@@ -451,6 +533,10 @@ int run_tc(const TcArgs& a) {
   p.sf_act = a.sf_act;
   p.sf_wgt = a.sf_wgt;
   p.sf_kt = a.sf_kt;
+  p.sfb_blocks = pl.sfb_blocks;
+  p.sf_rows_b = static_cast<int>(pl.swap ? a.m : a.n);
+  p.wait_limit = g_debug_wait_limit > 0 ? g_debug_wait_limit : static_cast<int>(kWaitSpinMax);
+  p.debug_stall = g_debug_stall;
   p.status = ws.status;
   const CUtensorMap& tm_a = pl.swap ? tm_wgt : tm_act;
   const CUtensorMap& tm_b = pl.swap ? tm_act : tm_wgt;
@@ -532,8 +618,18 @@ extern "C" size_t rk_workspace_bytes(int op, int64_t m, int64_t n, int64_t k) {
   return (bytes + 255) / 256 * 256;
 }
 
+namespace {
+int noalloc_scratch_address(uint8_t** out);
+}
+
 extern "C" int rk_read_status(void* workspace, int* code, void* stream) {
-  if (!workspace) return fail(RK_EWORKSPACE, "rk_read_status: null workspace");
+  if (!workspace) {
+    // NULL names the scratch array built into the library (the one rk_gemm_int4_noalloc uses)
+    uint8_t* builtin = nullptr;
+    const int rc = noalloc_scratch_address(&builtin);
+    if (rc != RK_OK) return rc;
+    workspace = builtin;
+  }
   cudaError_t e = cudaStreamSynchronize(as_stream(stream));
   if (e != cudaSuccess) return fail(RK_ECUDA, "rk_read_status: %s", cudaGetErrorString(e));
   int v = 0;
@@ -544,6 +640,13 @@ extern "C" int rk_read_status(void* workspace, int* code, void* stream) {
     cudaMemset(workspace, 0, sizeof(int));
     return fail(RK_EDEVICE, "a kernel gave up a bounded wait (device code %d)", v);
   }
+  return RK_OK;
+}
+
+extern "C" int rk_debug_wait_expiry(int on, int spin_limit) {
+  if (on && (spin_limit < 64 || spin_limit > (1 << 21))) return fail(RK_EINVAL, "rk_debug_wait_expiry: spin_limit must be 64..2^21");
+  g_debug_stall = on ? 1 : 0;
+  g_debug_wait_limit = on ? spin_limit : 0;
   return RK_OK;
 }
 
@@ -966,9 +1069,9 @@ extern "C" int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* 
   const size_t need = rk_workspace_bytes(RK_OP_W4A4, m, n, kpad);
   if (need > kNoAllocScratchBytes)
     return rk::fail(RK_EUNSUPPORTED,
-                    "%s: (m + n) * kpad = %lld bytes of int8 copies exceed the built-in %zu-byte scratch; "
-                    "use rk_gemm_int with a caller workspace",
-                    who, static_cast<long long>((m + n) * kpad), kNoAllocScratchBytes - 4096);
+                    "%s: 256 + round_up(m + n, 16) * kpad, rounded up to 256, = %zu bytes exceed the built-in "
+                    "%zu-byte scratch; use rk_gemm_int with a caller workspace",
+                    who, need, kNoAllocScratchBytes);
   uint8_t* scratch = nullptr;
   int rc = noalloc_scratch_address(&scratch);
   if (rc != RK_OK) return rc;
@@ -978,10 +1081,89 @@ extern "C" int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* 
   return gemm_int_common(a, sa, b, sb, bias, out, nullptr, m, n, kpad, 4, tactic, scratch, need, stream, who);
 }
 
-#ifdef RK_TRACE
-// Developer aid (trace builds only): copies the W4A16 role timestamps of CTA (0,0) to the host.
-extern "C" int rk_trace_read(long long* host, int count) {
-  if (count > 32 * 64) count = 32 * 64;
-  return cudaMemcpyFromSymbol(host, rk::rk_trace_buf, sizeof(long long) * count) == cudaSuccess ? 0 : -3;
+// ------------------------------------------------------------------ attention over a cached prefix
+extern "C" int rk_attention_prefix(const void* q, const void* k_cache, const void* vt_cache, void* out, int64_t batch,
+                                   int64_t tokens, int64_t heads, int64_t kv_heads, int64_t head_dim, int64_t cache_rows,
+                                   int64_t vt_pitch, int64_t kv_len, float scaling, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  const char* who = "rk_attention_prefix";
+  if (!q || !k_cache || !vt_cache || !out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (head_dim != kAttnDim) return fail(RK_EUNSUPPORTED, "%s: head_dim must be %d", who, kAttnDim);
+  if (batch < 1 || batch > 65535 || tokens < 1 || tokens > 128 || heads < 1 || kv_heads < 1 || heads % kv_heads != 0)
+    return fail(RK_EINVAL, "%s: bad batch / tokens (1..128) / heads", who);
+  if (kv_len < 1 || kv_len > cache_rows || kv_len > vt_pitch || vt_pitch % 8 != 0)
+    return fail(RK_EINVAL, "%s: kv_len must fit the caches and vt_pitch must be a multiple of 8", who);
+  if (kv_len > 2048) return fail(RK_EUNSUPPORTED, "%s: more than 2048 keys", who);
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(vt_cache) || !aligned16(out))
+    return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  Workspace ws;
+  int rc = carve_workspace(workspace, workspace_bytes, &ws, who);
+  if (rc != RK_OK) return rc;
+  // query heads per 128-lane tile: as many heads of one KV group as fit
+  const int per_kv = static_cast<int>(heads / kv_heads);
+  int group = 1;
+  for (int g = per_kv; g >= 1; --g)
+    if (per_kv % g == 0 && g * tokens <= 128) {
+      group = g;
+      break;
+    }
+  const int tiles = static_cast<int>(heads / group);
+  // key slices: enough CTAs to occupy the machine, at most 256 keys each, a power of two up to 8
+  int splits = 1;
+  while (splits < 8 && (tiles * batch * splits * 2 <= kNumSms || (kv_len + splits - 1) / splits > 256)) splits *= 2;
+  const int keys = static_cast<int>(round_up((kv_len + splits - 1) / splits, 32));
+  if (keys > 256) return fail(RK_EUNSUPPORTED, "%s: key slices above 256 keys", who);
+  CUtensorMap tm_q, tm_k, tm_vt;
+  // queries [batch * tokens, heads, 256]: a box is 64 dimensions x `group` heads x `tokens` rows
+  rc = make_map_3d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kAttnDim, heads, batch * tokens, kAttnDim * 2,
+                   heads * kAttnDim * 2, 64, static_cast<uint32_t>(group), static_cast<uint32_t>(tokens),
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != RK_OK) return rc;
+  // keys [batch * kv_heads, cache_rows, 256]; rows past kv_len are masked in the kernel, rows past cache_rows read as zero
+  rc = make_map_3d(&tm_k, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kAttnDim, cache_rows, batch * kv_heads, kAttnDim * 2,
+                   cache_rows * kAttnDim * 2, 64, static_cast<uint32_t>(keys), 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != RK_OK) return rc;
+  // transposed values [batch * kv_heads, 256, vt_pitch]: a box is 64 keys x 256 dimensions
+  rc = make_map_3d(&tm_vt, vt_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, vt_pitch, kAttnDim, batch * kv_heads, vt_pitch * 2,
+                   kAttnDim * vt_pitch * 2, 64, kAttnDim, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != RK_OK) return rc;
+  AttnParams p{};
+  p.tokens = static_cast<int>(tokens);
+  p.heads = static_cast<int>(heads);
+  p.kv_heads = static_cast<int>(kv_heads);
+  p.group = group;
+  p.kv_len = static_cast<int>(kv_len);
+  p.keys = keys;
+  p.splits = splits;
+  p.scaling = scaling;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = ws.status;
+  static bool configured_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured_dev[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(rk_attn_prefix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+    if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured_dev[dev & 63] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(splits, tiles, static_cast<unsigned>(batch));
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = kAttnSmem;
+  cfg.stream = as_stream(stream);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_attn_prefix_kernel, tm_q, tm_k, tm_vt, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_attn_prefix_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
 }
-#endif

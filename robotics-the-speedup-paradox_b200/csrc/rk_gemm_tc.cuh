@@ -60,6 +60,10 @@ struct GemmParams {
   const uint8_t* sf_act;      // block-scaled: swizzled scale-factor buffers
   const uint8_t* sf_wgt;
   int sf_kt;                  // 512-byte scale chunks per 128-row block along K
+  int sfb_blocks;             // 128-row scale blocks fetched per B-role tile (1..3; a tile may straddle blocks)
+  int sf_rows_b;              // rows of the B-role operand (its scale buffer holds ceil(rows / 128) blocks)
+  int wait_limit;             // spin limit of every bounded wait (kWaitSpinMax unless a test shortens it)
+  int debug_stall;            // test aid: the producer announces bytes that never arrive (first stage)
   int* status;                // device status word
 };
 
@@ -86,11 +90,10 @@ struct KindTraits<KIND_NVF4> {
   static constexpr int kSfChunksPerStage = 4;  // 256 elements of K = 16 scale factors per row
 };
 
-__host__ __device__ inline int gemm_stage_bytes(int kind, int bn) {
+__host__ __device__ inline int gemm_stage_bytes(int kind, int bn, int sfb_blocks) {
   int data = kTileA * kStageKBytes + bn * kStageKBytes;
   int chunks = kind == KIND_MXF8 ? 1 : (kind == KIND_NVF4 ? 4 : 0);
-  int rb = (bn + 127) / 128;
-  int sf = chunks * 512 * (1 + rb);
+  int sf = chunks * 512 * (1 + sfb_blocks);
   return (data + sf + 1023) / 1024 * 1024;
 }
 
@@ -147,8 +150,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* const smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));  // generic pointer to smem_base
-  const int stage_bytes = gemm_stage_bytes(KIND, p.bn);
-  const int rb_b = (p.bn + 127) / 128;  // 128-row scale blocks in the B tile
+  const int stage_bytes = gemm_stage_bytes(KIND, p.bn, p.sfb_blocks);
+  const int rb_b = p.sfb_blocks;  // 128-row scale blocks fetched per B tile
+  const uint32_t spin_max = static_cast<uint32_t>(p.wait_limit);
   // shared memory map: [pipeline stages][output staging, 1 or 2 x 16 KB][B-role scale + bias vectors]
   const uint32_t out_stage_off = p.stages * stage_bytes;
   const uint32_t vec_off = out_stage_off + p.out_bufs * kOutBufBytes;
@@ -230,7 +234,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         for (int i = 0; i < nkb; ++i) {
           const int s = ring.stage;
           const uint32_t ph = ring.phase;
-          if (!ready && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
+          if (!ready && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY, spin_max)) {
             alive = false;
             break;
           }
@@ -242,11 +246,14 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const int kb = kb_begin + i;
           uint32_t tx = tx_data;
           // scale chunks present in this K block (the last block of a ragged K holds fewer)
-          int cs = 0;
+          int cs = 0, nb = 0;
+          const int blk_b0 = row_b0 >> 7;  // first 128-row scale block of the B tile
           if constexpr (T::kBlockScaled) {
             cs = min(T::kSfChunksPerStage, p.sf_kt - kb * T::kSfChunksPerStage);
-            tx += cs * 512 * (1 + rb_b);
+            nb = min(rb_b, ((p.sf_rows_b + 127) >> 7) - blk_b0);  // blocks that exist in the buffer
+            tx += cs * 512 * (1 + nb);
           }
+          if (p.debug_stall && i == 0 && tile == tile_first) tx += 16;  // test aid: this phase never completes
           mbar_arrive_expect_tx(full, tx, on);
           tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a, on);
           tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b, on);
@@ -260,8 +267,8 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
                 "@q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
                 ::"r"(ssf), "l"(src_a), "r"(cs * 512), "r"(full), "r"(on) : "memory");
-            for (int rb = 0; rb < rb_b; ++rb) {
-              const uint8_t* src_b = sf_b + (static_cast<long long>(row_b0 / 128 + rb) * p.sf_kt + chunk0) * 512;
+            for (int rb = 0; rb < nb; ++rb) {
+              const uint8_t* src_b = sf_b + (static_cast<long long>(blk_b0 + rb) * p.sf_kt + chunk0) * 512;
               asm volatile(
                   "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
                   "@q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
@@ -293,13 +300,16 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int ab = racc.stage;
         // the epilogue must have drained this accumulator buffer (its previous use)
         if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[ab]), racc.phase ^ 1, &abort_flag, p.status,
-                               RK_DEV_TIMEOUT_ACC_FREE)) break;
+                               RK_DEV_TIMEOUT_ACC_FREE, spin_max)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * p.acc_stride;
+        // a B tile that starts inside a 128-row scale block reads its factors from the matching
+        // column of the block's four (one 32-bit column per 32 rows)
+        const uint32_t sfb_col0 = static_cast<uint32_t>((((tile % p.tiles_b) * p.bn) & 127) >> 5);
         for (int i = 0; i < nkb; ++i) {
           const int s = ring.stage;
           const uint32_t ph = ring.phase;
-          if (!ready && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
+          if (!ready && !mbar_wait_bounded(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL, spin_max)) {
             alive = false;
             break;
           }
@@ -338,9 +348,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 // four MMAs share one set of scale columns; byte k of each 32-bit column is theirs
                 // (scale-factor ids: bits [4,6) for B, [29,31) for A)
                 mma_mxf8(d_tmem, ad, bd, idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29),
-                         tmem_sfa, tmem_sfb, accumulate, on);
+                         tmem_sfa, tmem_sfb + sfb_col0, accumulate, on);
               } else {
-                mma_nvf4(d_tmem, ad, bd, idesc, tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4, accumulate, on);
+                mma_nvf4(d_tmem, ad, bd, idesc, tmem_sfa + k * 4, tmem_sfb + k * rb_b * 4 + sfb_col0, accumulate, on);
               }
             }
           }
@@ -394,7 +404,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         epi_bar_sync();
       }
       const bool ok = mbar_wait_group(smem_u32(&bar_acc_full[ab]), racc.phase, et == 0, 1, 128, &abort_flag, p.status,
-                                      RK_DEV_TIMEOUT_ACC, verdict_epi, epi_iter++);
+                                      RK_DEV_TIMEOUT_ACC, verdict_epi, epi_iter++, spin_max);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ab * p.acc_stride + (static_cast<uint32_t>(quad * 32) << 16);
 

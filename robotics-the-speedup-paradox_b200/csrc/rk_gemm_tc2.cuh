@@ -1,5 +1,5 @@
-// Two-CTA tcgen05 GEMM for large activation row counts: int8 x int8 -> s32 (W8A8) and
-// e4m3 x e4m3 -> f32 (per-tensor FP8).
+// Two-CTA tcgen05 GEMM for large activation row counts: int8 x int8 -> s32 (W8A8), e4m3 x e4m3 -> f32
+// (per-tensor FP8), and the block-scaled MXFP8 / NVFP4 kinds.
 //
 // A pair of CTAs (a cluster of two SMs) computes one 256 x bn output tile with
 // `tcgen05.mma.cta_group::2`: each CTA holds 128 of the 256 activation rows (its half of the
@@ -11,6 +11,15 @@
 // Every TMA load is issued by the CTA that owns the destination shared memory (no multicast);
 // the loads of both CTAs signal the leader CTA's "full" barrier, the leader issues the MMAs, and
 // `tcgen05.commit ... multicast::cluster` releases the stage in both CTAs.
+//
+// Block-scaled kinds: the scale-factor buffers are read through their own tensor maps ([chunks, 128]
+// 32-bit words: one row is one 512-byte chunk of 128 rows x 4 factors), so that their copies can be
+// counted on the leader's barrier like the operand tiles.  Each CTA fetches the chunks of its own 128
+// activation rows and of ALL bn weight rows (every CTA's half of the accumulator spans all columns);
+// the leader's `tcgen05.cp.cta_group::2` then moves each CTA's chunks into that CTA's tensor memory.
+// What bounds these kinds on one CTA is the rate at which an SM takes operand bytes from L2 (about
+// 64 bytes per clock): a pair halves the weight bytes per SM and MMA, which is where the speed-up
+// over the one-CTA kernel comes from.
 //
 // Warp roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation (+ MMA issue
 // in the leader), warps 2..5 = epilogue.
@@ -25,9 +34,12 @@ namespace rk {
 struct Gemm2Params {
   int m, n, kblocks;
   int k_valid_mmas_last;
-  int bn;        // weight rows per pair tile (128 or 256); each CTA loads bn / 2
+  int bn;        // weight rows per pair tile (128, 192 or 256); each CTA loads bn / 2
   int stages;
   int out_bufs;
+  int acc_bufs;  // accumulator buffers in tensor memory (2, or 1 when bn = 256 shares it with scale columns)
+  int sf_kt;     // block-scaled: 512-byte scale chunks per 128-row block along K
+  int sfb_blocks;  // 128-row scale blocks a weight tile touches (1 or 2)
   int tiles_m, tiles_n;  // pair tiles: 256 x bn
   long long ldo;
   const float* scale_act;
@@ -75,12 +87,40 @@ __device__ __forceinline__ void tc2_commit_both(uint32_t bar, uint32_t on = 1u) 
 RK_DEFINE_MMA2(mma2_i8, "i8")
 RK_DEFINE_MMA2(mma2_f8f6f4, "f8f6f4")
 #undef RK_DEFINE_MMA2
+__device__ __forceinline__ void mma2_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate, uint32_t on = 1u) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate), "r"(on)
+      : "memory");
+}
+__device__ __forceinline__ void mma2_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate, uint32_t on = 1u) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate), "r"(on)
+      : "memory");
+}
+// every CTA of the pair: 32 lanes x 128 bits of its own shared memory into its own tensor memory
+__device__ __forceinline__ void tmem_cp2_32x128b_warpx4(uint32_t taddr, uint64_t sdesc, uint32_t on = 1u) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc), "r"(on) : "memory");
+}
+
+__host__ __device__ inline int gemm2_stage_bytes(int kind, int bn, int sfb_blocks) {
+  const int chunks = kind == KIND_MXF8 ? 1 : (kind == KIND_NVF4 ? 4 : 0);
+  return ((kTileA + bn / 2) * kStageKBytes + chunks * 512 * (1 + sfb_blocks) + 1023) / 1024 * 1024;
+}
 
 template <int KIND>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                   const __grid_constant__ CUtensorMap tm_out, const Gemm2Params p) {
-  static_assert(KIND == KIND_I8 || KIND == KIND_F8, "two-CTA schedule: int8 and per-tensor FP8 only");
+                   const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_sfa,
+                   const __grid_constant__ CUtensorMap tm_sfb, const Gemm2Params p) {
+  using T = KindTraits<KIND>;
+  constexpr int kC = T::kSfChunksPerStage;  // scale chunks per stage and 128-row block
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];    // used in the leader: both CTAs' loads land
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];   // per CTA: the MMAs have read this stage
@@ -96,7 +136,8 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* const smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
   const int half_bn = p.bn / 2;
-  const int stage_bytes = (kTileA + half_bn) * kStageKBytes;
+  const int stage_bytes = gemm2_stage_bytes(KIND, p.bn, p.sfb_blocks);
+  const uint32_t sf_off = (kTileA + half_bn) * kStageKBytes;  // scale chunks of a stage: [A: kC][B: blocks x kC]
   const uint32_t out_stage_off = p.stages * stage_bytes;
   const uint32_t vec_off = out_stage_off + p.out_bufs * kOutBufBytes;
   const int num_tiles = p.tiles_m * p.tiles_n;
@@ -132,6 +173,9 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   tc_fence_after();
   pdl_wait();
   const uint32_t tmem_base = tmem_base_slot;
+  // tensor memory: accumulator buffers 256 columns apart, then the scale-factor columns
+  const uint32_t tmem_sfa = tmem_base + (p.acc_bufs == 2 ? 256 + p.bn : p.bn);
+  const uint32_t tmem_sfb = tmem_sfa + 16;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -159,10 +203,20 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           // both CTAs' bytes are counted on the leader's barrier; the leader announces the total
           const uint32_t full_leader = mapa_u32(smem_u32(&bar_full[s]), 0);
-          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * static_cast<uint32_t>(stage_bytes), on);
+          const uint32_t tx = sf_off + kC * 512 * (1 + p.sfb_blocks);  // per CTA; boxes count in full even when clipped
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * tx, on);
           const uint32_t sa = smem_base + s * stage_bytes;
           tma_load_2d_pair(sa, &tm_a, kb * kStageKBytes, row_a0, full_leader, pol_x, on);
           tma_load_2d_pair(sa + kTileA * kStageKBytes, &tm_b, kb * kStageKBytes, row_b0, full_leader, pol_w, on);
+          if constexpr (T::kBlockScaled) {
+            // chunk rows of the scale maps: (128-row block) * sf_kt + (K chunk)
+            const int blk_a = row_a0 >> 7;
+            const int blk_b = ((tile % p.tiles_n) * p.bn) >> 7;
+            tma_load_2d_pair(sa + sf_off, &tm_sfa, 0, blk_a * p.sf_kt + kb * kC, full_leader, pol_x, on);
+            for (int bb = 0; bb < p.sfb_blocks; ++bb)
+              tma_load_2d_pair(sa + sf_off + (1 + bb) * kC * 512, &tm_sfb, 0, (blk_b + bb) * p.sf_kt + kb * kC,
+                               full_leader, pol_w, on);
+          }
         }
       }
     }
@@ -174,17 +228,22 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       Ring ring{0, 0}, racc{0, 0};
       bool alive = true;
       uint32_t ready = 0;
-      const uint32_t idesc = KIND == KIND_I8 ? umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 256, p.bn)
-                                             : umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 256, p.bn);
+      uint32_t idesc;
+      if constexpr (KIND == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 256, p.bn);
+      else if constexpr (KIND == KIND_F8) idesc = umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 256, p.bn);
+      else if constexpr (KIND == KIND_MXF8) idesc = umma_idesc_bs(FMT_E4M3, FMT_E4M3, 256, p.bn, 1, 0, 0);
+      else idesc = umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 256, p.bn, 0, 0, 0);
       const uint64_t adesc0 = umma_desc_k128(smem_base);
       const uint64_t bdesc0 = umma_desc_k128(smem_base + kTileA * kStageKBytes);
       const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
-      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step, racc.advance(2)) {
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step, racc.advance(p.acc_bufs)) {
         const int ab = racc.stage;
         if (!mbar_wait_bounded(smem_u32(&bar_acc_empty[ab]), racc.phase ^ 1, &abort_flag, p.status,
                                RK_DEV_TIMEOUT_ACC_FREE)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * 256;
+        // a weight tile that starts inside a 128-row scale block: even column offset (tiles start on multiples of 64 rows)
+        const uint32_t sfb_col0 = static_cast<uint32_t>((((tile % p.tiles_n) * p.bn) & 127) >> 5);
         for (int kb = 0; kb < p.kblocks; ++kb) {
           const int s = ring.stage;
           if (!ready && !mbar_wait_bounded(smem_u32(&bar_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_FULL)) {
@@ -197,12 +256,32 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
           const int nmma = (kb == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
+          if constexpr (T::kBlockScaled) {
+            const uint32_t ssf = smem_base + s * stage_bytes + sf_off;
+            const int nb = p.sfb_blocks;
+            for (int j = 0; j < kC; ++j) {
+              tmem_cp2_32x128b_warpx4(tmem_sfa + j * 4, umma_desc_noswizzle(ssf + j * 512, 16, 128), on);
+              for (int bb = 0; bb < nb; ++bb)
+                tmem_cp2_32x128b_warpx4(tmem_sfb + (j * nb + bb) * 4,
+                                        umma_desc_noswizzle(ssf + ((1 + bb) * kC + j) * 512, 16, 128), on);
+            }
+          }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (k < nmma) {
               const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-              if constexpr (KIND == KIND_I8) mma2_i8(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate, on);
-              else mma2_f8f6f4(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate, on);
+              if constexpr (KIND == KIND_I8) {
+                mma2_i8(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate, on);
+              } else if constexpr (KIND == KIND_F8) {
+                mma2_f8f6f4(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate, on);
+              } else if constexpr (KIND == KIND_MXF8) {
+                mma2_mxf8(d_tmem, adesc + k * 2, bdesc + k * 2,
+                          idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29), tmem_sfa,
+                          tmem_sfb + sfb_col0, accumulate, on);
+              } else {
+                mma2_nvf4(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, tmem_sfa + k * 4,
+                          tmem_sfb + k * p.sfb_blocks * 4 + sfb_col0, accumulate, on);
+              }
             }
           }
           tc2_commit_both(smem_u32(&bar_empty[s]), on);
@@ -227,7 +306,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     Ring racc{0, 0};
     uint32_t epi_iter = 0;
     int pending_store = 0, obuf = 0;
-    for (int tile = tile_first; tile < num_tiles; tile += tile_step, racc.advance(2)) {
+    for (int tile = tile_first; tile < num_tiles; tile += tile_step, racc.advance(p.acc_bufs)) {
       const int ab = racc.stage;
       const int row_a0 = (tile / p.tiles_n) * 256 + static_cast<int>(rank) * kTileA;  // this CTA's 128 rows
       const int row_b0 = (tile % p.tiles_n) * p.bn;                                    // all bn columns

@@ -151,7 +151,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   tc_fence_after();
   pdl_wait();  // from here on global memory is read and written
   const uint32_t tmem_base = tmem_base_slot;
-  if (threadIdx.x == 0) RK_TRACE_REC(9, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer: weights run ahead of the slots
@@ -172,7 +171,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             const uint32_t full = smem_u32(&bar_w_full[s]);
             mbar_arrive_expect_tx(full, kW4PairBytes);
             tma_load_2d_hint(smem_base + w_off + s * kW4PairBytes, &tm_w, gw * 128, n0, full, pol_w);
-            RK_TRACE_REC(0, gw);
             ++gw;
             rw.advance(p.w_stages);
             progressed = true;
@@ -186,7 +184,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             mbar_arrive_expect_tx(full, kXBytes);
             // one copy brings both 64-element column blocks of the group: box {64, BN, 2}
             tma_load_3d_hint(smem_base + x_off + t * kXBytes, &tm_x, 0, m0, gx * 2, full, pol_x);
-            RK_TRACE_REC(1, gx);
             ++gx;
             rx.advance(kSlots);
             progressed = true;
@@ -226,10 +223,8 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       uint32_t ready = 0;
       for (int g = parity; g < G; g += 2) {
         const int t = rt.stage;
-        if (parity == 0 && on) RK_TRACE_REC(26, g);
         if (!ready && !mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) break;
         tc_fence_after();
-        if (parity == 0 && on) RK_TRACE_REC(5, g);
         rt.stage += 2;
         while (rt.stage >= kSlots) {
           rt.stage -= kSlots;
@@ -246,9 +241,7 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
           const uint64_t bd = bd0 + static_cast<uint64_t>(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
           mma_f16_ts(d_tmem, a_tmem + k * 8, bd, idesc, k > 0 ? 1u : 0u, on);
         }
-        if (parity == 0 && on) RK_TRACE_REC(12, g);
         tc_commit(smem_u32(&bar_acc_full[t]), on);
-        if (parity == 0 && on) RK_TRACE_REC(6, g);
       }
     }
   } else if (warp < kEpiWarp0) {
@@ -287,7 +280,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
         if (!__all_sync(0xffffffffu, ok)) break;
       }
-      if (leader) RK_TRACE_REC(2, g);
       // The raw pair was written with the 128-byte swizzle: 16-byte chunk c of row r sits at c ^ (r & 7);
       // chunks 0..3 belong to the even group of the pair, 4..7 to the odd one.
       const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
@@ -344,8 +336,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       }
       rt = rt2;
       rw = rw2;
-      if (leader) RK_TRACE_REC(4, g);
-      if (lane == 0 && uw < 8) RK_TRACE_REC(18 + uw, g);
     }
   } else if (warp < kMmaWarpB) {
     // ------------------------------------------------------------ epilogue: scale each group, accumulate, store
@@ -367,7 +357,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       alive = mbar_wait_group(smem_u32(&bar_acc_full[t]), rt.phase, epi_leader, 1, 128, &abort_flag, p.status,
                               RK_DEV_TIMEOUT_ACC, verdict_epi, static_cast<uint32_t>(g));
       tc_fence_after();
-      if (quad == 0 && lane == 0) RK_TRACE_REC(7, g);
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16];
@@ -381,7 +370,6 @@ rk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       // the MMAs of the group have completed (their commit was observed), so the slot's weight tile,
       // activation tile and - now drained - accumulator are all free
       if (lane == 0) mbar_arrive(smem_u32(&bar_slot_empty[t]));
-      if (quad == 0 && lane == 0) RK_TRACE_REC(8, g);
     }
     // every epilogue warp reaches this rendezvous, whether it completed or gave up
     if (!alive) *reinterpret_cast<volatile int*>(&epi_dead) = 1;

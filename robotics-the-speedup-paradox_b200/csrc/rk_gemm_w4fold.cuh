@@ -119,7 +119,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   tc_fence_after();
   pdl_wait();  // from here on global memory is read and written
   const uint32_t tmem_base = tmem_base_slot;
-  if (threadIdx.x == 0) RK_TRACE_REC(9, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -140,7 +139,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
             const uint32_t full = smem_u32(&bar_w_full[s]);
             mbar_arrive_expect_tx(full, kW4PairBytes);
             tma_load_2d_hint(smem_base + w_off + s * kW4PairBytes, &tm_w, kw * 128, n0, full, pol_w);
-            RK_TRACE_REC(0, gw);
             if (++kw == P) kw = 0;
             ++gw;
             rw.advance(p.w_stages);
@@ -153,7 +151,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
             const uint32_t full = smem_u32(&bar_slot_full[t]);
             mbar_arrive_expect_tx(full, kXBytes);
             tma_load_2d_hint(smem_base + x_off + t * kXBytes, &tm_x, kx * 64, m0, full, pol_x);
-            RK_TRACE_REC(1, sx);
             if (++kx == S) kx = 0;
             ++sx;
             rx.advance(kSlots);
@@ -191,13 +188,11 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       uint32_t ready = 0;
       for (int s = 0; s < S; ++s) {
         const int t = rt.stage;
-        if (on) RK_TRACE_REC(26, s);
         if (!ready && !mbar_wait_bounded(smem_u32(&bar_slot_full[t]), rt.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM)) {
           alive = false;
           break;
         }
         tc_fence_after();
-        if (on) RK_TRACE_REC(5, s);
         rt.advance(kSlots);
         ready = (s + 1 < S) ? mbar_test_wait(smem_u32(&bar_slot_full[rt.stage]), rt.phase) : 0u;
         const uint64_t bd0 = desc_x0 + static_cast<uint64_t>((t * kXBytes) >> 4);
@@ -205,9 +200,7 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           mma_f16_ts(d_tmem, a_tmem + k * 8, bd0 + static_cast<uint64_t>((k * 32) >> 4), idesc, (s | k) ? 1u : 0u, on);
-        if (on) RK_TRACE_REC(12, s);
         tc_commit(smem_u32(&bar_slot_empty[t]), on);  // frees the expanded weights and the activation tile
-        if (on) RK_TRACE_REC(6, s);
       }
       if (alive) tc_commit(smem_u32(&bar_acc_full), on);
     }
@@ -240,7 +233,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
           ok = ok && mbar_poll_lane(smem_u32(&bar_slot_empty[t]), rt.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
           if (!__all_sync(0xffffffffu, ok)) break;
         }
-        if (uw == 0 && lane == 0) RK_TRACE_REC(2, g);
         // 128-byte swizzle of the raw copy: 16-byte chunk c of row r sits at c ^ (r & 7); the step of
         // this warp owns chunks 4 * odd + 2 * h and the next one
         const uint8_t* raw = smem_gen + w_off + sw * kW4PairBytes + r * 128;
@@ -290,8 +282,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
         }
         rt = rt2;
         rw = rw2;
-        if (uw == 0 && lane == 0) RK_TRACE_REC(4, g);
-        if (lane == 0) RK_TRACE_REC(18 + uw, g);
       }
     }
     // ------------------------------------------------------------ epilogue: all twelve unpack and epilogue warps
@@ -308,7 +298,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     const int n = n0 + nl;
     const bool alive = mbar_poll_warp(smem_u32(&bar_acc_full), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC);
     tc_fence_after();
-    if (warp == kEpiWarp0 + 2 && lane == 0) RK_TRACE_REC(7, 0);
     // every one of the twelve warps reaches this rendezvous, whether it saw the accumulator complete or gave up
     if (!alive) *reinterpret_cast<volatile int*>(&epi_dead) = 1;
     asm volatile("bar.sync 1, 384;" ::: "memory");
@@ -332,7 +321,6 @@ rk_gemm_w4a16_fold_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
         tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
       }
     }
-    if (warp == kEpiWarp0 + 2 && lane == 0) RK_TRACE_REC(8, 0);
   }
 
   tc_fence_before();

@@ -54,6 +54,8 @@ struct RopeParams {
   const __nv_bfloat16 *cos, *sin;        // [batch, tokens, dim]
   __nv_bfloat16 *q_out;                  // [batch, heads, tokens, dim], or [batch, tokens, heads, dim] (token_major)
   __nv_bfloat16 *k_all, *v_all;          // [batch, kv_heads, cache_rows, dim]
+  __nv_bfloat16 *vt_all;                 // optional transposed values [batch, kv_heads, dim, vt_pitch]
+  long long vt_pitch;
   int batch, tokens, heads, kv_heads, dim, cache_rows, prefix, token_major;
 };
 
@@ -92,7 +94,19 @@ rope_cache_update_kernel(const RopeParams p) {
       const int head = unit - p.heads - p.kv_heads;
       const __nv_bfloat16* src = p.v + row * p.v_stride + head * p.dim;
       __nv_bfloat16* dst = p.v_all + ((static_cast<long long>(b) * p.kv_heads + head) * p.cache_rows + p.prefix + token) * p.dim;
-      *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(src + j);
+      const uint4 x = *reinterpret_cast<const uint4*>(src + j);
+      *reinterpret_cast<uint4*>(dst + j) = x;
+      if (p.vt_all != nullptr) {
+        // the same eight values into column (prefix + token) of the transposed cache
+        unsigned short* const col = reinterpret_cast<unsigned short*>(p.vt_all) +
+                                    (static_cast<long long>(b) * p.kv_heads + head) * p.dim * p.vt_pitch + p.prefix + token;
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          col[(j + 2 * e) * p.vt_pitch] = static_cast<unsigned short>(w[e] & 0xFFFFu);
+          col[(j + 2 * e + 1) * p.vt_pitch] = static_cast<unsigned short>(w[e] >> 16);
+        }
+      }
     }
   }
 }
@@ -100,12 +114,14 @@ rope_cache_update_kernel(const RopeParams p) {
 }  // namespace
 }  // namespace rk
 
-extern "C" int rk_rope_cache_update(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
-                                    int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
-                                    int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
-                                    void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* stream) {
+static int rope_cache_update_impl(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                  int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
+                                  int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
+                                  void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* vt_cache,
+                                  int64_t vt_pitch, void* stream, const char* who) {
   using namespace rk;
-  const char* who = "rk_rope_cache_update";
+  if (vt_cache != nullptr && (vt_pitch < prefix + tokens || (reinterpret_cast<uintptr_t>(vt_cache) & 1u)))
+    return fail(RK_EINVAL, "%s: the transposed value cache needs a pitch of at least prefix + tokens", who);
   if (!q || !k || !v || !cos || !sin || !q_out || !k_cache || !v_cache) return fail(RK_EINVAL, "%s: null pointer", who);
   if (batch < 1 || tokens < 1 || heads < 1 || kv_heads < 1) return fail(RK_EINVAL, "%s: empty problem", who);
   if (head_dim < 16 || head_dim % 16 != 0 || head_dim > 512)
@@ -132,6 +148,8 @@ extern "C" int rk_rope_cache_update(const void* q, int64_t q_stride, const void*
   p.q_out = static_cast<__nv_bfloat16*>(q_out);
   p.k_all = static_cast<__nv_bfloat16*>(k_cache);
   p.v_all = static_cast<__nv_bfloat16*>(v_cache);
+  p.vt_all = static_cast<__nv_bfloat16*>(vt_cache);
+  p.vt_pitch = vt_pitch;
   p.batch = static_cast<int>(batch);
   p.tokens = static_cast<int>(tokens);
   p.heads = static_cast<int>(heads);
@@ -145,4 +163,25 @@ extern "C" int rk_rope_cache_update(const void* q, int64_t q_stride, const void*
   const unsigned blocks = static_cast<unsigned>((jobs + warps - 1) / warps);
   rope_cache_update_kernel<<<blocks, warps * 32, 0, as_stream(stream)>>>(p);
   return check_launch(who);
+}
+
+
+extern "C" int rk_rope_cache_update(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                    int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
+                                    int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
+                                    void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* stream) {
+  return rope_cache_update_impl(q, q_stride, k, k_stride, v, v_stride, cos, sin, batch, tokens, heads, kv_heads, head_dim,
+                                q_out, q_token_major, k_cache, v_cache, cache_rows, prefix, nullptr, 0, stream,
+                                "rk_rope_cache_update");
+}
+
+extern "C" int rk_rope_cache_update_vt(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                       int64_t v_stride, const void* cos, const void* sin, int64_t batch, int64_t tokens,
+                                       int64_t heads, int64_t kv_heads, int64_t head_dim, void* q_out, int q_token_major,
+                                       void* k_cache, void* v_cache, int64_t cache_rows, int64_t prefix, void* vt_cache,
+                                       int64_t vt_pitch, void* stream) {
+  if (!vt_cache) return rk::fail(RK_EINVAL, "rk_rope_cache_update_vt: null transposed cache");
+  return rope_cache_update_impl(q, q_stride, k, k_stride, v, v_stride, cos, sin, batch, tokens, heads, kv_heads, head_dim,
+                                q_out, q_token_major, k_cache, v_cache, cache_rows, prefix, vt_cache, vt_pitch, stream,
+                                "rk_rope_cache_update_vt");
 }

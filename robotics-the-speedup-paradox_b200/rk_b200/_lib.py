@@ -32,6 +32,7 @@ SIGNATURES = {
     "rk_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "rk_sf_bytes": (_sz, [_i64, _i64]),
     "rk_read_status": (_int, [_vp, ctypes.POINTER(_int), _vp]),
+    "rk_debug_wait_expiry": (_int, [_int, _int]),
     "rk_probe_rcp_approx_448": (_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "rk_quant_rows": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _int, _int, _vp, _vp, _vp]),
     "rk_quant_weight_int": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
@@ -57,6 +58,10 @@ SIGNATURES = {
     "rk_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_rope_cache_update": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _int,
                                     _vp, _vp, _i64, _i64, _vp]),
+    "rk_rope_cache_update_vt": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp,
+                                       _int, _vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "rk_attention_prefix": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _vp, _sz,
+                                   _vp]),
 }
 
 _lock = threading.Lock()
@@ -133,18 +138,18 @@ def workspace(device, nbytes):
     """Zero-initialised scratch tensor for the current stream of `device`, at least `nbytes` long.
 
     Kernels keep the buffer zero-filled between calls, so it is cleared only when (re)allocated.
-    Growing replaces the buffer; callers that captured the old one in a CUDA graph keep it alive
-    through their own reference.
+    Growing allocates a larger buffer for later calls; the smaller ones are kept for the life of
+    the process, because a CUDA graph captured earlier on this stream handle (torch reuses its
+    pooled handles) may still write its scratch and its status word there on replay.
     """
     device = torch.device(device)
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
-    buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
+    buffers = _workspaces.setdefault(key, [])
+    if not buffers or buffers[-1].numel() < nbytes:
         size = max(int(nbytes), 1 << 20)
-        buf = torch.zeros(size, dtype=torch.uint8, device=device)
-        _workspaces[key] = buf
-    return buf
+        buffers.append(torch.zeros(size, dtype=torch.uint8, device=device))
+    return buffers[-1]
 
 
 def gemm_workspace(op, device, m, n, k):
@@ -152,8 +157,12 @@ def gemm_workspace(op, device, m, n, k):
     return workspace(device, need)
 
 
-def read_status(buf):
+def read_status(buf, device=None):
+    """Device status word of a workspace tensor; `buf=None` reads the scratch array built into the
+    library (the one `rk_gemm_int4_noalloc` uses) on `device`."""
     code = ctypes.c_int(0)
-    rc = load().rk_read_status(ptr(buf), ctypes.byref(code), stream_ptr(buf.device))
+    device = buf.device if buf is not None else torch.device(device if device is not None else "cuda")
+    with torch.cuda.device(device):
+        rc = load().rk_read_status(ptr(buf), ctypes.byref(code), stream_ptr(device))
     check(rc, "rk_read_status")
     return code.value

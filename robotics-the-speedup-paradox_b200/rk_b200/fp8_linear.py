@@ -10,12 +10,18 @@ Arithmetic runs in ``librk_b200.so``; there is no fallback.
 """
 
 from dataclasses import dataclass
+import os
 
 import torch
 
 from . import _lib
 
 FP8_DTYPE = torch.float8_e4m3fn
+PREFILL_SCALE_REFRESH_INTERVAL_ENV = "ROBOTICS_FP8_PREFILL_SCALE_REFRESH_INTERVAL"
+# roles whose multi-row (prefill) calls may keep an activation scale for several calls
+PERIODIC_PREFILL_SCALE_ROLES = frozenset(
+    {"attn_q", "attn_k", "attn_v", "attn_qkv", "attn_o", "mlp_gate", "mlp_up", "mlp_gate_up", "mlp_down"})
+_NEVER = 2 ** 31 - 1
 
 
 @dataclass
@@ -142,6 +148,106 @@ def linear_forward_packed(a, scale_a, b, scale_b, bias=None, tactic=0):
     return out
 
 
+# ---- periodic reuse of the dynamic activation scale ----------------------------------------------
+def resolve_fp8_prefill_scale_refresh_interval(value=None):
+    """How many prefill calls share one dynamic activation scale: a positive integer, or
+    "static" / "once" / "never" for a scale measured on the first call only.  `None` reads
+    ROBOTICS_FP8_PREFILL_SCALE_REFRESH_INTERVAL (default 1 = a fresh scale on every call).
+    Reference: blackwell/fp8_linear.py:90-115."""
+    text = str(os.environ.get(PREFILL_SCALE_REFRESH_INTERVAL_ENV, "1") if value is None else value).strip().lower()
+    if text in ("static", "once", "never"):
+        return _NEVER
+    try:
+        interval = int(text)
+    except ValueError as error:
+        raise ValueError(f"{PREFILL_SCALE_REFRESH_INTERVAL_ENV} must be a positive integer or 'static'") from error
+    if interval <= 0:
+        raise ValueError(f"{PREFILL_SCALE_REFRESH_INTERVAL_ENV} must be positive")
+    return interval
+
+
+class Fp8PrefillScaleState:
+    """Per-module memory of the last measured activation scale (reference: blackwell/fp8_linear.py:147-239).
+
+    The per-tensor quantizer needs two passes over the activations because its scale is global: an
+    amax reduction, then the conversion.  Between consecutive multi-row calls of one layer the
+    amax moves little, so with an interval n > 1 only every n-th call measures (`refreshes`); the
+    calls in between convert with the remembered scale in a single pass (`reuses`).  Single-row
+    calls and ineligible roles always measure."""
+
+    def __init__(self, interval=None, *, eligible=True):
+        self.eligible = bool(eligible)
+        self.configure(interval)
+
+    def configure(self, interval=None):
+        self.interval = resolve_fp8_prefill_scale_refresh_interval(interval) if self.eligible else 1
+        self.scale = None
+        self.prefill_calls = self.refreshes = self.reuses = self.operator_fallbacks = 0
+
+    def enabled_for(self, tensor, columns):
+        return self.interval > 1 and tensor.numel() // int(columns) > 1
+
+    def _due(self):
+        return self.scale is None or self.prefill_calls % self.interval == 0
+
+    def _run(self, enabled, measure, convert):
+        if not enabled:
+            return measure()
+        if self._due():
+            packed, scale = measure()
+            self.scale = scale
+            self.refreshes += 1
+        else:
+            packed, scale = convert(self.scale), self.scale
+            self.reuses += 1
+        self.prefill_calls += 1
+        return packed, scale
+
+    def quantize(self, tensor):
+        """-> (e4m3 codes, float32 scale[1]) of a contiguous bf16 tensor."""
+        return self._run(self.enabled_for(tensor, tensor.shape[-1]), lambda: quantize_bf16(tensor),
+                         lambda scale: quantize_bf16_with_scale(tensor, scale))
+
+    def quantize_swiglu(self, gate_up, intermediate_size):
+        inter = int(intermediate_size)
+        return self._run(self.enabled_for(gate_up, 2 * inter), lambda: quantize_swiglu_bf16(gate_up, inter),
+                         lambda scale: quantize_swiglu_bf16_with_scale(gate_up, inter, scale))
+
+    def to_dict(self):
+        return {"eligible": self.eligible, "interval": self.interval, "prefill_calls": self.prefill_calls,
+                "refreshes": self.refreshes, "reuses": self.reuses, "operator_fallbacks": self.operator_fallbacks}
+
+
+def _fp8_prefill_scale_states(model):
+    states = {}
+    for module in model.modules():
+        state = getattr(module, "_prefill_scale_state", None)
+        if isinstance(state, Fp8PrefillScaleState) and state.eligible:
+            states[id(state)] = state
+    return list(states.values())
+
+
+def configure_fp8_prefill_scale_refresh(model, interval=None):
+    """Sets the interval of every eligible layer of a loaded model and resets their counters."""
+    states = _fp8_prefill_scale_states(model)
+    if not states:
+        return {"interval": 1, "states": 0}
+    resolved = resolve_fp8_prefill_scale_refresh_interval(interval)
+    for state in states:
+        state.configure(resolved)
+    return {"interval": resolved, "states": len(states)}
+
+
+def fp8_prefill_scale_refresh_stats(model):
+    states = _fp8_prefill_scale_states(model)
+    totals = {"states": len(states), "prefill_calls": 0, "refreshes": 0, "reuses": 0, "operator_fallbacks": 0}
+    for state in states:
+        for key in ("prefill_calls", "refreshes", "reuses", "operator_fallbacks"):
+            totals[key] += getattr(state, key)
+    totals["intervals"] = sorted({state.interval for state in states})
+    return totals
+
+
 # ---- MXFP8 -----------------------------------------------------------------------------------
 def mxfp8_pack(x):
     """bf16 [rows, K] -> (e4m3 [rows, K], uint8 swizzled UE8M0 scale buffer); K % 32 == 0."""
@@ -187,6 +293,7 @@ class Fp8CutlassLinear(torch.nn.Module):
         self.target_name = target_name
         self.mode = mode
         self._unit_scale = None  # lazily created scalar 1.0 for the producer path
+        self._prefill_scale_state = Fp8PrefillScaleState(eligible=mode == "per_tensor" and role in PERIODIC_PREFILL_SCALE_ROLES)
         self.fp8_backend = "b200_tcgen05_e4m3" if mode == "per_tensor" else "b200_tcgen05_mxfp8_e4m3_ue8m0"
 
     @classmethod
@@ -219,7 +326,7 @@ class Fp8CutlassLinear(torch.nn.Module):
 
     def pack_input(self, x):
         flat = self._rows(x)
-        return quantize_bf16(flat) if self.mode == "per_tensor" else mxfp8_pack(flat)
+        return self._prefill_scale_state.quantize(flat) if self.mode == "per_tensor" else mxfp8_pack(flat)
 
     def forward_packed(self, packed, scale, shape=None):
         if self.mode == "per_tensor":
@@ -236,7 +343,7 @@ class Fp8CutlassLinear(torch.nn.Module):
         if int(intermediate_size) != self.in_features:
             raise ValueError(f"expected intermediate_size {self.in_features}, got {intermediate_size}")
         flat = gate_up.to(torch.bfloat16).reshape(-1, 2 * self.in_features).contiguous()
-        packed, scale = quantize_swiglu_bf16(flat, self.in_features)
+        packed, scale = self._prefill_scale_state.quantize_swiglu(flat, self.in_features)
         return self.forward_packed(packed, scale, leading_shape)
 
     def forward_producer(self, x):

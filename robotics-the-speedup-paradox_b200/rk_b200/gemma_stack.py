@@ -3,8 +3,11 @@
 action-expert flow-matching loop (18 layers, width 1024, MLP 4096, adaptive RMSNorm, chunk 50 x 32,
 10 Euler steps over a cached prefix KV).
 
-This is the caller side of the hot path, kept in plain torch: norms, RoPE, eager fp32-softmax
-attention and residuals follow the reference's owned runtime (models/pi05/modeling_gemma.py:62-106,
+This is the caller side of the hot path: norms, RoPE, attention and residuals follow the reference's
+owned runtime.  Attention is torch's fused scaled_dot_product_attention (bf16 flash arithmetic, which
+differs from the reference's eager fp32 softmax in its rounding points) unless
+``GemmaAttention.fused_attention`` routes the action expert through ``rk_attention_prefix``, which
+reproduces the eager arithmetic (models/pi05/modeling_gemma.py:62-106,
 126-128, 185-274, 315-443; models/pi05/modeling_pi05.py:673-720, 793-889).  Every bf16
 ``nn.Linear`` is a plain module so that ``quantize_linears`` can swap it; the fp32 adaptive-norm
 ``dense`` layers and the fp32 action projections stay unquantized, as in the reference
@@ -124,12 +127,14 @@ def rope_tables(positions, head_dim, theta, dtype):
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
 
-def rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv_heads, head_dim, token_major=False):
+def rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv_heads, head_dim, token_major=False,
+                      vt_all=None):
     """One kernel for rotary embedding + cache append (`rk_rope_cache_update`).  q, k, v: bf16
     [B, t, heads * d] / [B, t, kv_heads * d] whose rows are dense (slices of one projection output
     are fine); cos, sin [B, t, d]; k_all, v_all [B, kv_heads, rows, d] already holding `prefix`
     rows.  Returns the rotated queries as [B, heads, t, d]; with `token_major` that tensor is a
-    transposed view of [B, t, heads, d] storage, the layout fused attention reads without a copy."""
+    transposed view of [B, t, heads, d] storage, the layout fused attention reads without a copy.
+    `vt_all` [B, kv_heads, d, pitch]: the fresh values are also written transposed (`attention_prefix`)."""
     from . import _lib
 
     b, t = q.shape[0], q.shape[1]
@@ -141,16 +146,43 @@ def rope_cache_update(q, k, v, cos, sin, k_all, v_all, prefix, heads, kv_heads, 
         raise ValueError("cache buffers must be contiguous")
     shape = (b, t, heads, head_dim) if token_major else (b, heads, t, head_dim)
     q_out = torch.empty(shape, dtype=torch.bfloat16, device=q.device)
-    code = _lib.load().rk_rope_cache_update(
-        _lib.ptr(q), q.stride(1), _lib.ptr(k), k.stride(1), _lib.ptr(v), v.stride(1), _lib.ptr(cos), _lib.ptr(sin),
-        b, t, heads, kv_heads, head_dim, _lib.ptr(q_out), 1 if token_major else 0, _lib.ptr(k_all), _lib.ptr(v_all),
-        k_all.shape[2], prefix, _lib.stream_ptr(q.device))
+    args = (_lib.ptr(q), q.stride(1), _lib.ptr(k), k.stride(1), _lib.ptr(v), v.stride(1), _lib.ptr(cos), _lib.ptr(sin),
+            b, t, heads, kv_heads, head_dim, _lib.ptr(q_out), 1 if token_major else 0, _lib.ptr(k_all), _lib.ptr(v_all),
+            k_all.shape[2], prefix)
+    if vt_all is None:
+        code = _lib.load().rk_rope_cache_update(*args, _lib.stream_ptr(q.device))
+    else:
+        if not vt_all.is_contiguous():
+            raise ValueError("the transposed value cache must be contiguous")
+        code = _lib.load().rk_rope_cache_update_vt(*args, _lib.ptr(vt_all), vt_all.shape[-1], _lib.stream_ptr(q.device))
     _lib.check(code, "rk_rope_cache_update")
     return q_out.transpose(1, 2) if token_major else q_out
 
 
+def attention_prefix(q, k_all, vt_all, kv_len, scaling=None):
+    """Fresh query tokens over cached keys / values in one kernel (`rk_attention_prefix`): the arithmetic
+    of the reference's eager attention (models/pi05/modeling_gemma.py:247-274).  q bf16 [B, t, heads, 256]
+    contiguous (token major); k_all [B, kv_heads, rows, 256]; vt_all [B, kv_heads, 256, pitch] (values
+    transposed, finite beyond `kv_len`).  Returns bf16 [B, t, heads * 256]."""
+    from . import _lib
+
+    b, t, heads, d = q.shape
+    if q.dtype != torch.bfloat16 or not (q.is_contiguous() and k_all.is_contiguous() and vt_all.is_contiguous()):
+        raise ValueError("attention_prefix takes contiguous bf16 tensors")
+    out = torch.empty((b, t, heads * d), dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        ws = _lib.workspace(q.device, _lib.WORKSPACE_HEADER)
+        code = _lib.load().rk_attention_prefix(
+            _lib.ptr(q), _lib.ptr(k_all), _lib.ptr(vt_all), _lib.ptr(out), b, t, heads, k_all.shape[1], d, k_all.shape[2],
+            vt_all.shape[-1], kv_len, float(d ** -0.5 if scaling is None else scaling), _lib.ptr(ws), ws.numel(),
+            _lib.stream_ptr(q.device))
+    _lib.check(code, "rk_attention_prefix")
+    return out
+
+
 class GemmaAttention(nn.Module):
     fused_rope = False  # set on an instance (or the class) to route rope + cache append through one kernel
+    fused_attention = False  # with fused_rope and a transposed value cache: attention as one tcgen05 kernel
 
     def __init__(self, cfg):
         super().__init__()
@@ -163,10 +195,15 @@ class GemmaAttention(nn.Module):
     def forward(self, x, cos, sin, past_kv=None):
         b, t = _leading_shape(x)
         cfg = self.cfg
-        if self.fused_rope and past_kv is not None and len(past_kv) == 3 and cos.is_cuda:
-            k_all, v_all, prefix = past_kv
+        if self.fused_rope and past_kv is not None and len(past_kv) >= 3 and cos.is_cuda:
+            k_all, v_all, prefix = past_kv[:3]
+            vt_all = past_kv[3] if len(past_kv) > 3 and self.fused_attention and cfg.head_dim == 256 else None
             q = rope_cache_update(self.q_proj(x), self.k_proj(x), self.v_proj(x), cos, sin, k_all, v_all, prefix,
-                                  cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, token_major=True)
+                                  cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, token_major=True, vt_all=vt_all)
+            if vt_all is not None:
+                # q is a transposed view of token-major storage: hand the storage to the kernel
+                out = attention_prefix(q.transpose(1, 2), k_all, vt_all, prefix + t)
+                return self.o_proj(out), (k_all, v_all)
             out = F.scaled_dot_product_attention(q, k_all, v_all, is_causal=False, enable_gqa=True)
             out = out.transpose(1, 2).reshape(b, t, -1).contiguous()
             return self.o_proj(out), (k_all, v_all)
@@ -175,10 +212,10 @@ class GemmaAttention(nn.Module):
         v = self.v_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
         q = q * cos[:, None] + rotate_half(q) * sin[:, None]
         k = k * cos[:, None] + rotate_half(k) * sin[:, None]
-        if past_kv is not None and len(past_kv) == 3:
+        if past_kv is not None and len(past_kv) >= 3:
             # preallocated [B, kv_heads, prefix + t, head_dim] buffers whose first `prefix` rows already
             # hold the cached keys / values: only the t new rows are written (ActionExpert.forward)
-            k_all, v_all, prefix = past_kv
+            k_all, v_all, prefix = past_kv[:3]
             k_all[:, :, prefix:prefix + t] = k
             v_all[:, :, prefix:prefix + t] = v
             k, v = k_all, v_all
@@ -359,7 +396,15 @@ class ActionExpert(nn.Module):
         v_all = torch.empty(shape, dtype=prefix_v.dtype, device=prefix_v.device)
         k_all[:, :, :, :prefix_len] = prefix_k
         v_all[:, :, :, :prefix_len] = prefix_v
-        prefix_kv = [(k_all[i], v_all[i], prefix_len) for i in range(depth)]
+        if GemmaAttention.fused_attention and GemmaAttention.fused_rope and noise.is_cuda and head_dim == 256:
+            # the attention kernel reads the values transposed (keys contiguous): the prefix is
+            # transposed once per chunk, every step appends its rows as columns
+            pitch = (prefix_len + self.chunk + 7) // 8 * 8
+            vt_all = torch.zeros((depth, b, kv_heads, head_dim, pitch), dtype=prefix_v.dtype, device=prefix_v.device)
+            vt_all[..., :prefix_len] = prefix_v.transpose(-1, -2)
+            prefix_kv = [(k_all[i], v_all[i], prefix_len, vt_all[i]) for i in range(depth)]
+        else:
+            prefix_kv = [(k_all[i], v_all[i], prefix_len) for i in range(depth)]
         dt = -1.0 / self.steps
         x_t = noise
         for step in range(self.steps):

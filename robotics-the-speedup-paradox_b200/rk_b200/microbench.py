@@ -4,9 +4,6 @@
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py [w4a16] [w8a8] [fp8] [mxfp8] [nvfp4] [quant]
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py w8a8:400x8192x1024 quant:16384x2048   # explicit shapes
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py layer    # per-kernel device time of one expert layer
-    python robotics-the-speedup-paradox_b200/build.py --trace && \
-        RK_B200_SO=robotics-the-speedup-paradox_b200/rk_b200/librk_b200_trace.so \
-        python robotics-the-speedup-paradox_b200/rk_b200/microbench.py trace
 
 Each shape is timed as a CUDA graph of back-to-back launches that rotate through enough independent
 weight copies to exceed the 126 MB L2 (so a launch streams its weights from HBM), between two CUDA
@@ -145,45 +142,6 @@ class Bench:
               f"({nbytes / us / 1e3 / self.hbm * 100:5.1f}% of {self.hbm_src} copy bw)", flush=True)
 
 
-def role_trace(bench, m, n=16384, k=2048):
-    """Per-role progress of CTA (0, 0) of one W4A16 launch, in SM clocks since the CTA finished its
-    set-up.  Needs the developer build of the library (`build.py --trace`)."""
-    import ctypes
-
-    import numpy as np
-
-    lib, dev = bench.lib, bench.dev
-    try:
-        reader = lib.rk_trace_read
-    except AttributeError:
-        raise SystemExit("this library was not built with build.py --trace (set RK_B200_SO to the trace build)")
-    reader.restype = ctypes.c_int
-    reader.argtypes = [ctypes.c_void_p, ctypes.c_int]
-    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-    q = torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device=dev)
-    sc = torch.rand(k // 128, n, device=dev).to(torch.bfloat16)
-    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-    ws = L.gemm_workspace(L.OP_W4A16, dev, m, n, k)
-    for _ in range(3):
-        lib.rk_gemm_w4a16_g128(L.ptr(x), L.ptr(q), L.ptr(sc), None, L.ptr(out), m, n, k, 0, L.ptr(ws), ws.numel(),
-                               L.stream_ptr(dev))
-    torch.cuda.synchronize()
-    buf = np.zeros(32 * 64, dtype=np.int64)
-    reader(buf.ctypes.data, buf.size)
-    t = buf.reshape(32, 64)
-    t0 = t[9, 0]
-    rows = k // 128 if m <= 64 else k // 64
-    names = ("w_copy", "x_copy", "unpack_start", "unpack_done", "mma_top", "mma_ready", "mma_issued", "commit_done",
-             "epi_full", "epi_done")
-    slots = (0, 1, 2, 4, 26, 5, 12, 6, 7, 8)
-    print(f"--- W4A16 m={m} n={n} k={k}: SM clocks since set-up, one row per pipeline step "
-          f"({'K group' if m <= 64 else '64 elements of K'}); '-' = not recorded for this row")
-    print("step " + " ".join(f"{s:>12s}" for s in names))
-    for g in range(min(rows, 40)):
-        cells = [(t[i, g] - t0) for i in slots]
-        print(f"{g:4d} " + " ".join(f"{c:12d}" if 0 <= c < 10 ** 9 else f"{'-':>12s}" for c in cells))
-
-
 def layer_breakdown(envs=8, prefix=816, repeats=5):
     """Device time per kernel of ONE decoder layer of the action expert (width 1024, MLP 4096, 50
     action tokens x `envs` environments attending to `prefix` cached tokens), eager launches under
@@ -260,10 +218,6 @@ def main(argv):
     which = [a for a in which if ":" not in a]
     if "layer" in which:
         layer_breakdown()
-        return
-    if "trace" in which:
-        for m in (8, 50, 256):
-            role_trace(b, m)
         return
     if "w4a16" in which:
         for m in (1, 8, 50, 128, 256):

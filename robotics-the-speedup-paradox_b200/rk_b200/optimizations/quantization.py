@@ -52,7 +52,7 @@ def pi05_scope(name):
     return None
 
 
-def _factory(precision, *, tactic, pack_reuse, biasless_epilogue, site_bits):
+def _factory(precision, *, tactic, pack_reuse, biasless_epilogue, site_bits, fp4_global_scale=False):
     if precision in ("int8", "int4"):
         from ..integer import IntegerLinear
 
@@ -74,7 +74,8 @@ def _factory(precision, *, tactic, pack_reuse, biasless_epilogue, site_bits):
         return lambda module, name: Fp8CutlassLinear.from_linear(module, role="linear", target_name=name, mode=mode)
     from ..fp4_linear import Fp4CutlassLinear
 
-    return lambda module, name: Fp4CutlassLinear.from_linear(module, role="linear", target_name=name)
+    return lambda module, name: Fp4CutlassLinear.from_linear(module, role="linear", target_name=name,
+                                                             global_scale=fp4_global_scale)
 
 
 def _backend_of(module):
@@ -88,20 +89,26 @@ def _backend_of(module):
 @contextmanager
 def quantize_linears(model, precision, *, scopes=("text",), shared_quant=False, tactic=0, selector=pi05_scope,
                      grouped=False, pack_reuse=False, site_bits=None, group_qkv=False, group_gate_up=False,
-                     group_views=False, biasless_epilogue=False):
-    """Swap every BF16 ``nn.Linear`` whose `selector(name)` is in `scopes`; yield a report; undo on exit."""
+                     group_views=False, biasless_epilogue=False, fp4_global_scale=False):
+    """Swap every BF16 ``nn.Linear`` whose `selector(name)` is in `scopes`; yield a report; undo on exit.
+
+    `fp4_global_scale` (precision "fp4" only): pack weights and activations with the fp32 per-tensor
+    scale amax / (6 * 448) in front of the block scales; off reproduces the reference's format."""
     import torch
 
     if precision not in PRECISIONS:
         raise ValueError("Unknown low-precision backend")
     if not scopes or any(s not in SCOPES for s in scopes):
         raise ValueError("Explicit supported module scopes are required")
+    if fp4_global_scale and precision != "fp4":
+        raise ValueError("fp4_global_scale applies to the fp4 precision only")
     make = _factory(precision, tactic=tactic, pack_reuse=pack_reuse, biasless_epilogue=biasless_epilogue,
-                    site_bits=site_bits)
+                    site_bits=site_bits, fp4_global_scale=fp4_global_scale)
     patches = Patches()
     report = {
         "precision": precision, "scopes": list(scopes), "modules": {}, "skipped": {}, "shared_quant": shared_quant,
         "tactic": tactic, "grouped": {}, "pack_reuse": pack_reuse, "biasless_epilogue": biasless_epilogue,
+        "fp4_global_scale": fp4_global_scale,
     }
     try:
         swapped = 0

@@ -106,13 +106,58 @@ def finish() -> None:
         dist.destroy_process_group()
 
 
+def shard_rows(module, begin, end):
+    """Rows [begin, end) of the output channels of a linear as a module of the same kind.
+
+    A quantized linear is sliced AFTER quantization: the slab takes the matching rows of the packed
+    codes and of the per-row scales (or 128-row scale-factor blocks) and SHARES the per-tensor
+    scale of the whole weight, so that every slab computes exactly the columns the one-GPU linear
+    computes.  (Quantizing each slab by itself would give every slab its own per-tensor scale and a
+    slightly different result.)  Any module exposing `shard_output_rows(begin, end)` slices itself."""
+    if hasattr(module, "shard_output_rows"):
+        return module.shard_output_rows(begin, end)
+    if isinstance(module, torch.nn.Linear):
+        shard = torch.nn.Linear(module.in_features, end - begin, bias=module.bias is not None,
+                                device=module.weight.device, dtype=module.weight.dtype)
+        with torch.no_grad():
+            shard.weight.copy_(module.weight[begin:end])
+            if module.bias is not None:
+                shard.bias.copy_(module.bias[begin:end])
+        return shard.requires_grad_(False)
+    kind = type(module).__name__
+    bias = None if getattr(module, "bias", None) is None else module.bias[begin:end].contiguous()
+    rows = end - begin
+    if kind == "IntegerLinear":
+        return type(module)(module.packed_weight[begin:end].contiguous(), module.weight_scale[begin:end].contiguous(),
+                            bias, module.in_features, rows, module.bits, module.tactic, module.pack_reuse,
+                            module.biasless_epilogue)
+    if kind == "W4A16Linear":
+        return type(module)(module.packed_weight[begin:end].contiguous(), module.weight_scale[:, begin:end].contiguous(),
+                            bias, module.in_features, rows, module.tactic)
+    if kind in ("Fp8CutlassLinear", "Fp4CutlassLinear"):
+        codes = module.packed_weight[begin:end].contiguous()
+        block_scaled = kind == "Fp4CutlassLinear" or module.mode == "mxfp8"
+        scale = module.weight_scale  # per-tensor: one shared scalar
+        if block_scaled:
+            # scale factors live in 512-byte chunks per 128 rows: a slab is whole row blocks
+            if begin % 128 or (rows % 128 and end != module.out_features):
+                raise ValueError("block-scaled slabs must start and end on multiples of 128 rows")
+            per_block = module.weight_scale.numel() // ((module.out_features + 127) // 128)
+            scale = module.weight_scale[begin // 128 * per_block:(end + 127) // 128 * per_block].contiguous()
+        if kind == "Fp8CutlassLinear":
+            return type(module)(codes, scale, bias, module.in_features, rows, module.role, module.target_name, module.mode)
+        return type(module)(codes, scale, module.weight_global_scale, bias, module.in_features, rows, module.role,
+                            module.target_name)
+    raise TypeError(f"do not know how to take output rows of a {kind}")
+
+
 class ColumnParallelLinear(torch.nn.Module):
     """One exchange step across GPUs: the widest projections (gate/up, N = 16384) split along N.
 
-    Rank r builds its quantized linear from rows [r * N / G, (r + 1) * N / G) of the weight (and the
-    matching bias entries); activations are replicated; every rank computes its [M, N / G] slab and
-    an all-gather assembles [M, N] on all ranks.  `make_linear(nn.Linear) -> module` is any of the
-    quantized `from_linear` constructors (or the identity, for a bf16 slab)."""
+    The full linear is quantized ONCE (`make_linear`, or it already is a quantized module); rank r
+    then keeps rows [r * N / G, (r + 1) * N / G) of its packed codes and scales (`shard_rows`) and
+    the shared per-tensor scale.  Activations are replicated; every rank computes its [M, N / G]
+    slab and an all-gather assembles [M, N] on all ranks - bit-identical to the one-GPU output."""
 
     def __init__(self, linear, info: RankInfo, make_linear=None):
         super().__init__()
@@ -123,15 +168,8 @@ class ColumnParallelLinear(torch.nn.Module):
         self.out_features = n
         self.in_features = linear.in_features
         self.slab = n // info.world
-        rows = slice(info.rank * self.slab, (info.rank + 1) * self.slab)
-        shard = torch.nn.Linear(linear.in_features, self.slab, bias=linear.bias is not None,
-                                device=linear.weight.device, dtype=linear.weight.dtype)
-        with torch.no_grad():
-            shard.weight.copy_(linear.weight[rows])
-            if linear.bias is not None:
-                shard.bias.copy_(linear.bias[rows])
-        shard.requires_grad_(False)
-        self.local = make_linear(shard) if make_linear is not None else shard
+        full = make_linear(linear) if make_linear is not None else linear
+        self.local = shard_rows(full, info.rank * self.slab, (info.rank + 1) * self.slab)
 
     def forward(self, x):
         part = self.local(x)  # [..., N / G]

@@ -14,7 +14,9 @@ from rk_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
-SHAPES = [(16, 128, 128), (64, 256, 512), (100, 520, 448), (300, 264, 320), (816, 16384, 2048)]
+# the last three take the CTA-pair kernel (512 activation rows and more): ragged n and K, full size
+SHAPES = [(16, 128, 128), (64, 256, 512), (100, 520, 448), (300, 264, 320), (600, 328, 320), (1100, 520, 448),
+          (816, 16384, 2048)]
 
 
 @pytest.fixture(scope="module")

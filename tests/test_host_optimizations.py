@@ -256,3 +256,51 @@ def test_condition_caches_leave_the_flow_loop_output_unchanged():
     cache = ConstantProjectionCache(lambda v: (calls.append(1), v + 1)[1], lambda v: False)
     t = torch.zeros(2)
     assert torch.equal(cache(t), t + 1) and torch.equal(cache(t), t + 1) and len(calls) == 2 and len(cache) == 0
+
+
+def test_fp8_prefill_scale_state_measures_every_nth_multirow_call(monkeypatch):
+    """Periodic reuse of the dynamic FP8 activation scale (reference: blackwell/fp8_linear.py:147-239),
+    with the two quantizer entry points replaced by recorders."""
+    import torch
+
+    from rk_b200 import fp8_linear as P8
+
+    calls = []
+    monkeypatch.setattr(P8, "quantize_bf16", lambda t: (calls.append("measure") or "codes", torch.tensor([float(len(calls))])))
+    monkeypatch.setattr(P8, "quantize_bf16_with_scale", lambda t, s: calls.append(("reuse", float(s))) or "codes")
+    state = P8.Fp8PrefillScaleState(3)
+    x = torch.zeros(4, 8)
+    scales = [float(state.quantize(x)[1]) for _ in range(7)]
+    assert calls == ["measure", ("reuse", 1.0), ("reuse", 1.0), "measure", ("reuse", 4.0), ("reuse", 4.0), "measure"]
+    assert scales == [1.0, 1.0, 1.0, 4.0, 4.0, 4.0, 7.0]
+    assert state.to_dict() == {"eligible": True, "interval": 3, "prefill_calls": 7, "refreshes": 3, "reuses": 4,
+                               "operator_fallbacks": 0}
+    # single-row (decode) calls always measure and do not advance the schedule
+    calls.clear()
+    state.quantize(torch.zeros(1, 8))
+    assert calls == ["measure"] and state.prefill_calls == 7
+    # ineligible roles and interval 1 never reuse; "static" measures once
+    assert P8.Fp8PrefillScaleState(5, eligible=False).interval == 1
+    assert P8.resolve_fp8_prefill_scale_refresh_interval("static") == 2 ** 31 - 1
+    monkeypatch.setenv(P8.PREFILL_SCALE_REFRESH_INTERVAL_ENV, "4")
+    assert P8.Fp8PrefillScaleState().interval == 4
+    for bad in ("0", "-2", "soon"):
+        with pytest.raises(ValueError):
+            P8.resolve_fp8_prefill_scale_refresh_interval(bad)
+
+
+def test_fp8_prefill_scale_refresh_is_configured_per_model():
+    import torch
+
+    from rk_b200 import fp8_linear as P8
+
+    class Layer(torch.nn.Module):
+        def __init__(self, eligible):
+            super().__init__()
+            self._prefill_scale_state = P8.Fp8PrefillScaleState(eligible=eligible)
+
+    model = torch.nn.Sequential(Layer(True), Layer(True), Layer(False))
+    assert P8.configure_fp8_prefill_scale_refresh(model, 8) == {"interval": 8, "states": 2}
+    stats = P8.fp8_prefill_scale_refresh_stats(model)
+    assert stats["states"] == 2 and stats["intervals"] == [8] and stats["reuses"] == 0
+    assert P8.configure_fp8_prefill_scale_refresh(torch.nn.Sequential(Layer(False))) == {"interval": 1, "states": 0}

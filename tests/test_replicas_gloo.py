@@ -93,6 +93,73 @@ def test_column_parallel_slabs_gather_to_the_full_output_on_two_gloo_ranks():
         assert same  # a slab of a linear is bit-identical to the same columns of the full linear
 
 
+class _PerTensorQuantLinear(torch.nn.Module):
+    """CPU stand-in for a per-tensor-scaled quantized linear (codes = round(w / scale), one scale for
+    the whole weight), exposing the slicing hook the quantized modules are sharded through."""
+
+    def __init__(self, codes, scale):
+        super().__init__()
+        self.codes, self.scale = codes, scale
+        self.out_features, self.in_features = codes.shape
+
+    @classmethod
+    def from_linear(cls, linear):
+        scale = linear.weight.abs().max() / 127.0
+        return cls(torch.round(linear.weight / scale), scale)
+
+    def shard_output_rows(self, begin, end):
+        return _PerTensorQuantLinear(self.codes[begin:end].clone(), self.scale)
+
+    def forward(self, x):
+        return (x @ self.codes.T) * self.scale
+
+
+def _column_parallel_quantized_main(rank, world, port, results):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    sys.path.insert(0, str(root / "robotics-the-speedup-paradox_b200"))
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from rk_b200 import replicas
+
+    info = replicas.rank_info()
+    device = torch.device("cpu")
+    replicas.init(info, device)
+    torch.manual_seed(0)
+    full = torch.nn.Linear(64, 48, bias=False).requires_grad_(False)
+    with torch.no_grad():
+        full.weight[40] *= 9.0  # the largest weight sits in the last slab: slab-wise scales would differ
+    x = torch.randn(7, 64)
+    one_gpu = _PerTensorQuantLinear.from_linear(full)
+    layer = replicas.ColumnParallelLinear(full, info, _PerTensorQuantLinear.from_linear)
+    out, want = layer(x), one_gpu(x)
+    rel = float((out - want).norm() / want.norm())
+    # what the sharded mode must NOT do: quantize every slab by itself
+    slab = torch.nn.Linear(64, 24, bias=False).requires_grad_(False)
+    with torch.no_grad():
+        slab.weight.copy_(full.weight[rank * 24:(rank + 1) * 24])
+    own_scale = float(_PerTensorQuantLinear.from_linear(slab).scale)
+    results[rank] = (rel, float(layer.local.scale) == float(one_gpu.scale), own_scale == float(one_gpu.scale))
+    replicas.barrier(info, device)
+    replicas.finish()
+
+
+@pytest.mark.timeout(120)
+def test_column_parallel_quantized_slabs_share_the_one_gpu_scale():
+    """Quantize once, shard the codes: the gathered output equals the one-GPU output exactly
+    (relative Frobenius difference 0), because every slab keeps the whole weight's scale."""
+    world = 2
+    port = _free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_column_parallel_quantized_main, args=(world, port, results), nprocs=world, join=True)
+    assert results[0][0] == 0.0 and results[1][0] == 0.0
+    assert results[0][1] and results[1][1]          # both slabs carry the shared scale
+    assert not results[0][2] and results[1][2]      # a slab quantized alone would not (rank 0 lacks the largest weight)
+
+
 def test_single_process_defaults_and_validation():
     import sys
     from pathlib import Path
