@@ -139,7 +139,9 @@ int rk_gated_rmsnorm_quant_rows(const void* x, const void* branch, const void* g
 
 /* out[m, n] = bf16( (float(sum_k a*b) * sa[m]) * sb[n] (+ bias[n]) ), int32 accumulation.
  * Replaces `robotics_integer::gemm` / `gemm_biasless` (ampere_ada/csrc/integer_gemm.cu:22-195).
- *   bits 8: a int8 [m, kpad], b int8 [n, kpad].  bits 4: packed nibbles [., kpad/2].
+ *   bits 8: a int8 [m, kpad], b int8 [n, kpad].  bits 4: packed nibbles [., kpad/2]; the kernel
+ *   widens both operands to int8 in shared memory (tcgen05 has no 4-bit integer kind; products and
+ *   int32 sums are identical), so W4A4 needs no scratch beyond the workspace header.
  *   sa f32 [m], sb f32 [n], bias bf16 [n] or NULL; out bf16 [m, n] contiguous;
  *   kpad % 128 == 0, n % 8 == 0; tactic 0..7 is accepted and never changes the result. */
 int rk_gemm_int(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
@@ -231,6 +233,17 @@ int rk_rmsnorm_quant_fp8(const void* x, const void* residual, const void* weight
 int rk_swiglu_quant_fp8(const void* gate_up, int64_t rows, int64_t inter, const float* scale_in, void* q,
                         float* scale_out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The "producer" form of the FP8 GEMM: bf16 activations with a UNIT activation scale are converted
+ * to e4m3 (clamped to +-448) inside the kernel - raw bf16 rows land in shared memory by TMA and
+ * four warps rewrite them into the MMA's operand tile - so no e4m3 copy of the activations ever
+ * exists in global memory and there is no separate quantizer launch.
+ * out[m, n] = bf16( scale_b * sum_k e4m3(x) * b (+ bias[n]) ).  Replaces `linear_forward_producer` /
+ * `fp8_producer_gemm::run` (blackwell/csrc/fp8_cutlass_linear.cu:727-856, 1268-1315).
+ *   x bf16 [m, k] contiguous; b e4m3 [n, k]; scale_b: device pointer to one f32; k % 16 == 0, n % 8 == 0. */
+int rk_gemm_fp8_producer(const void* x, const void* b, const float* scale_b, const void* bias, void* out,
+                         int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
 /* ---- MXFP8 ------------------------------------------------------------------------------ */
 
 /* Per 32 consecutive k: SF = UE8M0 round-up of max|x| * rcp(448) (255 when the block holds a
@@ -276,6 +289,36 @@ int rk_nvfp4_global_scale(const void* x, int64_t elements, float* scale_out, voi
 int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, const void* b, const void* sfb,
                   const float* gb, const void* bias, void* out, int64_t m, int64_t n, int64_t k, int tactic,
                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same with a choice of gate/up layout: interleaved != 0 reads blocks of 128 columns holding 64 up
+ * values followed by their 64 gate values (the layout of a fused gate/up projection,
+ * blackwell/csrc/fp4_cutlass_linear.cu:958-965, 1051-1143); inter % 64 == 0 then. */
+int rk_swiglu_pack_nvfp4_layout(const void* gate_up, int64_t rows, int64_t inter, int interleaved, void* q, void* sf,
+                                void* stream);
+
+/* ---- W4A8 MX: MXFP4 weights x MXFP8 activations ------------------------------------------------ */
+
+/* Per 32 consecutive k: s = the smallest power of two >= max|w| / 6 (1.0 for a zero block), stored as
+ * a UE8M0 byte; q = e2m1(w / s), two codes per byte, low nibble = even k.  Replaces `pack_mxfp4_weight`
+ * (blackwell/csrc/fp4_mx_cutlass_linear.cu:59-100).  w bf16 [rows, k], k % 32 == 0; q uint8 [rows, k/2];
+ * sf: rk_sf_bytes(rows, k/32) bytes, fully written. */
+int rk_pack_mxfp4_weight(const void* w, int64_t rows, int64_t k, void* q, void* sf, void* stream);
+/* Per 32 consecutive k: s = the smallest power of two >= max|x| / 448; q = e4m3(clamp(x / s, +-448)).
+ * Replaces `pack_mxfp8_activation` (blackwell/csrc/fp4_mx_cutlass_linear.cu:103-132).  (The MXFP8 GEMM's
+ * own packer, rk_pack_mxfp8, rounds max|x| * rcp(448) up instead and marks non-finite blocks.) */
+int rk_pack_mxfp8_act_w4a8(const void* x, int64_t rows, int64_t k, void* q, void* sf, void* stream);
+/* SwiGLU in front of the same block quantizer: a = gate / (1 + exp(-gate)) * up in fp32 (not rounded
+ * to bf16).  Replaces `pack_swiglu_mxfp8` (blackwell/csrc/fp4_mx_cutlass_linear.cu:134-179).
+ *   gate_up bf16 [rows, 2*inter] (gate first, or the interleaved layout above); q e4m3 [rows, inter]. */
+int rk_swiglu_pack_mxfp8_w4a8(const void* gate_up, int64_t rows, int64_t inter, int interleaved, void* q, void* sf,
+                              void* stream);
+/* out = bf16( sum over 32-blocks (sfa * sfb * sum_k a*b) (+ bias[n]) ): MXFP8 activations against MXFP4
+ * weights.  The packed weights are expanded to e4m3 (which holds every e2m1 value exactly) in shared
+ * memory and the product runs as kind::mxf8f6f4 with both UE8M0 scale sets.  Replaces
+ * `linear_w4a8_packed` / `mx_gemm::run` / `mx_swap_gemm::run` (blackwell/csrc/fp4_mx_cutlass_linear.cu:285-555).
+ *   a e4m3 [m, k], sfa rk_sf_bytes(m, k/32); b uint8 [n, k/2], sfb rk_sf_bytes(n, k/32); k % 32 == 0, n % 8 == 0. */
+int rk_gemm_w4a8_mx(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias, void* out,
+                    int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- between the q/k/v projection and attention ------------------------------------------- */
 /* Rotary embedding of fresh query / key rows fused with the key / value cache update: one launch

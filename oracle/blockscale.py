@@ -129,6 +129,74 @@ def dequant_nvfp4(packed, sf, global_scale=None):
     return out
 
 
+# ---- W4A8 MX: MXFP4 weights x MXFP8 activations (blackwell/csrc/fp4_mx_cutlass_linear.cu:47-179) ------
+
+def ceil_pow2_ue8m0(v):
+    """UE8M0 byte of the smallest power of two >= v (`ceil_power_of_two`, :47-58): 127 (= 1.0) for v <= 0
+    or NaN; inputs below the smallest normal number map to byte 1."""
+    v = f32(v)
+    bits = v.view(np.uint32)
+    e = (bits >> 23).astype(np.int64)
+    e = e + ((bits & 0x7FFFFF) != 0)
+    e = np.where((bits >> 23) == 0, 1, e)
+    e = np.minimum(e, 254)
+    return np.where(v > 0, e, 127).astype(np.uint8)
+
+
+def pack_mxfp8_ceil(x):
+    """Activation side: per 32 k, s = ceil_pow2(amax / 448), q = e4m3(clamp(x / s, +-448)) (:103-132)."""
+    x = f32(x)
+    rows, k = x.shape
+    b = x.reshape(rows, k // 32, 32)
+    amax = np.abs(b).max(axis=2).astype(np.float32)
+    sf = ceil_pow2_ue8m0((amax / np.float32(448.0)).astype(np.float32))
+    inverse = ue8m0_decode((254 - sf.astype(np.int64)) & 255)
+    v = np.clip((b * inverse[:, :, None]).astype(np.float32), -448.0, 448.0)
+    return e4m3_encode(v).reshape(rows, k), sf, swizzle_sf(sf)
+
+
+def pack_mxfp4_ceil(w):
+    """Weight side: per 32 k, s = ceil_pow2(amax / 6), q = e2m1(w / s), low nibble = even k (:59-100)."""
+    w = f32(w)
+    rows, k = w.shape
+    b = w.reshape(rows, k // 32, 32)
+    amax = np.abs(b).max(axis=2).astype(np.float32)
+    sf = ceil_pow2_ue8m0((amax / np.float32(6.0)).astype(np.float32))
+    inverse = ue8m0_decode((254 - sf.astype(np.int64)) & 255)
+    codes = e2m1_encode((b * inverse[:, :, None]).astype(np.float32)).reshape(rows, k).astype(np.uint8)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    return packed, sf, swizzle_sf(sf)
+
+
+def dequant_mxfp4(packed, sf):
+    p = np.asarray(packed, dtype=np.uint8)
+    rows = p.shape[0]
+    codes = np.empty((rows, p.shape[1] * 2), dtype=np.uint8)
+    codes[:, 0::2] = p & 15
+    codes[:, 1::2] = p >> 4
+    k = codes.shape[1]
+    v = e2m1_decode(codes).reshape(rows, k // 32, 32).astype(np.float64)
+    return (v * ue8m0_decode(sf).astype(np.float64)[:, :, None]).reshape(rows, k)
+
+
+def deinterleave_gate_up(gate_up, inter):
+    """Interleaved layout (blocks of 128 columns: 64 up values, then their 64 gate values;
+    blackwell/csrc/fp4_cutlass_linear.cu:958-965) -> [gate | up]."""
+    g = np.asarray(gate_up)
+    rows = g.shape[0]
+    blocks = g.reshape(rows, inter // 64, 2, 64)
+    return np.concatenate([blocks[:, :, 1, :].reshape(rows, inter), blocks[:, :, 0, :].reshape(rows, inter)], axis=1)
+
+
+def swiglu_f32(gate_up, inter):
+    """gate / (1 + exp(-gate)) * up in fp32, NOT rounded to bf16 (the W4A8-MX producer, :134-179)."""
+    g = f32(gate_up[:, :inter])
+    u = f32(gate_up[:, inter:2 * inter])
+    with np.errstate(over="ignore"):
+        e = np.exp(-g.astype(np.float64)).astype(np.float32)
+    return ((g / (np.float32(1.0) + e)).astype(np.float32) * u).astype(np.float32)
+
+
 def gemm_dequantized(a, b, bias=None):
     """bf16(a . b^T (+ bias)) on dequantized float64 operands; returns (bf16-rounded, float64)."""
     acc = a @ b.T

@@ -13,8 +13,9 @@
 // 128 CTAs.  Per CTA:
 //   1. S = Q K^T for its slice with tcgen05 kind::f16 MMAs (Q and the K slice staged by TMA in the
 //      128-byte swizzle), fp32 accumulators in TMEM;
-//   2. softmax threads (one per row) find the slice's running max and sum; the KS CTAs exchange
-//      them through distributed shared memory, so every CTA knows the exact global max and sum;
+//   2. softmax threads (one per row) find the slice's maximum, the KS CTAs exchange the maxima
+//      through distributed shared memory, exp(score - max) is taken once per score and summed, the
+//      sums are exchanged: every CTA knows the exact global max and sum;
 //   3. p is written back to TMEM as packed bf16 (over the scores it replaces) and is the TMEM
 //      A operand of the second MMA, O_slice = P V, against V^T tiles (keys contiguous) from TMA;
 //   4. the partial outputs are parked in shared memory and summed across the cluster in rank
@@ -52,6 +53,12 @@ __device__ __forceinline__ float attn_round_bf16(float x) { return __bfloat162fl
 // score as the reference's bf16 tensor ops leave it: the matmul output rounded to bf16, times the scale, rounded again
 __device__ __forceinline__ float attn_score(uint32_t acc_bits, float scaling) {
   return attn_round_bf16(attn_round_bf16(__uint_as_float(acc_bits)) * scaling);
+}
+
+__device__ __forceinline__ float attn_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ void tmem_st_16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -188,6 +195,7 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     if (alive) tc_commit(smem_u32(&bar_s_full), on);
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1b
     // O = P V: the probabilities are the TMEM A operand (two bf16 per column), V^T blocks of 64 keys
     alive = alive && mbar_wait_bounded(smem_u32(&bar_p_full), 0, &abort_flag, p.status, RK_DEV_TIMEOUT_XFORM);
     tc_fence_after();
@@ -217,53 +225,66 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int valid = min(p.keys, p.kv_len - key0);  // keys of this slice that exist (may be <= 0 for a trailing slice)
     bool ok = mbar_wait_group(smem_u32(&bar_s_full), 0, r == 0, 1, 128, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC, verdict, 0);
     tc_fence_after();
-    // pass 1: running max and sum of exp over the slice
-    float m_run = -INFINITY, l_run = 0.0f;
+    // The softmax threads are one warp per scheduler, so their instruction stream is latency bound:
+    // the passes below are written for few instructions per score and independent chains.
+    // pass 1: the slice's maximum.  Rounding to bf16 and the positive scale are monotonic, so the
+    // maximum of the scores is the score of the largest raw accumulator.
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     for (int c0 = 0; c0 < p.keys; c0 += 32) {
       uint32_t a[32];
       __syncwarp();
       tmem_ld_32(tmem_s + lane_addr + c0, a);
       tc_wait_ld();
-      float sv[32], cm = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        sv[j] = (c0 + j < valid) ? attn_score(a[j], p.scaling) : -INFINITY;
-        cm = fmaxf(cm, sv[j]);
-      }
-      const float m_new = fmaxf(m_run, cm);
-      if (m_new > -INFINITY) {
-        float acc = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc += exp2f((sv[j] - m_new) * log2e);
-        l_run = l_run * exp2f((m_run - m_new) * log2e) + acc;
-        m_run = m_new;
-      }
+      for (int j = 0; j < 32; ++j)
+        if (c0 + j < valid) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(a[j]));
     }
-    row_max[r] = m_run;
-    row_sum[r] = l_run;
+    const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    row_max[r] = valid > 0 ? attn_score(__float_as_uint(m_raw), p.scaling) : -INFINITY;
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1
-    // exact global statistics: every CTA combines the KS slices in rank order
+    // the exact global maximum: every CTA reads the KS slice maxima
     float m_glob = -INFINITY;
-    float ms[8], ls[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      ms[q] = -INFINITY, ls[q] = 0.0f;
       if (q < p.splits) {
-        uint32_t am, al;
+        uint32_t am;
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(am) : "r"(smem_u32(&row_max[r])), "r"(q));
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(al) : "r"(smem_u32(&row_sum[r])), "r"(q));
-        ms[q] = dsmem_ld_f32(am);
-        ls[q] = dsmem_ld_f32(al);
-        m_glob = fmaxf(m_glob, ms[q]);
+        m_glob = fmaxf(m_glob, dsmem_ld_f32(am));
       }
     }
+    // pass 2: e = exp(score - max) once per score, summed, and written back over the score (fp32)
+    const float mneg = -m_glob * log2e;
+    float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int c0 = 0; c0 < p.keys; c0 += 32) {
+      uint32_t a[32];
+      __syncwarp();
+      tmem_ld_32(tmem_s + lane_addr + c0, a);
+      tc_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float e = 0.0f;
+        if (c0 + j < valid) e = attn_ex2(fmaf(attn_score(a[j], p.scaling), log2e, mneg));
+        ls[j & 3] += e;
+        a[j] = __float_as_uint(e);
+      }
+      __syncwarp();
+      tmem_st_32(tmem_s + lane_addr + c0, a);
+    }
+    tc_wait_st();
+    row_sum[r] = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1b
     float l_glob = 0.0f;
 #pragma unroll
-    for (int q = 0; q < 8; ++q)
-      if (q < p.splits && ms[q] > -INFINITY) l_glob += ls[q] * exp2f((ms[q] - m_glob) * log2e);
+    for (int q = 0; q < 8; ++q) {  // fixed order: slice 0, 1, ...
+      if (q < p.splits) {
+        uint32_t al;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(al) : "r"(smem_u32(&row_sum[r])), "r"(q));
+        l_glob += dsmem_ld_f32(al);
+      }
+    }
     const float inv_l = l_glob > 0.0f ? __fdiv_rn(1.0f, l_glob) : 0.0f;
-    // pass 2: probabilities as packed bf16 over the scores they replace (column j of P covers score
-    // columns 2j, 2j+1, which this thread has already read when it writes)
+    // pass 3: probabilities as packed bf16 over the values they replace (column j of P covers columns
+    // 2j, 2j+1, which this thread has already read when it writes)
     for (int c0 = 0; c0 < p.keys; c0 += 32) {
       uint32_t a[32];
       __syncwarp();
@@ -271,14 +292,8 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tc_wait_ld();
       uint32_t w[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float p0 = 0.0f, p1 = 0.0f;
-        if (c0 + 2 * j < valid)
-          p0 = exp2f((attn_score(a[2 * j], p.scaling) - m_glob) * log2e) * inv_l;
-        if (c0 + 2 * j + 1 < valid)
-          p1 = exp2f((attn_score(a[2 * j + 1], p.scaling) - m_glob) * log2e) * inv_l;
-        w[j] = pack_bf16x2(p0, p1);
-      }
+      for (int j = 0; j < 16; ++j)
+        w[j] = pack_bf16x2(__uint_as_float(a[2 * j]) * inv_l, __uint_as_float(a[2 * j + 1]) * inv_l);
       __syncwarp();
       tmem_st_16(tmem_s + lane_addr + (c0 >> 1), w);
     }
@@ -299,7 +314,10 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       for (int j = 0; j < 32; ++j) part[(c0 + j) * 128 + r] = ok ? __uint_as_float(a[j]) : 0.0f;
     }
   }
-  if (warp == 0) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1
+  if (warp == 0) {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1b
+  }
 
   // ---------------------------------------------------------------- sum the slices across the cluster
   __syncthreads();
@@ -318,13 +336,23 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     __nv_bfloat16* const dst =
         p.out + ((static_cast<long long>(b) * p.tokens + token) * p.heads + head) * kAttnDim + c_lo;
     for (int c8 = 0; c8 < per; c8 += 8) {
+      // all loads of eight columns from every slice first (up to 64 in flight), then the sums in slice order
+      float x[8][8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          x[q][u] = 0.0f;
+          if (q < p.splits) x[q][u] = dsmem_ld_f32(peer[q] + static_cast<uint32_t>((c_lo + c8 + u) * 128 + r) * 4u);
+        }
+      }
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        float t = 0.0f;
+        float t = x[0][u];
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          if (q < p.splits) t += dsmem_ld_f32(peer[q] + static_cast<uint32_t>((c_lo + c8 + u) * 128 + r) * 4u);
+        for (int q = 1; q < 8; ++q)
+          if (q < p.splits) t += x[q][u];
         v[u] = t;
       }
       if (r < rows_valid && !abort_flag)

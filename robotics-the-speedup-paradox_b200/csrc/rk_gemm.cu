@@ -216,7 +216,17 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   // B-role tiles; otherwise activations take the 128-lane axis and weights use wide tiles.
   pl.swap = (m <= 1024 && !(tactic & 1)) ? 1 : 0;
   pl.sfb_blocks = 0;
-  if (block_scaled) {
+  const bool rewriting = kind == KIND_I4 || kind == KIND_F8P || kind == KIND_MX48;
+  if (rewriting) {
+    // raw operands are rewritten in shared memory: activations on the 128-lane axis, 128-row weight
+    // tiles (their raw rows and the rewritten tile both live in the stage), persistent schedule
+    pl.swap = 0;
+    pl.bn = n < 128 ? static_cast<int>(round_up(n, 64)) : 128;
+    pl.tiles_a = static_cast<int>((m + 127) / 128);
+    pl.tiles_b = static_cast<int>((n + pl.bn - 1) / pl.bn);
+    pl.sfb_blocks = kind == KIND_MX48 ? 1 : 0;
+    tactic |= 2;
+  } else if (block_scaled) {
     // A-role tiles are whole 128-row scale blocks; B-role tiles start on multiples of 64 rows
     const int64_t rows_b = pl.swap ? m : n;
     pl.bn = block_scaled_tile_rows(rows_b);
@@ -264,7 +274,7 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   // TMEM: accumulator buffers (+ scale-factor columns for the block-scaled kinds: 16 for the A
   // role, then 4 per K chunk and 128-row block of the B role)
   pl.acc_stride = static_cast<int>(round_up(pl.bn, 32));
-  const int sf_cols = block_scaled ? 16 + 4 * (kind == KIND_NVF4 ? 4 : 1) * pl.sfb_blocks : 0;
+  const int sf_cols = (block_scaled || kind == KIND_MX48) ? 16 + 4 * (kind == KIND_NVF4 ? 4 : 1) * pl.sfb_blocks : 0;
   pl.acc_bufs = (2 * pl.acc_stride + sf_cols <= 512) ? 2 : 1;
   pl.tmem_cols = pow2_at_least(pl.acc_bufs * pl.acc_stride + sf_cols, 32);
   // split-K across a cluster when the tiles cannot occupy the machine; >= 2 K blocks per CTA
@@ -310,7 +320,7 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.grid_x, 1, pl.splits);
-  cfg.blockDim = dim3(kGemmThreads);
+  cfg.blockDim = dim3(KindTraits<KIND>::kThreads);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -328,6 +338,16 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
     return fail(RK_ECUDA, "rk_gemm_tc_kernel launch: %s", cudaGetErrorString(e));
   }
   return RK_OK;
+}
+
+// RK_B200_ISSUE_BLOCK=0 issues every tensor-core instruction under its own predicate instead of the
+// straight-line block of the elected lane (kept for comparison).
+int issue_block_mode() {
+  static const int mode = [] {
+    const char* v = std::getenv("RK_B200_ISSUE_BLOCK");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
+  return mode;
 }
 
 // Two-CTA schedule: RK_B200_TWO_CTA=0 never, =1 whenever the kind allows it, unset = for
@@ -378,7 +398,16 @@ int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorM
   return RK_OK;
 }
 
+// the column-parallel ("peer") mode of run_tc: see GemmParams::peer_*
+struct PeerArgs {
+  void* out[8];
+  int* flags[8];
+  int64_t ld, col0;
+  int count, rank, epoch;
+};
+
 struct TcArgs {
+  const PeerArgs* peer = nullptr;
   int kind;
   const void* act;       // [m, k_bytes] bytes
   const void* wgt;       // [n, k_bytes] bytes
@@ -400,7 +429,7 @@ struct TcArgs {
 };
 
 int run_tc(const TcArgs& a) {
-  if (!a.act || !a.wgt || (!a.out && !a.acc_out)) return fail(RK_EINVAL, "%s: null pointer", a.who);
+  if (!a.act || !a.wgt || (!a.out && !a.acc_out && !a.peer)) return fail(RK_EINVAL, "%s: null pointer", a.who);
   if (a.m < 1 || a.n < 1 || a.k_bytes < 16) return fail(RK_EINVAL, "%s: empty problem", a.who);
   if (a.m > (1 << 24) || a.n > (1 << 24) || a.k_bytes > (1 << 24)) return fail(RK_EUNSUPPORTED, "%s: dimension too large", a.who);
   if (a.n % 8 != 0) return fail(RK_EINVAL, "%s: n must be a multiple of 8", a.who);
@@ -409,14 +438,16 @@ int run_tc(const TcArgs& a) {
   if (rc != RK_OK) return rc;
   const int kblocks = static_cast<int>((a.k_bytes + kStageKBytes - 1) / kStageKBytes);
   const bool block_scaled = a.kind == KIND_MXF8 || a.kind == KIND_NVF4;
-  const bool two_cta_kind = a.acc_out == nullptr && a.out != nullptr;
+  const bool two_cta_kind = a.acc_out == nullptr && a.out != nullptr && a.kind <= KIND_NVF4 && a.peer == nullptr;
   const int mode = two_cta_mode();
-  // CTA pairs from 512 activation rows on (two 256-row pair tiles): one CTA cannot take operand bytes
-  // from L2 fast enough to keep its tensor pipe busy, a pair halves the weight bytes per SM
-  static const int64_t pair_min_m = [] {
+  // CTA pairs: from 512 activation rows on for the block-scaled kinds, whose main loop is paced by
+  // the issuing thread (scale copies + MMAs: up to 17 tensor-core instructions per stage; one
+  // instruction of a pair drives two SMs), beyond 1024 rows for the others (no gain below: measured)
+  static const int64_t pair_min_env = [] {
     const char* v = std::getenv("RK_B200_TWO_CTA_MIN_M");
-    return v ? static_cast<int64_t>(std::atoll(v)) : static_cast<int64_t>(512);
+    return v ? static_cast<int64_t>(std::atoll(v)) : static_cast<int64_t>(0);
   }();
+  const int64_t pair_min_m = pair_min_env > 0 ? pair_min_env : (block_scaled ? 512 : 1025);
   if (two_cta_kind && mode != 0 && ((mode == 1 && a.m > 256) || a.m >= pair_min_m) && a.n >= 128) {
     Gemm2Params p2{};
     p2.m = static_cast<int>(a.m);
@@ -435,12 +466,13 @@ int run_tc(const TcArgs& a) {
       // the scale factors need tensor-memory columns of their own: 192-column tiles keep two
       // accumulator buffers (the epilogue overlaps the next tile's MMAs), 256-column tiles have
       // one and pay for it with an exposed epilogue, which only long K loops amortise
-      p2.bn = ((a.tactic & 4) || a.n < 192) ? 128 : (kblocks >= 48 ? 256 : 192);
+      p2.bn = ((a.tactic & 4) || a.n < 192) ? 128 : (kblocks >= 24 ? 256 : 192);
       if (bn_env == 128 || bn_env == 192 || bn_env == 256) p2.bn = bn_env;
       p2.acc_bufs = p2.bn == 256 ? 1 : 2;
     }
     p2.sfb_blocks = block_scaled ? (p2.bn == 128 ? 1 : 2) : 0;
     p2.sf_kt = a.sf_kt;
+    p2.issue_block = issue_block_mode();
     p2.tiles_m = static_cast<int>((a.m + 255) / 256);
     p2.tiles_n = static_cast<int>((a.n + p2.bn - 1) / p2.bn);
     const int stage = gemm2_stage_bytes(a.kind, p2.bn, p2.sfb_blocks);
@@ -489,13 +521,24 @@ int run_tc(const TcArgs& a) {
   CUtensorMap tm_act, tm_wgt, tm_out;
   const uint32_t box_act = pl.swap ? pl.bn : kTileA;
   const uint32_t box_wgt = pl.swap ? kTileA : pl.bn;
-  rc = make_map_2d(&tm_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, box_act,
-                   CU_TENSOR_MAP_SWIZZLE_128B);
+  // an operand that is rewritten in shared memory is fetched as raw rows: `raw` bytes of every row per
+  // 128 MMA bytes of K, unswizzled; its row pitch is k_bytes * raw / 128
+  const int raw_act = gemm_raw_bytes_a(a.kind), raw_wgt = gemm_raw_bytes_b(a.kind);
+  if (raw_act)
+    rc = make_map_2d(&tm_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes * raw_act / kStageKBytes, a.m,
+                     a.k_bytes * raw_act / kStageKBytes, raw_act, box_act, CU_TENSOR_MAP_SWIZZLE_NONE);
+  else
+    rc = make_map_2d(&tm_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, box_act,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
-  rc = make_map_2d(&tm_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.n, a.k_bytes, kStageKBytes, box_wgt,
-                   CU_TENSOR_MAP_SWIZZLE_128B);
+  if (raw_wgt)
+    rc = make_map_2d(&tm_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes * raw_wgt / kStageKBytes, a.n,
+                     a.k_bytes * raw_wgt / kStageKBytes, raw_wgt, box_wgt, CU_TENSOR_MAP_SWIZZLE_NONE);
+  else
+    rc = make_map_2d(&tm_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.n, a.k_bytes, kStageKBytes, box_wgt,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
-  if (a.out != nullptr && a.acc_out == nullptr) {
+  if (a.out != nullptr && a.acc_out == nullptr && a.peer == nullptr) {
     // output tiles leave through TMA: 32 rows x 128 channels (swap) or 128 rows x 64 channels
     if (pl.swap)
       rc = make_map_2d(&tm_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 128, 32,
@@ -537,6 +580,19 @@ int run_tc(const TcArgs& a) {
   p.sf_rows_b = static_cast<int>(pl.swap ? a.m : a.n);
   p.wait_limit = g_debug_wait_limit > 0 ? g_debug_wait_limit : static_cast<int>(kWaitSpinMax);
   p.debug_stall = g_debug_stall;
+  p.issue_block = (issue_block_mode() && pl.sfb_blocks <= 2) ? 1 : 0;
+  if (a.peer != nullptr) {
+    for (int g = 0; g < a.peer->count; ++g) {
+      p.peer_out[g] = static_cast<__nv_bfloat16*>(a.peer->out[g]);
+      p.peer_flags[g] = a.peer->flags[g];
+    }
+    p.peer_ld = a.peer->ld;
+    p.peer_col0 = a.peer->col0;
+    p.peer_count = a.peer->count;
+    p.peer_rank = a.peer->rank;
+    p.peer_epoch = a.peer->epoch;
+    p.peer_counter = reinterpret_cast<unsigned*>(ws.status) + 32;  // a word of the workspace header, zero between launches
+  }
   p.status = ws.status;
   const CUtensorMap& tm_a = pl.swap ? tm_wgt : tm_act;
   const CUtensorMap& tm_b = pl.swap ? tm_act : tm_wgt;
@@ -544,7 +600,10 @@ int run_tc(const TcArgs& a) {
     case KIND_I8: return launch_tc<KIND_I8>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_F8: return launch_tc<KIND_F8>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_MXF8: return launch_tc<KIND_MXF8>(tm_a, tm_b, tm_out, p, pl, a.stream);
-    default: return launch_tc<KIND_NVF4>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_NVF4: return launch_tc<KIND_NVF4>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_I4: return launch_tc<KIND_I4>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_F8P: return launch_tc<KIND_F8P>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    default: return launch_tc<KIND_MX48>(tm_a, tm_b, tm_out, p, pl, a.stream);
   }
 }
 
@@ -652,7 +711,7 @@ extern "C" int rk_debug_wait_expiry(int on, int spin_limit) {
 
 static int gemm_int_common(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
                            int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits, int tactic, void* workspace,
-                           size_t workspace_bytes, void* stream, const char* who) {
+                           size_t workspace_bytes, void* stream, const char* who, bool widen_in_scratch = false) {
   if (bits != 8 && bits != 4) return fail(RK_EINVAL, "%s: bits must be 4 or 8", who);
   if (kpad < 128 || kpad % 128 != 0) return fail(RK_EINVAL, "%s: kpad must be a positive multiple of 128", who);
   if (tactic < 0 || tactic > 7) return fail(RK_EINVAL, "%s: tactic must be 0..7", who);
@@ -661,9 +720,33 @@ static int gemm_int_common(const void* a, const float* sa, const void* b, const 
   if (m < 1 || n < 1 || m > (1 << 24) || n > (1 << 24) || kpad > (1 << 24)) return fail(RK_EINVAL, "%s: bad dimensions", who);
   uint8_t* copies = nullptr;
   size_t copies_bytes = 0;
+  if (bits == 4 && !widen_in_scratch) {
+    // tcgen05 has no 4-bit integer kind: the kernel fetches the packed nibbles and widens both
+    // operands to int8 in shared memory (the products and the int32 sums are identical)
+    if (!aligned16(a) || !aligned16(b)) return fail(RK_EINVAL, "%s: operands must be 16-byte aligned", who);
+    TcArgs t{};
+    t.kind = KIND_I4;
+    t.act = a;
+    t.wgt = b;
+    t.m = m;
+    t.n = n;
+    t.k_bytes = kpad;
+    t.mma_bytes_last = 128;
+    t.scale_act = sa;
+    t.scale_wgt = sb;
+    t.bias = bias;
+    t.out = out;
+    t.acc_out = acc;
+    t.tactic = tactic;
+    t.workspace = workspace;
+    t.workspace_bytes = workspace_bytes;
+    t.stream = as_stream(stream);
+    t.who = who;
+    return run_tc(t);
+  }
   if (bits == 4) {
-    // tcgen05 has no 4-bit integer kind: widen both operands to int8 in the scratch buffer (the
-    // products and the int32 sums are identical), then run the int8 kernel on the copies.
+    // the variant that widens both operands to int8 in a scratch buffer first and then runs the int8
+    // kernel on the copies (kept for rk_gemm_int4_noalloc, whose scratch is built into the library)
     if (!aligned16(a) || !aligned16(b)) return fail(RK_EINVAL, "%s: operands must be 16-byte aligned", who);
     const size_t need = rk_workspace_bytes(RK_OP_W4A4, m, n, kpad);
     if (!workspace || workspace_bytes < need) return fail(RK_EWORKSPACE, "%s: workspace too small for the int8 copies", who);
@@ -742,6 +825,59 @@ extern "C" int rk_gemm_fp8(const void* a, const float* scale_a, const void* b, c
   t.workspace_bytes = workspace_bytes;
   t.stream = as_stream(stream);
   t.who = "rk_gemm_fp8";
+  return run_tc(t);
+}
+
+extern "C" int rk_gemm_fp8_producer(const void* x, const void* b, const float* scale_b, const void* bias, void* out,
+                                    int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  if (k < 16 || k % 16 != 0) return fail(RK_EINVAL, "rk_gemm_fp8_producer: k must be a positive multiple of 16");
+  if (!scale_b) return fail(RK_EINVAL, "rk_gemm_fp8_producer: null scale pointer");
+  TcArgs t{};
+  t.kind = KIND_F8P;
+  t.act = x;
+  t.wgt = b;
+  t.m = m;
+  t.n = n;
+  t.k_bytes = k;  // in MMA bytes (e4m3); the bf16 rows are twice as long
+  t.mma_bytes_last = static_cast<int>(k % 128 == 0 ? 128 : k % 128);
+  t.scale_act = nullptr;  // unit activation scale
+  t.scale_wgt = scale_b;
+  t.bias = bias;
+  t.out = out;
+  t.tactic = tactic & 7;
+  t.workspace = workspace;
+  t.workspace_bytes = workspace_bytes;
+  t.stream = as_stream(stream);
+  t.who = "rk_gemm_fp8_producer";
+  return run_tc(t);
+}
+
+extern "C" int rk_gemm_w4a8_mx(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias, void* out,
+                               int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  const char* who = "rk_gemm_w4a8_mx";
+  if (k < 32 || k % 32 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 32", who);
+  if (!sfa || !sfb) return fail(RK_EINVAL, "%s: null scale-factor pointer", who);
+  if (!aligned16(sfa) || !aligned16(sfb)) return fail(RK_EINVAL, "%s: scale-factor buffers must be 16-byte aligned", who);
+  TcArgs t{};
+  t.kind = KIND_MX48;
+  t.act = a;
+  t.wgt = b;
+  t.m = m;
+  t.n = n;
+  t.k_bytes = k;  // in MMA bytes (e4m3 after the weights are expanded); packed weight rows are k / 2
+  t.mma_bytes_last = static_cast<int>(k % 128 == 0 ? 128 : k % 128);
+  t.sf_act = static_cast<const uint8_t*>(sfa);
+  t.sf_wgt = static_cast<const uint8_t*>(sfb);
+  t.sf_kt = static_cast<int>((k + 127) / 128);
+  t.bias = bias;
+  t.out = out;
+  t.tactic = (tactic & 7) | 2;
+  t.workspace = workspace;
+  t.workspace_bytes = workspace_bytes;
+  t.stream = as_stream(stream);
+  t.who = who;
   return run_tc(t);
 }
 
@@ -1078,7 +1214,7 @@ extern "C" int rk_gemm_int4_noalloc(const void* a, const float* sa, const void* 
   // the status word at the head of the scratch must start at zero; the copies are overwritten anyway
   if (cudaMemsetAsync(scratch, 0, RK_WORKSPACE_HEADER, rk::as_stream(stream)) != cudaSuccess)
     return rk::fail(RK_ECUDA, "%s: cudaMemsetAsync failed", who);
-  return gemm_int_common(a, sa, b, sb, bias, out, nullptr, m, n, kpad, 4, tactic, scratch, need, stream, who);
+  return gemm_int_common(a, sa, b, sb, bias, out, nullptr, m, n, kpad, 4, tactic, scratch, need, stream, who, true);
 }
 
 // ------------------------------------------------------------------ attention over a cached prefix
@@ -1166,4 +1302,75 @@ extern "C" int rk_attention_prefix(const void* q, const void* k_cache, const voi
     return fail(RK_ECUDA, "rk_attn_prefix_kernel launch: %s", cudaGetErrorString(e));
   }
   return RK_OK;
+}
+
+// ------------------------------------------------------------------ column-parallel FP8 GEMM with a fused exchange
+namespace rk {
+__global__ void wait_peer_flags_kernel(const int* flags, int ranks, int self, int epoch, int spin_max, int* status) {
+  const int g = threadIdx.x;
+  if (g >= ranks || g == self) return;
+  const int* flag = flags + g;
+  for (int it = 0; it < spin_max; ++it) {
+    int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v - epoch >= 0) return;  // epochs only grow (wrap-around safe comparison)
+    __nanosleep(it < 64 ? 40 : 400);
+  }
+  atomicCAS(status, 0, 107);  // a peer's slab did not arrive in time
+}
+}  // namespace rk
+
+extern "C" int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, const void* b, const float* scale_b,
+                                           const void* bias, int64_t m, int64_t n_local, int64_t k,
+                                           void* const* out_ptrs, int64_t ld_total, int64_t col0, void* const* flag_ptrs,
+                                           int rank, int ranks, int epoch, void* workspace, size_t workspace_bytes,
+                                           void* stream) {
+  const char* who = "rk_gemm_fp8_column_parallel";
+  if (!out_ptrs || !flag_ptrs || !scale_a || !scale_b) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
+  if (k < 16 || k % 16 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 16", who);
+  if (col0 < 0 || col0 % 8 != 0 || ld_total % 8 != 0 || col0 + n_local > ld_total)
+    return fail(RK_EINVAL, "%s: the slab must lie inside the output and start on a multiple of 8 columns", who);
+  PeerArgs peer{};
+  for (int g = 0; g < ranks; ++g) {
+    if (!out_ptrs[g] || !flag_ptrs[g] || !aligned16(out_ptrs[g])) return fail(RK_EINVAL, "%s: bad pointer for rank %d", who, g);
+    peer.out[g] = out_ptrs[g];
+    peer.flags[g] = static_cast<int*>(flag_ptrs[g]);
+  }
+  peer.ld = ld_total;
+  peer.col0 = col0;
+  peer.count = ranks;
+  peer.rank = rank;
+  peer.epoch = epoch;
+  TcArgs t{};
+  t.peer = &peer;
+  t.kind = KIND_F8;
+  t.act = a;
+  t.wgt = b;
+  t.m = m;
+  t.n = n_local;
+  t.k_bytes = k;
+  t.mma_bytes_last = static_cast<int>(k % 128 == 0 ? 128 : k % 128);
+  t.scale_act = scale_a;
+  t.scale_wgt = scale_b;
+  t.bias = bias;
+  t.tactic = 1 | 2;  // activations on the 128-lane axis (16-byte row-wise stores), no split-K
+  t.workspace = workspace;
+  t.workspace_bytes = workspace_bytes;
+  t.stream = as_stream(stream);
+  t.who = who;
+  return run_tc(t);
+}
+
+extern "C" int rk_wait_peers(const void* flags, int rank, int ranks, int epoch, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  const char* who = "rk_wait_peers";
+  if (!flags) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
+  Workspace ws;
+  int rc = carve_workspace(workspace, workspace_bytes, &ws, who);
+  if (rc != RK_OK) return rc;
+  const int limit = g_debug_wait_limit > 0 ? g_debug_wait_limit : (1 << 21);  // with 400 ns sleeps: roughly a second
+  wait_peer_flags_kernel<<<1, 32, 0, as_stream(stream)>>>(static_cast<const int*>(flags), ranks, rank, epoch, limit, ws.status);
+  return check_launch(who);
 }

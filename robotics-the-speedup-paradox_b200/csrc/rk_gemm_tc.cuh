@@ -20,17 +20,35 @@
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4) .. +31).
+//
+// Three further kinds feed an operand that is NOT stored in the MMA's type: W4A4 (both operands
+// packed int4, widened to int8: tcgen05 has no 4-bit integer kind), the FP8 "producer" GEMM (bf16
+// activations converted to e4m3 with unit scale) and W4A8-MX (MXFP4 weights expanded to e4m3, which
+// represents every e2m1 value exactly, against MXFP8 activations).  For these, TMA lands the raw
+// bytes in a staging part of the pipeline stage and four more warps (6..9, 320 threads in all)
+// rewrite them in shared memory into the 128-byte-swizzled K-major tile the MMA reads; the
+// converted operand never exists in global memory.  These kinds run the persistent, non-swapped
+// schedule with 128-row weight tiles.
 #pragma once
 
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include "rk_common.cuh"
 
 namespace rk {
 
-enum GemmKind : int { KIND_I8 = 0, KIND_F8 = 1, KIND_MXF8 = 2, KIND_NVF4 = 3 };
+enum GemmKind : int {
+  KIND_I8 = 0, KIND_F8 = 1, KIND_MXF8 = 2, KIND_NVF4 = 3,
+  KIND_I4 = 4,    // int4 x int4, both widened to int8 in shared memory, then as KIND_I8
+  KIND_F8P = 5,   // bf16 activations converted to e4m3 in shared memory, e4m3 weights, then as KIND_F8
+  KIND_MX48 = 6,  // MXFP8 activations x MXFP4 weights (expanded to e4m3 in shared memory), then as KIND_MXF8
+};
+// how a raw operand tile is rewritten into the MMA's type
+enum XformOp : int { XF_NONE = 0, XF_INT4_TO_INT8 = 1, XF_BF16_TO_E4M3 = 2, XF_E2M1_TO_E4M3 = 3 };
 
 constexpr int kGemmThreads = 192;
+constexpr int kGemmThreadsXform = 320;  // + four operand-rewriting warps
 constexpr int kTileA = 128;        // rows of the A-role tile (MMA M)
 constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage (one 128-byte swizzle atom)
 constexpr int kMaxStages = 8;
@@ -64,37 +82,189 @@ struct GemmParams {
   int sf_rows_b;              // rows of the B-role operand (its scale buffer holds ceil(rows / 128) blocks)
   int wait_limit;             // spin limit of every bounded wait (kWaitSpinMax unless a test shortens it)
   int debug_stall;            // test aid: the producer announces bytes that never arrive (first stage)
+  int issue_block;            // issue a stage's tensor-core instructions as one straight-line block
+  // Column-parallel mode (peer_count > 0): this GPU computes columns [peer_col0, peer_col0 + n) of a
+  // wider output that every GPU of the group holds in full.  The epilogue stores its values into
+  // all of those buffers with ordinary stores through peer mappings (no TMA to or from a peer) and
+  // the last CTA to finish raises this rank's entry in every rank's flag array.
+  __nv_bfloat16* peer_out[8];  // [m, peer_ld] output of every rank, this rank's own included
+  int* peer_flags[8];          // every rank's flag array [ranks]
+  long long peer_ld;           // row stride of those outputs (elements)
+  long long peer_col0;         // first column of this rank's slab
+  int peer_count, peer_rank, peer_epoch;
+  unsigned* peer_counter;      // device word counting the CTAs of this launch that have finished
   int* status;                // device status word
 };
 
 template <int KIND>
 struct KindTraits;
+struct NoXform {
+  static constexpr int kXformA = XF_NONE, kXformB = XF_NONE;  // activations / weights (these kinds never swap)
+  static constexpr int kRawA = 0, kRawB = 0;                  // raw bytes per row and pipeline stage
+  static constexpr int kThreads = kGemmThreads;
+};
 template <>
-struct KindTraits<KIND_I8> {
+struct KindTraits<KIND_I8> : NoXform {
+  static constexpr int kBase = KIND_I8;
   static constexpr bool kBlockScaled = false;
   static constexpr int kSfChunksPerStage = 0;
 };
 template <>
-struct KindTraits<KIND_F8> {
+struct KindTraits<KIND_F8> : NoXform {
+  static constexpr int kBase = KIND_F8;
   static constexpr bool kBlockScaled = false;
   static constexpr int kSfChunksPerStage = 0;
 };
 template <>
-struct KindTraits<KIND_MXF8> {
+struct KindTraits<KIND_MXF8> : NoXform {
+  static constexpr int kBase = KIND_MXF8;
   static constexpr bool kBlockScaled = true;
   static constexpr int kSfChunksPerStage = 1;  // 128 elements of K = 4 scale factors per row = one 512 B chunk
 };
 template <>
-struct KindTraits<KIND_NVF4> {
+struct KindTraits<KIND_NVF4> : NoXform {
+  static constexpr int kBase = KIND_NVF4;
   static constexpr bool kBlockScaled = true;
   static constexpr int kSfChunksPerStage = 4;  // 256 elements of K = 16 scale factors per row
 };
+template <>
+struct KindTraits<KIND_I4> {
+  static constexpr int kBase = KIND_I8;
+  static constexpr bool kBlockScaled = false;
+  static constexpr int kSfChunksPerStage = 0;
+  static constexpr int kXformA = XF_INT4_TO_INT8, kXformB = XF_INT4_TO_INT8;
+  static constexpr int kRawA = 64, kRawB = 64;
+  static constexpr int kThreads = kGemmThreadsXform;
+};
+template <>
+struct KindTraits<KIND_F8P> {
+  static constexpr int kBase = KIND_F8;
+  static constexpr bool kBlockScaled = false;
+  static constexpr int kSfChunksPerStage = 0;
+  static constexpr int kXformA = XF_BF16_TO_E4M3, kXformB = XF_NONE;
+  static constexpr int kRawA = 256, kRawB = 0;
+  static constexpr int kThreads = kGemmThreadsXform;
+};
+template <>
+struct KindTraits<KIND_MX48> {
+  static constexpr int kBase = KIND_MXF8;
+  static constexpr bool kBlockScaled = true;
+  static constexpr int kSfChunksPerStage = 1;
+  static constexpr int kXformA = XF_NONE, kXformB = XF_E2M1_TO_E4M3;
+  static constexpr int kRawA = 0, kRawB = 64;
+  static constexpr int kThreads = kGemmThreadsXform;
+};
 
+__host__ __device__ inline int gemm_raw_bytes_a(int kind) { return kind == KIND_I4 ? 64 : (kind == KIND_F8P ? 256 : 0); }
+__host__ __device__ inline int gemm_raw_bytes_b(int kind) { return (kind == KIND_I4 || kind == KIND_MX48) ? 64 : 0; }
+
+// One pipeline stage: [A-role tile][B-role tile][scale chunks][raw A rows][raw B rows]
+__host__ __device__ inline int gemm_stage_sf_bytes(int kind, int sfb_blocks) {
+  int chunks = (kind == KIND_MXF8 || kind == KIND_MX48) ? 1 : (kind == KIND_NVF4 ? 4 : 0);
+  return chunks * 512 * (1 + sfb_blocks);
+}
 __host__ __device__ inline int gemm_stage_bytes(int kind, int bn, int sfb_blocks) {
   int data = kTileA * kStageKBytes + bn * kStageKBytes;
-  int chunks = kind == KIND_MXF8 ? 1 : (kind == KIND_NVF4 ? 4 : 0);
-  int sf = chunks * 512 * (1 + sfb_blocks);
-  return (data + sf + 1023) / 1024 * 1024;
+  int raw = kTileA * gemm_raw_bytes_a(kind) + bn * gemm_raw_bytes_b(kind);
+  return (data + gemm_stage_sf_bytes(kind, sfb_blocks) + raw + 1023) / 1024 * 1024;
+}
+
+// ---- rewriting a raw operand tile into the MMA's type (warps 6..9, 128 threads) -----------------
+// Destination: `rows` x 128 bytes, K-major, 128-byte swizzle (16-byte chunk c of row r at
+// r * 128 + ((c ^ (r & 7)) << 4)), exactly what a SWIZZLE_128B TMA box would have written.
+__device__ __forceinline__ uint32_t swz128(int row, int chunk) {
+  return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+// two's-complement nibbles (low nibble = even k) -> int8, eight per 32-bit word
+__device__ __forceinline__ void widen_int4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t even = __vsub4((w & 0x0F0F0F0Fu) ^ 0x08080808u, 0x08080808u);
+  const uint32_t odd = __vsub4(((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u, 0x08080808u);
+  lo = __byte_perm(even, odd, 0x5140);  // k0 k1 k2 k3
+  hi = __byte_perm(even, odd, 0x7362);  // k4 k5 k6 k7
+}
+// e2m1 codes (low nibble = even k) -> the e4m3 bytes of the same values: 0, .5, 1, 1.5, 2, 3, 4, 6
+__device__ __forceinline__ uint32_t e2m1x4_to_e4m3(uint32_t h) {  // four nibbles in the low 16 bits
+  // two byte permutes: the magnitude bits of every nibble select from the table of the eight e4m3
+  // magnitudes, the sign bit selects 0x00 or 0x80
+  const uint32_t mag = __byte_perm(0x3C383000u, 0x4C484440u, h & 0x7777u);
+  const uint32_t sign = __byte_perm(0x00008000u, 0u, (h >> 3) & 0x1111u);
+  return mag | sign;
+}
+// ROWS is a compile-time row count (a multiple of 32): the loops unroll completely, all shared-memory
+// loads of a thread are issued first and the conversions of different chunks interleave.  The four
+// rewriting warps are one warp per scheduler, so their stream is latency bound unless it carries
+// this much instruction-level parallelism.
+template <int OP, int ROWS>
+__device__ __forceinline__ void xform_tile(const uint8_t* raw, uint8_t* dst, int t) {
+  if constexpr (OP == XF_INT4_TO_INT8 || OP == XF_E2M1_TO_E4M3) {
+    // raw row = 64 bytes; a thread takes 16 raw bytes (32 codes) = two destination chunks
+    constexpr int kIter = ROWS * 4 / 128;
+    uint4 v[kIter];
+#pragma unroll
+    for (int it = 0; it < kIter; ++it) {
+      const int i = it * 128 + t;
+      v[it] = *reinterpret_cast<const uint4*>(raw + (i >> 2) * 64 + (i & 3) * 16);
+    }
+#pragma unroll
+    for (int it = 0; it < kIter; ++it) {
+      const int i = it * 128 + t;
+      const int r = i >> 2, c = i & 3;
+      const uint32_t w[4] = {v[it].x, v[it].y, v[it].z, v[it].w};
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if constexpr (OP == XF_INT4_TO_INT8) {
+          widen_int4(w[j], o[2 * j], o[2 * j + 1]);
+        } else {
+          o[2 * j] = e2m1x4_to_e4m3(w[j] & 0xFFFFu);
+          o[2 * j + 1] = e2m1x4_to_e4m3(w[j] >> 16);
+        }
+      }
+      *reinterpret_cast<uint4*>(dst + swz128(r, 2 * c)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(dst + swz128(r, 2 * c + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  } else if constexpr (OP == XF_BF16_TO_E4M3) {
+    // raw row = 256 bytes (128 bf16); a thread takes 32 raw bytes (16 values) = one destination chunk
+    constexpr int kIter = ROWS * 8 / 128;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {  // two batches of kIter / 2 chunks keep the register count moderate
+      uint4 a[kIter / 2], b[kIter / 2];
+#pragma unroll
+      for (int it = 0; it < kIter / 2; ++it) {
+        const int i = (half * (kIter / 2) + it) * 128 + t;
+        a[it] = *reinterpret_cast<const uint4*>(raw + (i >> 3) * 256 + (i & 7) * 32);
+        b[it] = *reinterpret_cast<const uint4*>(raw + (i >> 3) * 256 + (i & 7) * 32 + 16);
+      }
+#pragma unroll
+      for (int it = 0; it < kIter / 2; ++it) {
+        const int i = (half * (kIter / 2) + it) * 128 + t;
+        const int r = i >> 3, c = i & 7;
+        const uint32_t w[8] = {a[it].x, a[it].y, a[it].z, a[it].w, b[it].x, b[it].y, b[it].z, b[it].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t packed = 0;
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const uint32_t pair = w[2 * j + e];
+            // e4m3 of the value clamped to +-448 (unit scale), the arithmetic of the per-tensor quantizer
+            const float lo = fminf(448.0f, fmaxf(-448.0f, __uint_as_float(pair << 16)));
+            const float hi = fminf(448.0f, fmaxf(-448.0f, __uint_as_float(pair & 0xFFFF0000u)));
+            const uint32_t c2 = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+            packed |= c2 << (16 * e);
+          }
+          o[j] = packed;
+        }
+        *reinterpret_cast<uint4*>(dst + swz128(r, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+// B-role tiles of the rewriting kinds are 128 rows, or 64 for a narrow weight matrix
+template <int OP>
+__device__ __forceinline__ void xform_tile_b(const uint8_t* raw, uint8_t* dst, int rows, int t) {
+  if (rows == 128) xform_tile<OP, 128>(raw, dst, t);
+  else xform_tile<OP, 64>(raw, dst, t);
 }
 
 // The final value written for output element (m, n) from its 32-bit accumulator.
@@ -133,13 +303,17 @@ __device__ __forceinline__ uint32_t dsmem_ld_u32(uint32_t local_addr, uint32_t r
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(KindTraits<KIND>::kThreads, 1)
 rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
   using T = KindTraits<KIND>;
+  constexpr int BK = T::kBase;  // the MMA kind and epilogue this kind runs on
+  constexpr bool kXform = T::kXformA != XF_NONE || T::kXformB != XF_NONE;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_raw_full[kMaxStages];   // raw operand bytes have landed (rewriting kinds)
+  __shared__ __align__(8) uint64_t bar_raw_empty[kMaxStages];  // the rewriting warps have read them
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -153,6 +327,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int stage_bytes = gemm_stage_bytes(KIND, p.bn, p.sfb_blocks);
   const int rb_b = p.sfb_blocks;  // 128-row scale blocks fetched per B tile
   const uint32_t spin_max = static_cast<uint32_t>(p.wait_limit);
+  // offsets inside a stage: [A-role tile][B-role tile][scale chunks][raw A rows][raw B rows]
+  const uint32_t raw_a_off = (kTileA + p.bn) * kStageKBytes + gemm_stage_sf_bytes(KIND, p.sfb_blocks);
+  const uint32_t raw_b_off = raw_a_off + kTileA * T::kRawA;
   // shared memory map: [pipeline stages][output staging, 1 or 2 x 16 KB][B-role scale + bias vectors]
   const uint32_t out_stage_off = p.stages * stage_bytes;
   const uint32_t vec_off = out_stage_off + p.out_bufs * kOutBufBytes;
@@ -182,8 +359,10 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_full[s]), kXform ? 5 : 1);  // the producer's announcement (+ the four rewriting warps)
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_raw_full[s]), 1);
+      mbar_init(smem_u32(&bar_raw_empty[s]), 4);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
@@ -234,12 +413,29 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         for (int i = 0; i < nkb; ++i) {
           const int s = ring.stage;
           const uint32_t ph = ring.phase;
-          if (!ready && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY, spin_max)) {
-            alive = false;
-            break;
+          if constexpr (kXform) {
+            // raw rows may be refilled as soon as the rewriting warps have read them, long before the
+            // MMAs of the stage's previous use complete; only an operand that TMA writes straight into
+            // the MMA's tile has to wait for those
+            if (!mbar_wait_bounded(smem_u32(&bar_raw_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY, spin_max)) {
+              alive = false;
+              break;
+            }
+            if constexpr (T::kXformA == XF_NONE || T::kXformB == XF_NONE || T::kBlockScaled) {
+              if (!mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY, spin_max)) {
+                alive = false;
+                break;
+              }
+            }
+            ring.advance(p.stages);
+          } else {
+            if (!ready && !mbar_wait_bounded(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY, spin_max)) {
+              alive = false;
+              break;
+            }
+            ring.advance(p.stages);
+            ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           }
-          ring.advance(p.stages);
-          ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t sa = smem_base + s * stage_bytes;
           const uint32_t sb = sa + kTileA * kStageKBytes;
@@ -254,9 +450,26 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tx += cs * 512 * (1 + nb);
           }
           if (p.debug_stall && i == 0 && tile == tile_first) tx += 16;  // test aid: this phase never completes
-          mbar_arrive_expect_tx(full, tx, on);
-          tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a, on);
-          tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b, on);
+          if constexpr (!kXform) {
+            mbar_arrive_expect_tx(full, tx, on);
+            tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a, on);
+            tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b, on);
+          } else {
+            // operands stored in the MMA's type go straight to their tile; the others land as raw rows
+            // (unswizzled boxes of kRaw bytes per row) for the rewriting warps
+            const uint32_t raw_full = smem_u32(&bar_raw_full[s]);
+            uint32_t tx_direct = tx - tx_data, tx_raw = 0;
+            if constexpr (T::kXformA == XF_NONE) tx_direct += kTileA * kStageKBytes;
+            else tx_raw += kTileA * T::kRawA;
+            if constexpr (T::kXformB == XF_NONE) tx_direct += p.bn * kStageKBytes;
+            else tx_raw += p.bn * T::kRawB;
+            mbar_arrive_expect_tx(full, tx_direct, on);
+            mbar_arrive_expect_tx(raw_full, tx_raw, on);
+            if constexpr (T::kXformA == XF_NONE) tma_load_2d_hint(sa, &tm_a, kb * kStageKBytes, row_a0, full, pol_a, on);
+            else tma_load_2d_hint(sa + raw_a_off, &tm_a, kb * T::kRawA, row_a0, raw_full, pol_a, on);
+            if constexpr (T::kXformB == XF_NONE) tma_load_2d_hint(sb, &tm_b, kb * kStageKBytes, row_b0, full, pol_b, on);
+            else tma_load_2d_hint(sa + raw_b_off, &tm_b, kb * T::kRawB, row_b0, raw_full, pol_b, on);
+          }
           if constexpr (T::kBlockScaled) {
             // Scale factors: contiguous 512-byte chunks in the 128-row swizzled global layout.
             const uint32_t ssf = sb + p.bn * kStageKBytes;
@@ -289,9 +502,9 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t ready = 0;  // answer of the early probe of the next stage's "full" barrier
       // instruction descriptor(s) and the descriptor of stage 0 are loop invariants
       uint32_t idesc = 0;
-      if constexpr (KIND == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn);
-      else if constexpr (KIND == KIND_F8) idesc = umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn);
-      else if constexpr (KIND == KIND_MXF8) idesc = umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, 0, 0);
+      if constexpr (BK == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn);
+      else if constexpr (BK == KIND_F8) idesc = umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn);
+      else if constexpr (BK == KIND_MXF8) idesc = umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, 0, 0);
       else idesc = umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 128, p.bn, 0, 0, 0);
       const uint64_t adesc0 = umma_desc_k128(smem_base);
       const uint64_t bdesc0 = umma_desc_k128(smem_base + kTileA * kStageKBytes);
@@ -321,6 +534,49 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
           const int nmma = (kb_begin + i == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
+          if constexpr (T::kBlockScaled && !kXform) {
+            // Whole K blocks of the block-scaled kinds: up to 17 tensor-core instructions per stage (scale
+            // copies, MMAs, the commit).  The issuing thread's cost per instruction is what paces these
+            // kinds, so the elected lane runs them as one straight-line block without per-instruction
+            // predicates and with descriptors that differ from a per-stage base by constants (NVFP4
+            // 816 x 16384 x 2048: 34.1 -> 25.9 us).  For the kinds without scale copies (five
+            // instructions per stage) the same block measured slower than the predicated form below.
+            if (p.issue_block && nmma == 4 && (kb_begin + i + 1) * T::kSfChunksPerStage <= p.sf_kt) {
+              if (on) {
+                constexpr int c = T::kSfChunksPerStage;
+                const uint64_t sfdesc0 = umma_desc_noswizzle(sb + p.bn * kStageKBytes, 16, 128);
+                const uint32_t accumulate0 = i > 0 ? 1u : 0u;
+                if (rb_b == 1) {
+#pragma unroll
+                  for (int j = 0; j < c; ++j) {
+                    tmem_cp_32x128b_warpx4_np(tmem_sfa + j * 4, sfdesc0 + static_cast<uint64_t>(j * 32));
+                    tmem_cp_32x128b_warpx4_np(tmem_sfb + j * 4, sfdesc0 + static_cast<uint64_t>((c + j) * 32));
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < c; ++j) {
+                    tmem_cp_32x128b_warpx4_np(tmem_sfa + j * 4, sfdesc0 + static_cast<uint64_t>(j * 32));
+                    tmem_cp_32x128b_warpx4_np(tmem_sfb + j * 8, sfdesc0 + static_cast<uint64_t>((c + j) * 32));
+                    tmem_cp_32x128b_warpx4_np(tmem_sfb + j * 8 + 4, sfdesc0 + static_cast<uint64_t>((2 * c + j) * 32));
+                  }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint32_t accumulate = k > 0 ? 1u : accumulate0;
+                  if constexpr (BK == KIND_MXF8)
+                    mma_mxf8_np(d_tmem, adesc + k * 2, bdesc + k * 2,
+                                idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29), tmem_sfa,
+                                tmem_sfb + sfb_col0, accumulate);
+                  else
+                    mma_nvf4_np(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, tmem_sfa + k * 4,
+                                tmem_sfb + k * rb_b * 4 + sfb_col0, accumulate);
+                }
+                tc_commit_np(smem_u32(&bar_empty[s]));
+              }
+              __syncwarp();
+              continue;
+            }
+          }
           if constexpr (T::kBlockScaled) {
             const uint32_t ssf = sb + p.bn * kStageKBytes;
             const int c = T::kSfChunksPerStage;
@@ -340,11 +596,11 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               // 32 bytes of K per MMA: advance the descriptor start address by 32 >> 4.
               const uint64_t ad = adesc + static_cast<uint64_t>(k * 2);
               const uint64_t bd = bdesc + static_cast<uint64_t>(k * 2);
-              if constexpr (KIND == KIND_I8) {
+              if constexpr (BK == KIND_I8) {
                 mma_i8(d_tmem, ad, bd, idesc, accumulate, on);
-              } else if constexpr (KIND == KIND_F8) {
+              } else if constexpr (BK == KIND_F8) {
                 mma_f8f6f4(d_tmem, ad, bd, idesc, accumulate, on);
-              } else if constexpr (KIND == KIND_MXF8) {
+              } else if constexpr (BK == KIND_MXF8) {
                 // four MMAs share one set of scale columns; byte k of each 32-bit column is theirs
                 // (scale-factor ids: bits [4,6) for B, [29,31) for A)
                 mma_mxf8(d_tmem, ad, bd, idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29),
@@ -359,6 +615,36 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (alive) tc_commit(smem_u32(&bar_acc_full[ab]), on);  // accumulator complete
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ operand rewriting (warps 6..9, rewriting kinds only)
+    if constexpr (kXform) {
+      const int t = threadIdx.x - 192;  // 0..127
+      Ring ring{0, 0};
+      bool alive = true;
+      for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
+        for (int i = 0; i < nkb; ++i) {
+          const int s = ring.stage;
+          // the raw bytes are here, and the MMAs of the stage's previous use have read the tiles that
+          // are about to be overwritten
+          if (!mbar_poll_warp(smem_u32(&bar_raw_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW) ||
+              !mbar_poll_warp(smem_u32(&bar_empty[s]), ring.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
+            alive = false;
+            break;
+          }
+          ring.advance(p.stages);
+          uint8_t* const stage = smem_gen + s * stage_bytes;
+          if constexpr (T::kXformA != XF_NONE) xform_tile<T::kXformA, kTileA>(stage + raw_a_off, stage, t);
+          if constexpr (T::kXformB != XF_NONE)
+            xform_tile_b<T::kXformB>(stage + raw_b_off, stage + kTileA * kStageKBytes, p.bn, t);
+          fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&bar_full[s]));       // first: a refill announcement must not overtake this arrival
+            mbar_arrive(smem_u32(&bar_raw_empty[s]));
+          }
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;
@@ -369,7 +655,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     float* const vec_scale = reinterpret_cast<float*>(smem_gen + vec_off);  // [256] B-role scales
     float* const vec_bias = vec_scale + 256;                                // [256] B-role bias (non-swap)
     float s_act_scalar = 1.0f, s_wgt_scalar = 1.0f;
-    if constexpr (KIND != KIND_I8) {
+    if constexpr (BK != KIND_I8) {
       if (p.scale_act) s_act_scalar = *p.scale_act;
       if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
     }
@@ -386,7 +672,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       // per-thread constants of the A-role row, and the B-role vectors of this tile into shared memory
       float row_scale = 1.0f, row_bias = 0.0f;
       if (p.acc_out == nullptr) {
-        if constexpr (KIND == KIND_I8) {
+        if constexpr (BK == KIND_I8) {
           if (ra_ok) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
         }
         if (p.swap && has_bias && ra_ok) row_bias = __bfloat162float(p.bias[ra]);
@@ -395,7 +681,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const int rb = row_b0 + j;
           float sv = 1.0f, bv = 0.0f;
           if (rb < lim_b) {
-            if constexpr (KIND == KIND_I8) sv = p.swap ? p.scale_act[rb] : p.scale_wgt[rb];
+            if constexpr (BK == KIND_I8) sv = p.swap ? p.scale_act[rb] : p.scale_wgt[rb];
             if (!p.swap && has_bias) bv = __bfloat162float(p.bias[rb]);
           }
           vec_scale[j] = sv;
@@ -474,7 +760,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           // the per-column scales are read into registers BEFORE the first store: a shared-memory load
           // placed between the stores would have to wait for each of them (the two may alias)
           float sv0[16], sv1[16];
-          if constexpr (KIND == KIND_I8) {
+          if constexpr (BK == KIND_I8) {
             const float4* const vs4 = reinterpret_cast<const float4*>(vec_scale + c0);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -487,12 +773,12 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           float v0[16], v1[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            if constexpr (KIND == KIND_I8) {
-              v0[j] = finish_value<KIND>(r0[j], sv0[j], row_scale, has_bias, row_bias);
-              v1[j] = finish_value<KIND>(r1[j], sv1[j], row_scale, has_bias, row_bias);
+            if constexpr (BK == KIND_I8) {
+              v0[j] = finish_value<BK>(r0[j], sv0[j], row_scale, has_bias, row_bias);
+              v1[j] = finish_value<BK>(r1[j], sv1[j], row_scale, has_bias, row_bias);
             } else {
-              v0[j] = finish_value<KIND>(r0[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
-              v1[j] = finish_value<KIND>(r1[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
+              v0[j] = finish_value<BK>(r0[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
+              v1[j] = finish_value<BK>(r1[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
             }
           }
 #pragma unroll
@@ -513,6 +799,38 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           tma_store_commit();
           pending_store = 1;
         }
+        continue;
+      }
+
+      // ---- column-parallel mode: plain 16-byte stores into every rank's output (this rank's own too)
+      if (p.peer_count > 0) {
+        for (int c0 = 0; c0 < p.bn; c0 += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + c0, r);
+          tc_wait_ld();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float sv = vec_scale[c0 + j];
+            if constexpr (BK == KIND_I8) v[j] = finish_value<BK>(r[j], row_scale, sv, has_bias, vec_bias[c0 + j]);
+            else v[j] = finish_value<BK>(r[j], s_act_scalar, s_wgt_scalar, has_bias, vec_bias[c0 + j]);
+          }
+          const uint4 lo = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                      pack_bf16x2(v[6], v[7]));
+          const uint4 hi = make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]),
+                                      pack_bf16x2(v[14], v[15]));
+          const int col = row_b0 + c0;  // n is a multiple of 8: the two halves are stored or dropped whole
+          if (ra_ok && ok) {
+            const long long off = static_cast<long long>(ra) * p.peer_ld + p.peer_col0 + col;
+            for (int g = 0; g < p.peer_count; ++g) {
+              if (col + 8 <= lim_b) *reinterpret_cast<uint4*>(p.peer_out[g] + off) = lo;
+              if (col + 16 <= lim_b) *reinterpret_cast<uint4*>(p.peer_out[g] + off + 8) = hi;
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_acc_empty[ab]));
         continue;
       }
 
@@ -538,11 +856,11 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float sv = vec_scale[cc + c0 + j];
-            if constexpr (KIND == KIND_I8) {
-              v[j] = p.swap ? finish_value<KIND>(r[j], sv, row_scale, has_bias, row_bias)
-                            : finish_value<KIND>(r[j], row_scale, sv, has_bias, vec_bias[cc + c0 + j]);
+            if constexpr (BK == KIND_I8) {
+              v[j] = p.swap ? finish_value<BK>(r[j], sv, row_scale, has_bias, row_bias)
+                            : finish_value<BK>(r[j], row_scale, sv, has_bias, vec_bias[cc + c0 + j]);
             } else {
-              v[j] = finish_value<KIND>(r[j], s_act_scalar, s_wgt_scalar, has_bias,
+              v[j] = finish_value<BK>(r[j], s_act_scalar, s_wgt_scalar, has_bias,
                                         p.swap ? row_bias : vec_bias[cc + c0 + j]);
             }
           }
@@ -579,6 +897,22 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
     if (et == 0) tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
+    if (p.peer_count > 0) {
+      // every store of this CTA is performed system-wide before the CTA counts itself as finished;
+      // the last CTA of the launch then tells every rank that this rank's slab is complete
+      __threadfence_system();
+      epi_bar_sync();
+      if (et == 0) {
+        const unsigned done = atomicAdd(p.peer_counter, 1u);
+        if (done == gridDim.x - 1) {
+          *p.peer_counter = 0u;
+          __threadfence_system();
+          if (!abort_flag)
+            for (int g = 0; g < p.peer_count; ++g)
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(p.peer_epoch) : "memory");
+        }
+      }
+    }
   }
 
   // ---------------------------------------------------------------- split-K: reduce across the cluster
@@ -596,7 +930,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int ra = row_a0 + et;
       const bool has_bias = p.bias != nullptr && p.acc_out == nullptr;
       float s_act_scalar = 1.0f, s_wgt_scalar = 1.0f;
-      if constexpr (KIND != KIND_I8) {
+      if constexpr (BK != KIND_I8) {
         if (p.scale_act) s_act_scalar = *p.scale_act;
         if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
       }
@@ -606,7 +940,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int c_hi = min(p.bn, c_lo + per);
       float row_scale = 1.0f, row_bias = 0.0f;
       if (ra < lim_a && p.acc_out == nullptr) {
-        if constexpr (KIND == KIND_I8) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
+        if constexpr (BK == KIND_I8) row_scale = p.swap ? p.scale_wgt[ra] : p.scale_act[ra];
         if (p.swap && has_bias) row_bias = __bfloat162float(p.bias[ra]);
       }
       const float* const vec_scale_r = reinterpret_cast<const float*>(smem_gen + vec_off);
@@ -642,10 +976,10 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           float ftotal = 0.0f;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // fixed order: rank 0, 1, ... (absent ranks contribute zero)
-            if constexpr (KIND == KIND_I8) total += v[u][q];
+            if constexpr (BK == KIND_I8) total += v[u][q];
             else ftotal += __uint_as_float(v[u][q]);
           }
-          if constexpr (KIND != KIND_I8) total = __float_as_uint(ftotal);
+          if constexpr (BK != KIND_I8) total = __float_as_uint(ftotal);
           const int rbj = row_b0 + c;
           if (ra >= lim_a || rbj >= lim_b || abort_flag) continue;
           const long long om = p.swap ? rbj : ra, on = p.swap ? ra : rbj;
@@ -656,12 +990,12 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           float val;
           // B-role scale and bias of this column were staged in shared memory by the epilogue prologue
           const float bias_v = p.swap ? row_bias : vec_bias_r[c];
-          if constexpr (KIND == KIND_I8) {
+          if constexpr (BK == KIND_I8) {
             const float other = vec_scale_r[c];
-            val = p.swap ? finish_value<KIND>(total, other, row_scale, has_bias, bias_v)
-                         : finish_value<KIND>(total, row_scale, other, has_bias, bias_v);
+            val = p.swap ? finish_value<BK>(total, other, row_scale, has_bias, bias_v)
+                         : finish_value<BK>(total, row_scale, other, has_bias, bias_v);
           } else {
-            val = finish_value<KIND>(total, s_act_scalar, s_wgt_scalar, has_bias, bias_v);
+            val = finish_value<BK>(total, s_act_scalar, s_wgt_scalar, has_bias, bias_v);
           }
           p.out[om * p.ldo + on] = __float2bfloat16_rn(val);
         }

@@ -40,6 +40,7 @@ struct Gemm2Params {
   int acc_bufs;  // accumulator buffers in tensor memory (2, or 1 when bn = 256 shares it with scale columns)
   int sf_kt;     // block-scaled: 512-byte scale chunks per 128-row block along K
   int sfb_blocks;  // 128-row scale blocks a weight tile touches (1 or 2)
+  int issue_block; // issue a stage's tensor-core instructions as one straight-line block
   int tiles_m, tiles_n;  // pair tiles: 256 x bn
   long long ldo;
   const float* scale_act;
@@ -107,6 +108,43 @@ __device__ __forceinline__ void mma2_nvf4(uint32_t d_tmem, uint64_t adesc, uint6
 __device__ __forceinline__ void tmem_cp2_32x128b_warpx4(uint32_t taddr, uint64_t sdesc, uint32_t on = 1u) {
   asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
                "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc), "r"(on) : "memory");
+}
+
+// Unpredicated forms for the straight-line issue block of the leader's elected lane.
+#define RK_DEFINE_MMA2_NP(NAME, KIND)                                                                       \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,     \
+                                       uint32_t accumulate) {                                               \
+    asm volatile(                                                                                           \
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                  \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t}"                                 \
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                                  \
+        : "memory");                                                                                        \
+  }
+RK_DEFINE_MMA2_NP(mma2_i8_np, "i8")
+RK_DEFINE_MMA2_NP(mma2_f8f6f4_np, "f8f6f4")
+#undef RK_DEFINE_MMA2_NP
+__device__ __forceinline__ void mma2_mxf8_np(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma2_nvf4_np(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp2_32x128b_warpx4_np(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc2_commit_both_np(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
 }
 
 __host__ __device__ inline int gemm2_stage_bytes(int kind, int bn, int sfb_blocks) {
@@ -256,6 +294,51 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * stage_step);
           const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * stage_step);
           const int nmma = (kb == p.kblocks - 1) ? p.k_valid_mmas_last : 4;
+          if (T::kBlockScaled && p.issue_block && nmma == 4) {
+            // whole K blocks of the block-scaled kinds: the stage's up to 17 tensor-core instructions as one
+            // straight-line block of the elected lane (the issuing thread's cost per instruction paces
+            // these kinds; one instruction here drives both SMs, which is what makes the pair faster);
+            // the kinds without scale copies measured faster in the predicated form below
+            if (on) {
+              const uint32_t accumulate0 = kb > 0 ? 1u : 0u;
+              if constexpr (T::kBlockScaled) {
+                const uint64_t sfdesc0 = umma_desc_noswizzle(smem_base + s * stage_bytes + sf_off, 16, 128);
+                if (p.sfb_blocks == 1) {
+#pragma unroll
+                  for (int j = 0; j < kC; ++j) {
+                    tmem_cp2_32x128b_warpx4_np(tmem_sfa + j * 4, sfdesc0 + static_cast<uint64_t>(j * 32));
+                    tmem_cp2_32x128b_warpx4_np(tmem_sfb + j * 4, sfdesc0 + static_cast<uint64_t>((kC + j) * 32));
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < kC; ++j) {
+                    tmem_cp2_32x128b_warpx4_np(tmem_sfa + j * 4, sfdesc0 + static_cast<uint64_t>(j * 32));
+                    tmem_cp2_32x128b_warpx4_np(tmem_sfb + j * 8, sfdesc0 + static_cast<uint64_t>((kC + j) * 32));
+                    tmem_cp2_32x128b_warpx4_np(tmem_sfb + j * 8 + 4, sfdesc0 + static_cast<uint64_t>((2 * kC + j) * 32));
+                  }
+                }
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t accumulate = k > 0 ? 1u : accumulate0;
+                if constexpr (KIND == KIND_I8) {
+                  mma2_i8_np(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate);
+                } else if constexpr (KIND == KIND_F8) {
+                  mma2_f8f6f4_np(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, accumulate);
+                } else if constexpr (KIND == KIND_MXF8) {
+                  mma2_mxf8_np(d_tmem, adesc + k * 2, bdesc + k * 2,
+                               idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29), tmem_sfa,
+                               tmem_sfb + sfb_col0, accumulate);
+                } else {
+                  mma2_nvf4_np(d_tmem, adesc + k * 2, bdesc + k * 2, idesc, tmem_sfa + k * 4,
+                               tmem_sfb + k * p.sfb_blocks * 4 + sfb_col0, accumulate);
+                }
+              }
+              tc2_commit_both_np(smem_u32(&bar_empty[s]));
+            }
+            __syncwarp();
+            continue;
+          }
           if constexpr (T::kBlockScaled) {
             const uint32_t ssf = smem_base + s * stage_bytes + sf_off;
             const int nb = p.sfb_blocks;

@@ -542,6 +542,65 @@ pack_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long
   *reinterpret_cast<uint32_t*>(q + base) = out;
 }
 
+// The scale of the W4A8-MX formats: the smallest power of two >= v, as a UE8M0 exponent byte (1.0 for
+// v <= 0 or NaN; blackwell/csrc/fp4_mx_cutlass_linear.cu:47-58, `ceil_power_of_two`).
+__device__ __forceinline__ uint32_t ceil_pow2_ue8m0(float v) {
+  if (!(v > 0.0f)) return 127u;
+  const uint32_t bits = __float_as_uint(v);
+  uint32_t e = bits >> 23;             // biased exponent (v > 0: no sign bit)
+  if (e == 0u) return 1u;              // subnormal input: below 2^-126, the smallest normal scale covers it
+  if (bits & 0x7FFFFFu) ++e;           // not a power of two: round up
+  return e > 254u ? 254u : e;
+}
+
+// W4A8-MX, 32-element blocks, eight lanes per block (four elements per lane); FMT 0: MXFP8 activations
+// q = e4m3(clamp(x / s, +-448)), s = ceil_pow2(amax / 448); FMT 1: MXFP4 weights q = e2m1(x / s),
+// s = ceil_pow2(amax / 6), two codes per byte, low nibble = even k.  Reference:
+// blackwell/csrc/fp4_mx_cutlass_linear.cu:59-132.  Every byte of the scale buffer is written.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+pack_mx_ceil_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, uint8_t* __restrict__ q,
+                    uint8_t* __restrict__ sf) {
+  const long long groups_padded = (k + 127) / 128 * 4;
+  const long long rows_padded = (rows + 127) / 128 * 128;
+  const long long thread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long block_index = thread / 8;
+  const int lane8 = static_cast<int>(thread % 8);
+  const long long row = block_index / groups_padded;
+  const long long group = block_index % groups_padded;
+  if (row >= rows_padded) return;
+  const long long sfi = sf_offset(row, group, groups_padded / 4);
+  if (row >= rows || group * 32 >= k) {
+    if (lane8 == 0) sf[sfi] = 0;
+    return;
+  }
+  const long long base = row * k + group * 32 + lane8 * 4;
+  const uint2 u = *reinterpret_cast<const uint2*>(x + base);
+  const float v[4] = {bf16_bits_to_float(u.x & 0xFFFFu), bf16_bits_to_float(u.x >> 16), bf16_bits_to_float(u.y & 0xFFFFu),
+                      bf16_bits_to_float(u.y >> 16)};
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
+  const uint32_t e = ceil_pow2_ue8m0(__fdiv_rn(amax, FMT == 0 ? 448.0f : 6.0f));
+  if (lane8 == 0) sf[sfi] = static_cast<uint8_t>(e);
+  const float inverse = __uint_as_float((254u - e) << 23);  // 2^(127 - e), e in 1..254
+  if constexpr (FMT == 0) {
+    uint32_t out = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float t = fminf(448.0f, fmaxf(-448.0f, __fmul_rn(v[i], inverse)));
+      out |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    }
+    *reinterpret_cast<uint32_t*>(q + base) = out;
+  } else {
+    const uint32_t lo = __nv_cvt_float2_to_fp4x2(make_float2(__fmul_rn(v[0], inverse), __fmul_rn(v[1], inverse)), __NV_E2M1,
+                                                 cudaRoundNearest);
+    const uint32_t hi = __nv_cvt_float2_to_fp4x2(make_float2(__fmul_rn(v[2], inverse), __fmul_rn(v[3], inverse)), __NV_E2M1,
+                                                 cudaRoundNearest);
+    *reinterpret_cast<unsigned short*>(q + base / 2) = static_cast<unsigned short>((lo & 0xFFu) | ((hi & 0xFFu) << 8));
+  }
+}
+
 // NVFP4: one thread per 16-element block (two 128-bit loads, one 64-bit store).
 __global__ void __launch_bounds__(256)
 pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, const float* __restrict__ global,
@@ -600,18 +659,76 @@ __device__ __forceinline__ float swiglu_bf16_steps(float gate, float up) {
   return round_bf16(__fmul_rn(round_bf16(__fmul_rn(gate, r)), up));
 }
 
-// Eight consecutive SwiGLU outputs of row-major gate_up [rows, 2 * inter] (gate first, then up).
+// Eight consecutive SwiGLU outputs of row-major gate_up [rows, 2 * inter]: gate first, then up; or
+// `interleaved`: blocks of 128 columns, 64 up values followed by their 64 gate values (the layout a
+// fused gate/up projection writes: blackwell/csrc/fp4_cutlass_linear.cu:958-965).
 template <bool BF16_STEPS>
 __device__ __forceinline__ void load8_swiglu(const __nv_bfloat16* gate_up, long long inter, long long idx, int valid,
-                                             float (&v)[8]) {
+                                             float (&v)[8], bool interleaved = false) {
   const long long row = idx / inter, col = idx - row * inter;
   const __nv_bfloat16* g = gate_up + row * 2 * inter + col;
+  const __nv_bfloat16* u = g + inter;
+  if (interleaved) {  // eight consecutive columns never straddle a 64-column block
+    u = gate_up + row * 2 * inter + (col >> 6) * 128 + (col & 63);
+    g = u + 64;
+  }
   float gv[8], uv[8];
   const bool vec = (inter % 8) == 0;
   load8(g, vec, valid, gv);
-  load8(g + inter, vec, valid, uv);
+  load8(u, vec, valid, uv);
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = i < valid ? (BF16_STEPS ? swiglu_bf16_steps(gv[i], uv[i]) : swiglu_f32(gv[i], uv[i])) : 0.0f;
+}
+
+// SwiGLU -> MXFP8 with power-of-two (ceil) block scales, the activation side of W4A8-MX
+// (blackwell/csrc/fp4_mx_cutlass_linear.cu:134-179, `pack_swiglu_mxfp8_warp_kernel`): the product
+// gate / (1 + exp(-gate)) * up stays in fp32 (no bf16 rounding) before the block quantizer.
+__global__ void __launch_bounds__(256)
+swiglu_pack_mxfp8_ceil_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter, int interleaved,
+                              uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  const long long groups_padded = (inter + 127) / 128 * 4;
+  const long long rows_padded = (rows + 127) / 128 * 128;
+  const long long thread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long block_index = thread / 8;
+  const int lane8 = static_cast<int>(thread % 8);
+  const long long row = block_index / groups_padded;
+  const long long group = block_index % groups_padded;
+  if (row >= rows_padded) return;
+  const long long sfi = sf_offset(row, group, groups_padded / 4);
+  if (row >= rows || group * 32 >= inter) {
+    if (lane8 == 0) sf[sfi] = 0;
+    return;
+  }
+  const long long col = group * 32 + lane8 * 4;
+  const __nv_bfloat16* g = gate_up + row * 2 * inter + col;
+  const __nv_bfloat16* u = g + inter;
+  if (interleaved) {
+    u = gate_up + row * 2 * inter + (col >> 6) * 128 + (col & 63);
+    g = u + 64;
+  }
+  const uint2 gw = *reinterpret_cast<const uint2*>(g), uw = *reinterpret_cast<const uint2*>(u);
+  const float gv[4] = {bf16_bits_to_float(gw.x & 0xFFFFu), bf16_bits_to_float(gw.x >> 16), bf16_bits_to_float(gw.y & 0xFFFFu),
+                       bf16_bits_to_float(gw.y >> 16)};
+  const float uv[4] = {bf16_bits_to_float(uw.x & 0xFFFFu), bf16_bits_to_float(uw.x >> 16), bf16_bits_to_float(uw.y & 0xFFFFu),
+                       bf16_bits_to_float(uw.y >> 16)};
+  float v[4], amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[i] = __fmul_rn(__fdiv_rn(gv[i], __fadd_rn(1.0f, expf(-gv[i]))), uv[i]);
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
+  const uint32_t e = ceil_pow2_ue8m0(__fdiv_rn(amax, 448.0f));
+  if (lane8 == 0) sf[sfi] = static_cast<uint8_t>(e);
+  const float inverse = __uint_as_float((254u - e) << 23);
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float t = fminf(448.0f, fmaxf(-448.0f, __fmul_rn(v[i], inverse)));
+    out |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(q + row * inter + col) = out;
 }
 
 __global__ void __launch_bounds__(256)
@@ -688,7 +805,7 @@ __device__ __forceinline__ unsigned long long nvfp4_block(const float (&v)[16], 
 
 // SwiGLU -> NVFP4: one thread per 16-element block of the [rows, inter] activation.
 __global__ void __launch_bounds__(256)
-swiglu_pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter,
+swiglu_pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter, int interleaved,
                          uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
   const long long groups = inter / 16;
   const long long groups_padded = (groups + 3) / 4 * 4;
@@ -703,8 +820,8 @@ swiglu_pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate_up, long long ro
     return;
   }
   float v[16];
-  load8_swiglu<true>(gate_up, inter, row * inter + group * 16, 8, *reinterpret_cast<float(*)[8]>(&v[0]));
-  load8_swiglu<true>(gate_up, inter, row * inter + group * 16 + 8, 8, *reinterpret_cast<float(*)[8]>(&v[8]));
+  load8_swiglu<true>(gate_up, inter, row * inter + group * 16, 8, *reinterpret_cast<float(*)[8]>(&v[0]), interleaved != 0);
+  load8_swiglu<true>(gate_up, inter, row * inter + group * 16 + 8, 8, *reinterpret_cast<float(*)[8]>(&v[8]), interleaved != 0);
   uint8_t code;
   const unsigned long long packed = nvfp4_block(v, &code);
   *reinterpret_cast<unsigned long long*>(q + row * (inter / 2) + group * 8) = packed;
@@ -1085,16 +1202,61 @@ extern "C" int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const 
   return check_launch(who);
 }
 
-extern "C" int rk_swiglu_pack_nvfp4(const void* gate_up, int64_t rows, int64_t inter, void* q, void* sf, void* stream) {
+extern "C" int rk_swiglu_pack_nvfp4_layout(const void* gate_up, int64_t rows, int64_t inter, int interleaved, void* q,
+                                           void* sf, void* stream) {
   const char* who = "rk_swiglu_pack_nvfp4";
   if (!gate_up || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
   if (rows < 1 || inter < 32 || inter % 32 != 0) return fail(RK_EINVAL, "%s: the intermediate size must be a multiple of 32", who);
+  if (interleaved && inter % 64 != 0) return fail(RK_EINVAL, "%s: the interleaved layout needs a multiple of 64 columns", who);
   if (!aligned16(gate_up) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   const long long threads = ((rows + 127) / 128 * 128) * ((inter / 16 + 3) / 4 * 4);
   const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
   rk::swiglu_pack_nvfp4_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+                                                                   interleaved ? 1 : 0, static_cast<uint8_t*>(q),
+                                                                   static_cast<uint8_t*>(sf));
+  return check_launch(who);
+}
+
+extern "C" int rk_swiglu_pack_nvfp4(const void* gate_up, int64_t rows, int64_t inter, void* q, void* sf, void* stream) {
+  return rk_swiglu_pack_nvfp4_layout(gate_up, rows, inter, 0, q, sf, stream);
+}
+
+static int pack_mx_ceil(const void* x, int64_t rows, int64_t k, int fmt, void* q, void* sf, void* stream, const char* who) {
+  if (!x || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || k < 32 || k % 32 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 32", who);
+  if (!aligned16(x) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  const long long blocks32 = ((rows + 127) / 128 * 128) * ((k + 127) / 128 * 4);
+  const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
+  if (fmt == 0)
+    rk::pack_mx_ceil_kernel<0><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k,
+                                                                   static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
+  else
+    rk::pack_mx_ceil_kernel<1><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k,
                                                                    static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   return check_launch(who);
+}
+
+extern "C" int rk_swiglu_pack_mxfp8_w4a8(const void* gate_up, int64_t rows, int64_t inter, int interleaved, void* q, void* sf,
+                                         void* stream) {
+  const char* who = "rk_swiglu_pack_mxfp8_w4a8";
+  if (!gate_up || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || inter < 32 || inter % 32 != 0) return fail(RK_EINVAL, "%s: the intermediate size must be a multiple of 32", who);
+  if (interleaved && inter % 64 != 0) return fail(RK_EINVAL, "%s: the interleaved layout needs a multiple of 64 columns", who);
+  if (!aligned16(gate_up) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  const long long blocks32 = ((rows + 127) / 128 * 128) * ((inter + 127) / 128 * 4);
+  const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
+  rk::swiglu_pack_mxfp8_ceil_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+                                                                        interleaved ? 1 : 0, static_cast<uint8_t*>(q),
+                                                                        static_cast<uint8_t*>(sf));
+  return check_launch(who);
+}
+
+extern "C" int rk_pack_mxfp8_act_w4a8(const void* x, int64_t rows, int64_t k, void* q, void* sf, void* stream) {
+  return pack_mx_ceil(x, rows, k, 0, q, sf, stream, "rk_pack_mxfp8_act_w4a8");
+}
+
+extern "C" int rk_pack_mxfp4_weight(const void* w, int64_t rows, int64_t k, void* q, void* sf, void* stream) {
+  return pack_mx_ceil(w, rows, k, 1, q, sf, stream, "rk_pack_mxfp4_weight");
 }
 
 extern "C" int rk_probe_rcp_approx_448(uint32_t* bits) {

@@ -49,7 +49,13 @@ SIGNATURES = {
     "rk_rmsnorm_quant_fp8": (_int, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rk_swiglu_quant_fp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rk_gemm_fp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "rk_gemm_fp8_producer": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_swiglu_pack_nvfp4_layout": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "rk_pack_mxfp4_weight": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_pack_mxfp8_act_w4a8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_swiglu_pack_mxfp8_w4a8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "rk_gemm_w4a8_mx": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_pack_nvfp4": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "rk_rmsnorm_pack_nvfp4": (_int, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp, _vp, _vp]),

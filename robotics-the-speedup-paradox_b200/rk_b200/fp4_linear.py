@@ -95,19 +95,21 @@ def add_rms_norm_fp4_quant_bf16(x, residual, weight, epsilon, write_normalized=T
     return summed, normalized, q, sf
 
 
-def pack_swiglu_nvfp4(gate_up, intermediate_size):
-    """SiLU(gate) * up (bf16 arithmetic steps) packed straight to NVFP4: gate_up bf16 [rows, 2 * inter]."""
+def pack_swiglu_nvfp4(gate_up, intermediate_size, interleaved=False):
+    """SiLU(gate) * up (bf16 arithmetic steps) packed straight to NVFP4: gate_up bf16 [rows, 2 * inter], gate
+    first, or `interleaved`: blocks of 128 columns with 64 up values followed by their 64 gate values."""
     inter = int(intermediate_size)
     if (not gate_up.is_cuda or gate_up.dtype != torch.bfloat16 or not gate_up.is_contiguous() or gate_up.dim() != 2
-            or gate_up.shape[1] != 2 * inter or inter % 32):
-        raise ValueError("SwiGLU NVFP4 pack requires contiguous CUDA BF16 [rows, 2 * inter] with inter divisible by 32")
+            or gate_up.shape[1] != 2 * inter or inter % (64 if interleaved else 32)):
+        raise ValueError("SwiGLU NVFP4 pack requires contiguous CUDA BF16 [rows, 2 * inter] with inter divisible by 32 "
+                         "(64 for the interleaved layout)")
     rows = gate_up.shape[0]
     lib = _lib.load()
     q = torch.empty((rows, inter // 2), device=gate_up.device, dtype=torch.uint8)
     sf = torch.empty(lib.rk_sf_bytes(rows, inter // 16), device=gate_up.device, dtype=torch.uint8)
     with torch.cuda.device(gate_up.device):
-        code = lib.rk_swiglu_pack_nvfp4(_lib.ptr(gate_up), rows, inter, _lib.ptr(q), _lib.ptr(sf),
-                                        _lib.stream_ptr(gate_up.device))
+        code = lib.rk_swiglu_pack_nvfp4_layout(_lib.ptr(gate_up), rows, inter, 1 if interleaved else 0, _lib.ptr(q),
+                                               _lib.ptr(sf), _lib.stream_ptr(gate_up.device))
     _lib.check(code, "pack_swiglu_nvfp4")
     return q, sf
 
@@ -178,15 +180,14 @@ class Fp4CutlassLinear(torch.nn.Module):
 
     def forward_swiglu(self, gate_up, intermediate_size, interleaved=False):
         """SwiGLU, activation packing and this (down) projection (blackwell/fp4_linear.py:805-848 of the
-        reference); gate_up [..., 2 * intermediate_size], gate first."""
+        reference); gate_up [..., 2 * intermediate_size], gate first, or the reference's interleaved
+        layout (64 up columns, then their 64 gate columns, per block of 128)."""
         if int(intermediate_size) != self.in_features:
             raise ValueError(f"expected intermediate_size {self.in_features}, got {intermediate_size}")
-        if interleaved:
-            raise ValueError("the interleaved gate/up layout is not supported")
         if self.weight_global_scale is not None:
             raise RuntimeError("forward_swiglu packs without a per-tensor scale; build the layer with global_scale=False")
         flat = gate_up.to(torch.bfloat16).reshape(-1, 2 * self.in_features).contiguous()
-        q, sf = pack_swiglu_nvfp4(flat, self.in_features)
+        q, sf = pack_swiglu_nvfp4(flat, self.in_features, interleaved)
         return self.forward_packed(q, sf, None, gate_up.shape[:-1])
 
     def extra_repr(self):

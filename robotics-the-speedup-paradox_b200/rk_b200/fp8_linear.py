@@ -148,6 +148,22 @@ def linear_forward_packed(a, scale_a, b, scale_b, bias=None, tactic=0):
     return out
 
 
+def linear_forward_producer(x, weight, weight_scale, bias=None, tactic=0):
+    """bf16 [M, K] x e4m3 [N, K]^T with a unit activation scale: the activations are converted to e4m3
+    inside the GEMM kernel (`rk_gemm_fp8_producer`), no quantizer launch and no e4m3 copy in memory."""
+    _check_bf16(x, "linear_forward_producer input")
+    m, k = x.shape
+    n = weight.shape[0]
+    out = torch.empty((m, n), device=x.device, dtype=torch.bfloat16)
+    with torch.cuda.device(x.device):
+        ws = _lib.gemm_workspace(_lib.OP_FP8, x.device, m, n, k)
+        code = _lib.load().rk_gemm_fp8_producer(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(weight_scale), _lib.ptr(bias),
+                                                _lib.ptr(out), m, n, k, tactic, _lib.ptr(ws), ws.numel(),
+                                                _lib.stream_ptr(x.device))
+    _lib.check(code, "linear_forward_producer")
+    return out
+
+
 # ---- periodic reuse of the dynamic activation scale ----------------------------------------------
 def resolve_fp8_prefill_scale_refresh_interval(value=None):
     """How many prefill calls share one dynamic activation scale: a positive integer, or
@@ -347,17 +363,15 @@ class Fp8CutlassLinear(torch.nn.Module):
         return self.forward_packed(packed, scale, leading_shape)
 
     def forward_producer(self, x):
-        """BF16 activations converted to E4M3 with a unit activation scale, then the GEMM: the semantics of
-        `linear_forward_producer` (blackwell/csrc/fp8_cutlass_linear.cu:727-856, 1268-1315), which the
-        reference uses for small projections to skip the dynamic activation scale.  Here the conversion
-        is a separate launch in front of the GEMM rather than part of its main loop."""
+        """BF16 activations converted to E4M3 with a unit activation scale inside the GEMM's main loop: the
+        semantics of `linear_forward_producer` (blackwell/csrc/fp8_cutlass_linear.cu:727-856, 1268-1315),
+        which the reference uses for small projections to skip the dynamic activation scale and the
+        quantizer pass.  One launch; the converted activations never reach global memory."""
         if self.mode != "per_tensor":
             raise RuntimeError("forward_producer is a per-tensor path; this layer was packed as MXFP8")
         flat = self._rows(x)
-        if self._unit_scale is None or self._unit_scale.device != flat.device:
-            self._unit_scale = torch.ones(1, device=flat.device, dtype=torch.float32)
-        packed = quantize_bf16_with_scale(flat, self._unit_scale)
-        return self.forward_packed(packed, self._unit_scale, x.shape[:-1])
+        out = linear_forward_producer(flat, self.packed_weight, self.weight_scale, self.bias)
+        return out.reshape(*x.shape[:-1], self.out_features)
 
     def forward_mxfp8(self, x):
         if self.mode != "mxfp8":

@@ -169,11 +169,15 @@ def layer_breakdown(envs=8, prefix=816, repeats=5):
     expert._conditions[("probe",)] = cond  # registers the condition, so that its projections are cached
     GemmaAttention.fused_rope = True
 
+    pitch = (prefix + expert.chunk + 7) // 8 * 8
+    vt_all = torch.zeros((envs, cfg.num_kv_heads, cfg.head_dim, pitch), dtype=torch.bfloat16, device=dev)
+    vt_all[..., :prefix + expert.chunk] = v_all.transpose(-1, -2)
+
     def run(tag):
         with torch.no_grad():
             cos, sin = rope_tables(positions, cfg.head_dim, cfg.rope_theta, x.dtype)
             gate = layer.input_layernorm.modulation(cond)[2]
-            step = lambda: layer(x, cos, sin, (k_all, v_all, prefix), cond, (branch, gate))
+            step = lambda: layer(x, cos, sin, (k_all, v_all, prefix, vt_all), cond, (branch, gate))
             for _ in range(3):
                 step()
             torch.cuda.synchronize()
@@ -194,10 +198,13 @@ def layer_breakdown(envs=8, prefix=816, repeats=5):
         with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True, grouped=True,
                               group_views=True):
             norms = fuse_norm_quantize(expert.stack)
-            run("W8A8 linears, grouped, fused norm / residual / rope")
+            run("W8A8 linears, grouped, fused norm / residual / rope, torch SDPA")
+            GemmaAttention.fused_attention = True
+            run("W8A8 linears, grouped, fused norm / residual / rope, rk_attn_prefix_kernel")
             unfuse_norm_quantize(norms)
     finally:
         GemmaAttention.fused_rope = False
+        GemmaAttention.fused_attention = False
 
 
 def main(argv):

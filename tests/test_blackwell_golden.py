@@ -222,7 +222,7 @@ def test_cuda_fused_producers_match_reference_kernels(G, maker):
         pytest.skip("the fixture holds no producer outputs")
     x, res, weight, gate_up, inter = (_dev(t) if torch.is_tensor(t) else t for t in maker.producer_inputs())
     s, nrm, q, scale = P8.add_rms_norm_quantize_bf16(x, res, weight, 1e-6)
-    assert np.array_equal(s.view(torch.uint8).cpu().numpy().reshape(-1), G["prod_fp8_rms_sum"])
+    assert np.array_equal(s.view(torch.uint8).cpu().numpy().reshape(-1), G["prod_fp8_rms_sum"].reshape(-1))
     # the reference's rsqrt is the fast-math approximation: normalised values may differ in the last bf16 digit
     for key, ours in (("prod_fp8_rms_norm", nrm), ("prod_fp8_rms_codes", q)):
         count = int(G[key + "_diff_count"])
@@ -235,3 +235,105 @@ def test_cuda_fused_producers_match_reference_kernels(G, maker):
         s, nrm, q, sf = P4.add_rms_norm_fp4_quant_bf16(x, res, weight, 1e-6, True)
         assert patched_sha(G, "prod_nvfp4_rms_codes", q.cpu().numpy())[0] == str(G["prod_nvfp4_rms_codes_sha"])
         assert int(G["prod_nvfp4_rms_codes_diff_count"]) <= q.numel() // 50
+
+
+# ------------------------------------------------------------------ second fixture file: W4A8 MX, FP8 producer, SwiGLU chains
+EXT = GOLDEN / "blackwell_golden_ext.npz"
+needs_ext = pytest.mark.skipif(not EXT.exists(), reason="blackwell_golden_ext.npz has not been generated")
+
+
+@pytest.fixture(scope="module")
+def GX():
+    return np.load(EXT)
+
+
+@needs_ext
+def test_oracle_w4a8_mx_packers_match_reference_kernels(GX, maker):
+    """`pack_mxfp8_activation` / `pack_mxfp4_weight` of the reference (blackwell/csrc/fp4_mx_cutlass_linear.cu)
+    against the oracle: small case in full, the 816 x 2048 activation of the full-size case by digest."""
+    _, m, n, k = maker.EXT_CASES[0]
+    x, w, bias = maker.case_inputs("small", m, n, k)
+    ca, sa, swa = OB.pack_mxfp8_ceil(x.float().numpy())
+    pb, sb, swb = OB.pack_mxfp4_ceil(w.float().numpy())
+    assert np.array_equal(GX["small_w4a8_a_codes"].reshape(m, k), ca) and np.array_equal(GX["small_w4a8_a_sf"], swa)
+    assert np.array_equal(GX["small_w4a8_w_codes"].reshape(n, k // 2), pb) and np.array_equal(GX["small_w4a8_w_sf"], swb)
+    # the reference's GEMM output on those operands against dequantize -> float64 matmul
+    want, _ = OB.gemm_dequantized(OB.dequant_mxfp8(ca, sa), OB.dequant_mxfp4(pb, sb), bias.float().numpy())
+    got = (GX["small_w4a8_out"].astype(np.uint32) << 16).view(np.float32)
+    assert OB.rel_frobenius(got, want) < 2e-3
+    _, m, n, k = maker.EXT_CASES[1]
+    x, _, _ = maker.case_inputs("w4a8_gate_up", m, n, k)
+    ca, _, swa = OB.pack_mxfp8_ceil(x.float().numpy())
+    assert patched_sha(GX, "w4a8_gate_up_w4a8_a_codes", ca) == (str(GX["w4a8_gate_up_w4a8_a_codes_sha"]), 0)
+    assert patched_sha(GX, "w4a8_gate_up_w4a8_a_sf", swa) == (str(GX["w4a8_gate_up_w4a8_a_sf_sha"]), 0)
+
+
+@needs_ext
+def test_oracle_fp8_producer_matches_reference_output_small(GX, maker):
+    """The reference's producer GEMM (bf16 activations converted in its main loop, unit scale) against
+    the oracle: e4m3 of the clamped activations, reference weight codes and scale."""
+    _, m, n, k = maker.EXT_CASES[0]
+    x, _, bias = maker.case_inputs("small", m, n, k)
+    codes = OF.quantize_with_scale(x.float().numpy(), np.float32(1.0))
+    want, _ = OF.gemm(codes, np.float32(1.0), GX["small_fp8prod_w_codes"].reshape(n, k), GX["small_fp8prod_w_scale"][0],
+                      bias.float().numpy())
+    got = (GX["small_fp8prod_out"].astype(np.uint32) << 16).view(np.float32)
+    assert OB.rel_frobenius(got, want) < 2e-3
+
+
+@needs_ext
+@pytest.mark.gpu
+def test_cuda_w4a8_mx_and_producer_match_reference_kernels(GX, maker):
+    from rk_b200 import fp4_mx_linear as PM
+    from rk_b200 import fp8_linear as P8
+
+    for name, m, n, k in maker.EXT_CASES:
+        x, w, bias = (_dev(t) for t in maker.case_inputs(name, m, n, k))
+        if name != "producer_kv":
+            qa, fa = PM.pack_mxfp8_activation(x)
+            qb, fb = PM.pack_mxfp4_weight(w)
+            for tag, ours in (("a_codes", qa.view(torch.uint8)), ("a_sf", fa), ("w_codes", qb), ("w_sf", fb)):
+                key = f"{name}_w4a8_{tag}"
+                assert patched_sha(GX, key, ours.cpu().numpy()) == (str(GX[key + "_sha"]), 0), key  # bit-identical
+            out = PM.linear_w4a8_packed(qa, fa, qb, fb, bias)
+            assert np.array_equal(_sample(maker, out), GX[f"{name}_w4a8_out_ours_sample"])
+            _close_to_reference(_sample(maker, out), GX[f"{name}_w4a8_out_sample"])
+        if name != "w4a8_gate_up":
+            wq, wscale = P8.quantize_bf16(w)
+            if sha(wq.view(torch.uint8).cpu().numpy()) == str(GX[f"{name}_fp8prod_w_codes_sha"]):
+                # same weight codes as the reference's quantizer produced: outputs are comparable directly
+                ref_scale = torch.from_numpy(GX[f"{name}_fp8prod_w_scale"]).to(x.device)
+                out = P8.linear_forward_producer(x, wq, ref_scale, bias)
+                assert np.array_equal(_sample(maker, out), GX[f"{name}_fp8prod_out_ours_sample"])
+                _close_to_reference(_sample(maker, out), GX[f"{name}_fp8prod_out_sample"])
+
+
+@needs_ext
+@pytest.mark.gpu
+def test_cuda_swiglu_chains_match_reference_kernels(GX, maker):
+    """SwiGLU -> pack -> down projection, both gate/up layouts, NVFP4 and W4A8-MX: the reference's final
+    outputs (`linear_forward_swiglu_gemm_bf16`, `pack_swiglu_mxfp8` + `linear_w4a8_packed`)."""
+    from rk_b200 import fp4_linear as P4
+    from rk_b200 import fp4_mx_linear as PM
+
+    x, res, weight, gate_up, inter = (_dev(t) if torch.is_tensor(t) else t for t in maker.producer_inputs())
+    gen = torch.Generator().manual_seed(78)
+    wd = (torch.randn(256, inter, generator=gen) * 0.02).to(torch.bfloat16)
+    lin = torch.nn.Linear(inter, 256, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(wd)
+    lin = lin.to(gate_up.device).requires_grad_(False)
+    bits = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+    for interleaved in (False, True):
+        # the fixtures' gate_up is read in the requested layout as it stands (same bytes, other meaning)
+        if f"swiglu_nvfp4_out_{int(interleaved)}" in GX.files:
+            out = P4.Fp4CutlassLinear.from_linear(lin, "linear", "down").forward_swiglu(gate_up, inter, interleaved)
+            ref = GX[f"swiglu_nvfp4_out_{int(interleaved)}"]
+            assert (bits(out) != ref).mean() < 0.02
+        tag = f"swiglu_mxfp8_{int(interleaved)}"
+        if tag + "_out" in GX.files:
+            q, sf = PM.pack_swiglu_mxfp8(gate_up, inter, interleaved)
+            assert patched_sha(GX, tag + "_codes", q.view(torch.uint8).cpu().numpy())[0] == str(GX[tag + "_codes_sha"])
+            assert patched_sha(GX, tag + "_sf", sf.cpu().numpy())[0] == str(GX[tag + "_sf_sha"])
+            out = PM.Fp4MxLinear.from_linear(lin, "linear", "down").forward_swiglu(gate_up, inter, interleaved)
+            assert (bits(out) != GX[tag + "_out"]).mean() < 0.02

@@ -142,8 +142,12 @@ def test_swiglu_modules_end_to_end(H):
             tol = 0.15  # four-bit operands on both sides
         assert got.shape == (4, 7, width)
         assert H.rel_frobenius(H.to_np(got).reshape(-1, width), want.reshape(-1, width)) < tol
-    with pytest.raises(ValueError):
-        Fp4CutlassLinear.from_linear(lin, "linear", "down").forward_swiglu(gate_up, inter, interleaved=True)
+    # the interleaved gate/up layout (64 up columns, then their 64 gate columns) gives the same result
+    blocks = torch.stack([gate_up[..., inter:].reshape(4, 7, inter // 64, 64), gate_up[..., :inter].reshape(4, 7, inter // 64, 64)],
+                         dim=3)
+    layer = Fp4CutlassLinear.from_linear(lin, "linear", "down")
+    assert torch.equal(layer.forward_swiglu(blocks.reshape(4, 7, 2 * inter).contiguous(), inter, interleaved=True),
+                       layer.forward_swiglu(gate_up, inter))
 
 
 def test_fp8_producer_path_uses_a_unit_activation_scale(H):
