@@ -884,6 +884,13 @@ def column_parallel_leg(info, device, reps=30):
     make = lambda lin: Fp8CutlassLinear.from_linear(lin, "linear", "gate_up")
     single = make(full)
     sharded = replicas.ColumnParallelLinear(single, info)
+    fused, fused_error = None, None
+    try:  # the GEMM whose epilogue stores into every rank's buffer: needs peer mappings between the GPUs
+        fused = replicas.FusedColumnParallelLinear(single, info, max_rows=m)
+    except Exception as exc:  # reported, never silently replaced
+        fused_error = f"{type(exc).__name__}: {exc}"
+    # every rank must take the same branch below (the fused form's ranks wait on one another)
+    have = replicas.max_over_ranks([0.0 if fused is not None else 1.0], info, device)[0] == 0.0
 
     def timed(fn):
         for _ in range(3):
@@ -902,10 +909,26 @@ def column_parallel_leg(info, device, reps=30):
         us_single = timed(lambda: single(x))
         a, b = sharded(x).float(), single(x).float()
         rel = float((a - b).norm() / b.norm())  # the slabs share the one-GPU codes and scale: exactly 0
+        us_fused, rel_fused = None, None
+        if have:
+            us_fused = timed(lambda: fused(x))
+            replicas.barrier(info, device)
+            rel_fused = float((fused(x).float() - b).norm() / b.norm())
+            torch.cuda.synchronize(device)
+            replicas.barrier(info, device)
     us_sharded, us_single = replicas.max_over_ranks([us_sharded, us_single], info, device)
+    if have:
+        us_fused, rel_fused = replicas.max_over_ranks([us_fused, rel_fused], info, device)
+    # the slab each rank sends to each of its G - 1 peers, against the measured 770 GB/s per direction
+    sent = m * (n // info.world) * 2 * (info.world - 1)
     return {"op": "fp8 linear (dynamic activation scale) M=816 N=16384 K=2048", "ranks": info.world,
             "us_column_parallel_with_all_gather": us_sharded, "us_one_gpu": us_single,
-            "rel_frobenius_vs_one_gpu": rel, "collective": "nccl all_gather_into_tensor of bf16 slabs"}
+            "rel_frobenius_vs_one_gpu": rel, "collective": "nccl all_gather_into_tensor of bf16 slabs",
+            "us_fused_gemm_exchange": us_fused, "rel_frobenius_fused_vs_one_gpu": rel_fused,
+            "fused_unavailable": fused_error, "bytes_sent_per_rank": sent,
+            "us_link_floor_at_770GBs": sent / 770e9 * 1e6,
+            "fused": "GEMM epilogue stores every chunk into all ranks' buffers over NVLink (TMA stores through peer "
+                     "mappings), flags + a one-warp wait kernel instead of a collective"}
 
 
 def workload_config(copies):

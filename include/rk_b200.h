@@ -244,6 +244,38 @@ int rk_gemm_fp8_producer(const void* x, const void* b, const float* scale_b, con
                          int64_t m, int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* ---- column-parallel FP8 linear with the exchange fused into the GEMM -------------------------
+ *
+ * Every GPU of a group of `ranks` holds the full [m, ld_total] bf16 output; rank r computes the
+ * columns [col0, col0 + n_local) (its rows of the weight matrix) and the GEMM's epilogue stores
+ * each finished 128 x 64 chunk straight into EVERY rank's buffer (TMA stores through peer
+ * mappings; nothing is loaded from a peer), then raises flag[rank] = epoch in every rank's flag
+ * array once all of its stores have completed.  `rk_wait_peers` is the consumer side: a one-warp
+ * kernel on the caller's stream that returns once every other rank's flag has reached `epoch`, or
+ * records device code 107 in the workspace status word after about a second.  Together they
+ * replace GEMM -> all-gather of `ColumnParallelLinear` around `linear_forward_packed`
+ * (src/robotics_kernels/optimizations/tensor_parallel.py:33-77 + blackwell/fp8_linear.py:66-100)
+ * without a collective launch.  The caller owns the rendezvous: exchanging the buffer addresses,
+ * alternating between two output buffers and growing `epoch` by one per call, so that a fast rank
+ * never overwrites a buffer a slow rank still reads.
+ *
+ * rk_column_parallel_maps: encodes the `ranks` store descriptors of this rank's slab (one per
+ * destination buffer out_ptrs[g], device pointers valid on this GPU) into `maps_device`
+ * (ranks * 128 bytes of device memory, 128-byte aligned); once per set of output buffers.
+ * col0, n_local, ld_total multiples of 8. */
+int rk_column_parallel_maps(void* const* out_ptrs, int ranks, int64_t m, int64_t ld_total, int64_t col0,
+                            int64_t n_local, void* maps_device, void* stream);
+/*   a e4m3 [m, k]; b e4m3 [n_local, k] (this rank's rows of the weight); scales: device pointers to
+ *   one f32 each (the activation scale must be the same on every rank); bias bf16 [n_local] or NULL;
+ *   flag_ptrs[g]: rank g's int32 flag array [ranks] as mapped on this GPU. */
+int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, const void* b, const float* scale_b,
+                                const void* bias, int64_t m, int64_t n_local, int64_t k, const void* maps_device,
+                                void* const* flag_ptrs, int rank, int ranks, int epoch, void* workspace,
+                                size_t workspace_bytes, void* stream);
+/*   flags: this rank's own flag array [ranks]. */
+int rk_wait_peers(const void* flags, int rank, int ranks, int epoch, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
 /* ---- MXFP8 ------------------------------------------------------------------------------ */
 
 /* Per 32 consecutive k: SF = UE8M0 round-up of max|x| * rcp(448) (255 when the block holds a

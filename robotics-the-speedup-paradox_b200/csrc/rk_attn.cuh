@@ -22,8 +22,10 @@
 //      order; each CTA finishes 256 / KS of the head's columns and stores bf16 rows.
 // No global scratch, no atomics, fixed summation order.  Every wait is bounded.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 =
-// softmax / epilogue (warp w owns TMEM lanes 32 * (w % 4) .. + 31).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..9 =
+// softmax / epilogue: warp w works on TMEM lanes 32 * (w % 4) .. + 31 (one thread per query row) and
+// two warps share each row, taking alternate 32-column chunks.  The softmax stream is latency
+// bound (long dependent chains per row), so two warps per scheduler nearly halve it.
 #pragma once
 
 #include <cuda.h>
@@ -32,7 +34,8 @@
 
 namespace rk {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;
+constexpr int kAttnSoftmaxThreads = 256;
 constexpr int kAttnDim = 256;                 // head dimension this kernel is built for
 constexpr int kAttnQBytes = 128 * 128;        // one 64-element column block of the query tile
 constexpr int kAttnSlotBytes = 256 * 128;     // ring slot: a K block (keys x 128 B) or a V^T block (256 x 128 B)
@@ -86,7 +89,7 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int verdict[2];
-  __shared__ float row_max[128], row_sum[128];  // this slice's softmax statistics, read by the peers
+  __shared__ float row_max[2][128], row_sum[2][128];  // this slice's softmax statistics per warp of a row pair, read by the peers
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -110,7 +113,7 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     mbar_init(smem_u32(&bar_s_full), 1);
-    mbar_init(smem_u32(&bar_p_full), 128);
+    mbar_init(smem_u32(&bar_p_full), kAttnSoftmaxThreads);
     mbar_init(smem_u32(&bar_o_full), 1);
     abort_flag = 0;
     fence_barrier_init();
@@ -217,20 +220,20 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     if (alive) tc_commit(smem_u32(&bar_o_full), on);
   } else {
-    // ------------------------------------------------------------ softmax / epilogue: one thread per query row
+    // ------------------------------------------------------------ softmax / epilogue: two threads per query row
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which of the row's two threads: chunks half, half + 2, ...
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float log2e = 1.4426950408889634f;
     const int valid = min(p.keys, p.kv_len - key0);  // keys of this slice that exist (may be <= 0 for a trailing slice)
-    bool ok = mbar_wait_group(smem_u32(&bar_s_full), 0, r == 0, 1, 128, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC, verdict, 0);
+    bool ok = mbar_wait_group(smem_u32(&bar_s_full), 0, threadIdx.x == 64, 1, kAttnSoftmaxThreads, &abort_flag, p.status,
+                              RK_DEV_TIMEOUT_ACC, verdict, 0);
     tc_fence_after();
-    // The softmax threads are one warp per scheduler, so their instruction stream is latency bound:
-    // the passes below are written for few instructions per score and independent chains.
-    // pass 1: the slice's maximum.  Rounding to bf16 and the positive scale are monotonic, so the
-    // maximum of the scores is the score of the largest raw accumulator.
+    // pass 1: the maximum of this thread's chunks.  Rounding to bf16 and the positive scale are
+    // monotonic, so the maximum of the scores is the score of the largest raw accumulator.
     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    for (int c0 = 0; c0 < p.keys; c0 += 32) {
+    for (int c0 = half * 32; c0 < p.keys; c0 += 64) {
       uint32_t a[32];
       __syncwarp();
       tmem_ld_32(tmem_s + lane_addr + c0, a);
@@ -240,22 +243,22 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (c0 + j < valid) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(a[j]));
     }
     const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-    row_max[r] = valid > 0 ? attn_score(__float_as_uint(m_raw), p.scaling) : -INFINITY;
+    row_max[half][r] = m_raw > -INFINITY ? attn_score(__float_as_uint(m_raw), p.scaling) : -INFINITY;
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1
-    // the exact global maximum: every CTA reads the KS slice maxima
+    // the exact global maximum: every thread reads the 2 * KS partial maxima of its row
     float m_glob = -INFINITY;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       if (q < p.splits) {
         uint32_t am;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(am) : "r"(smem_u32(&row_max[r])), "r"(q));
-        m_glob = fmaxf(m_glob, dsmem_ld_f32(am));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(am) : "r"(smem_u32(&row_max[0][r])), "r"(q));
+        m_glob = fmaxf(m_glob, fmaxf(dsmem_ld_f32(am), dsmem_ld_f32(am + 128u * 4u)));
       }
     }
     // pass 2: e = exp(score - max) once per score, summed, and written back over the score (fp32)
     const float mneg = -m_glob * log2e;
     float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int c0 = 0; c0 < p.keys; c0 += 32) {
+    for (int c0 = half * 32; c0 < p.keys; c0 += 64) {
       uint32_t a[32];
       __syncwarp();
       tmem_ld_32(tmem_s + lane_addr + c0, a);
@@ -271,41 +274,54 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_st_32(tmem_s + lane_addr + c0, a);
     }
     tc_wait_st();
-    row_sum[r] = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+    row_sum[half][r] = (ls[0] + ls[1]) + (ls[2] + ls[3]);
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");  // #1b
     float l_glob = 0.0f;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {  // fixed order: slice 0, 1, ...
+    for (int q = 0; q < 8; ++q) {  // fixed order: slice 0 (even chunks, odd chunks), slice 1, ...
       if (q < p.splits) {
         uint32_t al;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(al) : "r"(smem_u32(&row_sum[r])), "r"(q));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(al) : "r"(smem_u32(&row_sum[0][r])), "r"(q));
         l_glob += dsmem_ld_f32(al);
+        l_glob += dsmem_ld_f32(al + 128u * 4u);
       }
     }
     const float inv_l = l_glob > 0.0f ? __fdiv_rn(1.0f, l_glob) : 0.0f;
-    // pass 3: probabilities as packed bf16 over the values they replace (column j of P covers columns
-    // 2j, 2j+1, which this thread has already read when it writes)
-    for (int c0 = 0; c0 < p.keys; c0 += 32) {
+    // pass 3: probabilities as packed bf16 over the values they replace.  Packed column j covers the
+    // fp32 columns 2j, 2j + 1; chunk c lands in the first (c even) or second (c odd) half of chunk
+    // c / 2, which one of the row's two threads read in this step or an earlier one: a barrier of
+    // the row's two warps between the reads and the writes of a step keeps every read before the
+    // write that replaces it.
+    for (int c0 = half * 32; c0 < ((p.keys + 63) & ~63); c0 += 64) {
       uint32_t a[32];
-      __syncwarp();
-      tmem_ld_32(tmem_s + lane_addr + c0, a);
-      tc_wait_ld();
       uint32_t w[16];
+      const bool mine = c0 < p.keys;  // the last step may hold a chunk for one of the two warps only
+      if (mine) {
+        __syncwarp();
+        tmem_ld_32(tmem_s + lane_addr + c0, a);
+        tc_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        w[j] = pack_bf16x2(__uint_as_float(a[2 * j]) * inv_l, __uint_as_float(a[2 * j + 1]) * inv_l);
-      __syncwarp();
-      tmem_st_16(tmem_s + lane_addr + (c0 >> 1), w);
+        for (int j = 0; j < 16; ++j)
+          w[j] = pack_bf16x2(__uint_as_float(a[2 * j]) * inv_l, __uint_as_float(a[2 * j + 1]) * inv_l);
+      }
+      tc_fence_before();
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+      tc_fence_after();
+      if (mine) {
+        __syncwarp();
+        tmem_st_16(tmem_s + lane_addr + (c0 >> 1), w);
+      }
     }
     tc_wait_st();
     tc_fence_before();
     mbar_arrive(smem_u32(&bar_p_full));
-    ok = mbar_wait_group(smem_u32(&bar_o_full), 0, r == 0, 1, 128, &abort_flag, p.status, RK_DEV_TIMEOUT_ACC, verdict, 1) && ok;
+    ok = mbar_wait_group(smem_u32(&bar_o_full), 0, threadIdx.x == 64, 1, kAttnSoftmaxThreads, &abort_flag, p.status,
+                         RK_DEV_TIMEOUT_ACC, verdict, 1) && ok;
     tc_fence_after();
     // park this slice's partial output, column-major [256][128] fp32, over the operand buffers
-    // (every MMA that read them has completed)
+    // (every MMA that read them has completed); each of the row's two threads takes 128 columns
     float* const part = reinterpret_cast<float*>(smem_gen);
-    for (int c0 = 0; c0 < 256; c0 += 32) {
+    for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
       uint32_t a[32];
       __syncwarp();
       tmem_ld_32(tmem_o + lane_addr + c0, a);
@@ -324,8 +340,8 @@ rk_attn_prefix_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   cluster_sync_all();  // #2: every CTA's partial output is in its shared memory
   if (warp >= 2) {
     const int r = (warp & 3) * 32 + lane;
-    const int per = 256 / p.splits;  // columns this CTA finishes (splits divides 256)
-    const int c_lo = split * per;
+    const int per = 128 / p.splits;  // columns this thread finishes: the CTA takes 256 / splits, each of the row's two threads half
+    const int c_lo = split * 2 * per + ((warp - 2) >> 2) * per;
     uint32_t peer[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {

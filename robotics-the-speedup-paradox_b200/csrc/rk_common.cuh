@@ -208,6 +208,8 @@ __device__ __forceinline__ void tma_store_wait_read() {
 }
 // Full completion (writes performed).  A CTA about to exit only needs tma_store_wait_read<0>(): the
 // grid's completion makes its bulk stores visible to whatever runs next.
+// orders the async proxy's global-memory accesses against the generic proxy's
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

@@ -225,7 +225,7 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
     pl.tiles_a = static_cast<int>((m + 127) / 128);
     pl.tiles_b = static_cast<int>((n + pl.bn - 1) / pl.bn);
     pl.sfb_blocks = kind == KIND_MX48 ? 1 : 0;
-    tactic |= 2;
+    if (kind == KIND_MX48) tactic |= 2;  // block scales: no split-K
   } else if (block_scaled) {
     // A-role tiles are whole 128-row scale blocks; B-role tiles start on multiples of 64 rows
     const int64_t rows_b = pl.swap ? m : n;
@@ -284,13 +284,16 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
     int s = static_cast<int>(kNumSms / tiles);
     if (s > 8) s = 8;
     if (s > kblocks / 2) s = kblocks / 2;
+    // non-swap 128-column tiles exchange 64 KB per CTA and peer through distributed shared memory:
+    // beyond four slices the exchange costs more than the shorter K loops save
+    if (rewriting && s > 4) s = 4;
     if (s > 1) pl.splits = s;
   }
   // shared memory: pipeline stages + output staging + per-tile vectors
   const int stage = gemm_stage_bytes(kind, pl.bn, pl.sfb_blocks);
   pl.out_bufs = 2;
   int budget = kSmemBudget - kVecBytes - pl.out_bufs * kOutBufBytes;
-  if (budget / stage < 4 && (kSmemBudget - kVecBytes - kOutBufBytes) / stage >= 4) {
+  if (rewriting || (budget / stage < 4 && (kSmemBudget - kVecBytes - kOutBufBytes) / stage >= 4)) {
     pl.out_bufs = 1;  // one more pipeline stage is worth more than a second staging buffer
     budget = kSmemBudget - kVecBytes - kOutBufBytes;
   }
@@ -398,16 +401,22 @@ int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorM
   return RK_OK;
 }
 
+// A box of the 16 x U4 -> 16-byte-aligned tensor-map type writes 128 bytes per row into shared memory
+// (8 data bytes + 8 bytes of gap per 16 elements) from 64 bytes of global memory, and the copy
+// counts the 64 GLOBAL bytes per row on its barrier (measured: announcing the shared-memory bytes
+// leaves the phase incomplete).  A stage therefore announces this much less per 4-bit row.
+constexpr int kU4TxDeficitPerRow = 64;
+
 // the column-parallel ("peer") mode of run_tc: see GemmParams::peer_*
 struct PeerArgs {
-  void* out[8];
+  const CUtensorMap* maps;  // device memory
   int* flags[8];
-  int64_t ld, col0;
   int count, rank, epoch;
 };
 
 struct TcArgs {
   const PeerArgs* peer = nullptr;
+  bool wgt_u4 = false;   // KIND_MXF8 with packed e2m1 weights [n, k / 2]: TMA expands them into the MMA's padded layout
   int kind;
   const void* act;       // [m, k_bytes] bytes
   const void* wgt;       // [n, k_bytes] bytes
@@ -463,10 +472,29 @@ int run_tc(const TcArgs& a) {
       p2.bn = ((a.tactic & 4) || a.n < 256) ? 128 : 256;
       p2.acc_bufs = 2;
     } else {
-      // the scale factors need tensor-memory columns of their own: 192-column tiles keep two
-      // accumulator buffers (the epilogue overlaps the next tile's MMAs), 256-column tiles have
-      // one and pay for it with an exposed epilogue, which only long K loops amortise
-      p2.bn = ((a.tactic & 4) || a.n < 192) ? 128 : (kblocks >= 24 ? 256 : 192);
+      // The scale factors need tensor-memory columns of their own: 128- and 192-column tiles keep two
+      // accumulator buffers (the epilogue overlaps the next tile's MMAs), 256-column tiles have one
+      // and pay for it with an exposed epilogue.  A stage costs the larger of the issuing thread's
+      // time (about 50 cycles per tensor-core instruction: 4 MMAs, the scale copies, the commit) and
+      // the tensor pipe's (bn / 2 cycles per MMA); the tile width with the least estimated time over
+      // all rounds of the 74 pairs wins.  (Measured: 816 x 16384 x 2048 NVFP4 19.4 us at 192 against
+      // 21.6 at 256; 4096 x 8192 x 8192 107 us at 256 against 126 at 192.)
+      const int chunks = a.kind == KIND_NVF4 ? 4 : 1;
+      const int64_t tiles_m = (a.m + 255) / 256;
+      int64_t best = -1;
+      p2.bn = 128;
+      for (int bn : {256, 192, 128}) {
+        if (bn > 128 && ((a.tactic & 4) || a.n < 192)) continue;
+        const int sfb = bn == 128 ? 1 : 2;
+        const int64_t issue = 50 * (4 + chunks * (1 + sfb) + 1);
+        const int64_t pipe = 4 * (bn / 2);
+        const int64_t stage = issue > pipe ? issue : pipe;
+        const int64_t tiles = tiles_m * ((a.n + bn - 1) / bn);
+        const int64_t rounds = (tiles + kNumSms / 2 - 1) / (kNumSms / 2);
+        const int64_t epilogue = 10 * bn;  // exposed after every tile without a second buffer, else after the last
+        const int64_t cost = rounds * (kblocks * stage + (bn == 256 ? epilogue : 0)) + (bn == 256 ? 0 : epilogue);
+        if (best < 0 || cost < best) best = cost, p2.bn = bn;
+      }
       if (bn_env == 128 || bn_env == 192 || bn_env == 256) p2.bn = bn_env;
       p2.acc_bufs = p2.bn == 256 ? 1 : 2;
     }
@@ -490,9 +518,13 @@ int run_tc(const TcArgs& a) {
     rc = make_map_2d(&t_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, kTileA,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != RK_OK) return rc;
-    rc = make_map_2d(&t_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.n, a.k_bytes, kStageKBytes,
-                     static_cast<uint32_t>(p2.bn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_map_2d(&t_wgt, a.wgt, a.wgt_u4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                     a.k_bytes, a.n, a.wgt_u4 ? a.k_bytes / 2 : a.k_bytes, kStageKBytes, static_cast<uint32_t>(p2.bn / 2),
+                     CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != RK_OK) return rc;
+    p2.fmt_a = FMT_E4M3;
+    p2.fmt_b = a.wgt_u4 ? FMT_E2M1_IN_F8 : FMT_E4M3;
+    p2.tx_deficit = a.wgt_u4 ? kU4TxDeficitPerRow * (p2.bn / 2) : 0;
     rc = make_map_2d(&t_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 64, 128,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != RK_OK) return rc;
@@ -535,8 +567,8 @@ int run_tc(const TcArgs& a) {
     rc = make_map_2d(&tm_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes * raw_wgt / kStageKBytes, a.n,
                      a.k_bytes * raw_wgt / kStageKBytes, raw_wgt, box_wgt, CU_TENSOR_MAP_SWIZZLE_NONE);
   else
-    rc = make_map_2d(&tm_wgt, a.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.n, a.k_bytes, kStageKBytes, box_wgt,
-                     CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_map_2d(&tm_wgt, a.wgt, a.wgt_u4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                     a.k_bytes, a.n, a.wgt_u4 ? a.k_bytes / 2 : a.k_bytes, kStageKBytes, box_wgt, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != RK_OK) return rc;
   if (a.out != nullptr && a.acc_out == nullptr && a.peer == nullptr) {
     // output tiles leave through TMA: 32 rows x 128 channels (swap) or 128 rows x 64 channels
@@ -581,13 +613,13 @@ int run_tc(const TcArgs& a) {
   p.wait_limit = g_debug_wait_limit > 0 ? g_debug_wait_limit : static_cast<int>(kWaitSpinMax);
   p.debug_stall = g_debug_stall;
   p.issue_block = (issue_block_mode() && pl.sfb_blocks <= 2) ? 1 : 0;
+  const int fmt_wgt = a.wgt_u4 ? FMT_E2M1_IN_F8 : FMT_E4M3;
+  p.fmt_a = pl.swap ? fmt_wgt : FMT_E4M3;
+  p.fmt_b = pl.swap ? FMT_E4M3 : fmt_wgt;
+  p.tx_deficit = a.wgt_u4 ? kU4TxDeficitPerRow * static_cast<int>(box_wgt) : 0;
   if (a.peer != nullptr) {
-    for (int g = 0; g < a.peer->count; ++g) {
-      p.peer_out[g] = static_cast<__nv_bfloat16*>(a.peer->out[g]);
-      p.peer_flags[g] = a.peer->flags[g];
-    }
-    p.peer_ld = a.peer->ld;
-    p.peer_col0 = a.peer->col0;
+    for (int g = 0; g < a.peer->count; ++g) p.peer_flags[g] = a.peer->flags[g];
+    p.peer_maps = a.peer->maps;
     p.peer_count = a.peer->count;
     p.peer_rank = a.peer->rank;
     p.peer_epoch = a.peer->epoch;
@@ -861,7 +893,12 @@ extern "C" int rk_gemm_w4a8_mx(const void* a, const void* sfa, const void* b, co
   if (!sfa || !sfb) return fail(RK_EINVAL, "%s: null scale-factor pointer", who);
   if (!aligned16(sfa) || !aligned16(sfb)) return fail(RK_EINVAL, "%s: scale-factor buffers must be 16-byte aligned", who);
   TcArgs t{};
-  t.kind = KIND_MX48;
+  // Packed e2m1 rows can go to the tensor core as they are when TMA may expand them into the padded
+  // 4-bit layout of kind::mxf8f6f4 (K a multiple of 128, 32-byte aligned rows); otherwise four warps
+  // rewrite them to e4m3 in shared memory.
+  const bool direct = k % 128 == 0 && reinterpret_cast<uintptr_t>(b) % 32 == 0;
+  t.kind = direct ? KIND_MXF8 : KIND_MX48;
+  t.wgt_u4 = direct;
   t.act = a;
   t.wgt = b;
   t.m = m;
@@ -1320,25 +1357,42 @@ __global__ void wait_peer_flags_kernel(const int* flags, int ranks, int self, in
 }
 }  // namespace rk
 
+extern "C" int rk_column_parallel_maps(void* const* out_ptrs, int ranks, int64_t m, int64_t ld_total, int64_t col0,
+                                       int64_t n_local, void* maps_device, void* stream) {
+  const char* who = "rk_column_parallel_maps";
+  if (!out_ptrs || !maps_device) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (ranks < 1 || ranks > 8) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
+  if (reinterpret_cast<uintptr_t>(maps_device) % 128 != 0) return fail(RK_EINVAL, "%s: descriptors need 128-byte alignment", who);
+  if (m < 1 || n_local < 8 || col0 < 0 || col0 % 8 != 0 || n_local % 8 != 0 || ld_total % 8 != 0 || col0 + n_local > ld_total)
+    return fail(RK_EINVAL, "%s: the slab must lie inside the output and start on a multiple of 8 columns", who);
+  CUtensorMap host[8];
+  for (int g = 0; g < ranks; ++g) {
+    if (!out_ptrs[g] || !aligned16(out_ptrs[g])) return fail(RK_EINVAL, "%s: bad pointer for rank %d", who, g);
+    // this rank's slab inside rank g's [m, ld_total] buffer; chunks of 128 rows x 64 columns, clipped at the slab's edge
+    const int rc = make_map_2d(&host[g], static_cast<const __nv_bfloat16*>(out_ptrs[g]) + col0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                               n_local, m, ld_total * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != RK_OK) return rc;
+  }
+  // pageable source: the copy is staged before the call returns, `host` may go out of scope
+  cudaError_t e = cudaMemcpyAsync(maps_device, host, sizeof(CUtensorMap) * ranks, cudaMemcpyHostToDevice, as_stream(stream));
+  if (e != cudaSuccess) return fail(RK_ECUDA, "%s: %s", who, cudaGetErrorString(e));
+  return RK_OK;
+}
+
 extern "C" int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, const void* b, const float* scale_b,
                                            const void* bias, int64_t m, int64_t n_local, int64_t k,
-                                           void* const* out_ptrs, int64_t ld_total, int64_t col0, void* const* flag_ptrs,
-                                           int rank, int ranks, int epoch, void* workspace, size_t workspace_bytes,
-                                           void* stream) {
+                                           const void* maps_device, void* const* flag_ptrs, int rank, int ranks, int epoch,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
   const char* who = "rk_gemm_fp8_column_parallel";
-  if (!out_ptrs || !flag_ptrs || !scale_a || !scale_b) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!maps_device || !flag_ptrs || !scale_a || !scale_b) return fail(RK_EINVAL, "%s: null pointer", who);
   if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
   if (k < 16 || k % 16 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 16", who);
-  if (col0 < 0 || col0 % 8 != 0 || ld_total % 8 != 0 || col0 + n_local > ld_total)
-    return fail(RK_EINVAL, "%s: the slab must lie inside the output and start on a multiple of 8 columns", who);
   PeerArgs peer{};
   for (int g = 0; g < ranks; ++g) {
-    if (!out_ptrs[g] || !flag_ptrs[g] || !aligned16(out_ptrs[g])) return fail(RK_EINVAL, "%s: bad pointer for rank %d", who, g);
-    peer.out[g] = out_ptrs[g];
+    if (!flag_ptrs[g]) return fail(RK_EINVAL, "%s: bad pointer for rank %d", who, g);
     peer.flags[g] = static_cast<int*>(flag_ptrs[g]);
   }
-  peer.ld = ld_total;
-  peer.col0 = col0;
+  peer.maps = static_cast<const CUtensorMap*>(maps_device);
   peer.count = ranks;
   peer.rank = rank;
   peer.epoch = epoch;
@@ -1354,7 +1408,7 @@ extern "C" int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, 
   t.scale_act = scale_a;
   t.scale_wgt = scale_b;
   t.bias = bias;
-  t.tactic = 1 | 2;  // activations on the 128-lane axis (16-byte row-wise stores), no split-K
+  t.tactic = 1 | 2;  // activations on the 128-lane axis (row-major staged chunks), no split-K
   t.workspace = workspace;
   t.workspace_bytes = workspace_bytes;
   t.stream = as_stream(stream);

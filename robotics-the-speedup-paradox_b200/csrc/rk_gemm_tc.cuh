@@ -24,8 +24,10 @@
 // Three further kinds feed an operand that is NOT stored in the MMA's type: W4A4 (both operands
 // packed int4, widened to int8: tcgen05 has no 4-bit integer kind), the FP8 "producer" GEMM (bf16
 // activations converted to e4m3 with unit scale) and W4A8-MX (MXFP4 weights expanded to e4m3, which
-// represents every e2m1 value exactly, against MXFP8 activations).  For these, TMA lands the raw
-// bytes in a staging part of the pipeline stage and four more warps (6..9, 320 threads in all)
+// represents every e2m1 value exactly, against MXFP8 activations; used when K is not a multiple of
+// 128 - otherwise TMA itself expands the packed rows into the padded 4-bit layout that
+// kind::mxf8f6f4 reads and the plain MXFP8 kind runs).  For these, TMA lands the raw
+// bytes in a staging part of the pipeline stage and eight more warps (6..13, 448 threads in all)
 // rewrite them in shared memory into the 128-byte-swizzled K-major tile the MMA reads; the
 // converted operand never exists in global memory.  These kinds run the persistent, non-swapped
 // schedule with 128-row weight tiles.
@@ -48,7 +50,9 @@ enum GemmKind : int {
 enum XformOp : int { XF_NONE = 0, XF_INT4_TO_INT8 = 1, XF_BF16_TO_E4M3 = 2, XF_E2M1_TO_E4M3 = 3 };
 
 constexpr int kGemmThreads = 192;
-constexpr int kGemmThreadsXform = 320;  // + four operand-rewriting warps
+constexpr int kXformWarps = 8;           // rewriting is ALU-latency bound: two warps per scheduler
+constexpr int kXformThreads = kXformWarps * 32;
+constexpr int kGemmThreadsXform = kGemmThreads + kXformThreads;
 constexpr int kTileA = 128;        // rows of the A-role tile (MMA M)
 constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage (one 128-byte swizzle atom)
 constexpr int kMaxStages = 8;
@@ -83,16 +87,18 @@ struct GemmParams {
   int wait_limit;             // spin limit of every bounded wait (kWaitSpinMax unless a test shortens it)
   int debug_stall;            // test aid: the producer announces bytes that never arrive (first stage)
   int issue_block;            // issue a stage's tensor-core instructions as one straight-line block
-  // Column-parallel mode (peer_count > 0): this GPU computes columns [peer_col0, peer_col0 + n) of a
-  // wider output that every GPU of the group holds in full.  The epilogue stores its values into
-  // all of those buffers with ordinary stores through peer mappings (no TMA to or from a peer) and
-  // the last CTA to finish raises this rank's entry in every rank's flag array.
-  __nv_bfloat16* peer_out[8];  // [m, peer_ld] output of every rank, this rank's own included
-  int* peer_flags[8];          // every rank's flag array [ranks]
-  long long peer_ld;           // row stride of those outputs (elements)
-  long long peer_col0;         // first column of this rank's slab
+  int fmt_a, fmt_b;           // KIND_MXF8: element formats of the A- and B-role operands (e4m3, or e2m1 for 4-bit
+                              // weights that TMA expands to the 16-byte-padded layout of kind::mxf8f6f4)
+  int tx_deficit;             // bytes per stage that the copies report short of the shared-memory bytes written
+  // Column-parallel mode (peer_count > 0): this GPU computes one slab of columns of a wider output
+  // that every GPU of the group holds in full.  The epilogue's staged chunks leave through TMA
+  // stores into every rank's buffer (peer_maps[g] describes this rank's slab inside rank g's
+  // buffer, this rank's own included); when the last CTA's stores have completed it raises this
+  // rank's entry in every rank's flag array.  Stores only: nothing is loaded from a peer.
+  const CUtensorMap* peer_maps;  // device memory, `peer_count` descriptors (128 bytes each)
+  int* peer_flags[8];            // every rank's flag array [ranks]
   int peer_count, peer_rank, peer_epoch;
-  unsigned* peer_counter;      // device word counting the CTAs of this launch that have finished
+  unsigned* peer_counter;        // device word counting the CTAs of this launch that have finished
   int* status;                // device status word
 };
 
@@ -198,16 +204,17 @@ template <int OP, int ROWS>
 __device__ __forceinline__ void xform_tile(const uint8_t* raw, uint8_t* dst, int t) {
   if constexpr (OP == XF_INT4_TO_INT8 || OP == XF_E2M1_TO_E4M3) {
     // raw row = 64 bytes; a thread takes 16 raw bytes (32 codes) = two destination chunks
-    constexpr int kIter = ROWS * 4 / 128;
+    constexpr int kIter = ROWS * 4 / kXformThreads;
+    static_assert(ROWS * 4 % kXformThreads == 0, "rows per tile must fill the rewriting threads");
     uint4 v[kIter];
 #pragma unroll
     for (int it = 0; it < kIter; ++it) {
-      const int i = it * 128 + t;
+      const int i = it * kXformThreads + t;
       v[it] = *reinterpret_cast<const uint4*>(raw + (i >> 2) * 64 + (i & 3) * 16);
     }
 #pragma unroll
     for (int it = 0; it < kIter; ++it) {
-      const int i = it * 128 + t;
+      const int i = it * kXformThreads + t;
       const int r = i >> 2, c = i & 3;
       const uint32_t w[4] = {v[it].x, v[it].y, v[it].z, v[it].w};
       uint32_t o[8];
@@ -225,19 +232,19 @@ __device__ __forceinline__ void xform_tile(const uint8_t* raw, uint8_t* dst, int
     }
   } else if constexpr (OP == XF_BF16_TO_E4M3) {
     // raw row = 256 bytes (128 bf16); a thread takes 32 raw bytes (16 values) = one destination chunk
-    constexpr int kIter = ROWS * 8 / 128;
+    constexpr int kIter = ROWS * 8 / kXformThreads;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {  // two batches of kIter / 2 chunks keep the register count moderate
       uint4 a[kIter / 2], b[kIter / 2];
 #pragma unroll
       for (int it = 0; it < kIter / 2; ++it) {
-        const int i = (half * (kIter / 2) + it) * 128 + t;
+        const int i = (half * (kIter / 2) + it) * kXformThreads + t;
         a[it] = *reinterpret_cast<const uint4*>(raw + (i >> 3) * 256 + (i & 7) * 32);
         b[it] = *reinterpret_cast<const uint4*>(raw + (i >> 3) * 256 + (i & 7) * 32 + 16);
       }
 #pragma unroll
       for (int it = 0; it < kIter / 2; ++it) {
-        const int i = (half * (kIter / 2) + it) * 128 + t;
+        const int i = (half * (kIter / 2) + it) * kXformThreads + t;
         const int r = i >> 3, c = i & 7;
         const uint32_t w[8] = {a[it].x, a[it].y, a[it].z, a[it].w, b[it].x, b[it].y, b[it].z, b[it].w};
         uint32_t o[4];
@@ -319,6 +326,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int verdict_epi[2];
+  __shared__ volatile int verdict_xf[2];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -359,10 +367,10 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), kXform ? 5 : 1);  // the producer's announcement (+ the four rewriting warps)
+      mbar_init(smem_u32(&bar_full[s]), kXform ? 1 + kXformWarps : 1);  // the producer's announcement (+ the rewriting warps)
       mbar_init(smem_u32(&bar_empty[s]), 1);
       mbar_init(smem_u32(&bar_raw_full[s]), 1);
-      mbar_init(smem_u32(&bar_raw_empty[s]), 4);
+      mbar_init(smem_u32(&bar_raw_empty[s]), kXformWarps);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
@@ -406,7 +414,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       // a barrier probe costs a shared-memory round trip: the probe of the NEXT stage is issued before
       // this stage's copies and read one trip later, so a stage that is already free costs no wait
       uint32_t ready = 0;
-      const uint32_t tx_data = (kTileA + p.bn) * kStageKBytes;
+      const uint32_t tx_data = (kTileA + p.bn) * kStageKBytes - p.tx_deficit;
       for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
         const int row_a0 = (tile / p.tiles_b) * kTileA;
         const int row_b0 = (tile % p.tiles_b) * p.bn;
@@ -504,7 +512,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t idesc = 0;
       if constexpr (BK == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 128, p.bn);
       else if constexpr (BK == KIND_F8) idesc = umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 128, p.bn);
-      else if constexpr (BK == KIND_MXF8) idesc = umma_idesc_bs(FMT_E4M3, FMT_E4M3, 128, p.bn, 1, 0, 0);
+      else if constexpr (BK == KIND_MXF8) idesc = umma_idesc_bs(p.fmt_a, p.fmt_b, 128, p.bn, 1, 0, 0);
       else idesc = umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 128, p.bn, 0, 0, 0);
       const uint64_t adesc0 = umma_desc_k128(smem_base);
       const uint64_t bdesc0 = umma_desc_k128(smem_base + kTileA * kStageKBytes);
@@ -616,18 +624,25 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
   } else if (warp >= 6) {
-    // ------------------------------------------------------------ operand rewriting (warps 6..9, rewriting kinds only)
+    // ------------------------------------------------------------ operand rewriting (warps 6..13, rewriting kinds only)
     if constexpr (kXform) {
-      const int t = threadIdx.x - 192;  // 0..127
+      const int t = threadIdx.x - kGemmThreads;  // 0..kXformThreads-1
       Ring ring{0, 0};
       bool alive = true;
+      uint32_t xf_iter = 0;
       for (int tile = tile_first; tile < num_tiles && alive; tile += tile_step) {
         for (int i = 0; i < nkb; ++i) {
           const int s = ring.stage;
           // the raw bytes are here, and the MMAs of the stage's previous use have read the tiles that
           // are about to be overwritten
-          if (!mbar_poll_warp(smem_u32(&bar_raw_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW) ||
-              !mbar_poll_warp(smem_u32(&bar_empty[s]), ring.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY)) {
+          // (one thread waits on the barriers, parked by the hardware; a named barrier releases the rest)
+          if (t == 0) {
+            const bool got = mbar_wait_bounded(smem_u32(&bar_raw_full[s]), ring.phase, &abort_flag, p.status, RK_DEV_TIMEOUT_RAW, spin_max) &&
+                             mbar_wait_bounded(smem_u32(&bar_empty[s]), ring.phase ^ 1, &abort_flag, p.status, RK_DEV_TIMEOUT_EMPTY, spin_max);
+            verdict_xf[xf_iter & 1] = got ? 1 : 0;
+          }
+          asm volatile("bar.sync 2, %0;" ::"n"(kXformThreads) : "memory");
+          if (verdict_xf[xf_iter++ & 1] == 0) {
             alive = false;
             break;
           }
@@ -802,38 +817,6 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         continue;
       }
 
-      // ---- column-parallel mode: plain 16-byte stores into every rank's output (this rank's own too)
-      if (p.peer_count > 0) {
-        for (int c0 = 0; c0 < p.bn; c0 += 16) {
-          uint32_t r[16];
-          __syncwarp();
-          tmem_ld_16(t_acc + c0, r);
-          tc_wait_ld();
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float sv = vec_scale[c0 + j];
-            if constexpr (BK == KIND_I8) v[j] = finish_value<BK>(r[j], row_scale, sv, has_bias, vec_bias[c0 + j]);
-            else v[j] = finish_value<BK>(r[j], s_act_scalar, s_wgt_scalar, has_bias, vec_bias[c0 + j]);
-          }
-          const uint4 lo = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                      pack_bf16x2(v[6], v[7]));
-          const uint4 hi = make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]),
-                                      pack_bf16x2(v[14], v[15]));
-          const int col = row_b0 + c0;  // n is a multiple of 8: the two halves are stored or dropped whole
-          if (ra_ok && ok) {
-            const long long off = static_cast<long long>(ra) * p.peer_ld + p.peer_col0 + col;
-            for (int g = 0; g < p.peer_count; ++g) {
-              if (col + 8 <= lim_b) *reinterpret_cast<uint4*>(p.peer_out[g] + off) = lo;
-              if (col + 16 <= lim_b) *reinterpret_cast<uint4*>(p.peer_out[g] + off + 8) = hi;
-            }
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(smem_u32(&bar_acc_empty[ab]));
-        continue;
-      }
-
       // ---- finish values, stage them in shared memory, store with TMA (clipped at the matrix edge)
       // swap:     chunk = 32 activation rows x 128 channels, row-major [32][128] bf16 (8 KB)
       // non-swap: chunk = 128 activation rows x 64 channels, 128-byte-swizzled rows (16 KB)
@@ -888,8 +871,13 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         epi_bar_sync();
         if (et == 0) {
           if (ok) {
-            if (p.swap) tma_store_2d(&tm_out, smem_u32(stage), row_a0, row_b0 + cc);
-            else tma_store_2d(&tm_out, smem_u32(stage), row_b0 + cc, row_a0);
+            if (p.peer_count > 0) {
+              for (int g = 0; g < p.peer_count; ++g) tma_store_2d(p.peer_maps + g, smem_u32(stage), row_b0 + cc, row_a0);
+            } else if (p.swap) {
+              tma_store_2d(&tm_out, smem_u32(stage), row_a0, row_b0 + cc);
+            } else {
+              tma_store_2d(&tm_out, smem_u32(stage), row_b0 + cc, row_a0);
+            }
           }
           tma_store_commit();
           pending_store = 1;
@@ -897,20 +885,19 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
     if (et == 0) tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
-    if (p.peer_count > 0) {
-      // every store of this CTA is performed system-wide before the CTA counts itself as finished;
-      // the last CTA of the launch then tells every rank that this rank's slab is complete
+    if (p.peer_count > 0 && et == 0) {
+      // this CTA's bulk stores have completed, and are ordered system-wide, before the CTA counts
+      // itself as finished; the last CTA of the launch then tells every rank that the slab is there
+      tma_store_wait_all();
+      fence_proxy_async_all();
       __threadfence_system();
-      epi_bar_sync();
-      if (et == 0) {
-        const unsigned done = atomicAdd(p.peer_counter, 1u);
-        if (done == gridDim.x - 1) {
-          *p.peer_counter = 0u;
-          __threadfence_system();
-          if (!abort_flag)
-            for (int g = 0; g < p.peer_count; ++g)
-              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(p.peer_epoch) : "memory");
-        }
+      const unsigned done = atomicAdd(p.peer_counter, 1u);
+      if (done == gridDim.x - 1) {
+        *p.peer_counter = 0u;
+        __threadfence_system();
+        if (!abort_flag)
+          for (int g = 0; g < p.peer_count; ++g)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(p.peer_epoch) : "memory");
       }
     }
   }
@@ -919,7 +906,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (split_mode) {
     __syncthreads();
     cluster_sync_all();  // every CTA's partial tile is in its shared memory
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int quad = warp & 3;
       const int et = quad * 32 + lane;
       const int tile = tile_first;

@@ -41,6 +41,8 @@ struct Gemm2Params {
   int sf_kt;     // block-scaled: 512-byte scale chunks per 128-row block along K
   int sfb_blocks;  // 128-row scale blocks a weight tile touches (1 or 2)
   int issue_block; // issue a stage's tensor-core instructions as one straight-line block
+  int fmt_a, fmt_b;  // KIND_MXF8: element formats (e4m3, or e2m1 for 4-bit weights expanded by TMA)
+  int tx_deficit;    // bytes per stage and CTA that the copies report short of the shared-memory bytes written
   int tiles_m, tiles_n;  // pair tiles: 256 x bn
   long long ldo;
   const float* scale_act;
@@ -241,7 +243,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           ready = mbar_test_wait(smem_u32(&bar_empty[ring.stage]), ring.phase ^ 1);
           // both CTAs' bytes are counted on the leader's barrier; the leader announces the total
           const uint32_t full_leader = mapa_u32(smem_u32(&bar_full[s]), 0);
-          const uint32_t tx = sf_off + kC * 512 * (1 + p.sfb_blocks);  // per CTA; boxes count in full even when clipped
+          const uint32_t tx = sf_off + kC * 512 * (1 + p.sfb_blocks) - p.tx_deficit;  // per CTA; boxes count in full even when clipped
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[s]), 2u * tx, on);
           const uint32_t sa = smem_base + s * stage_bytes;
           tma_load_2d_pair(sa, &tm_a, kb * kStageKBytes, row_a0, full_leader, pol_x, on);
@@ -269,7 +271,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       uint32_t idesc;
       if constexpr (KIND == KIND_I8) idesc = umma_idesc(DFMT_S32, FMT_S8, FMT_S8, 256, p.bn);
       else if constexpr (KIND == KIND_F8) idesc = umma_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 256, p.bn);
-      else if constexpr (KIND == KIND_MXF8) idesc = umma_idesc_bs(FMT_E4M3, FMT_E4M3, 256, p.bn, 1, 0, 0);
+      else if constexpr (KIND == KIND_MXF8) idesc = umma_idesc_bs(p.fmt_a, p.fmt_b, 256, p.bn, 1, 0, 0);
       else idesc = umma_idesc_bs(FMT_E2M1_MXF4, FMT_E2M1_MXF4, 256, p.bn, 0, 0, 0);
       const uint64_t adesc0 = umma_desc_k128(smem_base);
       const uint64_t bdesc0 = umma_desc_k128(smem_base + kTileA * kStageKBytes);

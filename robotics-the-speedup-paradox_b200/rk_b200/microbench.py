@@ -105,6 +105,28 @@ class Bench:
             calls = [(lambda sp, b=b: lib.rk_gemm_mxfp8(L.ptr(a), L.ptr(sfa), L.ptr(b), L.ptr(sfb), None, L.ptr(out), m, n,
                                                         k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
             nbytes = m * k + n * k + 2 * m * n + (m + n) * k // 32
+        elif kind == "fp8p":  # bf16 activations converted inside the kernel
+            ws = L.gemm_workspace(L.OP_FP8, dev, m, n, k)
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            calls = [(lambda sp, b=b: lib.rk_gemm_fp8_producer(L.ptr(x), L.ptr(b), L.ptr(one), None, L.ptr(out), m, n, k,
+                                                               tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = 2 * m * k + n * k + 2 * m * n
+        elif kind == "w4a8":  # MXFP4 weights expanded inside the kernel, MXFP8 activations
+            ws = L.gemm_workspace(L.OP_MXFP8, dev, m, n, k)
+            bs = [b[:, :k // 2].contiguous() for b in bs]
+            sfa = torch.full((lib.rk_sf_bytes(m, k // 32),), 127, dtype=torch.uint8, device=dev)
+            sfb = torch.full((lib.rk_sf_bytes(n, k // 32),), 127, dtype=torch.uint8, device=dev)
+            calls = [(lambda sp, b=b: lib.rk_gemm_w4a8_mx(L.ptr(a), L.ptr(sfa), L.ptr(b), L.ptr(sfb), None, L.ptr(out), m, n,
+                                                          k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = m * k + n * k // 2 + 2 * m * n + (m + n) * k // 32
+        elif kind == "w4a4":  # both operands packed int4, widened inside the kernel
+            ws = L.gemm_workspace(L.OP_W8A8, dev, m, n, k)
+            a4 = a[:, :k // 2].contiguous()
+            bs = [b[:, :k // 2].contiguous() for b in bs]
+            sa, sb = torch.rand(m, device=dev), torch.rand(n, device=dev)
+            calls = [(lambda sp, b=b: lib.rk_gemm_int(L.ptr(a4), L.ptr(sa), L.ptr(b), L.ptr(sb), None, L.ptr(out), m, n, k, 4,
+                                                      tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = (m * k + n * k) // 2 + 2 * m * n
         else:
             ws = L.gemm_workspace(L.OP_NVFP4, dev, m, n, k)
             a = a[:, :k // 2].contiguous()

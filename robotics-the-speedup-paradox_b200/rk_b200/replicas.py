@@ -182,3 +182,111 @@ class ColumnParallelLinear(torch.nn.Module):
         dist.all_gather_into_tensor(gathered, flat)  # rank r's slab lands in rows [r * M, (r + 1) * M)
         # [G, M, N / G] -> [M, G * N / G]: rank order along N is the order of the weight rows
         return gathered.view(self.info.world, rows, self.slab).permute(1, 0, 2).reshape(*lead, self.out_features)
+
+
+def _pointer_table(tensors):
+    import ctypes
+
+    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def exchange_device_buffers(tensor, info: RankInfo, group=None):
+    """Every rank's `tensor` (device memory from the ordinary allocator) as a tensor usable from this
+    process: the list holds this rank's own tensor at `info.rank` and, for the others, mappings of
+    their memory opened from the CUDA inter-process handles the ranks exchange through the process
+    group.  The owner must keep its tensor alive as long as any peer uses the mapping."""
+    if info.world == 1:
+        return [tensor]
+    from torch.multiprocessing.reductions import reduce_tensor
+
+    rebuild, args = reduce_tensor(tensor)
+    handles = [None] * info.world
+    dist.all_gather_object(handles, (rebuild, args), group=group)
+    peers = []
+    for g, (fn, a) in enumerate(handles):
+        peers.append(tensor if g == info.rank else fn(*a))
+    for g, t in enumerate(peers):
+        if g != info.rank and t.device != tensor.device:
+            if not torch.cuda.can_device_access_peer(tensor.device.index, t.device.index):
+                raise RuntimeError(f"GPU {tensor.device.index} cannot address the memory of GPU {t.device.index}")
+            # a first copy between the two devices switches peer access on for this process
+            torch.empty(1, dtype=t.dtype, device=tensor.device).copy_(t.reshape(-1)[:1])
+    return peers
+
+
+class FusedColumnParallelLinear(torch.nn.Module):
+    """`ColumnParallelLinear` for the per-tensor FP8 linear with the exchange inside the GEMM.
+
+    Every rank holds two full [max_rows, N] bf16 output buffers and maps all its peers' buffers.
+    A call quantizes the (replicated) activations, runs ONE kernel that computes this rank's N / G
+    columns and stores each finished chunk into the same place of every rank's buffer
+    (`rk_gemm_fp8_column_parallel`), and then a one-warp kernel that waits until every peer's slab
+    has arrived (`rk_wait_peers`): no collective launch, no gather copy, and the transfer of early
+    tiles overlaps the computation of later ones.  The result is a view of an internal buffer and
+    stays valid until the call after the next one (the two buffers alternate)."""
+
+    def __init__(self, linear, info: RankInfo, max_rows, make_linear=None, group=None):
+        super().__init__()
+        from . import _lib
+
+        n = linear.out_features
+        if n % info.world or (n // info.world) % 8:
+            raise ValueError(f"out_features {n} does not split into slabs of a multiple of 8 columns over {info.world} ranks")
+        full = make_linear(linear) if make_linear is not None else linear
+        if type(full).__name__ != "Fp8CutlassLinear" or full.mode != "per_tensor":
+            raise TypeError("the fused exchange is built for the per-tensor FP8 linear")
+        self.info, self.out_features, self.in_features = info, n, full.in_features
+        self.slab = n // info.world
+        self.local = shard_rows(full, info.rank * self.slab, (info.rank + 1) * self.slab)
+        self.max_rows = int(max_rows)
+        device = full.packed_weight.device
+        self.device = device
+        self.buffers = [torch.zeros((self.max_rows, n), dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.flags = torch.zeros(max(info.world, 8), dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        self._peer_buffers = [exchange_device_buffers(b, info, group) for b in self.buffers]  # keeps the mappings open
+        self._peer_flags = exchange_device_buffers(self.flags, info, group)
+        self._flag_table = _pointer_table(self._peer_flags)
+        self._maps = {}  # rows -> the two descriptor arrays (one per output buffer)
+        self.epoch = 0
+        self._lib = _lib
+
+    def _descriptors(self, rows):
+        maps = self._maps.get(rows)
+        if maps is None:
+            L = self._lib
+            maps = []
+            for peers in self._peer_buffers:
+                buf = torch.empty(128 * self.info.world, dtype=torch.uint8, device=self.device)
+                code = L.load().rk_column_parallel_maps(_pointer_table(peers), self.info.world, rows, self.out_features,
+                                                        self.info.rank * self.slab, self.slab, L.ptr(buf),
+                                                        L.stream_ptr(self.device))
+                L.check(code, "rk_column_parallel_maps")
+                maps.append(buf)
+            self._maps[rows] = maps
+        return maps
+
+    def forward(self, x):
+        L = self._lib
+        lead = x.shape[:-1]
+        flat = x.reshape(-1, self.in_features)
+        rows = flat.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed the {self.max_rows} rows the exchange buffers were sized for")
+        # replicated activations: every rank derives the same per-tensor scale
+        q, scale = self.local.pack_input(flat)
+        self.epoch += 1
+        which = self.epoch & 1
+        maps = self._descriptors(rows)[which]
+        with torch.cuda.device(self.device):
+            ws = L.gemm_workspace(L.OP_FP8, self.device, rows, self.slab, self.in_features)
+            stream = L.stream_ptr(self.device)
+            code = L.load().rk_gemm_fp8_column_parallel(
+                L.ptr(q), L.ptr(scale), L.ptr(self.local.packed_weight), L.ptr(self.local.weight_scale),
+                L.ptr(self.local.bias), rows, self.slab, self.in_features, L.ptr(maps), self._flag_table, self.info.rank,
+                self.info.world, self.epoch, L.ptr(ws), ws.numel(), stream)
+            L.check(code, "rk_gemm_fp8_column_parallel")
+            code = L.load().rk_wait_peers(L.ptr(self.flags), self.info.rank, self.info.world, self.epoch, L.ptr(ws),
+                                          ws.numel(), stream)
+            L.check(code, "rk_wait_peers")
+        return self.buffers[which][:rows].view(*lead, self.out_features)
