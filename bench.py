@@ -886,7 +886,7 @@ def column_parallel_leg(info, device, reps=30):
     sharded = replicas.ColumnParallelLinear(single, info)
     fused, fused_error = None, None
     try:  # the GEMM whose epilogue stores into every rank's buffer: needs peer mappings between the GPUs
-        fused = replicas.FusedColumnParallelLinear(single, info, max_rows=m)
+        fused = replicas.FusedColumnParallelLinear(single, info, max_rows=m, transport=os.environ.get("RK_B200_CP_TRANSPORT") or None)
     except Exception as exc:  # reported, never silently replaced
         fused_error = f"{type(exc).__name__}: {exc}"
     # every rank must take the same branch below (the fused form's ranks wait on one another)
@@ -904,7 +904,35 @@ def column_parallel_leg(info, device, reps=30):
         torch.cuda.synchronize(device)
         return a.elapsed_time(b) / reps * 1e3
 
+    def graph_timed(fn, calls=2, replays=20):
+        """Device time per call from replays of a CUDA graph holding `calls` calls (no host launch cost)."""
+        stream = torch.cuda.Stream(device)
+        with torch.cuda.stream(stream):
+            for _ in range(2 * calls):
+                fn()
+            torch.cuda.synchronize(device)
+            replicas.barrier(info, device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(calls):
+                    fn()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(device)
+            replicas.barrier(info, device)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(replays):
+                graph.replay()
+            b.record()
+            torch.cuda.synchronize(device)
+        return a.elapsed_time(b) / (replays * calls) * 1e3
+
     with torch.no_grad():
+        # GEMM + exchange alone, activations quantized beforehand, replayed from CUDA graphs
+        xq, xs = single.pack_input(x)
+        us_graph_single = graph_timed(lambda: single.forward_packed(xq, xs))
+        us_graph_fused = graph_timed(lambda: fused.forward_packed(xq, xs)) if have else None
         us_sharded = timed(lambda: sharded(x))
         us_single = timed(lambda: single(x))
         a, b = sharded(x).float(), single(x).float()
@@ -917,18 +945,28 @@ def column_parallel_leg(info, device, reps=30):
             torch.cuda.synchronize(device)
             replicas.barrier(info, device)
     us_sharded, us_single = replicas.max_over_ranks([us_sharded, us_single], info, device)
+    replicas.barrier(info, device)  # nobody unmaps while a peer may still store
+    if fused is not None:
+        fused.close()
+    us_graph_single = replicas.max_over_ranks([us_graph_single], info, device)[0]
     if have:
-        us_fused, rel_fused = replicas.max_over_ranks([us_fused, rel_fused], info, device)
+        us_fused, rel_fused, us_graph_fused = replicas.max_over_ranks([us_fused, rel_fused, us_graph_fused], info, device)
     # the slab each rank sends to each of its G - 1 peers, against the measured 770 GB/s per direction
     sent = m * (n // info.world) * 2 * (info.world - 1)
     return {"op": "fp8 linear (dynamic activation scale) M=816 N=16384 K=2048", "ranks": info.world,
             "us_column_parallel_with_all_gather": us_sharded, "us_one_gpu": us_single,
             "rel_frobenius_vs_one_gpu": rel, "collective": "nccl all_gather_into_tensor of bf16 slabs",
             "us_fused_gemm_exchange": us_fused, "rel_frobenius_fused_vs_one_gpu": rel_fused,
+            "us_gemm_only_one_gpu_graph": us_graph_single, "us_gemm_only_fused_graph": us_graph_fused,
+            "timing": "us_* = eager calls including the activation quantizer and host launches; us_gemm_only_* = device time "
+                      "per call from CUDA-graph replays, activations quantized beforehand",
             "fused_unavailable": fused_error, "bytes_sent_per_rank": sent,
             "us_link_floor_at_770GBs": sent / 770e9 * 1e6,
-            "fused": "GEMM epilogue stores every chunk into all ranks' buffers over NVLink (TMA stores through peer "
-                     "mappings), flags + a one-warp wait kernel instead of a collective"}
+            "fused_transport": fused.transport if fused is not None else None,
+            "fused_multicast_error": fused.multicast_error if fused is not None else None,
+            "fused": "GEMM epilogue stores every finished chunk into all ranks' buffers (multimem.st through the NVSwitch "
+                     "multicast address, or one TMA store per peer mapping), flags + a one-warp wait kernel instead of a "
+                     "collective"}
 
 
 def workload_config(copies):

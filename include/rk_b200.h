@@ -7,7 +7,8 @@
  *   - never allocates, frees or synchronises device memory (the caller owns every buffer,
  *     including the scratch "workspace"), so calls can be captured in a CUDA graph.  Two
  *     exceptions, both test aids: rk_read_status synchronises the stream and copies one word
- *     back; rk_probe_rcp_approx_448 allocates one word, runs on the default stream and synchronises,
+ *     back; rk_probe_rcp_approx_448 allocates one word, runs on the default stream and synchronises;
+ *     and the four rk_peer_* set-up calls, whose job is to allocate and map exchange memory,
  *   - returns RK_OK (0) or a negative RK_E* code; rk_last_error_string() describes the last
  *     failure on the calling thread.
  * There is no CPU fallback: unsupported shapes are errors.
@@ -249,32 +250,51 @@ int rk_gemm_fp8_producer(const void* x, const void* b, const float* scale_b, con
  * Every GPU of a group of `ranks` holds the full [m, ld_total] bf16 output; rank r computes the
  * columns [col0, col0 + n_local) (its rows of the weight matrix) and the GEMM's epilogue stores
  * each finished 128 x 64 chunk straight into EVERY rank's buffer (TMA stores through peer
- * mappings; nothing is loaded from a peer), then raises flag[rank] = epoch in every rank's flag
- * array once all of its stores have completed.  `rk_wait_peers` is the consumer side: a one-warp
- * kernel on the caller's stream that returns once every other rank's flag has reached `epoch`, or
- * records device code 107 in the workspace status word after about a second.  Together they
- * replace GEMM -> all-gather of `ColumnParallelLinear` around `linear_forward_packed`
+ * mappings; nothing is loaded from a peer).  When all stores of the launch have completed it
+ * increments this rank's call counter (`epoch_counter`, one int32 of device memory, zero at the
+ * start) and writes the new value to flag[rank] in every rank's flag array, its own included.
+ * `rk_wait_peers` is the consumer side: a one-warp kernel on the caller's stream that counts its
+ * own calls (`wait_counter`, another int32 of device memory, zero at the start) and returns once
+ * every rank's flag - this rank's own too - has reached that count, or records device code 107 in
+ * the workspace status word after about a second.  It is launched as a programmatic dependent: it
+ * may start while the GEMM still runs, and the kernel launched after it is held until it returns.
+ * Together they replace GEMM -> all-gather of `ColumnParallelLinear` around `linear_forward_packed`
  * (src/robotics_kernels/optimizations/tensor_parallel.py:33-77 + blackwell/fp8_linear.py:66-100)
- * without a collective launch.  The caller owns the rendezvous: exchanging the buffer addresses,
- * alternating between two output buffers and growing `epoch` by one per call, so that a fast rank
- * never overwrites a buffer a slow rank still reads.
+ * without a collective launch.  Both counters live on the device, so the calls can be captured in a
+ * CUDA graph and replayed.  The caller owns the rendezvous: every rank makes the same sequence of
+ * calls (one wait per GEMM), the buffer addresses are exchanged beforehand, and consecutive calls
+ * alternate between two output buffers so that a fast rank never overwrites a buffer that a slow
+ * rank still reads (a graph therefore holds an even number of calls).
  *
- * rk_column_parallel_maps: encodes the `ranks` store descriptors of this rank's slab (one per
- * destination buffer out_ptrs[g], device pointers valid on this GPU) into `maps_device`
- * (ranks * 128 bytes of device memory, 128-byte aligned); once per set of output buffers.
- * col0, n_local, ld_total multiples of 8. */
-int rk_column_parallel_maps(void* const* out_ptrs, int ranks, int64_t m, int64_t ld_total, int64_t col0,
-                            int64_t n_local, void* maps_device, void* stream);
-/*   a e4m3 [m, k]; b e4m3 [n_local, k] (this rank's rows of the weight); scales: device pointers to
+ * The stores take one of two routes.  TMA stores through peer mappings: `out_ptrs[g]` is rank g's
+ * [m, ld_total] buffer as mapped on this GPU (this rank's own at g = rank); the slab crosses this
+ * GPU's links ranks - 1 times and the rank's own copy stays local.  Or `multimem.st` to
+ * `multicast_out`, the multicast address of the output buffers (an NVSwitch multicast object bound
+ * to every rank's buffer, e.g. from torch's symmetric memory): one copy of the slab leaves this GPU
+ * and the switch delivers it to every rank, this one included.
+ *   a e4m3 [m, k]; b e4m3 [n_local, k] (this rank's rows of the weight); scales: device pointers to
  *   one f32 each (the activation scale must be the same on every rank); bias bf16 [n_local] or NULL;
+ *   exactly one of out_ptrs / multicast_out is given; col0, n_local, ld_total multiples of 8;
  *   flag_ptrs[g]: rank g's int32 flag array [ranks] as mapped on this GPU. */
 int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, const void* b, const float* scale_b,
-                                const void* bias, int64_t m, int64_t n_local, int64_t k, const void* maps_device,
-                                void* const* flag_ptrs, int rank, int ranks, int epoch, void* workspace,
-                                size_t workspace_bytes, void* stream);
-/*   flags: this rank's own flag array [ranks]. */
-int rk_wait_peers(const void* flags, int rank, int ranks, int epoch, void* workspace, size_t workspace_bytes,
+                                const void* bias, int64_t m, int64_t n_local, int64_t k, void* const* out_ptrs,
+                                void* multicast_out, int64_t ld_total, int64_t col0, void* const* flag_ptrs, int rank,
+                                int ranks, void* epoch_counter, void* workspace, size_t workspace_bytes, void* stream);
+/*   flags: this rank's own flag array [ranks]; wait_counter: one int32 of device memory owned by the waits. */
+int rk_wait_peers(const void* flags, int ranks, void* wait_counter, void* workspace, size_t workspace_bytes,
                   void* stream);
+
+/* Exchange memory for the calls above: device memory that the other processes of the node map.
+ * rk_peer_alloc: cudaMalloc of `bytes` (zero-filled) on the current device plus its 64-byte
+ * inter-process handle.  rk_peer_open: maps another process's allocation (its handle and the
+ * index of the device that owns it) with the CURRENT device, so that kernels on the current
+ * device may store into it; fails with RK_EUNSUPPORTED when the two devices have no peer path.
+ * rk_peer_close / rk_peer_free undo the two.  These four are set-up calls: they are the only
+ * entry points that allocate or map device memory, and they synchronize the device. */
+int rk_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int rk_peer_open(const void* handle64, int owner_device, void** ptr);
+int rk_peer_close(void* ptr);
+int rk_peer_free(void* ptr);
 
 /* ---- MXFP8 ------------------------------------------------------------------------------ */
 

@@ -284,9 +284,6 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
     int s = static_cast<int>(kNumSms / tiles);
     if (s > 8) s = 8;
     if (s > kblocks / 2) s = kblocks / 2;
-    // non-swap 128-column tiles exchange 64 KB per CTA and peer through distributed shared memory:
-    // beyond four slices the exchange costs more than the shorter K loops save
-    if (rewriting && s > 4) s = 4;
     if (s > 1) pl.splits = s;
   }
   // shared memory: pipeline stages + output staging + per-tile vectors
@@ -364,6 +361,35 @@ int two_cta_mode() {
   return mode;
 }
 
+int launch_tc_peer(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const PeerMaps& maps, const GemmParams& p, const Plan& pl,
+                   cudaStream_t st) {
+  static bool configured_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& configured = configured_dev[dev & 63];
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(rk_gemm_tc_peer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024);
+    if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.grid_x, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_peer_kernel, tm_a, tm_b, maps, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "rk_gemm_tc_peer_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return RK_OK;
+}
+
 template <int KIND>
 int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out, const CUtensorMap& tm_sfa,
                const CUtensorMap& tm_sfb, const Gemm2Params& p, int smem, cudaStream_t st) {
@@ -409,9 +435,12 @@ constexpr int kU4TxDeficitPerRow = 64;
 
 // the column-parallel ("peer") mode of run_tc: see GemmParams::peer_*
 struct PeerArgs {
-  const CUtensorMap* maps;  // device memory
+  void* out[8];    // every rank's [m, ld] output as mapped on this GPU (TMA form), or all null
+  void* mc_out;    // multicast address of the full output (multimem form), or null
+  int64_t ld, col0;
   int* flags[8];
-  int count, rank, epoch;
+  int* epoch;
+  int count, rank;
 };
 
 struct TcArgs {
@@ -619,15 +648,38 @@ int run_tc(const TcArgs& a) {
   p.tx_deficit = a.wgt_u4 ? kU4TxDeficitPerRow * static_cast<int>(box_wgt) : 0;
   if (a.peer != nullptr) {
     for (int g = 0; g < a.peer->count; ++g) p.peer_flags[g] = a.peer->flags[g];
-    p.peer_maps = a.peer->maps;
+    p.peer_mc = static_cast<__nv_bfloat16*>(a.peer->mc_out);
+    p.peer_ld = a.peer->ld;
+    p.peer_col0 = a.peer->col0;
     p.peer_count = a.peer->count;
     p.peer_rank = a.peer->rank;
+    p.peer_mask = 0xFFu;
+    if (const char* e = std::getenv("RK_B200_PEER_STORES")) {  // measurement aid: "local" / "remote" halves of the exchange
+      if (e[0] == 'l') p.peer_mask = 1u << a.peer->rank;
+      else if (e[0] == 'r') p.peer_mask = 0xFFu & ~(1u << a.peer->rank);
+    }
     p.peer_epoch = a.peer->epoch;
     p.peer_counter = reinterpret_cast<unsigned*>(ws.status) + 32;  // a word of the workspace header, zero between launches
   }
   p.status = ws.status;
   const CUtensorMap& tm_a = pl.swap ? tm_wgt : tm_act;
   const CUtensorMap& tm_b = pl.swap ? tm_act : tm_wgt;
+  if (a.peer != nullptr) {
+    PeerMaps maps{};
+    for (int g = 0; g < a.peer->count; ++g) {
+      maps.m[g] = tm_act;  // placeholder for the multicast form (never dereferenced)
+      if (a.peer->mc_out != nullptr) continue;
+      // this rank's slab inside rank g's [m, ld] buffer, clipped at the slab's edges: boxes of 32 rows x 128
+      // channels when the weights take the 128-lane axis, else of 128 rows x 64 channels
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(a.peer->out[g]) + a.peer->col0;
+      rc = pl.swap ? make_map_2d(&maps.m[g], base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.peer->ld * 2, 128, 32,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE)
+                   : make_map_2d(&maps.m[g], base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.peer->ld * 2, 64, 128,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != RK_OK) return rc;
+    }
+    return launch_tc_peer(tm_a, tm_b, maps, p, pl, a.stream);
+  }
   switch (a.kind) {
     case KIND_I8: return launch_tc<KIND_I8>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_F8: return launch_tc<KIND_F8>(tm_a, tm_b, tm_out, p, pl, a.stream);
@@ -1343,59 +1395,62 @@ extern "C" int rk_attention_prefix(const void* q, const void* k_cache, const voi
 
 // ------------------------------------------------------------------ column-parallel FP8 GEMM with a fused exchange
 namespace rk {
-__global__ void wait_peer_flags_kernel(const int* flags, int ranks, int self, int epoch, int spin_max, int* status) {
+// One warp; lane g watches rank g's entry of this rank's flag array until it reaches the number of
+// this wait (the kernel keeps its own call counter, so it does not depend on anything the GEMM of
+// the same call writes except the flags themselves, this rank's own flag included).  It is
+// launched as a programmatic dependent of that GEMM: it may start while the GEMM still runs - every
+// CTA of the GEMM is resident by then - and returns when the last slab has arrived.  The kernel
+// launched after it overlaps its prologue with all of that and is released when this one ends.
+__global__ void wait_peer_flags_kernel(const int* flags, int ranks, int* wait_counter, int spin_max, int* status) {
+  pdl_launch_dependents();
   const int g = threadIdx.x;
-  if (g >= ranks || g == self) return;
+  int expected = 0;
+  if (g == 0) {
+    expected = *wait_counter + 1;
+    *wait_counter = expected;
+  }
+  expected = __shfl_sync(0xffffffffu, expected, 0);
+  if (g >= ranks) return;
   const int* flag = flags + g;
   for (int it = 0; it < spin_max; ++it) {
     int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v - epoch >= 0) return;  // epochs only grow (wrap-around safe comparison)
+    if (v - expected >= 0) return;  // counters only grow (wrap-around safe comparison)
     __nanosleep(it < 64 ? 40 : 400);
   }
-  atomicCAS(status, 0, 107);  // a peer's slab did not arrive in time
+  atomicCAS(status, 0, 107);  // a slab did not arrive in time
 }
 }  // namespace rk
 
-extern "C" int rk_column_parallel_maps(void* const* out_ptrs, int ranks, int64_t m, int64_t ld_total, int64_t col0,
-                                       int64_t n_local, void* maps_device, void* stream) {
-  const char* who = "rk_column_parallel_maps";
-  if (!out_ptrs || !maps_device) return fail(RK_EINVAL, "%s: null pointer", who);
-  if (ranks < 1 || ranks > 8) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
-  if (reinterpret_cast<uintptr_t>(maps_device) % 128 != 0) return fail(RK_EINVAL, "%s: descriptors need 128-byte alignment", who);
-  if (m < 1 || n_local < 8 || col0 < 0 || col0 % 8 != 0 || n_local % 8 != 0 || ld_total % 8 != 0 || col0 + n_local > ld_total)
-    return fail(RK_EINVAL, "%s: the slab must lie inside the output and start on a multiple of 8 columns", who);
-  CUtensorMap host[8];
-  for (int g = 0; g < ranks; ++g) {
-    if (!out_ptrs[g] || !aligned16(out_ptrs[g])) return fail(RK_EINVAL, "%s: bad pointer for rank %d", who, g);
-    // this rank's slab inside rank g's [m, ld_total] buffer; chunks of 128 rows x 64 columns, clipped at the slab's edge
-    const int rc = make_map_2d(&host[g], static_cast<const __nv_bfloat16*>(out_ptrs[g]) + col0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                               n_local, m, ld_total * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != RK_OK) return rc;
-  }
-  // pageable source: the copy is staged before the call returns, `host` may go out of scope
-  cudaError_t e = cudaMemcpyAsync(maps_device, host, sizeof(CUtensorMap) * ranks, cudaMemcpyHostToDevice, as_stream(stream));
-  if (e != cudaSuccess) return fail(RK_ECUDA, "%s: %s", who, cudaGetErrorString(e));
-  return RK_OK;
-}
-
 extern "C" int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, const void* b, const float* scale_b,
                                            const void* bias, int64_t m, int64_t n_local, int64_t k,
-                                           const void* maps_device, void* const* flag_ptrs, int rank, int ranks, int epoch,
+                                           void* const* out_ptrs, void* multicast_out, int64_t ld_total, int64_t col0,
+                                           void* const* flag_ptrs, int rank, int ranks, void* epoch_counter,
                                            void* workspace, size_t workspace_bytes, void* stream) {
   const char* who = "rk_gemm_fp8_column_parallel";
-  if (!maps_device || !flag_ptrs || !scale_a || !scale_b) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!flag_ptrs || !scale_a || !scale_b || !epoch_counter) return fail(RK_EINVAL, "%s: null pointer", who);
+  if ((out_ptrs == nullptr) == (multicast_out == nullptr))
+    return fail(RK_EINVAL, "%s: give the ranks' output pointers or the multicast address, not both", who);
   if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
   if (k < 16 || k % 16 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 16", who);
+  if (col0 < 0 || col0 % 8 != 0 || ld_total % 8 != 0 || n_local % 8 != 0 || col0 + n_local > ld_total)
+    return fail(RK_EINVAL, "%s: the slab must lie inside the output and start on a multiple of 8 columns", who);
+  if (multicast_out != nullptr && !aligned16(multicast_out)) return fail(RK_EINVAL, "%s: misaligned multicast address", who);
   PeerArgs peer{};
   for (int g = 0; g < ranks; ++g) {
     if (!flag_ptrs[g]) return fail(RK_EINVAL, "%s: bad pointer for rank %d", who, g);
     peer.flags[g] = static_cast<int*>(flag_ptrs[g]);
   }
-  peer.maps = static_cast<const CUtensorMap*>(maps_device);
+  for (int g = 0; g < ranks && out_ptrs != nullptr; ++g) {
+    if (!out_ptrs[g] || !aligned16(out_ptrs[g])) return fail(RK_EINVAL, "%s: bad output pointer for rank %d", who, g);
+    peer.out[g] = out_ptrs[g];
+  }
+  peer.mc_out = multicast_out;
+  peer.ld = ld_total;
+  peer.col0 = col0;
   peer.count = ranks;
   peer.rank = rank;
-  peer.epoch = epoch;
+  peer.epoch = static_cast<int*>(epoch_counter);
   TcArgs t{};
   t.peer = &peer;
   t.kind = KIND_F8;
@@ -1408,7 +1463,7 @@ extern "C" int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, 
   t.scale_act = scale_a;
   t.scale_wgt = scale_b;
   t.bias = bias;
-  t.tactic = 1 | 2;  // activations on the 128-lane axis (row-major staged chunks), no split-K
+  t.tactic = 2;  // no split-K: every CTA stores finished values
   t.workspace = workspace;
   t.workspace_bytes = workspace_bytes;
   t.stream = as_stream(stream);
@@ -1416,15 +1471,29 @@ extern "C" int rk_gemm_fp8_column_parallel(const void* a, const float* scale_a, 
   return run_tc(t);
 }
 
-extern "C" int rk_wait_peers(const void* flags, int rank, int ranks, int epoch, void* workspace, size_t workspace_bytes,
+extern "C" int rk_wait_peers(const void* flags, int ranks, void* wait_counter, void* workspace, size_t workspace_bytes,
                              void* stream) {
   const char* who = "rk_wait_peers";
-  if (!flags) return fail(RK_EINVAL, "%s: null pointer", who);
-  if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
+  if (!flags || !wait_counter) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (ranks < 1 || ranks > 8) return fail(RK_EINVAL, "%s: 1..8 ranks", who);
   Workspace ws;
   int rc = carve_workspace(workspace, workspace_bytes, &ws, who);
   if (rc != RK_OK) return rc;
   const int limit = g_debug_wait_limit > 0 ? g_debug_wait_limit : (1 << 21);  // with 400 ns sleeps: roughly a second
-  wait_peer_flags_kernel<<<1, 32, 0, as_stream(stream)>>>(static_cast<const int*>(flags), ranks, rank, epoch, limit, ws.status);
-  return check_launch(who);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = as_stream(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, wait_peer_flags_kernel, static_cast<const int*>(flags), ranks,
+                                     static_cast<int*>(wait_counter), limit, ws.status);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RK_ECUDA, "%s: %s", who, cudaGetErrorString(e));
+  }
+  return RK_OK;
 }

@@ -91,13 +91,20 @@ struct GemmParams {
                               // weights that TMA expands to the 16-byte-padded layout of kind::mxf8f6f4)
   int tx_deficit;             // bytes per stage that the copies report short of the shared-memory bytes written
   // Column-parallel mode (peer_count > 0): this GPU computes one slab of columns of a wider output
-  // that every GPU of the group holds in full.  The epilogue's staged chunks leave through TMA
-  // stores into every rank's buffer (peer_maps[g] describes this rank's slab inside rank g's
-  // buffer, this rank's own included); when the last CTA's stores have completed it raises this
-  // rank's entry in every rank's flag array.  Stores only: nothing is loaded from a peer.
-  const CUtensorMap* peer_maps;  // device memory, `peer_count` descriptors (128 bytes each)
+  // that every GPU of the group holds in full.  A finished, staged chunk leaves either
+  //  - through TMA stores into every rank's buffer (one descriptor per rank, kernel parameters: each
+  //    describes this rank's slab inside that rank's buffer, this rank's own included), or
+  //  - when peer_mc is set, through `multimem.st` to the multicast address of the buffers: ONE store
+  //    leaves this GPU and the NVSwitch delivers it to every rank, so the bytes on this GPU's links
+  //    do not grow with the number of ranks.
+  // When the launch's last CTA has seen all stores complete it raises this rank's entry in every
+  // rank's flag array.  Stores only: nothing is loaded from a peer.
+  __nv_bfloat16* peer_mc;        // multicast address of the [m, peer_ld] output, or null
+  long long peer_ld, peer_col0;  // row stride of the full output and first column of this slab (multicast form)
   int* peer_flags[8];            // every rank's flag array [ranks]
-  int peer_count, peer_rank, peer_epoch;
+  int peer_count, peer_rank;
+  unsigned peer_mask;            // ranks whose buffer receives the TMA stores (all of them, unless a measurement narrows it)
+  int* peer_epoch;               // this rank's call counter (device memory): the launch that finishes call e writes e
   unsigned* peer_counter;        // device word counting the CTAs of this launch that have finished
   int* status;                // device status word
 };
@@ -309,10 +316,36 @@ __device__ __forceinline__ uint32_t dsmem_ld_u32(uint32_t local_addr, uint32_t r
   return v;
 }
 
+// one 16-byte store to a multicast address: the switch writes it into every bound GPU's memory
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Multicast form of the output stores, executed by all 128 epilogue threads on a staged region.
+//   swap layout:     `rows` activation rows x 128 channels, row-major (256 bytes per row)
+//   non-swap layout: 128 activation rows x 64 channels, rows of 128 bytes in the 128-byte swizzle
+// (m0, n0) = first activation row / first channel (inside the slab) of the region.
+__device__ __forceinline__ void multicast_store_region(const GemmParams& p, const uint8_t* stage, bool swap_layout, int rows,
+                                                       int m0, int n0, int et) {
+  const int per_row = swap_layout ? 16 : 8;
+  const int shift = swap_layout ? 4 : 3;
+  for (int pc = et; pc < rows * per_row; pc += 128) {
+    const int rr = pc >> shift, ch = pc & (per_row - 1);
+    const int gm = m0 + rr, gn = n0 + ch * 8;
+    if (gm < p.m && gn < p.n) {  // the slab's width is a multiple of 8: a piece exists whole or not at all
+      const uint8_t* src = swap_layout ? stage + rr * 256 + ch * 16 : stage + rr * 128 + ((ch ^ (rr & 7)) << 4);
+      multimem_st_16(p.peer_mc + static_cast<long long>(gm) * p.peer_ld + p.peer_col0 + gn, *reinterpret_cast<const uint4*>(src));
+    }
+  }
+}
+
+// The kernel body.  The tensor maps are kernel parameters of the callers below (`peer_maps`: the
+// store descriptors of the column-parallel mode, or null): descriptors that lived in global memory
+// made every TMA store of the epilogue wait for a descriptor fetch (+9 us on a 20 us GEMM).
 template <int KIND>
-__global__ void __launch_bounds__(KindTraits<KIND>::kThreads, 1)
-rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out,
+                                             const CUtensorMap* peer_maps, const GemmParams& p) {
   using T = KindTraits<KIND>;
   constexpr int BK = T::kBase;  // the MMA kind and epilogue this kind runs on
   constexpr bool kXform = T::kXformA != XF_NONE || T::kXformB != XF_NONE;
@@ -379,6 +412,7 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     abort_flag = 0;
     fence_barrier_init();
   }
+  if (warp == 0 && lane < p.peer_count && peer_maps != nullptr) tma_prefetch_desc(peer_maps + lane);
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
@@ -677,6 +711,15 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     Ring racc{0, 0};
     uint32_t epi_iter = 0;
     int pending_store = 0;  // epilogue thread 0: a TMA store may still be reading a staging buffer
+    // one staged box to its destination: this GPU's output, or the slab's place in every rank's buffer
+    auto store_box = [&](uint32_t src, int x, int y) {
+      if (p.peer_count > 0) {
+        for (int g = 0; g < p.peer_count; ++g)
+          if ((p.peer_mask >> g) & 1u) tma_store_2d(peer_maps + g, src, x, y);
+      } else {
+        tma_store_2d(&tm_out, src, x, y);
+      }
+    };
     int obuf = 0;
     for (int tile = tile_first; tile < num_tiles; tile += tile_step, racc.advance(p.acc_bufs)) {
       const int ab = racc.stage;
@@ -807,10 +850,11 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         mbar_arrive(smem_u32(&bar_acc_empty[ab]));
         fence_proxy_async_smem();
         epi_bar_sync();
-        if (et == 0) {
+        if (p.peer_mc != nullptr) {
+          if (ok) multicast_store_region(p, stage, true, p.bn, row_b0, row_a0, et);
+        } else if (et == 0) {
           if (ok)
-            for (int r0w = 0; r0w < p.bn; r0w += 32)
-              tma_store_2d(&tm_out, smem_u32(stage + r0w * 256), row_a0, row_b0 + r0w);
+            for (int r0w = 0; r0w < p.bn; r0w += 32) store_box(smem_u32(stage + r0w * 256), row_a0, row_b0 + r0w);
           tma_store_commit();
           pending_store = 1;
         }
@@ -869,15 +913,15 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         fence_proxy_async_smem();
         epi_bar_sync();
-        if (et == 0) {
+        if (p.peer_mc != nullptr) {
           if (ok) {
-            if (p.peer_count > 0) {
-              for (int g = 0; g < p.peer_count; ++g) tma_store_2d(p.peer_maps + g, smem_u32(stage), row_b0 + cc, row_a0);
-            } else if (p.swap) {
-              tma_store_2d(&tm_out, smem_u32(stage), row_a0, row_b0 + cc);
-            } else {
-              tma_store_2d(&tm_out, smem_u32(stage), row_b0 + cc, row_a0);
-            }
+            if (p.swap) multicast_store_region(p, stage, true, min(32, p.bn - cc), row_b0 + cc, row_a0, et);
+            else multicast_store_region(p, stage, false, 128, row_a0, row_b0 + cc, et);
+          }
+        } else if (et == 0) {
+          if (ok) {
+            if (p.swap) store_box(smem_u32(stage), row_a0, row_b0 + cc);
+            else store_box(smem_u32(stage), row_b0 + cc, row_a0);
           }
           tma_store_commit();
           pending_store = 1;
@@ -885,19 +929,30 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
     if (et == 0) tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
-    if (p.peer_count > 0 && et == 0) {
-      // this CTA's bulk stores have completed, and are ordered system-wide, before the CTA counts
-      // itself as finished; the last CTA of the launch then tells every rank that the slab is there
-      tma_store_wait_all();
-      fence_proxy_async_all();
-      __threadfence_system();
-      const unsigned done = atomicAdd(p.peer_counter, 1u);
-      if (done == gridDim.x - 1) {
-        *p.peer_counter = 0u;
+    if (p.peer_count > 0) {
+      // Every store of this CTA is complete and ordered system-wide before the CTA counts itself
+      // as finished; the last CTA of the launch then tells every rank that the slab is there.
+      if (p.peer_mc != nullptr) {
+        __threadfence_system();  // each thread's own multicast stores
+        epi_bar_sync();
+      }
+      if (et == 0) {
+        if (p.peer_mc == nullptr) {
+          tma_store_wait_all();
+          fence_proxy_async_all();
+        }
         __threadfence_system();
-        if (!abort_flag)
-          for (int g = 0; g < p.peer_count; ++g)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(p.peer_epoch) : "memory");
+        const unsigned done = atomicAdd(p.peer_counter, 1u);
+        if (done == gridDim.x - 1) {
+          *p.peer_counter = 0u;
+          // the call counter lives in device memory, so a replayed CUDA graph announces a fresh value
+          const int epoch = *p.peer_epoch + 1;
+          *p.peer_epoch = epoch;
+          __threadfence_system();
+          if (!abort_flag)
+            for (int g = 0; g < p.peer_count; ++g)
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(epoch) : "memory");
+        }
       }
     }
   }
@@ -999,6 +1054,23 @@ rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(KindTraits<KIND>::kThreads, 1)
+rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
+  gemm_tc_body<KIND>(tm_a, tm_b, tm_out, nullptr, p);
+}
+
+// The per-tensor FP8 GEMM in column-parallel mode: one store descriptor per rank instead of one output map.
+struct PeerMaps {
+  CUtensorMap m[8];
+};
+__global__ void __launch_bounds__(kGemmThreads, 1)
+rk_gemm_tc_peer_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                       const __grid_constant__ PeerMaps maps, const GemmParams p) {
+  gemm_tc_body<KIND_F8>(tm_a, tm_b, tm_a, maps.m, p);
 }
 
 }  // namespace rk

@@ -50,9 +50,12 @@ SIGNATURES = {
     "rk_swiglu_quant_fp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rk_gemm_fp8": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_gemm_fp8_producer": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
-    "rk_column_parallel_maps": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _vp, _vp]),
-    "rk_gemm_fp8_column_parallel": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
-    "rk_wait_peers": (_int, [_vp, _int, _int, _int, _vp, _sz, _vp]),
+    "rk_gemm_fp8_column_parallel": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _int, _int, _vp, _vp, _sz, _vp]),
+    "rk_wait_peers": (_int, [_vp, _int, _vp, _vp, _sz, _vp]),
+    "rk_peer_alloc": (_int, [_sz, ctypes.POINTER(ctypes.c_void_p), _vp]),
+    "rk_peer_open": (_int, [_vp, _int, ctypes.POINTER(ctypes.c_void_p), ]),
+    "rk_peer_close": (_int, [_vp]),
+    "rk_peer_free": (_int, [_vp]),
     "rk_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
     "rk_swiglu_pack_nvfp4_layout": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "rk_pack_mxfp4_weight": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),

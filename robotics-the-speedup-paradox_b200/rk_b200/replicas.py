@@ -184,34 +184,114 @@ class ColumnParallelLinear(torch.nn.Module):
         return gathered.view(self.info.world, rows, self.slab).permute(1, 0, 2).reshape(*lead, self.out_features)
 
 
-def _pointer_table(tensors):
+class _DevicePointer:
+    """Lets torch view device memory that this module owns (`torch.as_tensor` reads the interface)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class ExchangeMemory:
+    """One block of device memory per rank that every other rank of the node maps.
+
+    `rk_peer_alloc` allocates the block and returns its inter-process handle; the handles travel
+    through the process group; `rk_peer_open` maps every peer's block with THIS rank's device
+    current, which is what makes the mapping usable by kernels running here.  `pointers[g]` is
+    rank g's block as seen from this process (this rank's own allocation at `info.rank`)."""
+
+    def __init__(self, nbytes, device, info: RankInfo, group=None):
+        import ctypes
+
+        from . import _lib
+
+        self._lib, self.info, self.device, self.nbytes = _lib, info, device, int(nbytes)
+        self._opened = []
+        lib = _lib.load()
+        ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(device):
+            _lib.check(lib.rk_peer_alloc(self.nbytes, ctypes.byref(ptr), handle), "rk_peer_alloc")
+        self.ptr = ptr.value
+        self.pointers = [self.ptr]
+        if info.world > 1:
+            gathered = [None] * info.world
+            dist.all_gather_object(gathered, (bytes(handle), device.index), group=group)
+            self.pointers = []
+            with torch.cuda.device(device):
+                for g, (peer_handle, owner) in enumerate(gathered):
+                    if g == info.rank:
+                        self.pointers.append(self.ptr)
+                        continue
+                    mapped = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(peer_handle)
+                    _lib.check(lib.rk_peer_open(buf, owner, ctypes.byref(mapped)), "rk_peer_open")
+                    self._opened.append(mapped.value)
+                    self.pointers.append(mapped.value)
+        self._view = torch.as_tensor(_DevicePointer(self.ptr, self.nbytes), device=device)
+
+    def tensor(self, offset, shape, dtype):
+        """A tensor over [offset, offset + size) of this rank's own block."""
+        count = 1
+        for d in shape:
+            count *= d
+        nbytes = count * torch.empty(0, dtype=dtype).element_size()
+        return self._view[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def close(self):
+        """Unmaps the peers' blocks and frees this rank's; every rank must have stopped using them."""
+        lib = self._lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._opened:
+                lib.rk_peer_close(p)
+            self._opened = []
+            if self.ptr:
+                self._view = None
+                lib.rk_peer_free(self.ptr)
+                self.ptr = 0
+
+
+class SymmetricExchangeMemory:
+    """The same block per rank as `ExchangeMemory`, from torch's symmetric-memory allocator, which also
+    binds the ranks' blocks to one NVSwitch multicast object: `multicast_ptr` is an address whose
+    stores (`multimem.st`) the switch delivers to every rank's block.  `pointers[g]` are the plain
+    peer mappings.  Raises when the allocator, the rendezvous or the multicast binding is missing."""
+
+    def __init__(self, nbytes, device, info: RankInfo, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.info, self.device, self.nbytes = info, device, int(nbytes)
+        group = group if group is not None else dist.group.WORLD
+        with torch.cuda.device(device):
+            self._view = symm.empty((self.nbytes,), dtype=torch.uint8, device=device)
+            self._handle = symm.rendezvous(self._view, group.group_name)
+            self._view.zero_()
+            torch.cuda.synchronize(device)
+        self.pointers = [int(p) for p in self._handle.buffer_ptrs]
+        self.multicast_ptr = int(getattr(self._handle, "multicast_ptr", 0) or 0)
+        self.ptr = self.pointers[info.rank]
+        if self.multicast_ptr == 0:
+            raise RuntimeError("no multicast object behind the symmetric memory of this group")
+        dist.barrier(group=group, device_ids=[device.index])  # every block is zero before anyone stores into it
+
+    tensor = ExchangeMemory.tensor
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        self._view, self._handle = None, None
+
+
+def _pointer_array(values):
     import ctypes
 
-    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    return (ctypes.c_void_p * len(values))(*values)
 
 
-def exchange_device_buffers(tensor, info: RankInfo, group=None):
-    """Every rank's `tensor` (device memory from the ordinary allocator) as a tensor usable from this
-    process: the list holds this rank's own tensor at `info.rank` and, for the others, mappings of
-    their memory opened from the CUDA inter-process handles the ranks exchange through the process
-    group.  The owner must keep its tensor alive as long as any peer uses the mapping."""
+def _all_ranks_agree(ok, info: RankInfo, group=None):
     if info.world == 1:
-        return [tensor]
-    from torch.multiprocessing.reductions import reduce_tensor
-
-    rebuild, args = reduce_tensor(tensor)
-    handles = [None] * info.world
-    dist.all_gather_object(handles, (rebuild, args), group=group)
-    peers = []
-    for g, (fn, a) in enumerate(handles):
-        peers.append(tensor if g == info.rank else fn(*a))
-    for g, t in enumerate(peers):
-        if g != info.rank and t.device != tensor.device:
-            if not torch.cuda.can_device_access_peer(tensor.device.index, t.device.index):
-                raise RuntimeError(f"GPU {tensor.device.index} cannot address the memory of GPU {t.device.index}")
-            # a first copy between the two devices switches peer access on for this process
-            torch.empty(1, dtype=t.dtype, device=tensor.device).copy_(t.reshape(-1)[:1])
-    return peers
+        return ok
+    votes = [None] * info.world
+    dist.all_gather_object(votes, bool(ok), group=group)
+    return all(votes)
 
 
 class FusedColumnParallelLinear(torch.nn.Module):
@@ -222,16 +302,30 @@ class FusedColumnParallelLinear(torch.nn.Module):
     columns and stores each finished chunk into the same place of every rank's buffer
     (`rk_gemm_fp8_column_parallel`), and then a one-warp kernel that waits until every peer's slab
     has arrived (`rk_wait_peers`): no collective launch, no gather copy, and the transfer of early
-    tiles overlaps the computation of later ones.  The result is a view of an internal buffer and
-    stays valid until the call after the next one (the two buffers alternate)."""
+    tiles overlaps the computation of later ones.
 
-    def __init__(self, linear, info: RankInfo, max_rows, make_linear=None, group=None):
+    `transport`: "peer" (the default) - CUDA inter-process mappings and one TMA store per
+    destination: the rank's own copy stays on its GPU and (G - 1) / G of the output crosses the
+    links in each direction; "multicast" - the buffers come from torch's symmetric memory and the
+    kernel stores to their NVSwitch multicast address: one copy of the slab leaves each GPU, but
+    every GPU then RECEIVES the whole output over its links, its own slab included.  An all-gather
+    is bound by what each GPU receives, so multicast does not help it (measured slower on two GPUs).
+
+    The result is a view of an internal buffer and stays valid until the call after the next one
+    (the two buffers alternate).  Every rank must make the same sequence of calls; `close()` (after
+    a barrier of the ranks) releases the memory.  The call counter that the ranks compare lives in
+    device memory, so the calls may be captured in a CUDA graph - with an even number of calls per
+    graph, because the buffer a call writes is fixed at capture."""
+
+    def __init__(self, linear, info: RankInfo, max_rows, make_linear=None, group=None, transport=None):
         super().__init__()
         from . import _lib
 
         n = linear.out_features
         if n % info.world or (n // info.world) % 8:
             raise ValueError(f"out_features {n} does not split into slabs of a multiple of 8 columns over {info.world} ranks")
+        if transport not in (None, "multicast", "peer"):
+            raise ValueError("transport must be 'peer' (also None) or 'multicast'")
         full = make_linear(linear) if make_linear is not None else linear
         if type(full).__name__ != "Fp8CutlassLinear" or full.mode != "per_tensor":
             raise TypeError("the fused exchange is built for the per-tensor FP8 linear")
@@ -241,52 +335,66 @@ class FusedColumnParallelLinear(torch.nn.Module):
         self.max_rows = int(max_rows)
         device = full.packed_weight.device
         self.device = device
-        self.buffers = [torch.zeros((self.max_rows, n), dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self.flags = torch.zeros(max(info.world, 8), dtype=torch.int32, device=device)
-        torch.cuda.synchronize(device)
-        self._peer_buffers = [exchange_device_buffers(b, info, group) for b in self.buffers]  # keeps the mappings open
-        self._peer_flags = exchange_device_buffers(self.flags, info, group)
-        self._flag_table = _pointer_table(self._peer_flags)
-        self._maps = {}  # rows -> the two descriptor arrays (one per output buffer)
-        self.epoch = 0
+        # one block: two output buffers, then the flag array and this rank's call counter
+        self._buffer_bytes = (self.max_rows * n * 2 + 255) // 256 * 256
+        nbytes = 2 * self._buffer_bytes + 256
+        self.memory, self.transport, self.multicast_error = None, "peer", None
+        if transport == "multicast" and info.world > 1:
+            memory = None
+            try:
+                memory = SymmetricExchangeMemory(nbytes, device, info, group)
+            except Exception as exc:  # reported; the peer transport takes over unless multicast was demanded
+                self.multicast_error = f"{type(exc).__name__}: {exc}"
+            if _all_ranks_agree(memory is not None, info, group):
+                self.memory, self.transport = memory, "multicast"
+            elif transport == "multicast":
+                raise RuntimeError(f"multicast transport unavailable: {self.multicast_error or 'another rank failed'}")
+        if self.memory is None:
+            self.memory = ExchangeMemory(nbytes, device, info, group)
+        self.buffers = [self.memory.tensor(i * self._buffer_bytes, (self.max_rows, n), torch.bfloat16) for i in range(2)]
+        self.flags = self.memory.tensor(2 * self._buffer_bytes, (8,), torch.int32)
+        self.epoch_counter = self.memory.tensor(2 * self._buffer_bytes + 64, (1,), torch.int32)  # this rank's calls, on the device
+        self.wait_counter = self.memory.tensor(2 * self._buffer_bytes + 128, (1,), torch.int32)  # the wait kernel's own count
+        self._flag_table = _pointer_array([p + 2 * self._buffer_bytes for p in self.memory.pointers])
+        self._out_tables = [_pointer_array([p + which * self._buffer_bytes for p in self.memory.pointers]) for which in range(2)]
+        self.calls = 0  # host mirror: only its parity (which buffer) matters
         self._lib = _lib
 
-    def _descriptors(self, rows):
-        maps = self._maps.get(rows)
-        if maps is None:
-            L = self._lib
-            maps = []
-            for peers in self._peer_buffers:
-                buf = torch.empty(128 * self.info.world, dtype=torch.uint8, device=self.device)
-                code = L.load().rk_column_parallel_maps(_pointer_table(peers), self.info.world, rows, self.out_features,
-                                                        self.info.rank * self.slab, self.slab, L.ptr(buf),
-                                                        L.stream_ptr(self.device))
-                L.check(code, "rk_column_parallel_maps")
-                maps.append(buf)
-            self._maps[rows] = maps
-        return maps
-
     def forward(self, x):
-        L = self._lib
         lead = x.shape[:-1]
         flat = x.reshape(-1, self.in_features)
-        rows = flat.shape[0]
-        if rows > self.max_rows:
-            raise ValueError(f"{rows} rows exceed the {self.max_rows} rows the exchange buffers were sized for")
+        if flat.shape[0] > self.max_rows:
+            raise ValueError(f"{flat.shape[0]} rows exceed the {self.max_rows} rows the exchange buffers were sized for")
         # replicated activations: every rank derives the same per-tensor scale
         q, scale = self.local.pack_input(flat)
-        self.epoch += 1
-        which = self.epoch & 1
-        maps = self._descriptors(rows)[which]
+        return self.forward_packed(q, scale).view(*lead, self.out_features)
+
+    def forward_packed(self, q, scale):
+        """e4m3 activations [rows, K] and their scale (the same on every rank) -> [rows, N] on every rank."""
+        L = self._lib
+        rows = q.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed the {self.max_rows} rows the exchange buffers were sized for")
+        self.calls += 1
+        which = self.calls & 1
+        outs, multicast = None, None
+        if self.transport == "multicast":
+            multicast = self.memory.multicast_ptr + which * self._buffer_bytes
+        else:
+            outs = self._out_tables[which]
         with torch.cuda.device(self.device):
             ws = L.gemm_workspace(L.OP_FP8, self.device, rows, self.slab, self.in_features)
             stream = L.stream_ptr(self.device)
             code = L.load().rk_gemm_fp8_column_parallel(
                 L.ptr(q), L.ptr(scale), L.ptr(self.local.packed_weight), L.ptr(self.local.weight_scale),
-                L.ptr(self.local.bias), rows, self.slab, self.in_features, L.ptr(maps), self._flag_table, self.info.rank,
-                self.info.world, self.epoch, L.ptr(ws), ws.numel(), stream)
+                L.ptr(self.local.bias), rows, self.slab, self.in_features, outs, multicast, self.out_features,
+                self.info.rank * self.slab, self._flag_table, self.info.rank, self.info.world, L.ptr(self.epoch_counter),
+                L.ptr(ws), ws.numel(), stream)
             L.check(code, "rk_gemm_fp8_column_parallel")
-            code = L.load().rk_wait_peers(L.ptr(self.flags), self.info.rank, self.info.world, self.epoch, L.ptr(ws),
-                                          ws.numel(), stream)
+            code = L.load().rk_wait_peers(L.ptr(self.flags), self.info.world, L.ptr(self.wait_counter), L.ptr(ws), ws.numel(), stream)
             L.check(code, "rk_wait_peers")
-        return self.buffers[which][:rows].view(*lead, self.out_features)
+        return self.buffers[which][:rows]
+
+    def close(self):
+        self.buffers, self.flags, self.epoch_counter, self.wait_counter = [], None, None, None
+        self.memory.close()

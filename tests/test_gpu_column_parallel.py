@@ -27,8 +27,8 @@ def _table(tensors):
     return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
 
 
-# slab widths that are and are not multiples of the 64-column store chunk; rows not a multiple of 128
-@pytest.mark.parametrize("m,slab,k,ranks", [(300, 256, 448, 2), (816, 160, 512, 2), (50, 64, 128, 4), (130, 2048, 2048, 2)])
+# slab widths that are and are not multiples of the store chunk; row counts on both sides of the swap threshold (1024)
+@pytest.mark.parametrize("m,slab,k,ranks", [(300, 256, 448, 2), (816, 160, 512, 2), (50, 64, 128, 4), (130, 2048, 2048, 2), (1300, 320, 256, 2)])
 def test_two_emulated_ranks_fill_every_buffer(H, m, slab, k, ranks):
     from rk_b200 import fp8_linear as P8
 
@@ -42,21 +42,19 @@ def test_two_emulated_ranks_fill_every_buffer(H, m, slab, k, ranks):
 
     outs = [torch.full((m + 1, n), 3.0, dtype=torch.bfloat16, device=H.DEVICE) for _ in range(ranks)]
     flags = [torch.zeros(8, dtype=torch.int32, device=H.DEVICE) for _ in range(ranks)]
+    counters = [torch.zeros(1, dtype=torch.int32, device=H.DEVICE) for _ in range(ranks)]  # one call counter per rank
+    waits = [torch.zeros(1, dtype=torch.int32, device=H.DEVICE) for _ in range(ranks)]  # and one per rank's wait kernel
     ws = _lib.gemm_workspace(_lib.OP_FP8, H.DEVICE, m, slab, k)
     stream = H.stream()
-    maps = []
-    for r in range(ranks):
-        buf = torch.empty(128 * ranks, dtype=torch.uint8, device=H.DEVICE)
-        H.call("rk_column_parallel_maps", _table(outs), ranks, m, n, r * slab, slab, _lib.ptr(buf), stream)
-        maps.append(buf)
     for epoch in (1, 2):
         for r in range(ranks):
             w_r = wq[r * slab:(r + 1) * slab].contiguous()
             b_r = bd[r * slab:(r + 1) * slab].contiguous()
             H.call("rk_gemm_fp8_column_parallel", _lib.ptr(xq), _lib.ptr(xscale), _lib.ptr(w_r), _lib.ptr(wscale), _lib.ptr(b_r),
-                   m, slab, k, _lib.ptr(maps[r]), _table(flags), r, ranks, epoch, _lib.ptr(ws), ws.numel(), stream)
+                   m, slab, k, _table(outs), None, n, r * slab, _table(flags), r, ranks, _lib.ptr(counters[r]), _lib.ptr(ws),
+                   ws.numel(), stream)
         for r in range(ranks):
-            H.call("rk_wait_peers", _lib.ptr(flags[r]), r, ranks, epoch, _lib.ptr(ws), ws.numel(), stream)
+            H.call("rk_wait_peers", _lib.ptr(flags[r]), ranks, _lib.ptr(waits[r]), _lib.ptr(ws), ws.numel(), stream)
         assert _lib.read_status(ws) == 0
         for r in range(ranks):
             assert flags[r][:ranks].tolist() == [epoch] * ranks
@@ -68,19 +66,21 @@ def test_two_emulated_ranks_fill_every_buffer(H, m, slab, k, ranks):
 def test_wait_gives_up_on_a_flag_nothing_sets(H):
     lib = _lib.load()
     flags = torch.zeros(8, dtype=torch.int32, device=H.DEVICE)
+    counter = torch.full((1,), 4, dtype=torch.int32, device=H.DEVICE)  # four waits so far: this one expects 5
     ws = torch.zeros(_lib.WORKSPACE_HEADER, dtype=torch.uint8, device=H.DEVICE)
+    flags[0] = 5  # this rank's own slab is there, the peer's never arrives
     assert lib.rk_debug_wait_expiry(1, 4096) == _lib.RK_OK
     try:
-        assert lib.rk_wait_peers(_lib.ptr(flags), 0, 2, 5, _lib.ptr(ws), ws.numel(), H.stream()) == _lib.RK_OK
+        assert lib.rk_wait_peers(_lib.ptr(flags), 2, _lib.ptr(counter), _lib.ptr(ws), ws.numel(), H.stream()) == _lib.RK_OK
         code = ctypes.c_int(0)
         rc = lib.rk_read_status(_lib.ptr(ws), ctypes.byref(code), H.stream())
     finally:
         assert lib.rk_debug_wait_expiry(0, 0) == _lib.RK_OK
-    assert rc == _lib.RK_EDEVICE and code.value == 107
-    # an epoch that has been reached returns without a status
-    flags[1] = 5
-    assert lib.rk_wait_peers(_lib.ptr(flags), 0, 2, 5, _lib.ptr(ws), ws.numel(), H.stream()) == _lib.RK_OK
-    assert _lib.read_status(ws) == 0
+    assert rc == _lib.RK_EDEVICE and code.value == 107 and counter.item() == 5
+    # flags that have reached the next count return without a status
+    flags[:2] = 6
+    assert lib.rk_wait_peers(_lib.ptr(flags), 2, _lib.ptr(counter), _lib.ptr(ws), ws.numel(), H.stream()) == _lib.RK_OK
+    assert _lib.read_status(ws) == 0 and counter.item() == 6
 
 
 def test_module_with_one_rank_equals_the_plain_linear(H):
@@ -102,3 +102,4 @@ def test_module_with_one_rank_equals_the_plain_linear(H):
         assert float((got - want).norm() / want.norm()) < 1e-3
     with pytest.raises(ValueError):
         fused(H.randn_bf16((300, k), 1.0, 94).to(H.DEVICE))
+    fused.close()

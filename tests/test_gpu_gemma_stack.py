@@ -68,6 +68,49 @@ def test_expert_loop_w8a8_linears_match_oracle_and_graph_replays(H):
     assert rel < 0.1
 
 
+def test_full_size_expert_every_linear_matches_oracle(H):
+    """The benchmark's own expert - 18 layers, width 1024, MLP 4096, 8 heads of 256 over one KV head,
+    8 environments x 50 action tokens against an 816-token prefix - for one denoising step: each of
+    the 18 x 6 hooked W8A8 linears (q, k, v, o, gate, up) is held to the oracle bit for bit on the
+    activations it actually saw (M = 400; N = 256 ... 4096; K = 1024 or 2048)."""
+    from rk_b200.gemma_stack import ActionExpert, expert_scope
+    from rk_b200.integer import IntegerLinear
+    from rk_b200.optimizations import quantize_linears
+
+    expert = ActionExpert(steps=1).init_random(2).to(H.DEVICE).eval()
+    cfg = expert.cfg
+    assert (cfg.depth, cfg.width, cfg.mlp_dim, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim) == (18, 1024, 4096, 8, 1, 256)
+    envs, prefix = 8, 816
+    gen = torch.Generator().manual_seed(5)
+    noise = torch.randn(envs, expert.chunk, expert.action_dim, generator=gen).to(H.DEVICE)
+    shape = (cfg.depth, envs, cfg.num_kv_heads, prefix, cfg.head_dim)
+    pk = torch.randn(shape, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    pv = torch.randn(shape, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    with torch.no_grad():
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope) as report:
+            assert len(report["modules"]) == cfg.depth * 7 and not report["skipped"]
+            seen = {}
+            hooks = [m.register_forward_hook(lambda mod, args, out, name=n: seen.__setitem__(name, (args[0], out)))
+                     for n, m in expert.named_modules() if isinstance(m, IntegerLinear)]
+            out = expert(noise, pk, pv)
+            for hook in hooks:
+                hook.remove()
+            torch.cuda.synchronize()
+            assert torch.isfinite(out).all()
+            checked = 0
+            for name, (x, y) in seen.items():
+                if getattr(x, "_robotics_packed_input", False):
+                    continue
+                layer = expert.get_submodule(name)
+                xs = H.to_np(x).reshape(-1, layer.in_features)
+                assert xs.shape[0] == envs * expert.chunk
+                a, sa, _ = OI.quantize_rows(xs, 8)
+                want, _ = OI.gemm(a, sa, layer.packed_weight.cpu().numpy(), layer.weight_scale.cpu().numpy(), None, 8)
+                assert np.array_equal(H.bits(y).reshape(-1, layer.out_features), F.bf16_bits(want)), name
+                checked += 1
+            assert checked == cfg.depth * 6
+
+
 def test_grouped_projections_and_fused_norm_quantizer_keep_the_loop_output(H):
     """Grouping q/k/v and gate/up into one GEMM each is exact; fusing adaRMSNorm + modulation + row
     quantizer into one kernel changes only the rounding of the normalized activations."""
@@ -226,3 +269,51 @@ def test_prefix_stack_nvfp4_close_to_bf16(H):
             rel = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
             assert rel < tol, (precision, rel)
             assert kv[0][0].shape == (1, 1, 816, 128)
+
+
+def test_full_width_prefix_layers_nvfp4_every_linear_matches_oracle(H):
+    """Two layers of the benchmark's prefix model at its real widths (width 2048, MLP 16384, 8 heads of
+    256 over one KV head; 816 tokens) with every linear in NVFP4 + the fp32 per-tensor scale on weights
+    and activations: each of the 14 linears - shapes (816, 2048, 2048), (816, 256, 2048),
+    (816, 16384, 2048) and (816, 2048, 16384) - is held to the oracle on the activations it saw: the
+    per-tensor scale and the packed codes / scale factors bit for bit, the product within 1e-2."""
+    from oracle import blockscale as OB
+    from oracle import fp8 as OF
+    from rk_b200.fp4_linear import Fp4CutlassLinear
+    from rk_b200.gemma_stack import GemmaConfig, GemmaStack, prefix_scope
+    from rk_b200.optimizations import quantize_linears
+
+    cfg = GemmaConfig(width=2048, mlp_dim=16384, depth=2, num_heads=8, num_kv_heads=1, head_dim=256)
+    model = GemmaStack(cfg).to(torch.bfloat16).init_random(4).to(H.DEVICE).eval()
+    x = H.randn_bf16((1, 816, 2048), 1.0, 6).to(H.DEVICE)
+    pos = torch.arange(816, device=H.DEVICE)[None]
+    with torch.no_grad():
+        with quantize_linears(model, "fp4", scopes=("text",), selector=prefix_scope, fp4_global_scale=True) as report:
+            assert len(report["modules"]) == 14
+            seen = {}
+            hooks = [m.register_forward_hook(lambda mod, args, out, name=n: seen.__setitem__(name, (args[0], out)))
+                     for n, m in model.named_modules() if isinstance(m, Fp4CutlassLinear)]
+            out, _ = model(x, pos)
+            for hook in hooks:
+                hook.remove()
+            torch.cuda.synchronize()
+            assert torch.isfinite(out).all() and len(seen) == 14
+            shapes = set()
+            for name, (a, y) in seen.items():
+                layer = model.get_submodule(name)
+                flat = a.reshape(-1, layer.in_features)
+                xs = H.to_np(flat)
+                shapes.add((xs.shape[0], layer.out_features, layer.in_features))
+                ga = OF.tensor_scale(xs, np.float32(6.0 * 448.0))
+                pa, sa, swa = OB.pack_nvfp4(xs, ga)
+                q, sf, g = layer.pack_input(flat)
+                assert g.item() == ga, name
+                assert np.array_equal(q.cpu().numpy(), pa) and np.array_equal(sf.cpu().numpy(), swa), name
+                # the weight codes were packed by the kernel under test: unswizzle its scale factors for the oracle product
+                gw = float(layer.weight_global_scale.item())
+                sw = OB.unswizzle_sf(layer.weight_scale.cpu().numpy(), layer.out_features, layer.in_features // 16)
+                _, want = OB.gemm_dequantized(OB.dequant_nvfp4(pa, sa, ga),
+                                              OB.dequant_nvfp4(layer.packed_weight.cpu().numpy(), sw, gw))
+                got = H.to_np(y.reshape(-1, layer.out_features))
+                assert H.rel_frobenius(got, want) < 1e-2, name
+            assert shapes == {(816, 2048, 2048), (816, 256, 2048), (816, 16384, 2048), (816, 2048, 16384)}
