@@ -258,9 +258,10 @@ int rk_gemm_fp8_producer(const void* x, const void* b, const float* scale_b, con
  * every rank's flag - this rank's own too - has reached that count, or records device code 107 in
  * the workspace status word after about a second.  It is launched as a programmatic dependent: it
  * may start while the GEMM still runs, and the kernel launched after it is held until it returns.
- * Together they replace GEMM -> all-gather of `ColumnParallelLinear` around `linear_forward_packed`
- * (src/robotics_kernels/optimizations/tensor_parallel.py:33-77 + blackwell/fp8_linear.py:66-100)
- * without a collective launch.  Both counters live on the device, so the calls can be captured in a
+ * Together they stand in for `linear_forward_packed` (blackwell/fp8_linear.py:66-100) followed by an
+ * all-gather of the ranks' slabs, without a collective launch (the reference runs its linears on
+ * one GPU; the split along the output channels is the multi-GPU mode this library adds for the
+ * widest projections).  Both counters live on the device, so the calls can be captured in a
  * CUDA graph and replayed.  The caller owns the rendezvous: every rank makes the same sequence of
  * calls (one wait per GEMM), the buffer addresses are exchanged beforehand, and consecutive calls
  * alternate between two output buffers so that a fast rank never overwrites a buffer that a slow
@@ -341,6 +342,21 @@ int rk_nvfp4_global_scale(const void* x, int64_t elements, float* scale_out, voi
 int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, const void* b, const void* sfb,
                   const float* gb, const void* bias, void* out, int64_t m, int64_t n, int64_t k, int tactic,
                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* The gate/up projection of a SwiGLU MLP in NVFP4 with the activation fused into the GEMM: the
+ * weight rows are stored in the 64-row interleaved order (of every 128 rows the first 64 belong to
+ * `up`, the next 64 to the matching `gate` channels), so one output tile holds both factors of 64
+ * channels.  The epilogue forms silu(gate) * up - the two-launch path's arithmetic step for step:
+ * bf16(alpha * acc), SwiGLU in bf16 steps - and packs it to NVFP4: the [m, n] bf16 intermediate
+ * never exists.  Runs on CTA pairs (`tcgen05.mma.cta_group::2`) for every m.  The computation of
+ * `Sm100BlockScaledPersistentDenseGemmSwigluFusionKernel` (blackwell/cute_fp4_swiglu_kernel.py:75-2629;
+ * wrapper `cutlass_swiglu_fp4_packed`, blackwell/cute_fp4_swiglu.py:186-282) without its multicast
+ * loads, and of `linear_forward_swiglu_gemm_bf16`'s producer half (blackwell/csrc/fp4_cutlass_linear.cu:997-1143).
+ *   a, sfa, ga / b_interleaved [n, k/2], sfb, gb as for rk_gemm_nvfp4; n = 2 * intermediate size, n % 128 == 0;
+ *   q_out uint8 [m, n/4]; sf_out rk_sf_bytes(m, n/32) bytes (every byte of the 128-row blocks is written). */
+int rk_gemm_nvfp4_swiglu(const void* a, const void* sfa, const float* ga, const void* b_interleaved, const void* sfb,
+                         const float* gb, void* q_out, void* sf_out, int64_t m, int64_t n, int64_t k, int tactic,
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* The same with a choice of gate/up layout: interleaved != 0 reads blocks of 128 columns holding 64 up
  * values followed by their 64 gate values (the layout of a fused gate/up projection,

@@ -407,7 +407,7 @@ int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorM
   const int clusters = tiles < kNumSms / 2 ? tiles : kNumSms / 2;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(2 * clusters, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads);
+  cfg.blockDim = dim3(p.sw_q != nullptr ? kGemm2ThreadsSwiglu : kGemmThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -446,6 +446,8 @@ struct PeerArgs {
 struct TcArgs {
   const PeerArgs* peer = nullptr;
   bool wgt_u4 = false;   // KIND_MXF8 with packed e2m1 weights [n, k / 2]: TMA expands them into the MMA's padded layout
+  void* swiglu_q = nullptr;   // KIND_NVF4, interleaved gate/up weights: the epilogue packs silu(gate) * up to NVFP4
+  void* swiglu_sf = nullptr;  //   (codes and swizzled scale factors) instead of writing bf16
   int kind;
   const void* act;       // [m, k_bytes] bytes
   const void* wgt;       // [n, k_bytes] bytes
@@ -467,7 +469,7 @@ struct TcArgs {
 };
 
 int run_tc(const TcArgs& a) {
-  if (!a.act || !a.wgt || (!a.out && !a.acc_out && !a.peer)) return fail(RK_EINVAL, "%s: null pointer", a.who);
+  if (!a.act || !a.wgt || (!a.out && !a.acc_out && !a.peer && !a.swiglu_q)) return fail(RK_EINVAL, "%s: null pointer", a.who);
   if (a.m < 1 || a.n < 1 || a.k_bytes < 16) return fail(RK_EINVAL, "%s: empty problem", a.who);
   if (a.m > (1 << 24) || a.n > (1 << 24) || a.k_bytes > (1 << 24)) return fail(RK_EUNSUPPORTED, "%s: dimension too large", a.who);
   if (a.n % 8 != 0) return fail(RK_EINVAL, "%s: n must be a multiple of 8", a.who);
@@ -476,7 +478,7 @@ int run_tc(const TcArgs& a) {
   if (rc != RK_OK) return rc;
   const int kblocks = static_cast<int>((a.k_bytes + kStageKBytes - 1) / kStageKBytes);
   const bool block_scaled = a.kind == KIND_MXF8 || a.kind == KIND_NVF4;
-  const bool two_cta_kind = a.acc_out == nullptr && a.out != nullptr && a.kind <= KIND_NVF4 && a.peer == nullptr;
+  const bool two_cta_kind = a.acc_out == nullptr && (a.out != nullptr || a.swiglu_q != nullptr) && a.kind <= KIND_NVF4 && a.peer == nullptr;
   const int mode = two_cta_mode();
   // CTA pairs: from 512 activation rows on for the block-scaled kinds, whose main loop is paced by
   // the issuing thread (scale copies + MMAs: up to 17 tensor-core instructions per stage; one
@@ -486,7 +488,7 @@ int run_tc(const TcArgs& a) {
     return v ? static_cast<int64_t>(std::atoll(v)) : static_cast<int64_t>(0);
   }();
   const int64_t pair_min_m = pair_min_env > 0 ? pair_min_env : (block_scaled ? 512 : 1025);
-  if (two_cta_kind && mode != 0 && ((mode == 1 && a.m > 256) || a.m >= pair_min_m) && a.n >= 128) {
+  if (two_cta_kind && ((mode != 0 && ((mode == 1 && a.m > 256) || a.m >= pair_min_m) && a.n >= 128) || a.swiglu_q != nullptr)) {
     Gemm2Params p2{};
     p2.m = static_cast<int>(a.m);
     p2.n = static_cast<int>(a.n);
@@ -514,6 +516,8 @@ int run_tc(const TcArgs& a) {
       p2.bn = 128;
       for (int bn : {256, 192, 128}) {
         if (bn > 128 && ((a.tactic & 4) || a.n < 192)) continue;
+        // the re-packing epilogue is as long as the tile's MMAs: it needs the second accumulator buffer to hide behind them
+        if (a.swiglu_q != nullptr && bn != 128) continue;
         const int sfb = bn == 128 ? 1 : 2;
         const int64_t issue = 50 * (4 + chunks * (1 + sfb) + 1);
         const int64_t pipe = 4 * (bn / 2);
@@ -542,6 +546,9 @@ int run_tc(const TcArgs& a) {
     p2.scale_wgt = a.scale_wgt;
     p2.bias = static_cast<const __nv_bfloat16*>(a.bias);
     p2.out = static_cast<__nv_bfloat16*>(a.out);
+    p2.sw_q = static_cast<uint8_t*>(a.swiglu_q);
+    p2.sw_sf = static_cast<uint8_t*>(a.swiglu_sf);
+    p2.sw_kt = static_cast<int>(a.n / 128);
     p2.status = ws.status;
     CUtensorMap t_act, t_wgt, t_out, t_sfa, t_sfb;
     rc = make_map_2d(&t_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, kTileA,
@@ -554,9 +561,13 @@ int run_tc(const TcArgs& a) {
     p2.fmt_a = FMT_E4M3;
     p2.fmt_b = a.wgt_u4 ? FMT_E2M1_IN_F8 : FMT_E4M3;
     p2.tx_deficit = a.wgt_u4 ? kU4TxDeficitPerRow * (p2.bn / 2) : 0;
-    rc = make_map_2d(&t_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 64, 128,
-                     CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != RK_OK) return rc;
+    if (a.out != nullptr) {
+      rc = make_map_2d(&t_out, a.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.n, a.m, a.n * 2, 64, 128,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != RK_OK) return rc;
+    } else {
+      t_out = t_act;  // the re-packing epilogue stores with ordinary instructions
+    }
     t_sfa = t_act;
     t_sfb = t_act;
     if (block_scaled) {
@@ -1024,6 +1035,38 @@ extern "C" int rk_gemm_nvfp4(const void* a, const void* sfa, const float* ga, co
   t.workspace_bytes = workspace_bytes;
   t.stream = as_stream(stream);
   t.who = "rk_gemm_nvfp4";
+  return run_tc(t);
+}
+
+extern "C" int rk_gemm_nvfp4_swiglu(const void* a, const void* sfa, const float* ga, const void* b_interleaved,
+                                    const void* sfb, const float* gb, void* q_out, void* sf_out, int64_t m, int64_t n,
+                                    int64_t k, int tactic, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "rk_gemm_nvfp4_swiglu";
+  if (k < 64 || k % 64 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 64", who);
+  if (n < 128 || n % 128 != 0) return fail(RK_EINVAL, "%s: n (gate and up rows together) must be a multiple of 128", who);
+  if (!sfa || !sfb || !q_out || !sf_out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!aligned16(sfa) || !aligned16(sfb) || !aligned16(q_out) || !aligned16(sf_out))
+    return fail(RK_EINVAL, "%s: buffers must be 16-byte aligned", who);
+  TcArgs t{};
+  t.kind = KIND_NVF4;
+  t.act = a;
+  t.wgt = b_interleaved;
+  t.m = m;
+  t.n = n;
+  t.k_bytes = k / 2;
+  t.mma_bytes_last = static_cast<int>((k / 2) % 128 == 0 ? 128 : (k / 2) % 128);
+  t.scale_act = ga;
+  t.scale_wgt = gb;
+  t.sf_act = static_cast<const uint8_t*>(sfa);
+  t.sf_wgt = static_cast<const uint8_t*>(sfb);
+  t.sf_kt = static_cast<int>((k / 16 + 3) / 4);
+  t.swiglu_q = q_out;
+  t.swiglu_sf = sf_out;
+  t.tactic = (tactic & 4) | 2;
+  t.workspace = workspace;
+  t.workspace_bytes = workspace_bytes;
+  t.stream = as_stream(stream);
+  t.who = who;
   return run_tc(t);
 }
 

@@ -27,9 +27,17 @@
 
 #include <cuda.h>
 
+#include "rk_blockscale.cuh"
 #include "rk_gemm_tc.cuh"
 
 namespace rk {
+
+// The SwiGLU-requantising epilogue is ALU heavy and latency bound (an exponential, two IEEE
+// reciprocals and five bf16 roundings per activation, in one dependent chain): it runs on sixteen
+// epilogue warps (four per TMEM lane quadrant, one 16-element block of every group each) instead of
+// four.  816 x 32768 x 2048: 131.7 us with four warps, 82.5 with eight.
+constexpr int kGemm2SwigluSets = 4;
+constexpr int kGemm2ThreadsSwiglu = 64 + 128 * kGemm2SwigluSets;
 
 struct Gemm2Params {
   int m, n, kblocks;
@@ -43,6 +51,12 @@ struct Gemm2Params {
   int issue_block; // issue a stage's tensor-core instructions as one straight-line block
   int fmt_a, fmt_b;  // KIND_MXF8: element formats (e4m3, or e2m1 for 4-bit weights expanded by TMA)
   int tx_deficit;    // bytes per stage and CTA that the copies report short of the shared-memory bytes written
+  // SwiGLU-requantising epilogue (NVFP4 gate/up projection with the 64-column interleaved weight
+  // layout: of every 128 output columns the first 64 are `up`, the next 64 their `gate`): when sw_q
+  // is set the tile never leaves as bf16 - the epilogue forms silu(gate) * up and packs it to NVFP4.
+  uint8_t* sw_q;     // [m, n / 4] bytes: two e2m1 codes per byte of the [m, n / 2] activation
+  uint8_t* sw_sf;    // its UE4M3 scale factors in the swizzled 128 x 4 layout
+  int sw_kt;         // 512-byte scale chunks per 128-row block of that buffer = (n / 2) / 64
   int tiles_m, tiles_n;  // pair tiles: 256 x bn
   long long ldo;
   const float* scale_act;
@@ -155,7 +169,7 @@ __host__ __device__ inline int gemm2_stage_bytes(int kind, int bn, int sfb_block
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemm2ThreadsSwiglu, 1)
 rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_sfa,
                    const __grid_constant__ CUtensorMap tm_sfb, const Gemm2Params p) {
@@ -192,7 +206,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[b]), 8);  // four epilogue warps in each CTA of the pair
+      mbar_init(smem_u32(&bar_acc_empty[b]), p.sw_q != nullptr ? 8 * kGemm2SwigluSets : 8);  // the epilogue warps of both CTAs of the pair
     }
     abort_flag = 0;
     fence_barrier_init();
@@ -386,6 +400,9 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       if (p.scale_act) s_act_scalar = *p.scale_act;
       if (p.scale_wgt) s_wgt_scalar = *p.scale_wgt;
     }
+    const int epi_threads = static_cast<int>(blockDim.x) - 64;  // 128, or 512 with the re-packing epilogue
+    const int set = (warp - 2) >> 2;                              // which of a lane quadrant's warps (re-packing epilogue)
+    auto epi_sync = [](int n) { asm volatile("bar.sync 1, %0;" ::"r"(n) : "memory"); };
     const uint32_t acc_empty_leader0 = mapa_u32(smem_u32(&bar_acc_empty[0]), 0);
     const uint32_t acc_empty_leader1 = mapa_u32(smem_u32(&bar_acc_empty[1]), 0);
     Ring racc{0, 0};
@@ -400,7 +417,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       if constexpr (KIND == KIND_I8) {
         if (ra < p.m) row_scale = p.scale_act[ra];
       }
-      epi_bar_sync();
+      epi_sync(epi_threads);
       for (int j = et; j < p.bn; j += 128) {
         const int rb = row_b0 + j;
         float sv = 1.0f, bv = 0.0f;
@@ -411,11 +428,49 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         vec_scale[j] = sv;
         vec_bias[j] = bv;
       }
-      epi_bar_sync();
-      const bool ok = mbar_wait_group(smem_u32(&bar_acc_full[ab]), racc.phase, et == 0, 1, 128, &abort_flag, p.status,
+      epi_sync(epi_threads);
+      const bool ok = mbar_wait_group(smem_u32(&bar_acc_full[ab]), racc.phase, threadIdx.x == 64, 1, epi_threads, &abort_flag, p.status,
                                       RK_DEV_TIMEOUT_ACC, verdict_epi, epi_iter++);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ab * 256 + (static_cast<uint32_t>(quad * 32) << 16);
+      if (p.sw_q != nullptr) {
+        // ---- SwiGLU + NVFP4 re-pack: this thread owns one activation row of the tile.  Per 128 output
+        // columns: 64 `up` then 64 `gate` values -> 64 activations = four 16-element blocks = 32 code
+        // bytes and 4 scale bytes (one aligned word of the swizzled layout).  The arithmetic is the
+        // two-launch path's, step for step: bf16(alpha * acc), SwiGLU in bf16 steps, block pack.  Four warps
+        // share a row: each takes one of the group's four blocks.
+        const float alpha = s_act_scalar * s_wgt_scalar;
+        const int rows_sf = (p.m + 127) & ~127;  // the scale buffer covers whole 128-row blocks; padding rows get zeros
+        for (int cc = 0; cc < p.bn; cc += 128) {
+          const int col0 = row_b0 + cc;       // first output column of this 128-column group
+          const int ch0 = col0 >> 1;          // first activation channel of the group
+          // warp set s packs block s of the group (channels 16 s .. 16 s + 15)
+          const int c0 = set * 16;
+          uint32_t ru[16], rg[16];
+          __syncwarp();
+          tmem_ld_16(t_acc + cc + c0, ru);
+          tmem_ld_16(t_acc + cc + 64 + c0, rg);
+          tc_wait_ld();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float up = round_bf16(__fmul_rn(alpha, __uint_as_float(ru[j])));
+            const float gate = round_bf16(__fmul_rn(alpha, __uint_as_float(rg[j])));
+            v[j] = swiglu_bf16_steps(gate, up);
+          }
+          uint8_t code;
+          const unsigned long long packed = nvfp4_block(v, &code);
+          if (ok && col0 < p.n) {
+            if (ra < p.m)
+              *reinterpret_cast<unsigned long long*>(p.sw_q + static_cast<long long>(ra) * (p.n >> 2) + (ch0 >> 1) + set * 8) = packed;
+            if (ra < rows_sf) p.sw_sf[sf_offset(ra, (ch0 >> 4) + set, p.sw_kt)] = ra < p.m ? code : static_cast<uint8_t>(0);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(ab == 0 ? acc_empty_leader0 : acc_empty_leader1);
+        continue;
+      }
       for (int cc = 0; cc < p.bn; cc += 64, obuf = (p.out_bufs == 2) ? (obuf ^ 1) : 0) {
         uint8_t* const stage = smem_gen + out_stage_off + obuf * kOutBufBytes;
         if (et == 0 && pending_store) {

@@ -12,6 +12,7 @@
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
+#include "rk_blockscale.cuh"
 #include "rk_common.cuh"
 #include "rk_host.h"
 
@@ -48,7 +49,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, bool vec, int vali
   }
 }
 
-__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 
 // clamp(rint(v / scale)) as an int in [-limit, limit]
 __device__ __forceinline__ int quant_code(float v, float scale, float limit) {
@@ -477,10 +478,6 @@ to_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long elements, const flo
 }
 
 // ------------------------------------------------------------------ block-scale packers
-__device__ __forceinline__ long long sf_offset(long long row, long long group, long long kt) {
-  return ((row / 128) * kt + group / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + group % 4;
-}
-
 __device__ __forceinline__ float rcp_approx_ftz(float x) {
   float r;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -650,15 +647,6 @@ pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long
 __device__ __forceinline__ float swiglu_f32(float gate, float up) {
   return round_bf16(__fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up));
 }
-// SwiGLU in bf16 steps, as the reference's NVFP4 producer evaluates it with packed bf16 arithmetic
-// (blackwell/csrc/fp4_cutlass_linear.cu:1029-1033): every intermediate is rounded to bf16.
-__device__ __forceinline__ float swiglu_bf16_steps(float gate, float up) {
-  const float e = round_bf16(expf(-gate));
-  const float d = round_bf16(__fadd_rn(1.0f, e));
-  const float r = round_bf16(__fdiv_rn(1.0f, d));
-  return round_bf16(__fmul_rn(round_bf16(__fmul_rn(gate, r)), up));
-}
-
 // Eight consecutive SwiGLU outputs of row-major gate_up [rows, 2 * inter]: gate first, then up; or
 // `interleaved`: blocks of 128 columns, 64 up values followed by their 64 gate values (the layout a
 // fused gate/up projection writes: blackwell/csrc/fp4_cutlass_linear.cu:958-965).
@@ -779,28 +767,6 @@ swiglu_to_fp8_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, 
     o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
     *reinterpret_cast<uint2*>(q + idx) = o;
   }
-}
-
-// One 16-element NVFP4 block: UE4M3 scale byte and eight code bytes (two E2M1 codes each, low nibble first).
-// Same arithmetic as pack_nvfp4_kernel (blackwell/csrc/fp4_cutlass_linear.cu:789-841, no per-tensor scale).
-__device__ __forceinline__ unsigned long long nvfp4_block(const float (&v)[16], uint8_t* code_out) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float scale = amax > 0.0f ? __fdiv_rn(amax, 6.0f) : 1.0f;
-  const uint8_t code = static_cast<uint8_t>(__nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E4M3)) & 0x7F;
-  float deq = __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
-  if (!(deq > 0.0f)) deq = scale;
-  const float reciprocal = __fdiv_rn(1.0f, deq);
-  unsigned long long packed = 0;
-#pragma unroll
-  for (int i = 0; i < 16; i += 2) {
-    const __nv_fp4x2_storage_t pair = __nv_cvt_float2_to_fp4x2(
-        make_float2(__fmul_rn(v[i], reciprocal), __fmul_rn(v[i + 1], reciprocal)), __NV_E2M1, cudaRoundNearest);
-    packed |= static_cast<unsigned long long>(static_cast<uint8_t>(pair)) << (4 * i);
-  }
-  *code_out = code;
-  return packed;
 }
 
 // SwiGLU -> NVFP4: one thread per 16-element block of the [rows, inter] activation.

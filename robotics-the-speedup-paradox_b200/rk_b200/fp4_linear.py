@@ -126,6 +126,37 @@ def linear_forward_packed_gemm_bf16(a, sfa, ga, b, sfb, gb, bias, k, tactic=0):
     return out
 
 
+def interleave_gate_up_rows(weight, intermediate_size):
+    """Rows of a fused gate/up weight [2 * inter, K] ([gate | up] along the output channels) in the
+    64-row interleaved order the fused SwiGLU GEMM reads: of every 128 rows the first 64 are `up`
+    channels 64 j .. 64 j + 63, the next 64 their `gate` channels.  inter must be a multiple of 64."""
+    inter = intermediate_size
+    if weight.shape[0] != 2 * inter or inter % 64:
+        raise ValueError("expected a [2 * inter, K] weight with inter a multiple of 64")
+    gate = weight[:inter].reshape(inter // 64, 64, -1)
+    up = weight[inter:].reshape(inter // 64, 64, -1)
+    return torch.stack([up, gate], dim=1).reshape(2 * inter, -1).contiguous()
+
+
+def linear_swiglu_packed_gemm(a, sfa, ga, b_interleaved, sfb, gb, k, tactic=0):
+    """NVFP4 gate/up projection with SwiGLU and the NVFP4 re-pack in the GEMM's epilogue
+    (`rk_gemm_nvfp4_swiglu`): packed activations [M, K/2] x interleaved packed weight [2 * inter, K/2]
+    -> (codes [M, inter/2], swizzled scale factors) ready for the down projection.  The counterpart
+    of `cutlass_swiglu_fp4_packed` (blackwell/cute_fp4_swiglu.py:186-282)."""
+    m, n = a.shape[0], b_interleaved.shape[0]
+    if n % 128:
+        raise ValueError("the fused SwiGLU projection needs 2 * inter to be a multiple of 128")
+    q = torch.empty((m, n // 4), device=a.device, dtype=torch.uint8)
+    sf = torch.empty(_lib.load().rk_sf_bytes(m, n // 32), device=a.device, dtype=torch.uint8)
+    with torch.cuda.device(a.device):
+        ws = _lib.gemm_workspace(_lib.OP_NVFP4, a.device, m, n, k)
+        code = _lib.load().rk_gemm_nvfp4_swiglu(_lib.ptr(a), _lib.ptr(sfa), _lib.ptr(ga), _lib.ptr(b_interleaved), _lib.ptr(sfb),
+                                                _lib.ptr(gb), _lib.ptr(q), _lib.ptr(sf), m, n, k, tactic, _lib.ptr(ws),
+                                                ws.numel(), _lib.stream_ptr(a.device))
+    _lib.check(code, "linear_swiglu_packed_gemm")
+    return q, sf
+
+
 class Fp4CutlassLinear(torch.nn.Module):
     def __init__(self, packed, scales, weight_global, bias, in_features, out_features, role, target_name):
         super().__init__()
@@ -192,3 +223,41 @@ class Fp4CutlassLinear(torch.nn.Module):
 
     def extra_repr(self):
         return f"in_features={self.in_features}, out_features={self.out_features}, role={self.role}"
+
+
+class Fp4GateUpSwiglu(torch.nn.Module):
+    """The gate and up projections of a SwiGLU MLP as ONE NVFP4 GEMM whose epilogue applies SwiGLU and
+    packs the result to NVFP4 (`linear_swiglu_packed_gemm`): `forward(x)` returns the packed
+    activations (codes, scale factors) that the down projection's `forward_packed` consumes, and the
+    [M, 2 * inter] bf16 intermediate never exists.  No bias, no per-tensor scale (the reference's
+    NVFP4 format); the weight rows are stored in the 64-row interleaved order."""
+
+    def __init__(self, packed, scales, in_features, intermediate_size):
+        super().__init__()
+        self.register_buffer("packed_weight", packed)
+        self.register_buffer("weight_scale", scales)
+        self.in_features = in_features
+        self.intermediate_size = intermediate_size
+        self.fp4_backend = "b200_tcgen05_nvfp4_swiglu"
+
+    @classmethod
+    def from_linears(cls, gate, up):
+        if gate.weight.shape != up.weight.shape or gate.bias is not None or up.bias is not None:
+            raise ValueError("gate and up must be bias-free linears of the same shape")
+        if not gate.weight.is_cuda or gate.weight.dtype != torch.bfloat16:
+            raise ValueError("Fp4GateUpSwiglu requires CUDA BF16 weights")
+        require_fp4_backend(gate.weight.device)
+        inter, k = gate.weight.shape
+        if inter % 64 or k % 64:
+            raise ValueError("Fp4GateUpSwiglu requires intermediate_size % 64 == 0 and in_features % 64 == 0")
+        fused = interleave_gate_up_rows(torch.cat([gate.weight.detach(), up.weight.detach()], dim=0), inter)
+        packed, scales = pack_nvfp4(fused, None)
+        return cls(packed, scales, k, inter)
+
+    def forward(self, x):
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Wrong input feature count")
+        flat = x.reshape(-1, self.in_features)
+        q, sf = pack_nvfp4(flat if flat.is_contiguous() else flat.contiguous(), None)
+        return linear_swiglu_packed_gemm(q, sf, None, self.packed_weight, self.weight_scale, None, self.in_features)
+

@@ -105,6 +105,17 @@ class Bench:
             calls = [(lambda sp, b=b: lib.rk_gemm_mxfp8(L.ptr(a), L.ptr(sfa), L.ptr(b), L.ptr(sfb), None, L.ptr(out), m, n,
                                                         k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
             nbytes = m * k + n * k + 2 * m * n + (m + n) * k // 32
+        elif kind == "nvfp4sw":  # gate/up GEMM (n = 2 * inter, interleaved rows) with SwiGLU + NVFP4 re-pack in the epilogue
+            ws = L.gemm_workspace(L.OP_NVFP4, dev, m, n, k)
+            a = a[:, :k // 2].contiguous()
+            bs = [b[:, :k // 2].contiguous() for b in bs]
+            sfa = torch.full((lib.rk_sf_bytes(m, k // 16),), 0x38, dtype=torch.uint8, device=dev)
+            sfb = torch.full((lib.rk_sf_bytes(n, k // 16),), 0x38, dtype=torch.uint8, device=dev)
+            q = torch.empty((m, n // 4), dtype=torch.uint8, device=dev)
+            sfo = torch.empty(lib.rk_sf_bytes(m, n // 32), dtype=torch.uint8, device=dev)
+            calls = [(lambda sp, b=b: lib.rk_gemm_nvfp4_swiglu(L.ptr(a), L.ptr(sfa), None, L.ptr(b), L.ptr(sfb), None, L.ptr(q),
+                                                                L.ptr(sfo), m, n, k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = (m * k + n * k) // 2 + m * n // 4 + (m + n) * k // 16 + m * n // 32
         elif kind == "fp8p":  # bf16 activations converted inside the kernel
             ws = L.gemm_workspace(L.OP_FP8, dev, m, n, k)
             x = torch.randn(m, k, device=dev).to(torch.bfloat16)
@@ -162,6 +173,19 @@ class Bench:
         nbytes = rows * k * 3
         print(f"quant  rows{rows:6d} k{k:6d} int{bits}: {us:8.2f} us  {nbytes / us / 1e3:8.1f} GB/s "
               f"({nbytes / us / 1e3 / self.hbm * 100:5.1f}% of {self.hbm_src} copy bw)", flush=True)
+
+
+def swiglu_pack(bench, rows, inter, interleaved=1):
+    """SwiGLU -> NVFP4 pack of a bf16 [rows, 2 * inter] gate/up tensor (the second launch of the two-launch MLP path)."""
+    dev, lib = bench.dev, bench.lib
+    xs = [torch.randn(rows, 2 * inter, device=dev).to(torch.bfloat16) for _ in range(bench.copies(rows * inter * 4))]
+    q = torch.empty((rows, inter // 2), dtype=torch.uint8, device=dev)
+    sf = torch.empty(lib.rk_sf_bytes(rows, inter // 16), dtype=torch.uint8, device=dev)
+    calls = [(lambda sp, x=x: lib.rk_swiglu_pack_nvfp4_layout(L.ptr(x), rows, inter, interleaved, L.ptr(q), L.ptr(sf), sp)) for x in xs]
+    us = bench.time_us(calls)
+    nbytes = rows * inter * 4 + rows * inter // 2 + rows * inter // 16
+    print(f"swiglu_pack rows{rows:6d} inter{inter:6d}: {us:8.2f} us  {nbytes / us / 1e3:8.1f} GB/s "
+          f"({nbytes / us / 1e3 / bench.hbm * 100:5.1f}% of {bench.hbm_src} copy bw)", flush=True)
 
 
 def layer_breakdown(envs=8, prefix=816, repeats=5):
@@ -238,6 +262,8 @@ def main(argv):
         dims = [int(d) for d in dims.split("x")]
         if kind == "quant":
             b.quant_rows(*dims)
+        elif kind == "swiglu_pack":
+            swiglu_pack(b, *dims)
         elif kind == "w4a16":
             b.w4a16(*dims)
         elif kind == "w8a8":

@@ -165,3 +165,78 @@ def test_fp8_producer_path_uses_a_unit_activation_scale(H):
     want, _ = OF.gemm(xa, np.float32(1.0), wb, ws, H.to_np(lin.bias))
     assert H.rel_frobenius(got, want) < 1e-2
     assert F.e4m3_decode(xa)[0, 0] == 448.0
+
+
+# ---------------------------------------------------------------- SwiGLU + NVFP4 re-pack inside the gate/up GEMM
+@pytest.mark.parametrize("shape", [(130, 256, 256), (816, 1024, 512), (300, 384, 2048), (816, 4096, 2048)])
+def test_gate_up_gemm_with_fused_swiglu_repack_equals_the_two_launch_path(H, shape):
+    """`rk_gemm_nvfp4_swiglu` (interleaved gate/up weight rows, SwiGLU and the NVFP4 block pack in the
+    GEMM's epilogue) against GEMM -> bf16 [M, 2 * inter] -> `rk_swiglu_pack_nvfp4_layout(interleaved)`:
+    the fused kernel follows the same arithmetic step for step, so codes and scale factors are equal
+    bit for bit; the two-launch path itself is held to the reference's kernels by the golden fixtures."""
+    from rk_b200 import fp4_linear as P4
+
+    m, inter, k = shape
+    x = H.randn_bf16((m, k), 1.0, 101).to(H.DEVICE)
+    w = H.randn_bf16((2 * inter, k), 0.05, 102).to(H.DEVICE)  # [gate | up] along the output channels
+    wi = P4.interleave_gate_up_rows(w, inter)
+    assert torch.equal(wi[:64], w[inter:inter + 64]) and torch.equal(wi[64:128], w[:64])
+    qa, sfa = P4.pack_nvfp4(x)
+    qb, sfb = P4.pack_nvfp4(wi)
+    two = P4.linear_forward_packed_gemm_bf16(qa, sfa, None, qb, sfb, None, None, k)  # interleaved columns
+    q2, sf2 = P4.pack_swiglu_nvfp4(two, inter, interleaved=True)
+    q1, sf1 = P4.linear_swiglu_packed_gemm(qa, sfa, None, qb, sfb, None, k)
+    ws = _lib.gemm_workspace(_lib.OP_NVFP4, H.DEVICE, m, 2 * inter, k)
+    assert _lib.read_status(ws) == 0
+    assert torch.equal(q1, q2)
+    assert torch.equal(sf1, sf2)
+    # and with the fp32 per-tensor scales on both operands (alpha = ga * gb in front of the rounding)
+    ga, gb = P4.tensor_global_scale(x), P4.tensor_global_scale(wi)
+    qa, sfa = P4.pack_nvfp4(x, ga)
+    qb, sfb = P4.pack_nvfp4(wi, gb)
+    two = P4.linear_forward_packed_gemm_bf16(qa, sfa, ga, qb, sfb, gb, None, k)
+    q2, sf2 = P4.pack_swiglu_nvfp4(two, inter, interleaved=True)
+    q1, sf1 = P4.linear_swiglu_packed_gemm(qa, sfa, ga, qb, sfb, gb, k)
+    assert torch.equal(q1, q2) and torch.equal(sf1, sf2)
+
+
+def test_fused_swiglu_gemm_rejects_bad_shapes(H):
+    from rk_b200 import fp4_linear as P4
+
+    x = H.randn_bf16((64, 128), 1.0, 103).to(H.DEVICE)
+    w = H.randn_bf16((192, 128), 0.05, 104).to(H.DEVICE)  # 2 * inter = 192: not a multiple of 128
+    qa, sfa = P4.pack_nvfp4(x)
+    qb, sfb = P4.pack_nvfp4(w)
+    with pytest.raises(ValueError):
+        P4.linear_swiglu_packed_gemm(qa, sfa, None, qb, sfb, None, 128)
+    with pytest.raises(ValueError):
+        P4.interleave_gate_up_rows(w, 96)
+
+
+def test_gate_up_swiglu_module_feeds_the_down_projection(H):
+    from rk_b200 import fp4_linear as P4
+
+    m, inter, k = 200, 512, 256
+    gate = torch.nn.Linear(k, inter, bias=False, dtype=torch.bfloat16)
+    up = torch.nn.Linear(k, inter, bias=False, dtype=torch.bfloat16)
+    down = torch.nn.Linear(inter, k, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        gate.weight.copy_(H.randn_bf16((inter, k), 0.05, 111))
+        up.weight.copy_(H.randn_bf16((inter, k), 0.05, 112))
+        down.weight.copy_(H.randn_bf16((k, inter), 0.05, 113))
+    gate, up, down = (l.to(H.DEVICE).requires_grad_(False) for l in (gate, up, down))
+    x = H.randn_bf16((2, m // 2, k), 1.0, 114).to(H.DEVICE)
+    fused = P4.Fp4GateUpSwiglu.from_linears(gate, up)
+    down_q = P4.Fp4CutlassLinear.from_linear(down, "linear", "down")
+    q, sf = fused(x)
+    got = down_q.forward_packed(q, sf, None, x.shape[:-1])
+    # the same MLP with separate launches: NVFP4 gate and up linears, bf16 [gate | up], SwiGLU pack, down
+    gate_q = P4.Fp4CutlassLinear.from_linear(gate, "linear", "gate")
+    up_q = P4.Fp4CutlassLinear.from_linear(up, "linear", "up")
+    want = down_q.forward_swiglu(torch.cat([gate_q(x), up_q(x)], dim=-1), inter)
+    assert torch.equal(got, want)
+    # and close to the bf16 MLP
+    ref = torch.nn.functional.silu(gate(x).float()) * up(x).float()
+    ref = (ref.to(torch.bfloat16) @ down.weight.t()).float()
+    assert float((got.float() - ref).norm() / ref.norm()) < 0.35  # two chained 4-bit GEMMs
+
