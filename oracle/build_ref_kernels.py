@@ -100,10 +100,17 @@ def build_one(backend, verbose=False, force=False):
     return out, log
 
 
-def build(backends=None, verbose=False, force=False):
+def build(backends=None, verbose=False, force=False, jobs=None):
+    """Builds (or finds up to date) the requested extensions, several compilers at a time: each of
+    these translation units takes minutes."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    names = list(backends or BACKENDS)
+    jobs = jobs or int(os.environ.get("MAX_JOBS", "3"))
+    with ThreadPoolExecutor(max_workers=max(1, jobs)) as pool:
+        outcomes = list(pool.map(lambda b: build_one(b, verbose, force), names))
     results = {}
-    for b in backends or BACKENDS:
-        path, log = build_one(b, verbose, force)
+    for b, (path, log) in zip(names, outcomes):
         results[b] = path
         if verbose or path is None:
             print(log, flush=True)

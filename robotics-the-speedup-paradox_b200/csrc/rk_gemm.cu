@@ -280,7 +280,12 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   // split-K across a cluster when the tiles cannot occupy the machine; >= 2 K blocks per CTA
   const long long tiles = static_cast<long long>(pl.tiles_a) * pl.tiles_b;
   pl.splits = 1;
-  if (!(tactic & 2) && tiles * 4 <= kNumSms) {  // a two-way split does not pay for its exchange
+  // A split costs a cluster launch and the exchange through distributed shared memory (+1 ... +7 us
+  // measured on K loops of 4 ... 16 blocks: 64 x 2048 x 2048 W8A8 6.5 us split eight ways, 5.75 us
+  // unsplit), so it is taken only when the K loop it shortens is long: 32 blocks of 128 bytes for the
+  // direct kinds, 8 for the rewriting kinds, whose stages take ~1 us each.
+  const bool long_loop = rewriting ? kblocks >= 8 : kblocks >= 32;
+  if (!(tactic & 2) && tiles * 4 <= kNumSms && long_loop) {  // a two-way split does not pay for its exchange
     int s = static_cast<int>(kNumSms / tiles);
     if (s > 8) s = 8;
     if (s > kblocks / 2) s = kblocks / 2;

@@ -67,7 +67,8 @@ def test_weight_quantizer_matches_reference_fixture(H, golden, case, bits):
 
 
 @pytest.mark.parametrize("shape", [(16, 128, 128), (128, 128, 128), (64, 128, 512), (1, 40, 256), (50, 80, 256),
-                                   (64, 2048, 2048), (400, 1024, 1024), (300, 520, 384), (1764, 2048, 2048)])
+                                   (64, 2048, 2048), (400, 1024, 1024), (300, 520, 384), (1764, 2048, 2048),
+                                   (64, 256, 4096), (100, 384, 8192)])  # the last two: few tiles, long K: cluster split-K
 @pytest.mark.parametrize("tactic", [0, 1, 2, 5])
 def test_int8_accumulators_are_exact(H, shape, tactic):
     m, n, k = shape

@@ -32,8 +32,8 @@ def _case(m, n, k, seed):
     return a, b, sa, sb
 
 
-# tactic 2 forbids split-K: (64, 256, 512) then runs the persistent schedule, tactic 0 the cluster split-K one
-@pytest.mark.parametrize("shape,tactic", [((64, 256, 512), 2), ((64, 256, 2048), 0), ((300, 1024, 256), 0)])
+# tactic 2 forbids split-K: (64, 256, 512) then runs the persistent schedule; K = 4096 with tactic 0 takes the cluster split-K one
+@pytest.mark.parametrize("shape,tactic", [((64, 256, 512), 2), ((64, 256, 4096), 0), ((300, 1024, 256), 0)])
 def test_wait_expiry_sets_status_and_the_next_launch_is_exact(shape, tactic):
     lib = _lib.load()
     device = torch.device("cuda:0")
