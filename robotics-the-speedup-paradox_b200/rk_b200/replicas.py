@@ -205,7 +205,7 @@ class ExchangeMemory:
         from . import _lib
 
         self._lib, self.info, self.device, self.nbytes = _lib, info, device, int(nbytes)
-        self._opened = []
+        self._opened, self._group = [], group
         lib = _lib.load()
         ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
         with torch.cuda.device(device):
@@ -237,13 +237,17 @@ class ExchangeMemory:
         return self._view[offset:offset + nbytes].view(dtype).view(*shape)
 
     def close(self):
-        """Unmaps the peers' blocks and frees this rank's; every rank must have stopped using them."""
+        """Unmaps the peers' blocks, waits until every rank has done so, and frees this rank's block
+        (an allocation must not be freed while another process still maps it).  Collective: every
+        rank calls it, after all of them have stopped using the memory."""
         lib = self._lib.load()
         with torch.cuda.device(self.device):
             torch.cuda.synchronize(self.device)
             for p in self._opened:
                 lib.rk_peer_close(p)
             self._opened = []
+            if self.info.world > 1 and dist.is_initialized():
+                dist.barrier(group=self._group, device_ids=[self.device.index])
             if self.ptr:
                 self._view = None
                 lib.rk_peer_free(self.ptr)
