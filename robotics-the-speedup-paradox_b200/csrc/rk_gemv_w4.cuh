@@ -22,6 +22,10 @@
 // shared memory; eight bf16 outputs leave in one store.  Summation is fp32 throughout (a different
 // order than the tensor-core kernels; same tolerance).
 //
+// The kernel is issue bound, not latency bound: a variant that streamed the packed rows through
+// per-team shared-memory rings with bulk copies (192 KB of weights in flight per SM instead of
+// 64 KB at best) measured 9.0 us against 8.2 us for this form at N = 16384, K = 2048.
+//
 // Packed word format as everywhere: byte b of a word holds weights k_b (low nibble) and k_{b+4}.
 #pragma once
 
@@ -44,10 +48,12 @@ struct GemvParams {
   int n, k;
 };
 
-// sum over the 32 weights of one 16-byte piece of x[e] * (1 + u / 128); xs holds the chunk's activations
-__device__ __forceinline__ float gemv_chunk(const uint4& piece, const float (&xs)[32]) {
+// sum over the 32 weights of one 16-byte piece of x[e] * (1 + u / 128).  xs2[4 * j + b] holds the
+// chunk's activations (8 j + b, 8 j + 4 + b): the two weights that share byte b of word j.  One packed
+// `fma.rn.f32x2` advances both running sums (the same two chains, rounded identically, as two FMAs).
+__device__ __forceinline__ float gemv_chunk(const uint4& piece, const float2 (&xs2)[16]) {
   const uint32_t words[4] = {piece.x, piece.y, piece.z, piece.w};
-  float acc0 = 0.0f, acc1 = 0.0f;
+  float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     // bytes of `lo`: 0x80 | (k_b + 8) for weights k_0..k_3 of the word, of `hi`: k_4..k_7
@@ -59,11 +65,10 @@ __device__ __forceinline__ float gemv_chunk(const uint4& piece, const float (&xs
       // result bytes (low to high): 0, 0, byte b of the source, 0x3F
       const float f_lo = __uint_as_float(__byte_perm(lo, 0x3F000000u, 0x7044u | (b << 8)));
       const float f_hi = __uint_as_float(__byte_perm(hi, 0x3F000000u, 0x7044u | (b << 8)));
-      acc0 = fmaf(xs[8 * j + b], f_lo, acc0);
-      acc1 = fmaf(xs[8 * j + 4 + b], f_hi, acc1);
+      acc = __ffma2_rn(xs2[4 * j + b], make_float2(f_lo, f_hi), acc);
     }
   }
-  return acc0 + acc1;
+  return acc.x + acc.y;
 }
 
 __global__ void __launch_bounds__(kGemvWarps * 32, 2)
@@ -93,23 +98,25 @@ rk_gemv_w4a16_kernel(const GemvParams p) {
       const uint8_t* row = p.q + static_cast<long long>(n0 + r) * row_bytes + (k0 >> 1);
       piece[r] = __ldcs(reinterpret_cast<const uint4*>(row + lane * 16));
     }
-    // this lane's chunk of the slab: activations to registers, and their plain sum
-    float xs[32];
+    // this lane's chunk of the slab: activations to registers (paired as gemv_chunk wants them), and their plain sum
+    float2 xs2[16];
     float xsum = 0.0f;
     {
       const uint4* src = reinterpret_cast<const uint4*>(p.x + k0 + lane * 32);
+      float2 sum2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
+      for (int v = 0; v < 4; ++v) {  // eight activations: words 0, 1 hold elements 0..3, words 2, 3 elements 4..7
         const uint4 t = src[v];
         const uint32_t tw[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          xs[8 * v + 2 * c] = __uint_as_float(tw[c] << 16);
-          xs[8 * v + 2 * c + 1] = __uint_as_float(tw[c] & 0xFFFF0000u);
+        for (int c = 0; c < 2; ++c) {
+          xs2[4 * v + 2 * c] = make_float2(__uint_as_float(tw[c] << 16), __uint_as_float(tw[c + 2] << 16));
+          xs2[4 * v + 2 * c + 1] = make_float2(__uint_as_float(tw[c] & 0xFFFF0000u), __uint_as_float(tw[c + 2] & 0xFFFF0000u));
         }
       }
 #pragma unroll
-      for (int e = 0; e < 32; ++e) xsum += xs[e];
+      for (int e = 0; e < 16; ++e) sum2 = __fadd2_rn(sum2, xs2[e]);
+      xsum = sum2.x + sum2.y;
     }
     // group scales of the eight channels: chunk c lies in group c / 4
     const int group = (k0 >> 7) + (lane >> 2);
@@ -117,7 +124,7 @@ rk_gemv_w4a16_kernel(const GemvParams p) {
     const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
     for (int r = 0; r < kGemvRows; ++r) {
-      const float acc = gemv_chunk(piece[r], xs);
+      const float acc = gemv_chunk(piece[r], xs2);
       const float dot = fmaf(128.0f, acc, -136.0f * xsum);  // sum x * q over the chunk
       const float scale = (r & 1) ? __uint_as_float(sw[r >> 1] & 0xFFFF0000u) : __uint_as_float(sw[r >> 1] << 16);
       total[r] = fmaf(scale, dot, total[r]);
