@@ -317,3 +317,26 @@ def test_full_width_prefix_layers_nvfp4_every_linear_matches_oracle(H):
                 got = H.to_np(y.reshape(-1, layer.out_features))
                 assert H.rel_frobenius(got, want) < 1e-2, name
             assert shapes == {(816, 2048, 2048), (816, 256, 2048), (816, 16384, 2048), (816, 2048, 16384)}
+
+
+def test_shared_float_packs_leave_the_prefix_output_unchanged(H):
+    """q/k/v and gate/up sharing one packed activation (fp8, mxfp8, fp4 with and without the per-tensor
+    scale) give exactly the output of the unshared modules: the same codes reach the same GEMMs."""
+    from rk_b200.gemma_stack import GemmaConfig, GemmaStack, prefix_scope
+    from rk_b200.optimizations import quantize_linears
+
+    cfg = GemmaConfig(width=256, mlp_dim=1024, depth=2, num_heads=2, num_kv_heads=1, head_dim=128)
+    model = GemmaStack(cfg).to(torch.bfloat16).init_random(3).to(H.DEVICE).eval()
+    x = H.randn_bf16((1, 200, 256), 1.0, 8).to(H.DEVICE)
+    pos = torch.arange(200, device=H.DEVICE)[None]
+    with torch.no_grad():
+        for precision, extra in (("fp8", {}), ("mxfp8", {}), ("fp4", {}), ("fp4", {"fp4_global_scale": True})):
+            with quantize_linears(model, precision, scopes=("text",), selector=prefix_scope, **extra):
+                plain, _ = model(x, pos)
+            with quantize_linears(model, precision, scopes=("text",), selector=prefix_scope, shared_quant=True, **extra) as report:
+                assert report["shared_float_packs"] == 2 * cfg.depth
+                shared, _ = model(x, pos)
+            assert torch.equal(plain, shared), precision
+    with pytest.raises(ValueError):
+        with quantize_linears(model, "fp8", scopes=("text",), selector=prefix_scope, grouped=True):
+            pass
