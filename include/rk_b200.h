@@ -138,6 +138,29 @@ int rk_gated_rmsnorm_quant_rows(const void* x, const void* branch, const void* g
                                 const void* shift, int64_t tokens, int64_t rows, int64_t k, float eps, int bits,
                                 void* sum_out, void* norm_out, void* q, float* scales, void* stream);
 
+/* The same Gemma RMSNorm (plain residual add, plain or adaptive weights) without a row quantizer:
+ * writes the bf16 result to norm_out and, when scale_out is given, the per-tensor scale
+ * max(amax(result) / divisor, 1e-12) of that result (non-finite values ignored) - the first half
+ * of norm -> per-tensor-scaled FP8 / NVFP4 packing (divisor 448 or 6 * 448) in front of
+ * rk_quant_tensor_fp8_with_scale or rk_pack_nvfp4.  The arithmetic is the model's norm
+ * (models/pi05/modeling_gemma.py:62-106), not the two-rounding form of the reference's serving
+ * producers (`add_rms_norm_fp4_quant_bf16`), so a stack keeps its numerics when it switches this on.
+ *   scale_out == NULL: norm only (workspace unused); otherwise a workspace header is needed. */
+int rk_rmsnorm_tensor_scale(const void* x, const void* residual, const void* scale, const void* shift, int64_t tokens,
+                            int64_t rows, int64_t k, float eps, float divisor, void* sum_out, void* norm_out,
+                            float* scale_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* out[r, c] = bf16(table[x[r, c]] * up[r, c]) - the gated-activation arithmetic of rk_quant_rows'
+ * RK_ACT_LUT_MUL mode (ampere_ada/integer.py:101-130: a 65536-entry bf16 table indexed by the bit
+ * pattern) written as a bf16 matrix - and, when scale_out is given, max(amax(out) / divisor, 1e-12):
+ * the activation in front of a down projection whose packer needs a per-tensor scale (NVFP4 with
+ * global scales: divisor 6 * 448; FP8 per tensor: 448).
+ *   x, up bf16 rows of k elements, row strides in elements (multiples of 8); out bf16 [rows, k]
+ *   contiguous; k % 8 == 0; scale_out == NULL: product only (workspace unused). */
+int rk_lut_mul_tensor_scale(const void* x, int64_t x_stride, const void* up, int64_t up_stride, const void* lut,
+                            int64_t rows, int64_t k, float divisor, void* out, float* scale_out, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
 /* out[m, n] = bf16( (float(sum_k a*b) * sa[m]) * sb[n] (+ bias[n]) ), int32 accumulation.
  * Replaces `robotics_integer::gemm` / `gemm_biasless` (ampere_ada/csrc/integer_gemm.cu:22-195).
  *   bits 8: a int8 [m, kpad], b int8 [n, kpad].  bits 4: packed nibbles [., kpad/2]; the kernel

@@ -49,7 +49,19 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, bool vec, int vali
   }
 }
 
-
+// eight values that are already bf16-representable (or are to be rounded to nearest even) as one 16-byte store
+__device__ __forceinline__ void store8(__nv_bfloat16* p, bool vec, int valid, const float (&v)[8]) {
+  if (vec && valid >= 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < valid) p[i] = __float2bfloat16_rn(v[i]);
+  }
+}
 
 // clamp(rint(v / scale)) as an int in [-limit, limit]
 __device__ __forceinline__ int quant_code(float v, float scale, float limit) {
@@ -231,6 +243,46 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const
   }
 }
 
+// ------------------------------------------------------------------ table activation * up -> bf16 + tensor amax
+// out = bf16(table[x] * up) element by element (the arithmetic of the GELU-table mode of the row
+// quantizer above) and the absolute maximum of the finite results, for a per-tensor scale that a
+// block packer needs before it can run.  Eight elements per thread and step; rows may be strided.
+__global__ void __launch_bounds__(256)
+lut_mul_amax_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const __nv_bfloat16* __restrict__ up,
+                    long long up_stride, const __nv_bfloat16* __restrict__ lut, long long rows, int k,
+                    __nv_bfloat16* __restrict__ out, unsigned* __restrict__ staging) {
+  __shared__ float scratch[8];
+  const int per_row = k >> 3;
+  const long long total = rows * per_row;
+  float local = 0.0f;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / per_row;
+    const int col = static_cast<int>(i - row * per_row) << 3;
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + row * x_stride + col);
+    const uint4 uv = *reinterpret_cast<const uint4*>(up + row * up_stride + col);
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float t0 = __bfloat162float(lut[xw[w] & 0xFFFFu]);
+      const float t1 = __bfloat162float(lut[xw[w] >> 16]);
+      const float r0 = round_bf16(__fmul_rn(t0, __uint_as_float(uw[w] << 16)));
+      const float r1 = round_bf16(__fmul_rn(t1, __uint_as_float(uw[w] & 0xFFFF0000u)));
+      const float a0 = fabsf(r0), a1 = fabsf(r1);
+      if (a0 <= 3.4028234664e38f) local = fmaxf(local, a0);
+      if (a1 <= 3.4028234664e38f) local = fmaxf(local, a1);
+      ow[w] = (__float_as_uint(r0) >> 16) | (__float_as_uint(r1) & 0xFFFF0000u);
+    }
+    *reinterpret_cast<uint4*>(out + row * k + col) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+  if (staging != nullptr) {
+    const float block_max = block_reduce(local, true, scratch);
+    if (threadIdx.x == 0 && block_max > 0.0f) atomicMax(staging, __float_as_uint(block_max));
+  }
+}
+
 // ------------------------------------------------------------------ AdaLN modulation (+LayerNorm, +gated residual)
 template <int BITS>
 __global__ void __launch_bounds__(kRowThreads)
@@ -263,8 +315,8 @@ quant_rows_modulated_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
         for (int i = 0; i < 8; ++i) {
           // residual = bf16(x + bf16(y * gate))
           vals[it][i] = round_bf16(__fadd_rn(vals[it][i], round_bf16(__fmul_rn(yv[i], gv[i]))));
-          if (i < valid) residual_out[xoff + idx + i] = __float2bfloat16_rn(vals[it][i]);
         }
+        store8(residual_out + xoff + idx, vec, valid, vals[it]);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) sum += (i < valid) ? vals[it][i] : 0.0f;
@@ -324,7 +376,7 @@ rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
   const int row = blockIdx.x;
   const long long xoff = static_cast<long long>(row) * k;
   const long long aoff = tokens > 0 ? static_cast<long long>(row / tokens) * k : 0;
-  uint8_t* qrow = q + static_cast<long long>(row) * (BITS == 8 ? kpad : kpad / 2);
+  uint8_t* qrow = BITS == 16 ? q : q + static_cast<long long>(row) * (BITS == 8 ? kpad : kpad / 2);
   const bool vec = (k % 8) == 0;
   float vals[kMaxVec][8];
   float sq = 0.0f;
@@ -348,13 +400,10 @@ rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 #pragma unroll
         for (int i = 0; i < 8; ++i) vals[it][i] = round_bf16(__fadd_rn(vals[it][i], rv[i]));
       }
+      if (sum_out != nullptr) store8(sum_out + xoff + idx, vec, valid, vals[it]);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (i < valid) {
-          if (sum_out != nullptr) sum_out[xoff + idx + i] = __float2bfloat16_rn(vals[it][i]);
-          sq += vals[it][i] * vals[it][i];
-        }
-      }
+      for (int i = 0; i < 8; ++i)
+        if (i < valid) sq += vals[it][i] * vals[it][i];
     }
   }
   const float var = __fdiv_rn(block_reduce(sq, false, scratch), static_cast<float>(k));
@@ -373,11 +422,28 @@ rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
         if (b_ptr != nullptr) t = __fadd_rn(t, bv[i]);
         t = (i < valid) ? round_bf16(t) : 0.0f;
         vals[it][i] = t;
-        if (norm_out != nullptr && i < valid) norm_out[xoff + idx + i] = __float2bfloat16_rn(t);
       }
+      if (norm_out != nullptr) store8(norm_out + xoff + idx, vec, valid, vals[it]);
     }
   }
-  finish_row<BITS>(vals, k, kpad, qrow, scales + row, false, scratch);
+  if constexpr (BITS == 16) {
+    // no row quantizer: the bf16 result is the output (norm_out) and the tensor's absolute maximum
+    // (finite values only) is collected for a per-tensor scale; `q` is that staging word, or null
+    if (q != nullptr) {
+      float local = 0.0f;
+#pragma unroll
+      for (int it = 0; it < kMaxVec; ++it)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float a = fabsf(vals[it][i]);
+          if (a <= 3.4028234664e38f) local = fmaxf(local, a);
+        }
+      const float row_max = block_reduce(local, true, scratch);
+      if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned*>(q), __float_as_uint(row_max));
+    }
+  } else {
+    finish_row<BITS>(vals, k, kpad, qrow, scales + row, false, scratch);
+  }
 }
 
 // ------------------------------------------------------------------ W4 group-128 weight packer
@@ -828,10 +894,7 @@ rmsnorm_producer_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
         load8(residual + xoff + idx, true, 8, rv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) vals[it][i] = round_bf16(__fadd_rn(vals[it][i], rv[i]));
-        if (sum_out != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sum_out[xoff + idx + i] = __float2bfloat16_rn(vals[it][i]);
-        }
+        if (sum_out != nullptr) store8(sum_out + xoff + idx, true, 8, vals[it]);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) sq = fmaf(vals[it][i], vals[it][i], sq);
@@ -849,10 +912,10 @@ rmsnorm_producer_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       for (int i = 0; i < 8; ++i) {
         const float y = round_bf16(__fmul_rn(round_bf16(__fmul_rn(vals[it][i], inv)), wv[i]));
         vals[it][i] = y;
-        if (norm_out != nullptr) norm_out[xoff + idx + i] = __float2bfloat16_rn(y);
         const float a = fabsf(y);
         if (a <= 3.4028234664e38f) local_max = fmaxf(local_max, a);
       }
+      if (norm_out != nullptr) store8(norm_out + xoff + idx, true, 8, vals[it]);
     }
   }
   if (FMT == 0) {
@@ -967,7 +1030,8 @@ extern "C" int rk_quant_rows_modulated(const void* x, const void* scale, const v
   if (k > kCachedK) return fail(RK_EUNSUPPORTED, "rk_quant_rows_modulated: k > %d", kCachedK);
   if ((y == nullptr) != (gate == nullptr) || (y != nullptr && residual_out == nullptr))
     return fail(RK_EINVAL, "rk_quant_rows_modulated: y, gate and residual_out go together");
-  if (!aligned16(x) || !aligned16(scale) || !aligned16(shift) || (y && (!aligned16(y) || !aligned16(gate))))
+  if (!aligned16(x) || !aligned16(scale) || !aligned16(shift) || (y && (!aligned16(y) || !aligned16(gate))) ||
+      (residual_out && !aligned16(residual_out)))
     return fail(RK_EINVAL, "rk_quant_rows_modulated: pointers must be 16-byte aligned");
   const int kpad = static_cast<int>(round_up(k, 128));
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
@@ -993,7 +1057,7 @@ int launch_rmsnorm_quant_rows(const char* who, const void* x, const void* residu
   if (gate && (!residual || tokens < 1)) return fail(RK_EINVAL, "%s: a gate needs a residual branch and tokens > 0", who);
   if (k > kCachedK) return fail(RK_EUNSUPPORTED, "%s: k > %d", who, kCachedK);
   if (!aligned16(x) || !aligned16(scale) || (residual && !aligned16(residual)) || (shift && !aligned16(shift)) ||
-      (gate && !aligned16(gate)))
+      (gate && !aligned16(gate)) || (sum_out && !aligned16(sum_out)) || (norm_out && !aligned16(norm_out)))
     return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   const int kpad = static_cast<int>(round_up(k, 128));
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
@@ -1023,6 +1087,56 @@ extern "C" int rk_gated_rmsnorm_quant_rows(const void* x, const void* branch, co
   if (!branch || !gate) return fail(RK_EINVAL, "rk_gated_rmsnorm_quant_rows: null pointer");
   return launch_rmsnorm_quant_rows("rk_gated_rmsnorm_quant_rows", x, branch, gate, scale, shift, tokens, rows, k, eps,
                                    bits, sum_out, norm_out, q, scales, stream);
+}
+
+extern "C" int rk_rmsnorm_tensor_scale(const void* x, const void* residual, const void* scale, const void* shift,
+                                       int64_t tokens, int64_t rows, int64_t k, float eps, float divisor, void* sum_out,
+                                       void* norm_out, float* scale_out, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  const char* who = "rk_rmsnorm_tensor_scale";
+  if (!x || !scale || !norm_out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || k < 1 || tokens < 0 || (tokens > 0 && rows % tokens != 0))
+    return fail(RK_EINVAL, "%s: bad row / token counts", who);
+  if (k > kCachedK) return fail(RK_EUNSUPPORTED, "%s: k > %d", who, kCachedK);
+  if (!aligned16(x) || !aligned16(scale) || !aligned16(norm_out) || (residual && !aligned16(residual)) ||
+      (shift && !aligned16(shift)) || (sum_out && !aligned16(sum_out)))
+    return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  unsigned* staging = nullptr;
+  if (scale_out != nullptr) {
+    if (!(divisor > 0.0f)) return fail(RK_EINVAL, "%s: the divisor must be positive", who);
+    if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
+    staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);  // zero between calls
+  }
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  rmsnorm_quant_rows_kernel<16><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+      b(x), b(residual), nullptr, b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), 0, eps,
+      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), reinterpret_cast<uint8_t*>(staging), nullptr);
+  if (staging != nullptr) finalize_scale_kernel<<<1, 1, 0, as_stream(stream)>>>(staging, divisor, scale_out);
+  return check_launch(who);
+}
+
+extern "C" int rk_lut_mul_tensor_scale(const void* x, int64_t x_stride, const void* up, int64_t up_stride,
+                                       const void* lut, int64_t rows, int64_t k, float divisor, void* out,
+                                       float* scale_out, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "rk_lut_mul_tensor_scale";
+  if (!x || !up || !lut || !out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || k < 8 || k % 8 != 0 || k > (1 << 30)) return fail(RK_EINVAL, "%s: rows >= 1 and k a multiple of 8", who);
+  if (x_stride < k || up_stride < k || x_stride % 8 != 0 || up_stride % 8 != 0)
+    return fail(RK_EINVAL, "%s: row strides must be multiples of 8 and >= k", who);
+  if (!aligned16(x) || !aligned16(up) || !aligned16(out)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  unsigned* staging = nullptr;
+  if (scale_out != nullptr) {
+    if (!(divisor > 0.0f)) return fail(RK_EINVAL, "%s: the divisor must be positive", who);
+    if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
+    staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);  // zero between calls
+  }
+  const long long vectors = rows * (k / 8);
+  const unsigned blocks = static_cast<unsigned>(std::min<long long>((vectors + 255) / 256, 148LL * 8));
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  lut_mul_amax_kernel<<<blocks, 256, 0, as_stream(stream)>>>(b(x), x_stride, b(up), up_stride, b(lut), rows,
+                                                             static_cast<int>(k), static_cast<__nv_bfloat16*>(out), staging);
+  if (staging != nullptr) finalize_scale_kernel<<<1, 1, 0, as_stream(stream)>>>(staging, divisor, scale_out);
+  return check_launch(who);
 }
 
 extern "C" int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, void* scales, void* stream) {
@@ -1114,7 +1228,8 @@ extern "C" int rk_rmsnorm_quant_fp8(const void* x, const void* residual, const v
   if (!x || !weight || !norm_out || !q || !scale_out) return fail(RK_EINVAL, "%s: null pointer", who);
   if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
   if (rows < 1 || k < 16 || k % 16 != 0 || k > rk::kCachedK) return fail(RK_EINVAL, "%s: k must be a multiple of 16, at most %d", who, rk::kCachedK);
-  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(norm_out))
+  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(norm_out) ||
+      (sum_out && !aligned16(sum_out)))
     return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   cudaStream_t st = as_stream(stream);
   unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
@@ -1157,7 +1272,8 @@ extern "C" int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const 
   const char* who = "rk_rmsnorm_pack_nvfp4";
   if (!x || !weight || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
   if (rows < 1 || k < 32 || k % 32 != 0 || k > rk::kCachedK) return fail(RK_EINVAL, "%s: k must be a multiple of 32, at most %d", who, rk::kCachedK);
-  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(q))
+  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(q) ||
+      (sum_out && !aligned16(sum_out)) || (norm_out && !aligned16(norm_out)))
     return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
   const unsigned rows_padded = static_cast<unsigned>((rows + 127) / 128 * 128);

@@ -38,6 +38,8 @@ SIGNATURES = {
     "rk_quant_weight_int": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "rk_quant_rows_modulated": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _f32, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "rk_rmsnorm_quant_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _vp, _vp, _vp, _vp]),
+    "rk_rmsnorm_tensor_scale": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _f32, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "rk_lut_mul_tensor_scale": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp, _vp, _sz, _vp]),
     "rk_gated_rmsnorm_quant_rows": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _vp, _vp, _vp, _vp]),
     "rk_gemm_int": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
     "rk_gemm_int_acc": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),

@@ -95,6 +95,81 @@ def add_rms_norm_fp4_quant_bf16(x, residual, weight, epsilon, write_normalized=T
     return summed, normalized, q, sf
 
 
+class PackedNvfp4Activation:
+    """An activation that already is NVFP4 (codes, swizzled block scales, fp32 per-tensor scale or None):
+    what a fused norm hands to the `Fp4CutlassLinear` layers that read it.  `shape` is the shape of
+    the bf16 tensor it stands for."""
+
+    _robotics_packed_input = True
+
+    def __init__(self, codes, scale_factors, global_scale, leading_shape, features):
+        self.codes, self.scale_factors, self.global_scale = codes, scale_factors, global_scale
+        self.leading_shape = tuple(leading_shape)
+        self.features = int(features)
+
+    @property
+    def shape(self):
+        return torch.Size((*self.leading_shape, self.features))
+
+    @property
+    def device(self):
+        return self.codes.device
+
+    def packs_for(self, layer):
+        if self.features != layer.in_features:
+            raise ValueError("Wrong input feature count")
+        if (self.global_scale is None) != (layer.weight_global_scale is None):
+            raise ValueError("the packed activation and the layer disagree on per-tensor scales")
+        return self.codes, self.scale_factors, self.global_scale
+
+
+def gemma_rms_norm_pack_nvfp4(x, weight, eps, residual=None, global_scale=True):
+    """Gemma RMSNorm (fp32 statistics, x * inv * (1 + w), one rounding to bf16; plain residual add in
+    front) handed on as NVFP4: one kernel for add + norm + the tensor's absolute maximum
+    (`rk_rmsnorm_tensor_scale`) and the block packer.  x, residual bf16 [..., K] contiguous.
+    Returns (PackedNvfp4Activation, residual stream)."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.shape[-1] % 32:
+        raise ValueError("gemma_rms_norm_pack_nvfp4 requires contiguous CUDA BF16 [..., K] with K divisible by 32")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype or not residual.is_contiguous()):
+        raise ValueError("the residual must match the input")
+    k = x.shape[-1]
+    rows = x.numel() // k
+    lib = _lib.load()
+    normed = torch.empty((rows, k), dtype=torch.bfloat16, device=x.device)
+    stream_out = torch.empty_like(x) if residual is not None else x
+    ga = torch.empty(1, dtype=torch.float32, device=x.device) if global_scale else None
+    with torch.cuda.device(x.device):
+        ws = _lib.workspace(x.device, _lib.WORKSPACE_HEADER)
+        code = lib.rk_rmsnorm_tensor_scale(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), None, 0, rows, k, float(eps),
+                                           6.0 * 448.0, _lib.ptr(stream_out) if residual is not None else None,
+                                           _lib.ptr(normed), _lib.ptr(ga), _lib.ptr(ws), ws.numel(),
+                                           _lib.stream_ptr(x.device))
+    _lib.check(code, "gemma_rms_norm_pack_nvfp4")
+    q, sf = pack_nvfp4(normed, ga)
+    return PackedNvfp4Activation(q, sf, ga, x.shape[:-1], k), stream_out
+
+
+def table_mul_tensor_scale(x, up, table, divisor=None):
+    """bf16(table[x] * up) as a contiguous [rows, K] matrix plus, with `divisor`, the per-tensor scale
+    max(amax / divisor, 1e-12) of it (`rk_lut_mul_tensor_scale`).  x, up: bf16 with dense last axis and
+    one row stride (slices of a wider matrix are fine)."""
+    k = x.shape[-1]
+    x2, up2 = x.reshape(-1, k), up.reshape(-1, k)
+    for t in (x2, up2):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(-1) != 1:
+            raise ValueError("table_mul_tensor_scale takes CUDA BF16 rows")
+    rows = x2.shape[0]
+    out = torch.empty((rows, k), dtype=torch.bfloat16, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device) if divisor is not None else None
+    with torch.cuda.device(x.device):
+        ws = _lib.workspace(x.device, _lib.WORKSPACE_HEADER)
+        code = _lib.load().rk_lut_mul_tensor_scale(_lib.ptr(x2), x2.stride(0), _lib.ptr(up2), up2.stride(0), _lib.ptr(table),
+                                                   rows, k, float(divisor or 1.0), _lib.ptr(out), _lib.ptr(scale),
+                                                   _lib.ptr(ws), ws.numel(), _lib.stream_ptr(x.device))
+    _lib.check(code, "table_mul_tensor_scale")
+    return out, scale
+
+
 def pack_swiglu_nvfp4(gate_up, intermediate_size, interleaved=False):
     """SiLU(gate) * up (bf16 arithmetic steps) packed straight to NVFP4: gate_up bf16 [rows, 2 * inter], gate
     first, or `interleaved`: blocks of 128 columns with 64 up values followed by their 64 gate values."""
@@ -191,6 +266,8 @@ class Fp4CutlassLinear(torch.nn.Module):
         return self._weight_descriptor
 
     def pack_input(self, x):
+        if isinstance(x, PackedNvfp4Activation):
+            return x.packs_for(self)
         if x.shape[-1] != self.in_features:
             raise ValueError("Wrong input feature count")
         flat = x.reshape(-1, self.in_features)
@@ -207,6 +284,20 @@ class Fp4CutlassLinear(torch.nn.Module):
 
     def forward(self, x):
         q, sf, ga = self.pack_input(x)
+        return self.forward_packed(q, sf, ga, x.shape[:-1])
+
+    def forward_gelu(self, x, up=None, *, approximate="tanh"):
+        """GELU(x) (* up) through the 65536-entry bf16 table of the integer layers' `forward_gelu`, the
+        per-tensor scale collected by the same kernel, then the block packer and the GEMM."""
+        from .integer import prepare_gelu
+
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Wrong input feature count")
+        if up is None:
+            return self.forward(torch.nn.functional.gelu(x, approximate=approximate))
+        table = prepare_gelu(x.device, x.dtype, approximate)
+        product, ga = table_mul_tensor_scale(x, up, table, 6.0 * 448.0 if self.weight_global_scale is not None else None)
+        q, sf = pack_nvfp4(product, ga)
         return self.forward_packed(q, sf, ga, x.shape[:-1])
 
     def forward_swiglu(self, gate_up, intermediate_size, interleaved=False):

@@ -56,6 +56,7 @@ class GemmaRMSNorm(nn.Module):
         super().__init__()
         self.eps = eps
         self.fused_bits = None
+        self.fused_fp4 = None  # "global" / "block": hand NVFP4 packs (with / without a per-tensor scale) to the linears
         self.projection_cache = None  # a ConstantProjectionCache over `modulation` (see ActionExpert)
         if cond_dim is None:
             self.weight = nn.Parameter(torch.zeros(dim, dtype=torch.bfloat16))
@@ -99,6 +100,17 @@ class GemmaRMSNorm(nn.Module):
                                      return_sum=branch is not None)
             packed, stream = result if branch is not None else (result, x)
             return packed, (None if self.dense is None else gate), stream
+        if self.fused_fp4 is not None and self.dense is None and x.is_cuda and x.dtype == torch.bfloat16:
+            from .fp4_linear import gemma_rms_norm_pack_nvfp4
+
+            if branch is not None and branch_gate is not None:
+                branch = branch * branch_gate
+            x = x if x.is_contiguous() else x.contiguous()
+            if branch is not None and not branch.is_contiguous():
+                branch = branch.contiguous()
+            packed, stream = gemma_rms_norm_pack_nvfp4(x, self.weight.detach(), self.eps, residual=branch,
+                                                       global_scale=self.fused_fp4 == "global")
+            return packed, None, stream
         if branch is not None:
             x = x + branch if branch_gate is None else x + branch * branch_gate
         xf = x.float()
@@ -111,7 +123,8 @@ class GemmaRMSNorm(nn.Module):
 def _leading_shape(x):
     """Shape without the feature axis, for a tensor or a packed-activation carrier."""
     if getattr(x, "_robotics_packed_input", False):
-        return tuple(next(iter(x.packs.values())).shape)
+        leading = getattr(x, "leading_shape", None)
+        return tuple(leading) if leading is not None else tuple(next(iter(x.packs.values())).shape)
     return tuple(x.shape[:-1])
 
 
@@ -437,6 +450,32 @@ def fuse_norm_quantize(stack, bits=8):
 def unfuse_norm_quantize(norms):
     for norm in norms:
         norm.fused_bits = None
+        norm.fused_fp4 = None
+
+
+def fuse_norm_pack_fp4(stack):
+    """The NVFP4 counterpart of `fuse_norm_quantize`: every plain (non-adaptive) layer norm whose
+    consumers are all `Fp4CutlassLinear` layers with the same per-tensor-scale setting hands them
+    one packed activation (add + norm + amax in one kernel, then the block packer).  Call it inside
+    the `quantize_linears` context; undo with `unfuse_norm_quantize`."""
+    from .fp4_linear import Fp4CutlassLinear
+
+    def mode(modules):
+        if not all(isinstance(m, Fp4CutlassLinear) for m in modules):
+            return None
+        kinds = {m.weight_global_scale is None for m in modules}
+        return None if len(kinds) != 1 else ("block" if kinds.pop() else "global")
+
+    switched = []
+    for layer in stack.layers:
+        attn, mlp = layer.self_attn, layer.mlp
+        for norm, consumers in ((layer.input_layernorm, (attn.q_proj, attn.k_proj, attn.v_proj)),
+                                (layer.post_attention_layernorm, (mlp.gate_proj, mlp.up_proj))):
+            kind = mode(consumers)
+            if kind is not None and norm.dense is None:
+                norm.fused_fp4 = kind
+                switched.append(norm)
+    return switched
 
 
 def expert_scope(name):

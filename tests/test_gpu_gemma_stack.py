@@ -293,9 +293,16 @@ def test_full_width_prefix_layers_nvfp4_every_linear_matches_oracle(H):
             seen = {}
             hooks = [m.register_forward_hook(lambda mod, args, out, name=n: seen.__setitem__(name, (args[0], out)))
                      for n, m in model.named_modules() if isinstance(m, Fp4CutlassLinear)]
+            # the down projections' fused GELU * up path bypasses module hooks (test_gpu_modules holds it to
+            # these tensor ops bit for bit): route them through `forward` here so that they are seen too
+            downs = [layer.mlp.down_proj for layer in model.layers]
+            for m in downs:
+                m.forward_gelu = lambda gate, up, m=m: m(torch.nn.functional.gelu(gate, approximate="tanh") * up)
             out, _ = model(x, pos)
             for hook in hooks:
                 hook.remove()
+            for m in downs:
+                del m.forward_gelu
             torch.cuda.synchronize()
             assert torch.isfinite(out).all() and len(seen) == 14
             shapes = set()
@@ -340,3 +347,43 @@ def test_shared_float_packs_leave_the_prefix_output_unchanged(H):
     with pytest.raises(ValueError):
         with quantize_linears(model, "fp8", scopes=("text",), selector=prefix_scope, grouped=True):
             pass
+
+
+def test_prefix_pass_with_fused_norm_packers_and_cache_writes(H):
+    """The prefix pass as a serving stack runs it: norms that hand NVFP4 packs to q/k/v and gate/up,
+    GELU * up fused in front of the down projection's packer, rotary embedding written straight into
+    preallocated caches.  GELU and rope paths are bit-exact against tensor ops; the fused norm differs
+    from the tensor-op norm by the summation order of mean(x^2) only (at most one bf16 ulp in front of
+    the packer), so the pass stays within 2e-2 of the unfused one and the caches hold the keys / values."""
+    from rk_b200.gemma_stack import (GemmaAttention, GemmaConfig, GemmaStack, fuse_norm_pack_fp4, prefix_scope,
+                                     unfuse_norm_quantize)
+    from rk_b200.optimizations import quantize_linears
+
+    cfg = GemmaConfig(width=256, mlp_dim=1024, depth=2, num_heads=2, num_kv_heads=1, head_dim=128)
+    model = GemmaStack(cfg).to(torch.bfloat16).init_random(3).to(H.DEVICE).eval()
+    t = 200
+    x = H.randn_bf16((1, t, 256), 1.0, 8).to(H.DEVICE)
+    pos = torch.arange(t, device=H.DEVICE)[None]
+    with torch.no_grad():
+        for extra in ({"fp4_global_scale": True}, {}):
+            with quantize_linears(model, "fp4", scopes=("text",), selector=prefix_scope, shared_quant=True, **extra):
+                plain, kv = model(x, pos)
+                caches = [(torch.zeros(1, 1, t, 128, dtype=torch.bfloat16, device=H.DEVICE),
+                           torch.zeros(1, 1, t, 128, dtype=torch.bfloat16, device=H.DEVICE), 0) for _ in range(cfg.depth)]
+                GemmaAttention.fused_rope = True
+                try:
+                    roped, kv2 = model(x, pos, past=caches)
+                    assert torch.equal(roped, plain)
+                    for (k0, v0), (k1, v1) in zip(kv, kv2):
+                        assert torch.equal(k0, k1) and torch.equal(v0, v1)
+                    norms = fuse_norm_pack_fp4(model)
+                    assert len(norms) == 2 * cfg.depth
+                    assert {n.fused_fp4 for n in norms} == {"global" if extra else "block"}
+                    fused, kv3 = model(x, pos, past=caches)
+                    unfuse_norm_quantize(norms)
+                finally:
+                    GemmaAttention.fused_rope = False
+                rel = ((fused.float() - plain.float()).norm() / plain.float().norm()).item()
+                assert rel < 2e-2, rel
+                assert kv3[0][0].data_ptr() == caches[0][0].data_ptr()
+    assert all(n.fused_fp4 is None for n in norms)

@@ -180,6 +180,94 @@ def test_gated_residual_rmsnorm_pack(H, bits):
                         tokens=tokens)  # a gate without a branch
 
 
+@pytest.mark.parametrize("global_scale", [True, False])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_gemma_rmsnorm_pack_nvfp4(H, global_scale, with_residual):
+    """(add +) Gemma RMSNorm + per-tensor amax in one kernel, then the block packer: the stream is
+    exact, the normalized values within one bf16 ulp of the numpy restatement (reduction order), the
+    scale and the pack exactly what the oracle makes of the kernel's own normalized values."""
+    from oracle import blockscale as OB
+    from rk_b200 import _lib
+    from rk_b200.fp4_linear import gemma_rms_norm_pack_nvfp4, pack_nvfp4, tensor_global_scale
+
+    rows, k = 3 * 67, 2048
+    x = H.randn_bf16((3, 67, k), 1.0, 21)
+    res = H.randn_bf16((3, 67, k), 1.0, 22) if with_residual else None
+    w = H.randn_bf16((k,), 0.2, 23)
+    carrier, stream = gemma_rms_norm_pack_nvfp4(x.to(H.DEVICE), w.to(H.DEVICE), 1e-6,
+                                                residual=None if res is None else res.to(H.DEVICE),
+                                                global_scale=global_scale)
+    assert carrier.shape == (3, 67, k) and carrier.leading_shape == (3, 67)
+    s, n = _rmsnorm_oracle(H.to_np(x).reshape(rows, k), H.to_np(w)[None, :].repeat(rows, 0), 1e-6,
+                           None if res is None else H.to_np(res).reshape(rows, k))
+    assert np.array_equal(H.bits(stream).reshape(rows, k), F.bf16_bits(s))
+    # the normalized tensor the kernel produced, recovered through the unfused path on the same stream
+    lib = _lib.load()
+    normed = torch.empty((rows, k), dtype=torch.bfloat16, device=H.DEVICE)
+    flat = stream.reshape(rows, k).contiguous()
+    _lib.check(lib.rk_rmsnorm_tensor_scale(_lib.ptr(flat), None, _lib.ptr(w.to(H.DEVICE)), None, 0, rows, k, 1e-6, 1.0, None,
+                                           _lib.ptr(normed), None, None, 0, _lib.stream_ptr(H.DEVICE)), "norm only")
+    got_n = H.to_np(normed)
+    assert np.abs(got_n - n).max() <= 2.0 ** -7 * np.abs(n).max()
+    ga = OF.tensor_scale(got_n, np.float32(6.0 * 448.0)) if global_scale else None
+    if global_scale:
+        assert carrier.global_scale.item() == ga == tensor_global_scale(normed).item()
+    else:
+        assert carrier.global_scale is None
+    pa, _, swa = OB.pack_nvfp4(got_n, ga)
+    assert np.array_equal(carrier.codes.cpu().numpy(), pa) and np.array_equal(carrier.scale_factors.cpu().numpy(), swa)
+    q, sf = pack_nvfp4(normed, carrier.global_scale)
+    assert torch.equal(q, carrier.codes) and torch.equal(sf, carrier.scale_factors)
+
+
+def test_gemma_rmsnorm_tensor_scale_ignores_non_finite_and_refuses_bad_arguments(H):
+    from rk_b200 import _lib
+    from rk_b200.fp4_linear import gemma_rms_norm_pack_nvfp4
+
+    lib = _lib.load()
+    k = 256
+    x = H.randn_bf16((4, k), 1.0, 31).to(H.DEVICE)
+    x[1, 7] = float("inf")  # that row normalizes to NaN / 0: neither may reach the scale
+    w = torch.zeros(k, dtype=torch.bfloat16, device=H.DEVICE)
+    normed = torch.empty_like(x)
+    scale = torch.empty(1, dtype=torch.float32, device=H.DEVICE)
+    ws = _lib.workspace(H.DEVICE, _lib.WORKSPACE_HEADER)
+    args = lambda kk, div, wsb: (_lib.ptr(x), None, _lib.ptr(w), None, 0, 4, kk, 1e-6, div, None, _lib.ptr(normed),
+                                 _lib.ptr(scale), _lib.ptr(ws), wsb, _lib.stream_ptr(H.DEVICE))
+    _lib.check(lib.rk_rmsnorm_tensor_scale(*args(k, 448.0, ws.numel())), "scale")
+    finite = normed.float()[torch.isfinite(normed.float())]
+    assert scale.item() == np.float32(finite.abs().max().item()) / np.float32(448.0)
+    assert lib.rk_rmsnorm_tensor_scale(*args(k, 0.0, ws.numel())) == _lib.RK_EINVAL
+    assert lib.rk_rmsnorm_tensor_scale(*args(k, 448.0, 8)) == _lib.RK_EWORKSPACE
+    assert lib.rk_rmsnorm_tensor_scale(*args(1 << 20, 448.0, ws.numel())) == _lib.RK_EUNSUPPORTED
+    with pytest.raises(ValueError):
+        gemma_rms_norm_pack_nvfp4(x[:, :40].contiguous(), w[:40], 1e-6)  # K % 32
+
+
+@pytest.mark.parametrize("global_scale", [True, False])
+def test_fp4_forward_gelu_equals_tensor_ops(H, global_scale):
+    """`Fp4CutlassLinear.forward_gelu`: table GELU * up + amax in one kernel, packer, GEMM - the same
+    bits as GELU and the product computed with tensor ops in front of `forward`; gate and up may be
+    column slices of one wider matrix."""
+    from rk_b200.fp4_linear import Fp4CutlassLinear, table_mul_tensor_scale
+    from rk_b200.integer import prepare_gelu
+
+    torch.manual_seed(5)
+    lin = torch.nn.Linear(1024, 264, bias=False, device="cuda", dtype=torch.bfloat16)
+    layer = Fp4CutlassLinear.from_linear(lin, role="linear", target_name="probe", global_scale=global_scale)
+    both = torch.randn(2, 75, 2048, device="cuda", dtype=torch.bfloat16) * 2
+    gate, up = both[..., :1024], both[..., 1024:]
+    want = layer(torch.nn.functional.gelu(gate, approximate="tanh") * up)
+    assert torch.equal(layer.forward_gelu(gate, up), want)
+    assert torch.equal(layer.forward_gelu(gate.contiguous(), up.contiguous()), want)
+    product, scale = table_mul_tensor_scale(gate, up, prepare_gelu(gate.device, gate.dtype, "tanh"), 448.0)
+    eager = (torch.nn.functional.gelu(gate, approximate="tanh") * up).reshape(-1, 1024)
+    assert torch.equal(product, eager)
+    assert scale.item() == np.float32(eager.float().abs().max().item()) / np.float32(448.0)
+    with pytest.raises(ValueError):
+        table_mul_tensor_scale(gate[..., :1020], up[..., :1020], prepare_gelu(gate.device, gate.dtype, "tanh"))
+
+
 # ---------------------------------------------------------------- FP8 / MXFP8 / NVFP4 modules
 @pytest.mark.parametrize("mode", ["per_tensor", "mxfp8"])
 def test_fp8_linear_module(H, mode):
