@@ -8,6 +8,7 @@
 #pragma once
 
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -444,6 +445,34 @@ __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Host side: RK_B200_PDL=0 in the environment launches every kernel fully serialized (a debugging aid).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("RK_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+// Launch of a kernel without dynamic shared memory as a programmatic dependent of its predecessor in
+// the stream.  Such a kernel must execute `pdl_wait()` in EVERY thread before it touches global
+// memory or returns: then its completion implies its predecessor's, and the chain stays ordered.
+// A launch failure surfaces through cudaGetLastError() like one of the <<< >>> form.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------- small numeric helpers
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }

@@ -25,14 +25,6 @@ constexpr int kNumSms = 148;
 
 // Programmatic dependent launch lets a GEMM's on-chip set-up overlap the tail of the kernel before
 // it in the stream.  RK_B200_PDL=0 in the environment turns it off.
-bool use_pdl() {
-  static const bool on = [] {
-    const char* v = std::getenv("RK_B200_PDL");
-    return !(v && v[0] == '0');
-  }();
-  return on;
-}
-
 // Test aid (rk_debug_wait_expiry): a shortened spin limit and a first pipeline stage whose byte
 // count is never met, so that the bounded waits of the next GEMM launches run out.
 int g_debug_wait_limit = 0;
@@ -336,7 +328,7 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_kernel<KIND>, tm_a, tm_b, tm_out, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -386,7 +378,7 @@ int launch_tc_peer(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const PeerM
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_peer_kernel, tm_a, tm_b, maps, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -423,7 +415,7 @@ int launch_tc2(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorM
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc2_kernel<KIND>, tm_a, tm_b, tm_out, tm_sfa, tm_sfb, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -756,7 +748,7 @@ int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMa
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_kernel<BN, UW>, tm_w, tm_x, tm_s, tm_o, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -1097,7 +1089,7 @@ int launch_w4_fold(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUten
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_fold_kernel<BN>, tm_w, tm_x, tm_s, tm_o, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -1132,7 +1124,7 @@ int launch_w4_fold2(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUte
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_w4a16_fold2_kernel, tm_w, tm_x, tm_s, tm_o, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -1228,7 +1220,7 @@ extern "C" int rk_gemm_w4a16_g128(const void* x, const void* q, const void* scal
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = use_pdl() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemv_w4a16_kernel, g);
     if (e != cudaSuccess) {
       cudaGetLastError();
@@ -1432,7 +1424,7 @@ extern "C" int rk_attention_prefix(const void* q, const void* k_cache, const voi
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 2 : 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, rk_attn_prefix_kernel, tm_q, tm_k, tm_vt, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -1536,7 +1528,7 @@ extern "C" int rk_wait_peers(const void* flags, int ranks, void* wait_counter, v
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, wait_peer_flags_kernel, static_cast<const int*>(flags), ranks,
                                      static_cast<int*>(wait_counter), limit, ws.status);
   if (e != cudaSuccess) {

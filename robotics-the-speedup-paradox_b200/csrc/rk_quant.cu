@@ -174,6 +174,8 @@ __global__ void __launch_bounds__(kRowThreads)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const __nv_bfloat16* __restrict__ up,
                   long long up_stride, const __nv_bfloat16* __restrict__ lut, int k, int kpad, int n_rows,
                   uint8_t* __restrict__ q, float* __restrict__ scales, int true_division, int vec_ok) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[kRowThreads / 32];
   const int row = blockIdx.x;
   const int qbytes = BITS == 8 ? kpad : kpad / 2;
@@ -251,6 +253,8 @@ __global__ void __launch_bounds__(256)
 lut_mul_amax_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const __nv_bfloat16* __restrict__ up,
                     long long up_stride, const __nv_bfloat16* __restrict__ lut, long long rows, int k,
                     __nv_bfloat16* __restrict__ out, unsigned* __restrict__ staging) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[8];
   const int per_row = k >> 3;
   const long long total = rows * per_row;
@@ -291,6 +295,8 @@ quant_rows_modulated_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
                             float eps, const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ gate,
                             __nv_bfloat16* __restrict__ residual_out, uint8_t* __restrict__ q,
                             float* __restrict__ scales) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[kRowThreads / 32];
   const int row = blockIdx.x;
   const long long xoff = static_cast<long long>(row) * k;
@@ -372,6 +378,8 @@ rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
                           const __nv_bfloat16* __restrict__ a_ptr, const __nv_bfloat16* __restrict__ b_ptr,
                           int tokens, int k, int kpad, float eps, __nv_bfloat16* __restrict__ sum_out,
                           __nv_bfloat16* __restrict__ norm_out, uint8_t* __restrict__ q, float* __restrict__ scales) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[kRowThreads / 32];
   const int row = blockIdx.x;
   const long long xoff = static_cast<long long>(row) * k;
@@ -451,6 +459,8 @@ rmsnorm_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 __global__ void __launch_bounds__(256)
 pack_w4_g128_kernel(const __nv_bfloat16* __restrict__ w, int n, int k, uint8_t* __restrict__ q,
                     __nv_bfloat16* __restrict__ scales) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const int groups = k / 128;
   const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -483,6 +493,8 @@ pack_w4_g128_kernel(const __nv_bfloat16* __restrict__ w, int n, int k, uint8_t* 
 // ------------------------------------------------------------------ per-tensor FP8
 __global__ void __launch_bounds__(256)
 amax_finite_kernel(const __nv_bfloat16* __restrict__ x, long long elements, unsigned* __restrict__ amax_bits) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[8];
   float local = 0.0f;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
@@ -509,6 +521,8 @@ amax_finite_kernel(const __nv_bfloat16* __restrict__ x, long long elements, unsi
 
 // scale = max(amax / divisor, 1e-12); also clears the staging word for the next call
 __global__ void finalize_scale_kernel(unsigned* amax_bits, float divisor, float* scale_out) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const float amax = __uint_as_float(*amax_bits);
   *scale_out = fmaxf(__fdiv_rn(amax, divisor), 1e-12f);
   *amax_bits = 0u;
@@ -517,6 +531,8 @@ __global__ void finalize_scale_kernel(unsigned* amax_bits, float divisor, float*
 __global__ void __launch_bounds__(256)
 to_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long elements, const float* __restrict__ scale,
               uint8_t* __restrict__ q) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const float inverse = __fdiv_rn(1.0f, *scale);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
   for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; idx < elements;
@@ -563,6 +579,8 @@ __device__ __forceinline__ uint32_t ue8m0_roundup(float x) {
 __global__ void __launch_bounds__(256)
 pack_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, uint8_t* __restrict__ q,
                   uint8_t* __restrict__ sf) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const long long groups_padded = (k + 127) / 128 * 4;
   const long long rows_padded = (rows + 127) / 128 * 128;
   const long long thread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -624,6 +642,8 @@ template <int FMT>
 __global__ void __launch_bounds__(256)
 pack_mx_ceil_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, uint8_t* __restrict__ q,
                     uint8_t* __restrict__ sf) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const long long groups_padded = (k + 127) / 128 * 4;
   const long long rows_padded = (rows + 127) / 128 * 128;
   const long long thread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -668,6 +688,8 @@ pack_mx_ceil_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long lo
 __global__ void __launch_bounds__(256)
 pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, const float* __restrict__ global,
                   uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const long long groups = k / 16;
   const long long groups_padded = (groups + 3) / 4 * 4;
   const long long rows_padded = (rows + 127) / 128 * 128;
@@ -740,6 +762,8 @@ __device__ __forceinline__ void load8_swiglu(const __nv_bfloat16* gate_up, long 
 __global__ void __launch_bounds__(256)
 swiglu_pack_mxfp8_ceil_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter, int interleaved,
                               uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const long long groups_padded = (inter + 127) / 128 * 4;
   const long long rows_padded = (rows + 127) / 128 * 128;
   const long long thread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -788,6 +812,8 @@ swiglu_pack_mxfp8_ceil_kernel(const __nv_bfloat16* __restrict__ gate_up, long lo
 __global__ void __launch_bounds__(256)
 swiglu_amax_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter,
                    unsigned* __restrict__ amax_bits) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[8];
   float local = 0.0f;
   const long long elements = rows * inter;
@@ -815,6 +841,8 @@ swiglu_amax_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, lo
 __global__ void __launch_bounds__(256)
 swiglu_to_fp8_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter,
                      const float* __restrict__ scale, uint8_t* __restrict__ q) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const float inverse = __fdiv_rn(1.0f, *scale);
   const long long elements = rows * inter;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
@@ -839,6 +867,8 @@ swiglu_to_fp8_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, 
 __global__ void __launch_bounds__(256)
 swiglu_pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter, int interleaved,
                          uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const long long groups = inter / 16;
   const long long groups_padded = (groups + 3) / 4 * 4;
   const long long rows_padded = (rows + 127) / 128 * 128;
@@ -871,6 +901,8 @@ rmsnorm_producer_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ weight, int rows, int k, float eps,
                         __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ norm_out,
                         unsigned* __restrict__ amax_bits, uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   __shared__ float scratch[kRowThreads / 32];
   const int row = blockIdx.x;
   const int groups = k / 16;
@@ -971,16 +1003,16 @@ int launch_quant_rows(const void* x, int64_t rows, int64_t total_rows, int64_t k
   if (total_rows >= 1024) threads = kpad <= 2048 ? 64 : (kpad <= 4096 ? 128 : kRowThreads);
   switch (mode) {
     case RK_ACT_PLAIN:
-      quant_rows_kernel<BITS, RK_ACT_PLAIN><<<grid, threads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
+      launch_pdl(quant_rows_kernel<BITS, RK_ACT_PLAIN>, grid, threads, st, xb, xs, ub, us, lb, static_cast<int>(k), kpad,
                                                                           static_cast<int>(rows), qb, scales,
                                                                           true_division, vec_ok);
       break;
     case RK_ACT_LUT_MUL:
-      quant_rows_kernel<BITS, RK_ACT_LUT_MUL><<<grid, threads, 0, st>>>(
+      launch_pdl(quant_rows_kernel<BITS, RK_ACT_LUT_MUL>, grid, threads, st, 
           xb, xs, ub, us, lb, static_cast<int>(k), kpad, static_cast<int>(rows), qb, scales, true_division, vec_ok);
       break;
     default:
-      quant_rows_kernel<BITS, RK_ACT_LUT><<<grid, threads, 0, st>>>(xb, xs, ub, us, lb, static_cast<int>(k), kpad,
+      launch_pdl(quant_rows_kernel<BITS, RK_ACT_LUT>, grid, threads, st, xb, xs, ub, us, lb, static_cast<int>(k), kpad,
                                                                         static_cast<int>(rows), qb, scales,
                                                                         true_division, vec_ok);
   }
@@ -1036,11 +1068,11 @@ extern "C" int rk_quant_rows_modulated(const void* x, const void* scale, const v
   const int kpad = static_cast<int>(round_up(k, 128));
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
   if (bits == 8)
-    quant_rows_modulated_kernel<8><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+    launch_pdl(quant_rows_modulated_kernel<8>, static_cast<unsigned>(rows), kRowThreads, as_stream(stream), 
         b(x), b(scale), b(shift), static_cast<int>(k), kpad, static_cast<int>(tokens), layer_norm, eps, b(y), b(gate),
         static_cast<__nv_bfloat16*>(residual_out), static_cast<uint8_t*>(q), scales);
   else
-    quant_rows_modulated_kernel<4><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+    launch_pdl(quant_rows_modulated_kernel<4>, static_cast<unsigned>(rows), kRowThreads, as_stream(stream), 
         b(x), b(scale), b(shift), static_cast<int>(k), kpad, static_cast<int>(tokens), layer_norm, eps, b(y), b(gate),
         static_cast<__nv_bfloat16*>(residual_out), static_cast<uint8_t*>(q), scales);
   return check_launch("quant_rows_modulated");
@@ -1062,11 +1094,11 @@ int launch_rmsnorm_quant_rows(const char* who, const void* x, const void* residu
   const int kpad = static_cast<int>(round_up(k, 128));
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
   if (bits == 8)
-    rmsnorm_quant_rows_kernel<8><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+    launch_pdl(rmsnorm_quant_rows_kernel<8>, static_cast<unsigned>(rows), kRowThreads, as_stream(stream), 
         b(x), b(residual), b(gate), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
         static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), static_cast<uint8_t*>(q), scales);
   else
-    rmsnorm_quant_rows_kernel<4><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+    launch_pdl(rmsnorm_quant_rows_kernel<4>, static_cast<unsigned>(rows), kRowThreads, as_stream(stream), 
         b(x), b(residual), b(gate), b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), kpad, eps,
         static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), static_cast<uint8_t*>(q), scales);
   return check_launch(who);
@@ -1108,10 +1140,10 @@ extern "C" int rk_rmsnorm_tensor_scale(const void* x, const void* residual, cons
     staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);  // zero between calls
   }
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
-  rmsnorm_quant_rows_kernel<16><<<static_cast<unsigned>(rows), kRowThreads, 0, as_stream(stream)>>>(
+  launch_pdl(rmsnorm_quant_rows_kernel<16>, static_cast<unsigned>(rows), kRowThreads, as_stream(stream), 
       b(x), b(residual), nullptr, b(scale), b(shift), static_cast<int>(tokens), static_cast<int>(k), 0, eps,
       static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), reinterpret_cast<uint8_t*>(staging), nullptr);
-  if (staging != nullptr) finalize_scale_kernel<<<1, 1, 0, as_stream(stream)>>>(staging, divisor, scale_out);
+  if (staging != nullptr) launch_pdl(finalize_scale_kernel, 1, 1, as_stream(stream), staging, divisor, scale_out);
   return check_launch(who);
 }
 
@@ -1133,9 +1165,9 @@ extern "C" int rk_lut_mul_tensor_scale(const void* x, int64_t x_stride, const vo
   const long long vectors = rows * (k / 8);
   const unsigned blocks = static_cast<unsigned>(std::min<long long>((vectors + 255) / 256, 148LL * 8));
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
-  lut_mul_amax_kernel<<<blocks, 256, 0, as_stream(stream)>>>(b(x), x_stride, b(up), up_stride, b(lut), rows,
+  launch_pdl(lut_mul_amax_kernel, blocks, 256, as_stream(stream), b(x), x_stride, b(up), up_stride, b(lut), rows,
                                                              static_cast<int>(k), static_cast<__nv_bfloat16*>(out), staging);
-  if (staging != nullptr) finalize_scale_kernel<<<1, 1, 0, as_stream(stream)>>>(staging, divisor, scale_out);
+  if (staging != nullptr) launch_pdl(finalize_scale_kernel, 1, 1, as_stream(stream), staging, divisor, scale_out);
   return check_launch(who);
 }
 
@@ -1145,7 +1177,7 @@ extern "C" int rk_pack_w4_g128(const void* w, int64_t n, int64_t k, void* q, voi
   if (!aligned16(w)) return fail(RK_EINVAL, "rk_pack_w4_g128: w must be 16-byte aligned");
   const long long warps = static_cast<long long>(n) * (k / 128);
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
-  pack_w4_g128_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(w), static_cast<int>(n),
+  launch_pdl(pack_w4_g128_kernel, blocks, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(w), static_cast<int>(n),
                                                              static_cast<int>(k), static_cast<uint8_t*>(q),
                                                              static_cast<__nv_bfloat16*>(scales));
   return check_launch("pack_w4_g128");
@@ -1160,9 +1192,9 @@ int tensor_amax_scale(const void* x, int64_t elements, float divisor, float* sca
   unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
   long long blocks = (elements + 2047) / 2048;
   if (blocks > 1184) blocks = 1184;  // 148 SMs x 8 CTAs
-  amax_finite_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), elements,
+  launch_pdl(amax_finite_kernel, static_cast<unsigned>(blocks), 256, st, static_cast<const __nv_bfloat16*>(x), elements,
                                                                     staging);
-  finalize_scale_kernel<<<1, 1, 0, st>>>(staging, divisor, scale_out);
+  launch_pdl(finalize_scale_kernel, 1, 1, st, staging, divisor, scale_out);
   return check_launch(who);
 }
 }  // namespace
@@ -1174,7 +1206,7 @@ extern "C" int rk_quant_tensor_fp8_with_scale(const void* x, int64_t elements, c
     return fail(RK_EINVAL, "rk_quant_tensor_fp8_with_scale: bad size or alignment");
   long long blocks = (elements + 2047) / 2048;
   if (blocks > 2368) blocks = 2368;
-  to_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+  launch_pdl(to_fp8_kernel, static_cast<unsigned>(blocks), 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x),
                                                                               elements, scale, static_cast<uint8_t*>(q));
   return check_launch("to_fp8");
 }
@@ -1204,7 +1236,7 @@ extern "C" int rk_pack_mxfp8(const void* x, int64_t rows, int64_t k, void* q, vo
   if (!aligned16(x) || !aligned16(q)) return fail(RK_EINVAL, "rk_pack_mxfp8: pointers must be 16-byte aligned");
   const long long blocks32 = ((rows + 127) / 128 * 128) * ((k + 127) / 128 * 4);
   const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
-  pack_mxfp8_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k,
+  launch_pdl(pack_mxfp8_kernel, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x), rows, k,
                                                          static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   return check_launch("pack_mxfp8");
 }
@@ -1216,7 +1248,7 @@ extern "C" int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float
   if (!aligned16(x) || !aligned16(q)) return fail(RK_EINVAL, "rk_pack_nvfp4: pointers must be 16-byte aligned");
   const long long threads = ((rows + 127) / 128 * 128) * ((k / 16 + 3) / 4 * 4);
   const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
-  pack_nvfp4_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k, global_scale,
+  launch_pdl(pack_nvfp4_kernel, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x), rows, k, global_scale,
                                                          static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   return check_launch("pack_nvfp4");
 }
@@ -1234,10 +1266,10 @@ extern "C" int rk_rmsnorm_quant_fp8(const void* x, const void* residual, const v
   cudaStream_t st = as_stream(stream);
   unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
-  rk::rmsnorm_producer_kernel<0><<<static_cast<unsigned>(rows), rk::kRowThreads, 0, st>>>(
+  launch_pdl(rk::rmsnorm_producer_kernel<0>, static_cast<unsigned>(rows), rk::kRowThreads, st, 
       b(x), b(residual), b(weight), static_cast<int>(rows), static_cast<int>(k), eps,
       static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), staging, nullptr, nullptr);
-  rk::finalize_scale_kernel<<<1, 1, 0, st>>>(staging, 448.0f, scale_out);
+  launch_pdl(rk::finalize_scale_kernel, 1, 1, st, staging, 448.0f, scale_out);
   int rc = check_launch(who);
   if (rc != RK_OK) return rc;
   return rk_quant_tensor_fp8_with_scale(norm_out, rows * k, scale_out, q, stream);
@@ -1257,12 +1289,12 @@ extern "C" int rk_swiglu_quant_fp8(const void* gate_up, int64_t rows, int64_t in
   if (scale_in == nullptr) {
     if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
     unsigned* staging = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64);
-    rk::swiglu_amax_kernel<<<static_cast<unsigned>(blocks > 1184 ? 1184 : blocks), 256, 0, st>>>(
+    launch_pdl(rk::swiglu_amax_kernel, static_cast<unsigned>(blocks > 1184 ? 1184 : blocks), 256, st, 
         static_cast<const __nv_bfloat16*>(gate_up), rows, inter, staging);
-    rk::finalize_scale_kernel<<<1, 1, 0, st>>>(staging, 448.0f, scale_out);
+    launch_pdl(rk::finalize_scale_kernel, 1, 1, st, staging, 448.0f, scale_out);
     scale = scale_out;
   }
-  rk::swiglu_to_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up), rows,
+  launch_pdl(rk::swiglu_to_fp8_kernel, static_cast<unsigned>(blocks), 256, st, static_cast<const __nv_bfloat16*>(gate_up), rows,
                                                                           inter, scale, static_cast<uint8_t*>(q));
   return check_launch(who);
 }
@@ -1277,7 +1309,7 @@ extern "C" int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const 
     return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
   const unsigned rows_padded = static_cast<unsigned>((rows + 127) / 128 * 128);
-  rk::rmsnorm_producer_kernel<1><<<rows_padded, rk::kRowThreads, 0, as_stream(stream)>>>(
+  launch_pdl(rk::rmsnorm_producer_kernel<1>, rows_padded, rk::kRowThreads, as_stream(stream), 
       b(x), b(residual), b(weight), static_cast<int>(rows), static_cast<int>(k), eps,
       static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), nullptr, static_cast<uint8_t*>(q),
       static_cast<uint8_t*>(sf));
@@ -1293,7 +1325,7 @@ extern "C" int rk_swiglu_pack_nvfp4_layout(const void* gate_up, int64_t rows, in
   if (!aligned16(gate_up) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   const long long threads = ((rows + 127) / 128 * 128) * ((inter / 16 + 3) / 4 * 4);
   const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
-  rk::swiglu_pack_nvfp4_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+  launch_pdl(rk::swiglu_pack_nvfp4_kernel, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
                                                                    interleaved ? 1 : 0, static_cast<uint8_t*>(q),
                                                                    static_cast<uint8_t*>(sf));
   return check_launch(who);
@@ -1310,10 +1342,10 @@ static int pack_mx_ceil(const void* x, int64_t rows, int64_t k, int fmt, void* q
   const long long blocks32 = ((rows + 127) / 128 * 128) * ((k + 127) / 128 * 4);
   const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
   if (fmt == 0)
-    rk::pack_mx_ceil_kernel<0><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k,
+    launch_pdl(rk::pack_mx_ceil_kernel<0>, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x), rows, k,
                                                                    static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   else
-    rk::pack_mx_ceil_kernel<1><<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), rows, k,
+    launch_pdl(rk::pack_mx_ceil_kernel<1>, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x), rows, k,
                                                                    static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   return check_launch(who);
 }
@@ -1327,7 +1359,7 @@ extern "C" int rk_swiglu_pack_mxfp8_w4a8(const void* gate_up, int64_t rows, int6
   if (!aligned16(gate_up) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
   const long long blocks32 = ((rows + 127) / 128 * 128) * ((inter + 127) / 128 * 4);
   const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
-  rk::swiglu_pack_mxfp8_ceil_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+  launch_pdl(rk::swiglu_pack_mxfp8_ceil_kernel, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
                                                                         interleaved ? 1 : 0, static_cast<uint8_t*>(q),
                                                                         static_cast<uint8_t*>(sf));
   return check_launch(who);

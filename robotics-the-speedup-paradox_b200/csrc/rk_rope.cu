@@ -17,6 +17,7 @@
 
 #include <cuda_bf16.h>
 
+#include "rk_common.cuh"
 #include "rk_host.h"
 
 namespace rk {
@@ -61,6 +62,8 @@ struct RopeParams {
 
 __global__ void __launch_bounds__(256)
 rope_cache_update_kernel(const RopeParams p) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int units = p.heads + 2 * p.kv_heads;  // per row: query heads, key heads, value heads
@@ -161,7 +164,7 @@ static int rope_cache_update_impl(const void* q, int64_t q_stride, const void* k
   const long long jobs = batch * tokens * (heads + 2 * kv_heads);
   const int warps = 8;
   const unsigned blocks = static_cast<unsigned>((jobs + warps - 1) / warps);
-  rope_cache_update_kernel<<<blocks, warps * 32, 0, as_stream(stream)>>>(p);
+  launch_pdl(rope_cache_update_kernel, blocks, warps * 32, as_stream(stream), p);
   return check_launch(who);
 }
 
