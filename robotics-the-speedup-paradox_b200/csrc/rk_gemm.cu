@@ -662,10 +662,6 @@ int run_tc(const TcArgs& a) {
     p.peer_count = a.peer->count;
     p.peer_rank = a.peer->rank;
     p.peer_mask = 0xFFu;
-    if (const char* e = std::getenv("RK_B200_PEER_STORES")) {  // measurement aid: "local" / "remote" halves of the exchange
-      if (e[0] == 'l') p.peer_mask = 1u << a.peer->rank;
-      else if (e[0] == 'r') p.peer_mask = 0xFFu & ~(1u << a.peer->rank);
-    }
     p.peer_epoch = a.peer->epoch;
     p.peer_counter = reinterpret_cast<unsigned*>(ws.status) + 32;  // a word of the workspace header, zero between launches
   }

@@ -103,7 +103,7 @@ struct GemmParams {
   long long peer_ld, peer_col0;  // row stride of the full output and first column of this slab (multicast form)
   int* peer_flags[8];            // every rank's flag array [ranks]
   int peer_count, peer_rank;
-  unsigned peer_mask;            // ranks whose buffer receives the TMA stores (all of them, unless a measurement narrows it)
+  unsigned peer_mask;            // ranks whose buffer receives the TMA stores (all of them)
   int* peer_epoch;               // this rank's call counter (device memory): the launch that finishes call e writes e
   unsigned* peer_counter;        // device word counting the CTAs of this launch that have finished
   int* status;                // device status word

@@ -4,6 +4,7 @@
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py [w4a16] [w8a8] [fp8] [mxfp8] [nvfp4] [quant]
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py w8a8:400x8192x1024 quant:16384x2048   # explicit shapes
     python robotics-the-speedup-paradox_b200/rk_b200/microbench.py layer    # per-kernel device time of one expert layer
+    python robotics-the-speedup-paradox_b200/rk_b200/microbench.py prefix_layer   # the same for one NVFP4 prefix layer
 
 Each shape is timed as a CUDA graph of back-to-back launches that rotate through enough independent
 weight copies to exceed the 126 MB L2 (so a launch streams its weights from HBM), between two CUDA
@@ -253,6 +254,55 @@ def layer_breakdown(envs=8, prefix=816, repeats=5):
         GemmaAttention.fused_attention = False
 
 
+def prefix_layer_breakdown(tokens=816, depth=2, repeats=5):
+    """Per-kernel device time of one layer of the cfg4 prefix stack (Gemma-2B widths, every linear NVFP4
+    with the fp32 per-tensor scale, shared packs): tensor-op elementwise work against the fused form
+    (norm + amax kernel, GELU * up + amax kernel, rotary embedding into preallocated caches)."""
+    from dataclasses import replace
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from rk_b200.gemma_stack import GemmaStack, fuse_norm_pack_fp4, gemma_2b, prefix_scope, unfuse_norm_quantize
+    from rk_b200.optimizations import quantize_linears
+
+    dev = torch.device("cuda:0")
+    cfg = replace(gemma_2b(), depth=depth)
+    model = GemmaStack(cfg).to(torch.bfloat16).init_random(1).to(dev).eval()
+    x = torch.randn(1, tokens, cfg.width, device=dev).to(torch.bfloat16)
+    pos = torch.arange(tokens, device=dev)[None]
+    caches = [tuple(torch.zeros(1, cfg.num_kv_heads, tokens, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+                    for _ in range(2)) + (0,) for _ in range(depth)]
+
+    def run(tag, past):
+        with torch.no_grad():
+            for _ in range(3):
+                model(x, pos, past=past)
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(repeats):
+                    model(x, pos, past=past)
+                torch.cuda.synchronize()
+        rows = [(e.device_time_total / repeats / depth, e.count / repeats / depth, e.key) for e in prof.key_averages()
+                if e.device_time_total > 0]
+        rows.sort(reverse=True)
+        print(f"--- {tag}: {sum(r[0] for r in rows):.1f} us of device time per layer ({tokens} tokens)")
+        for t, count, key in rows[:16]:
+            print(f"{t:8.1f} us  x{count:4.1f}  {key[:120]}")
+
+    with quantize_linears(model, "fp4", scopes=("text",), selector=prefix_scope, fp4_global_scale=True, shared_quant=True):
+        downs = [layer.mlp.down_proj for layer in model.layers]
+        for m in downs:  # tensor-op GELU * up in front of the down projection, as the reference's harness runs it
+            m.forward_gelu = lambda gate, up, m=m: m(torch.nn.functional.gelu(gate, approximate="tanh") * up)
+        run("NVFP4 linears, tensor-op norms / GELU / rotary embedding", None)
+        for m in downs:
+            del m.forward_gelu
+        norms = fuse_norm_pack_fp4(model)
+        for layer in model.layers:
+            layer.self_attn.fused_rope = True
+        run("NVFP4 linears, fused norm + amax, GELU * up + amax, rotary embedding into caches", caches)
+        unfuse_norm_quantize(norms)
+
+
 def main(argv):
     which = argv or ["w4a16", "w8a8", "fp8", "mxfp8", "nvfp4", "quant"]
     b = Bench()
@@ -273,6 +323,9 @@ def main(argv):
     which = [a for a in which if ":" not in a]
     if "layer" in which:
         layer_breakdown()
+        return
+    if "prefix_layer" in which:
+        prefix_layer_breakdown()
         return
     if "w4a16" in which:
         for m in (1, 8, 50, 128, 256):
