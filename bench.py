@@ -1174,11 +1174,18 @@ def main():
     host_out = {m: torch.empty((m, N), dtype=torch.bfloat16).pin_memory() for m in M_LIST}
     dev_x = {m: torch.empty_like(xs[m]) for m in M_LIST}
 
+    # the four launches of a step go out on two streams, largest first, so that the copy of one launch's
+    # result back to the host (8.4 MB at M = 256: the longest item of a step) overlaps the others'
+    # uploads and kernels; every step ends with all results in host memory
+    e2e_streams = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
+    e2e_order = sorted(M_LIST, reverse=True)
+
     def e2e_step(i):
-        for j, m in enumerate(M_LIST):
-            dev_x[m].copy_(host_x[m], non_blocking=True)
-            y = layers[(i * len(M_LIST) + j) % copies](dev_x[m])
-            host_out[m].copy_(y, non_blocking=True)
+        for j, m in enumerate(e2e_order):
+            with torch.cuda.stream(e2e_streams[j % 2]):
+                dev_x[m].copy_(host_x[m], non_blocking=True)
+                y = layers[(i * len(M_LIST) + j) % copies](dev_x[m])
+                host_out[m].copy_(y, non_blocking=True)
         torch.cuda.synchronize(device)
 
     e2e_steps = max(10, min(args.steps, 100))
@@ -1260,7 +1267,8 @@ def main():
             "config": workload_config(copies), "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TOPS",
                     "h2d_bytes_per_step": sum(m * K * 2 for m in M_LIST),
-                    "d2h_bytes_per_step": sum(m * N * 2 for m in M_LIST), "steps": e2e_steps},
+                    "d2h_bytes_per_step": sum(m * N * 2 for m in M_LIST), "steps": e2e_steps,
+                    "streams": len(e2e_streams)},
             "gpu_launches": timed_launches, "roofline": roofline, "per_case": per_case,
             "cpu_baseline": cpu_baseline, "device_status": status, "action_chunk": chunk,
             "per_config": per_config, "column_parallel": column_parallel,
