@@ -304,3 +304,64 @@ def test_fp8_prefill_scale_refresh_is_configured_per_model():
     stats = P8.fp8_prefill_scale_refresh_stats(model)
     assert stats["states"] == 2 and stats["intervals"] == [8] and stats["reuses"] == 0
     assert P8.configure_fp8_prefill_scale_refresh(torch.nn.Sequential(Layer(False))) == {"interval": 1, "states": 0}
+
+
+def _fake_fp4(in_features, out_features, global_scale):
+    import torch
+
+    from rk_b200.fp4_linear import Fp4CutlassLinear
+
+    return Fp4CutlassLinear(torch.zeros(out_features, in_features // 2, dtype=torch.uint8), torch.zeros(16, dtype=torch.uint8),
+                            torch.ones(1) if global_scale else None, None, in_features, out_features, "linear", "probe")
+
+
+def test_fused_fp4_norms_need_uniform_fp4_consumers_and_plain_weights():
+    """`fuse_norm_pack_fp4` switches a norm only when every linear that reads it is an NVFP4 layer with the
+    same per-tensor-scale setting, never an adaptive norm; `unfuse_norm_quantize` switches them back."""
+    from rk_b200.gemma_stack import GemmaConfig, GemmaStack, fuse_norm_pack_fp4, unfuse_norm_quantize
+
+    cfg = GemmaConfig(width=128, mlp_dim=256, depth=3, num_heads=2, num_kv_heads=1, head_dim=64)
+    stack = GemmaStack(cfg)
+    qd, kvd = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+    # layer 0: everything NVFP4 with per-tensor scales; layer 1: q/k/v mixed scale settings, gate/up block-only;
+    # layer 2: one bf16 projection left in each group
+    l0, l1, l2 = stack.layers
+    l0.self_attn.q_proj, l0.self_attn.k_proj, l0.self_attn.v_proj = (_fake_fp4(128, qd, True), _fake_fp4(128, kvd, True),
+                                                                      _fake_fp4(128, kvd, True))
+    l0.mlp.gate_proj, l0.mlp.up_proj = _fake_fp4(128, 256, True), _fake_fp4(128, 256, True)
+    l1.self_attn.q_proj, l1.self_attn.k_proj, l1.self_attn.v_proj = (_fake_fp4(128, qd, True), _fake_fp4(128, kvd, False),
+                                                                      _fake_fp4(128, kvd, True))
+    l1.mlp.gate_proj, l1.mlp.up_proj = _fake_fp4(128, 256, False), _fake_fp4(128, 256, False)
+    l2.self_attn.q_proj = _fake_fp4(128, qd, True)
+    l2.mlp.gate_proj = _fake_fp4(128, 256, True)
+    norms = fuse_norm_pack_fp4(stack)
+    assert norms == [l0.input_layernorm, l0.post_attention_layernorm, l1.post_attention_layernorm]
+    assert [n.fused_fp4 for n in norms] == ["global", "global", "block"]
+    assert l1.input_layernorm.fused_fp4 is None and l2.input_layernorm.fused_fp4 is None
+    assert stack.norm.fused_fp4 is None  # the final norm feeds no linear
+    unfuse_norm_quantize(norms)
+    assert all(n.fused_fp4 is None for n in norms)
+    adaptive = GemmaStack(GemmaConfig(width=128, mlp_dim=256, depth=1, num_heads=2, num_kv_heads=1, head_dim=64,
+                                      adarms_cond_dim=128))
+    layer = adaptive.layers[0]
+    layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj = (_fake_fp4(128, qd, True), _fake_fp4(128, kvd, True),
+                                                                                _fake_fp4(128, kvd, True))
+    assert fuse_norm_pack_fp4(adaptive) == []
+
+
+def test_packed_nvfp4_activation_carrier():
+    import torch
+
+    from rk_b200.fp4_linear import PackedNvfp4Activation
+    from rk_b200.gemma_stack import _leading_shape
+
+    carrier = PackedNvfp4Activation(torch.zeros(6, 64, dtype=torch.uint8), torch.zeros(512, dtype=torch.uint8), torch.ones(1),
+                                    (2, 3), 128)
+    assert carrier.shape == (2, 3, 128) and carrier.shape[:-1] == (2, 3) and _leading_shape(carrier) == (2, 3)
+    layer = _fake_fp4(128, 64, True)
+    q, sf, ga = layer.pack_input(carrier)
+    assert q is carrier.codes and sf is carrier.scale_factors and ga is carrier.global_scale
+    with pytest.raises(ValueError):
+        _fake_fp4(256, 64, True).pack_input(carrier)      # feature count
+    with pytest.raises(ValueError):
+        _fake_fp4(128, 64, False).pack_input(carrier)     # a per-tensor scale the layer does not expect
