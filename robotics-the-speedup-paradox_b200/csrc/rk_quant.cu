@@ -706,9 +706,25 @@ pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long
   load8(x + row * k + group * 16, true, 8, *reinterpret_cast<float(*)[8]>(&v[0]));
   load8(x + row * k + group * 16 + 8, true, 8, *reinterpret_cast<float(*)[8]>(&v[8]));
   if (global != nullptr) {
+    // v / g for sixteen values and one divisor.  With r = fl(1 / g) correctly rounded, q = fl(v r)
+    // corrected by its exact residual - e = fma(-q, g, v), q' = fma(e, r, q) - IS the correctly rounded
+    // quotient (Markstein's theorem) unless the significand of g is all ones; the magnitude window
+    // keeps every intermediate in the normal range.  Everything else (zeros, whose sign the division
+    // keeps, tiny and huge values, such a divisor) takes the IEEE division.  16 divisions cost ~10
+    // instructions each and made this kernel instruction bound.
     const float g = *global;
+    const float r = __frcp_rn(g);
+    const bool divisor_ok = (__float_as_uint(g) & 0x7FFFFFu) != 0x7FFFFFu && g >= 0x1p-40f && g <= 0x1p40f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __fdiv_rn(v[i], g);
+    for (int i = 0; i < 16; ++i) {
+      const float a = fabsf(v[i]);
+      if (divisor_ok && a >= 0x1p-60f && a <= 0x1p60f) {
+        const float q = __fmul_rn(v[i], r);
+        v[i] = __fmaf_rn(__fmaf_rn(-q, g, v[i]), r, q);
+      } else {
+        v[i] = __fdiv_rn(v[i], g);
+      }
+    }
   }
   float amax = 0.0f;
 #pragma unroll

@@ -154,6 +154,30 @@ def test_nvfp4_pack_and_gemm_reference_mode(H, shape):
     assert H.rel_frobenius(H.to_np(out), want) < TOL
 
 
+@pytest.mark.parametrize("divisor", [0.0123, 2.0 ** -9, float(np.float32(1.9999999) * np.float32(2.0 ** -7)), 2.0 ** -50, 3.0e5])
+def test_nvfp4_pack_division_by_the_tensor_scale_is_exact(H, divisor):
+    """The packer divides by the per-tensor scale with a reciprocal and an exact residual correction where
+    that is provably the IEEE quotient, and with the IEEE division elsewhere (zeros of either sign, tiny
+    and huge values, a divisor whose significand is all ones, divisors outside 2^-40 .. 2^40): every bf16
+    value with an exponent in -70 .. 70, both signs, and the zeros give the oracle's codes and scale bytes."""
+    bits = np.arange(65536, dtype=np.uint32)
+    vals = (bits << 16).view(np.float32)
+    mag = np.abs(vals)
+    keep = (mag == 0) | ((mag >= 2.0 ** -70) & (mag <= 2.0 ** 70))
+    vals = vals[keep]
+    rng = np.random.default_rng(5)
+    vals = np.concatenate([vals, rng.permutation(vals)])  # blocks of neighbours and blocks of mixed magnitudes
+    pad = (-len(vals)) % 64
+    vals = np.concatenate([vals, np.zeros(pad, dtype=np.float32)]).reshape(-1, 64)
+    x = torch.from_numpy(vals).to(torch.bfloat16)
+    assert np.array_equal(H.to_np(x), vals)  # all values are bf16 already
+    g = np.float32(divisor)
+    q, sf = nv_pack(H, x.to(H.DEVICE), torch.tensor([g], dtype=torch.float32, device=H.DEVICE))
+    want_q, _, want_sf = OB.pack_nvfp4(vals, g)
+    assert np.array_equal(sf.cpu().numpy(), want_sf)
+    assert np.array_equal(q.cpu().numpy(), want_q)
+
+
 def test_nvfp4_with_per_tensor_scales(H):
     """The benchmark's variant: fp32 per-tensor scale amax / (6 * 448) on both operands."""
     m, n, k = 64, 256, 512
