@@ -11,7 +11,7 @@ tree; the output directory is ignored by git.  nvcc cross-compiles without a GPU
 are loaded with `torch.ops.load_library` on a machine that has a B200.
 
 Their large-tile GEMM specialisations use thread-block clusters with multicast copies, so the
-libraries are listed in `.gpurunignore.multi` and are only ever loaded by single-GPU processes
+libraries are kept out of multi-GPU runs and are only ever loaded by single-GPU processes
 (`oracle/ref_kernels.py`).
 
 Usage: python oracle/build_ref_kernels.py [backend ...]     (default: all of BACKENDS)
