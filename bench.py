@@ -1211,7 +1211,12 @@ def main():
             chunk["box_chunks_per_s"] = replicas.whole_job_rate(chunk["envs"], info, worst)
 
     elapsed_ms, e2e_ms = replicas.max_over_ranks([elapsed_ms, e2e_s * 1e3], info, device)
-    column_parallel = column_parallel_leg(info, device) if world > 1 else None
+    column_parallel = None
+    if world > 1:
+        try:
+            column_parallel = column_parallel_leg(info, device)
+        except Exception as exc:  # an auxiliary figure must not cost the headline line; the failure is reported in its place
+            column_parallel = {"error": f"{type(exc).__name__}: {exc}"}
 
     step_ops = sum(algorithmic_ops(m) for m in M_LIST)
     value = replicas.whole_job_rate(step_ops * args.steps, info, elapsed_ms) / 1e12
