@@ -1,6 +1,6 @@
 """The column-parallel FP8 GEMM whose epilogue performs the exchange, on ONE GPU.
 
-Two "ranks" are emulated as two launches on the same device, one after the other on one stream:
+Two to eight "ranks" are emulated as launches on the same device, one after the other on one stream:
 each computes its slab of columns and stores it into BOTH full-width output buffers, then raises its
 flag in both flag arrays.  The wait kernels are launched only after both GEMMs (nothing ever waits
 for a kernel that has not been launched), so they return at once.  Both buffers must equal the
@@ -28,7 +28,8 @@ def _table(tensors):
 
 
 # slab widths that are and are not multiples of the store chunk; row counts on both sides of the swap threshold (1024)
-@pytest.mark.parametrize("m,slab,k,ranks", [(300, 256, 448, 2), (816, 160, 512, 2), (50, 64, 128, 4), (130, 2048, 2048, 2), (1300, 320, 256, 2)])
+@pytest.mark.parametrize("m,slab,k,ranks", [(300, 256, 448, 2), (816, 160, 512, 2), (50, 64, 128, 4), (130, 2048, 2048, 2), (1300, 320, 256, 2),
+                                            (64, 64, 128, 8), (816, 2048, 2048, 8)])  # the last: the benchmark's projection over eight ranks
 def test_two_emulated_ranks_fill_every_buffer(H, m, slab, k, ranks):
     from rk_b200 import fp8_linear as P8
 
