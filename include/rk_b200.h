@@ -171,6 +171,19 @@ int rk_lut_mul_tensor_scale(const void* x, int64_t x_stride, const void* up, int
 int rk_gemm_int(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
                 int64_t m, int64_t n, int64_t kpad, int bits, int tactic, void* workspace,
                 size_t workspace_bytes, void* stream);
+/* rk_gemm_int with the residual update of a decoder layer applied in the epilogue, so that the
+ * projection (o_proj, down_proj) writes the new residual stream itself:
+ *   out[r, c] = bf16( residual[r, c] + t ),  t = y  (gate == NULL)  or  bf16( y * gate[r / tokens, c] ),
+ * y = the bf16 value rk_gemm_int stores for the same arguments.  The arithmetic - and its three
+ * roundings - is that of the tensor ops `x + y` / `x + y * gate` of the reference
+ * (common/fused.py:47-58, models/pi05/modeling_gemma.py:226-244), i.e. of a projection followed by
+ * the residual kernels; it equals handing (y, gate) to rk_gated_rmsnorm_quant_rows bit for bit.
+ *   residual bf16 [m, n] contiguous; gate bf16 [m / tokens, n] contiguous or NULL; m % tokens == 0;
+ *   out must not overlap residual.  One CTA per tile (no CTA-pair schedule). */
+int rk_gemm_int_residual(const void* a, const float* sa, const void* b, const float* sb, const void* bias,
+                         const void* residual, const void* gate, int64_t tokens, void* out, int64_t m, int64_t n,
+                         int64_t kpad, int bits, int tactic, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Same product, but writes the raw int32 accumulators [m, n] (parity aid; no reference counterpart). */
 int rk_gemm_int_acc(const void* a, const void* b, int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits,
                     int tactic, void* workspace, size_t workspace_bytes, void* stream);

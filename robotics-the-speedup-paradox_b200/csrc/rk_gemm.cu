@@ -442,6 +442,9 @@ struct PeerArgs {
 
 struct TcArgs {
   const PeerArgs* peer = nullptr;
+  const void* residual = nullptr;  // gated residual update in the epilogue (GemmParams::residual)
+  const void* res_gate = nullptr;
+  int64_t res_tokens = 1;
   bool wgt_u4 = false;   // KIND_MXF8 with packed e2m1 weights [n, k / 2]: TMA expands them into the MMA's padded layout
   void* swiglu_q = nullptr;   // KIND_NVF4, interleaved gate/up weights: the epilogue packs silu(gate) * up to NVFP4
   void* swiglu_sf = nullptr;  //   (codes and swizzled scale factors) instead of writing bf16
@@ -475,7 +478,8 @@ int run_tc(const TcArgs& a) {
   if (rc != RK_OK) return rc;
   const int kblocks = static_cast<int>((a.k_bytes + kStageKBytes - 1) / kStageKBytes);
   const bool block_scaled = a.kind == KIND_MXF8 || a.kind == KIND_NVF4;
-  const bool two_cta_kind = a.acc_out == nullptr && (a.out != nullptr || a.swiglu_q != nullptr) && a.kind <= KIND_NVF4 && a.peer == nullptr;
+  const bool two_cta_kind = a.acc_out == nullptr && (a.out != nullptr || a.swiglu_q != nullptr) && a.kind <= KIND_NVF4 && a.peer == nullptr &&
+                            a.residual == nullptr;  // the residual epilogue lives in the one-CTA kernel
   const int mode = two_cta_mode();
   // CTA pairs: from 512 activation rows on for the block-scaled kinds, whose main loop is paced by
   // the issuing thread (scale copies + MMAs: up to 17 tensor-core instructions per stage; one
@@ -654,6 +658,9 @@ int run_tc(const TcArgs& a) {
   p.fmt_a = pl.swap ? fmt_wgt : FMT_E4M3;
   p.fmt_b = pl.swap ? FMT_E4M3 : fmt_wgt;
   p.tx_deficit = a.wgt_u4 ? kU4TxDeficitPerRow * static_cast<int>(box_wgt) : 0;
+  p.residual = static_cast<const __nv_bfloat16*>(a.residual);
+  p.res_gate = static_cast<const __nv_bfloat16*>(a.res_gate);
+  p.res_magic = a.res_tokens > 1 ? static_cast<unsigned>((1ull << 32) / static_cast<unsigned long long>(a.res_tokens) + 1ull) : 0u;
   if (a.peer != nullptr) {
     for (int g = 0; g < a.peer->count; ++g) p.peer_flags[g] = a.peer->flags[g];
     p.peer_mc = static_cast<__nv_bfloat16*>(a.peer->mc_out);
@@ -799,7 +806,8 @@ extern "C" int rk_debug_wait_expiry(int on, int spin_limit) {
 
 static int gemm_int_common(const void* a, const float* sa, const void* b, const float* sb, const void* bias, void* out,
                            int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits, int tactic, void* workspace,
-                           size_t workspace_bytes, void* stream, const char* who, bool widen_in_scratch = false) {
+                           size_t workspace_bytes, void* stream, const char* who, bool widen_in_scratch = false,
+                           const void* residual = nullptr, const void* res_gate = nullptr, int64_t res_tokens = 1) {
   if (bits != 8 && bits != 4) return fail(RK_EINVAL, "%s: bits must be 4 or 8", who);
   if (kpad < 128 || kpad % 128 != 0) return fail(RK_EINVAL, "%s: kpad must be a positive multiple of 128", who);
   if (tactic < 0 || tactic > 7) return fail(RK_EINVAL, "%s: tactic must be 0..7", who);
@@ -830,6 +838,9 @@ static int gemm_int_common(const void* a, const float* sa, const void* b, const 
     t.workspace_bytes = workspace_bytes;
     t.stream = as_stream(stream);
     t.who = who;
+    t.residual = residual;
+    t.res_gate = res_gate;
+    t.res_tokens = res_tokens;
     return run_tc(t);
   }
   if (bits == 4) {
@@ -868,6 +879,9 @@ static int gemm_int_common(const void* a, const float* sa, const void* b, const 
   t.workspace_bytes = workspace_bytes;
   t.stream = as_stream(stream);
   t.who = who;
+  t.residual = residual;
+  t.res_gate = res_gate;
+  t.res_tokens = res_tokens;
   int rc = run_tc(t);
   if (rc == RK_OK && copies != nullptr) {
     // leave the whole scratch buffer zero-filled, as every entry point promises
@@ -882,6 +896,21 @@ extern "C" int rk_gemm_int(const void* a, const float* sa, const void* b, const 
                            size_t workspace_bytes, void* stream) {
   return gemm_int_common(a, sa, b, sb, bias, out, nullptr, m, n, kpad, bits, tactic, workspace, workspace_bytes, stream,
                          "rk_gemm_int");
+}
+
+extern "C" int rk_gemm_int_residual(const void* a, const float* sa, const void* b, const float* sb, const void* bias,
+                                    const void* residual, const void* gate, int64_t tokens, void* out, int64_t m, int64_t n,
+                                    int64_t kpad, int bits, int tactic, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  const char* who = "rk_gemm_int_residual";
+  if (!residual || !out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (tokens < 1 || m < 1 || m % tokens != 0) return fail(RK_EINVAL, "%s: m must be a positive multiple of tokens", who);
+  if (static_cast<unsigned long long>(m) * static_cast<unsigned long long>(tokens) >= (1ull << 32))
+    return fail(RK_EUNSUPPORTED, "%s: m * tokens must stay below 2^32", who);
+  if (n % 8 != 0 || (reinterpret_cast<uintptr_t>(residual) & 1u) || (gate && (reinterpret_cast<uintptr_t>(gate) & 1u)))
+    return fail(RK_EINVAL, "%s: n must be a multiple of 8 and the bf16 pointers 2-byte aligned", who);
+  return gemm_int_common(a, sa, b, sb, bias, out, nullptr, m, n, kpad, bits, tactic, workspace, workspace_bytes, stream, who,
+                         false, residual, gate, tokens);
 }
 
 extern "C" int rk_gemm_int_acc(const void* a, const void* b, int32_t* acc, int64_t m, int64_t n, int64_t kpad, int bits,

@@ -42,6 +42,7 @@ SIGNATURES = {
     "rk_lut_mul_tensor_scale": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _f32, _vp, _vp, _vp, _sz, _vp]),
     "rk_gated_rmsnorm_quant_rows": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _vp, _vp, _vp, _vp]),
     "rk_gemm_int": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
+    "rk_gemm_int_residual": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
     "rk_gemm_int_acc": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
     "rk_gemm_int4_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "rk_pack_w4_g128": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),

@@ -205,7 +205,13 @@ class GemmaAttention(nn.Module):
         self.v_proj = nn.Linear(cfg.width, cfg.num_kv_heads * cfg.head_dim, bias=False)
         self.o_proj = nn.Linear(cfg.num_heads * cfg.head_dim, cfg.width, bias=False)
 
-    def forward(self, x, cos, sin, past_kv=None):
+    def _project_out(self, out, residual):
+        """o_proj; with `residual` = (stream, gate) its epilogue returns stream + o (* gate) (integer layers only)."""
+        if residual is None:
+            return self.o_proj(out)
+        return self.o_proj(out, residual=residual[0], gate=residual[1])
+
+    def forward(self, x, cos, sin, past_kv=None, residual=None):
         b, t = _leading_shape(x)
         cfg = self.cfg
         if self.fused_rope and past_kv is not None and len(past_kv) >= 3 and cos.is_cuda:
@@ -216,10 +222,10 @@ class GemmaAttention(nn.Module):
             if vt_all is not None:
                 # q is a transposed view of token-major storage: hand the storage to the kernel
                 out = attention_prefix(q.transpose(1, 2), k_all, vt_all, prefix + t)
-                return self.o_proj(out), (k_all, v_all)
+                return self._project_out(out, residual), (k_all, v_all)
             out = F.scaled_dot_product_attention(q, k_all, v_all, is_causal=False, enable_gqa=True)
             out = out.transpose(1, 2).reshape(b, t, -1).contiguous()
-            return self.o_proj(out), (k_all, v_all)
+            return self._project_out(out, residual), (k_all, v_all)
         q = self.q_proj(x).view(b, t, cfg.num_heads, cfg.head_dim).transpose(1, 2)
         k = self.k_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
         v = self.v_proj(x).view(b, t, cfg.num_kv_heads, cfg.head_dim).transpose(1, 2)
@@ -242,7 +248,7 @@ class GemmaAttention(nn.Module):
         # materialising one copy per query head.
         out = F.scaled_dot_product_attention(q, k, v, is_causal=False, enable_gqa=True)
         out = out.transpose(1, 2).reshape(b, t, -1).contiguous()
-        return self.o_proj(out), present
+        return self._project_out(out, residual), present
 
 
 class GemmaMLP(nn.Module):
@@ -252,9 +258,12 @@ class GemmaMLP(nn.Module):
         self.up_proj = nn.Linear(cfg.width, cfg.mlp_dim, bias=False)
         self.down_proj = nn.Linear(cfg.mlp_dim, cfg.width, bias=False)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """`residual` = (stream, gate): the down projection's epilogue returns stream + mlp (* gate)."""
         gate, up = self.gate_proj(x), self.up_proj(x)
         fused = getattr(self.down_proj, "forward_gelu", None)
+        if residual is not None:
+            return fused(gate, up, residual=residual[0], gate=residual[1])
         if fused is not None:  # quantized down_proj: GELU(gate) * up fused into its row quantizer
             return fused(gate, up)
         return self.down_proj(F.gelu(gate, approximate="tanh") * up)
@@ -273,11 +282,28 @@ class GemmaLayer(nn.Module):
         stream BEFORE this layer's own MLP update plus that update as the new `pending`, so that the
         next norm can apply it inside its kernel (a norm without the fused path applies it eagerly;
         the arithmetic - bf16(x + bf16(branch * gate)) - is the same either way)."""
+        if self.residual_epilogue and x.is_cuda and self._integer_out_projections():
+            # the o_proj and down_proj GEMMs write the updated stream themselves (`rk_gemm_int_residual`):
+            # nothing is pending between layers and the norms read one tensor
+            h, gate, x = self.input_layernorm(x, cond, pending)
+            x, present = self.self_attn(h, cos, sin, past_kv, residual=(x, gate))
+            h, gate2, x = self.post_attention_layernorm(x, cond, None)
+            return self.mlp(h, residual=(x, gate2)), present, None
         h, gate, x = self.input_layernorm(x, cond, pending)
         h, present = self.self_attn(h, cos, sin, past_kv)
         h, gate2, x = self.post_attention_layernorm(x, cond, (h, gate))
         h = self.mlp(h)
         return x, present, (h, gate2)
+
+    # set on an instance (or the class): apply the residual updates in the epilogues of the integer o_proj / down_proj
+    # GEMMs instead of inside the next norm kernel (the same arithmetic; the reference's torch ops either way)
+    residual_epilogue = False
+
+    def _integer_out_projections(self):
+        from .integer import IntegerLinear
+
+        return all(isinstance(m, IntegerLinear) and m.out_features == m.packed_weight.shape[0]
+                   for m in (self.self_attn.o_proj, self.mlp.down_proj))
 
 
 class GemmaStack(nn.Module):

@@ -108,8 +108,12 @@ def quantize_weight(weight, bits):
     return packed, scales
 
 
-def integer_gemm(a, sa, b, sb, bias, bits, tactic):
-    """``robotics_integer::gemm`` call shape (reference: csrc/integer_gemm.cu:130-176)."""
+def integer_gemm(a, sa, b, sb, bias, bits, tactic, residual=None, gate=None):
+    """``robotics_integer::gemm`` call shape (reference: csrc/integer_gemm.cu:130-176).
+
+    With `residual` [M, N] (bf16, contiguous) the epilogue writes the decoder layer's new residual
+    stream instead of the projection: residual + y, or residual + y * gate[row // (M / B)] for a
+    `gate` [B, N] (`rk_gemm_int_residual`; the same roundings as the tensor ops)."""
     if not (a.is_cuda and b.is_cuda and sa.is_cuda and sb.is_cuda):
         raise RuntimeError("integer GEMM operands must be CUDA tensors")
     if a.dim() != 2 or b.dim() != 2 or a.size(1) != b.size(1) or not a.is_contiguous() or not b.is_contiguous():
@@ -121,12 +125,29 @@ def integer_gemm(a, sa, b, sb, bias, bits, tactic):
     m, n = a.size(0), b.size(0)
     kpad = a.size(1) * (2 if bits == 4 else 1)
     out = torch.empty((m, n), device=a.device, dtype=torch.bfloat16)
+    tokens = 1
+    if residual is not None:
+        if residual.dtype != torch.bfloat16 or tuple(residual.shape) != (m, n) or not residual.is_contiguous():
+            raise RuntimeError("integer GEMM residual must be contiguous BF16 [M, N]")
+        if gate is not None:
+            if gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.size(1) != n or not gate.is_contiguous() \
+                    or gate.size(0) < 1 or m % gate.size(0):
+                raise RuntimeError("integer GEMM gate must be contiguous BF16 [B, N] with M divisible by B")
+            tokens = m // gate.size(0)
+    elif gate is not None:
+        raise RuntimeError("integer GEMM: a gate needs a residual")
     with torch.cuda.device(a.device):
         ws = _lib.gemm_workspace(_lib.OP_W8A8 if bits == 8 else _lib.OP_W4A4, a.device, m, n, kpad)
-        code = _lib.load().rk_gemm_int(
-            _lib.ptr(a), _lib.ptr(sa), _lib.ptr(b), _lib.ptr(sb), _lib.ptr(bias), _lib.ptr(out),
-            m, n, kpad, bits, tactic, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
-        )
+        if residual is None:
+            code = _lib.load().rk_gemm_int(
+                _lib.ptr(a), _lib.ptr(sa), _lib.ptr(b), _lib.ptr(sb), _lib.ptr(bias), _lib.ptr(out),
+                m, n, kpad, bits, tactic, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
+            )
+        else:
+            code = _lib.load().rk_gemm_int_residual(
+                _lib.ptr(a), _lib.ptr(sa), _lib.ptr(b), _lib.ptr(sb), _lib.ptr(bias), _lib.ptr(residual), _lib.ptr(gate),
+                tokens, _lib.ptr(out), m, n, kpad, bits, tactic, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
+            )
     if code == _lib.RK_EINVAL:
         raise RuntimeError(f"integer GEMM: {_lib.last_error()}")
     _lib.check(code, "integer GEMM")
@@ -186,31 +207,43 @@ class IntegerLinear(torch.nn.Module):
             raise ValueError("Wrong input feature count")
         return prepare_activation(x, self.bits, pack_reuse=self.pack_reuse)
 
-    def forward_packed(self, packed):
+    def forward_packed(self, packed, residual=None, gate=None):
+        """`residual` [..., out_features] (+ `gate` [B, out_features] or [B, 1, out_features]): the GEMM's
+        epilogue returns the updated residual stream residual + y (* gate) instead of y."""
         if (
             packed.logical_k != self.in_features
             or packed.bits != self.bits
             or packed.format_version != "symmetric-row-v1"
         ):
             raise ValueError("Incompatible activation pack")
+        if residual is not None:
+            if self.out_features != self.packed_weight.shape[0]:
+                raise ValueError("The residual epilogue needs out_features to be a multiple of 8")
+            residual = residual.reshape(-1, self.out_features)
+            residual = residual if residual.is_contiguous() else residual.contiguous()
+            if gate is not None:
+                gate = gate.reshape(-1, self.out_features)
+                gate = gate if gate.is_contiguous() else gate.contiguous()
         # The reference's biasless epilogue skips the bias visitor; with a null bias the kernel's
         # epilogue is already that one, so both settings take the same path.
         output = integer_gemm(
-            packed.data, packed.scales, self.packed_weight, self.weight_scale, self.bias, self.bits, self.tactic
+            packed.data, packed.scales, self.packed_weight, self.weight_scale, self.bias, self.bits, self.tactic,
+            residual=residual, gate=gate,
         )
         if self.out_features != output.shape[1]:
             output = output[:, : self.out_features].contiguous()
         return output.reshape(*packed.shape, self.out_features)
 
-    def forward_gelu(self, x, up=None, *, approximate="tanh"):
+    def forward_gelu(self, x, up=None, *, approximate="tanh", residual=None, gate=None):
         if x.shape[-1] != self.in_features:
             raise ValueError("Wrong input feature count")
         return self.forward_packed(
-            prepare_activation(x, self.bits, up=up, gelu=approximate, pack_reuse=self.pack_reuse)
+            prepare_activation(x, self.bits, up=up, gelu=approximate, pack_reuse=self.pack_reuse),
+            residual=residual, gate=gate,
         )
 
-    def forward(self, x):
-        return self.forward_packed(self.pack_input(x))
+    def forward(self, x, residual=None, gate=None):
+        return self.forward_packed(self.pack_input(x), residual=residual, gate=gate)
 
 
 class IntegerProjectionGroup(torch.nn.Module):

@@ -140,6 +140,39 @@ def test_grouped_projections_and_fused_norm_quantizer_keep_the_loop_output(H):
     assert rel < 2e-2
 
 
+def test_residual_updates_in_the_gemm_epilogues_keep_the_loop_output(H):
+    """The gated residual updates applied by the o_proj / down_proj epilogues (`rk_gemm_int_residual`)
+    instead of inside the next norm kernel: the same three roundings, so the loop output is unchanged -
+    with tensor-op norms and with the fused norm -> quantize kernels."""
+    from rk_b200.gemma_stack import GemmaLayer, expert_scope, fuse_norm_quantize, unfuse_norm_quantize
+    from rk_b200.optimizations import quantize_linears
+
+    expert = small_expert(H.DEVICE)
+    b, t = 4, 64
+    gen = torch.Generator().manual_seed(6)
+    noise = torch.randn(b, 50, 32, generator=gen).to(H.DEVICE)
+    pk = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    pv = torch.randn(2, b, 1, t, 128, generator=gen).to(torch.bfloat16).to(H.DEVICE)
+    with torch.no_grad():
+        with quantize_linears(expert, "int8", scopes=("expert",), selector=expert_scope, shared_quant=True, grouped=True):
+            plain = expert(noise, pk, pv)
+            norms = fuse_norm_quantize(expert.stack)
+            fused = expert(noise, pk, pv)
+            GemmaLayer.residual_epilogue = True
+            try:
+                assert torch.equal(expert(noise, pk, pv), fused)
+                unfuse_norm_quantize(norms)
+                assert torch.equal(expert(noise, pk, pv), plain)
+            finally:
+                GemmaLayer.residual_epilogue = False
+                unfuse_norm_quantize(norms)
+        GemmaLayer.residual_epilogue = True
+        try:  # bf16 linears: the switch changes nothing
+            assert torch.equal(expert(noise, pk, pv), expert(noise, pk, pv))
+        finally:
+            GemmaLayer.residual_epilogue = False
+
+
 def test_condition_caches_and_chunk_buffers_under_graph_capture(H):
     """With the timestep conditions and their projections cached (filled by the eager warm-up
     calls) the captured loop reads them as constants: same output as the uncached eager loop, for

@@ -249,3 +249,60 @@ def test_w8a8_under_cuda_graph_replay_with_changed_inputs(H):
         torch.cuda.synchronize()
         want, _ = OI.linear(H.to_np(x), H.to_np(lin.weight), None, 8)
         assert np.array_equal(H.bits(static_y), F.bf16_bits(want))
+
+
+# (m, n, k): swapped whole tiles, a split-K shape, the chunked paths on both sides of the swap threshold, a ragged n
+@pytest.mark.parametrize("shape,tokens", [((400, 1024, 2048), 50), ((400, 1024, 4096), 50), ((64, 256, 4096), 1),
+                                          ((100, 384, 8192), 100), ((1300, 512, 256), 130), ((816, 264, 384), 816),
+                                          ((130, 2048, 128), 65)])
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("gated", [True, False])
+def test_residual_epilogue_equals_the_tensor_ops(H, shape, tokens, bits, gated):
+    """`rk_gemm_int_residual`: the projection's epilogue writes stream + y (* gate) with the three roundings
+    of the tensor ops on the bf16 output y of the plain GEMM - bit for bit, in every epilogue layout."""
+    from rk_b200 import integer as I
+
+    m, n, k = shape
+    x = H.randn_bf16((m, k), 1.0, 71).to(H.DEVICE)
+    lin = torch.nn.Linear(k, n, bias=True, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(H.randn_bf16((n, k), 0.02, 72))
+        lin.bias.copy_(H.randn_bf16((n,), 0.01, 73))
+    layer = I.IntegerLinear.from_linear(lin.to(H.DEVICE), bits=bits)
+    stream = H.randn_bf16((m, n), 1.0, 74).to(H.DEVICE)
+    gate = H.randn_bf16((m // tokens, n), 0.5, 75).to(H.DEVICE) if gated else None
+    packed = layer.pack_input(x)
+    y = layer.forward_packed(packed)
+    want = stream + (y if gate is None else y * gate.repeat_interleave(tokens, 0))
+    got = layer.forward_packed(packed, residual=stream, gate=gate)
+    assert got.shape == (m, n) and torch.equal(got, want)
+    # leading axes and a [B, 1, N] gate, as the decoder layers pass them
+    if gated and m % tokens == 0:
+        got3 = layer.forward_packed(I.PackedActivation(packed.data, packed.scales, (m // tokens, tokens), packed.logical_k, bits),
+                                    residual=stream.reshape(m // tokens, tokens, n), gate=gate[:, None, :])
+        assert torch.equal(got3.reshape(m, n), want)
+
+
+def test_residual_epilogue_refuses_bad_arguments(H):
+    from rk_b200 import _lib
+    from rk_b200 import integer as I
+
+    lin = torch.nn.Linear(256, 128, bias=False, dtype=torch.bfloat16).to(H.DEVICE)
+    layer = I.IntegerLinear.from_linear(lin, bits=8)
+    packed = layer.pack_input(H.randn_bf16((60, 256), 1.0, 1).to(H.DEVICE))
+    stream = torch.zeros(60, 128, dtype=torch.bfloat16, device=H.DEVICE)
+    with pytest.raises(RuntimeError):
+        layer.forward_packed(packed, residual=stream, gate=torch.zeros(7, 128, dtype=torch.bfloat16, device=H.DEVICE))  # 60 % 7
+    with pytest.raises(RuntimeError):
+        layer.forward_packed(packed, residual=stream.float())
+    with pytest.raises(RuntimeError):
+        I.integer_gemm(packed.data, packed.scales, layer.packed_weight, layer.weight_scale, None, 8, 0, gate=stream[:1])
+    lib = _lib.load()
+    ws = _lib.gemm_workspace(_lib.OP_W8A8, H.DEVICE, 60, 128, 256)
+    out = torch.empty_like(stream)
+    args = lambda res, tok: (_lib.ptr(packed.data), _lib.ptr(packed.scales), _lib.ptr(layer.packed_weight), _lib.ptr(layer.weight_scale),
+                             None, res, None, tok, _lib.ptr(out), 60, 128, 256, 8, 0, _lib.ptr(ws), ws.numel(), H.stream())
+    assert lib.rk_gemm_int_residual(*args(None, 1)) == _lib.RK_EINVAL
+    assert lib.rk_gemm_int_residual(*args(_lib.ptr(stream), 7)) == _lib.RK_EINVAL
+    assert lib.rk_gemm_int_residual(*args(_lib.ptr(stream), 0)) == _lib.RK_EINVAL
+    assert lib.rk_gemm_int_residual(*args(_lib.ptr(stream), 60)) == _lib.RK_OK
