@@ -340,6 +340,14 @@ int rk_peer_free(void* ptr);
  * (blackwell/csrc/mxfp8_cutlass_linear.cu:31-105).  x bf16 [rows, k], k % 32 == 0;
  * q e4m3 [rows, k]; sf: rk_sf_bytes(rows, k/32) bytes, fully written (padding = 0). */
 int rk_pack_mxfp8(const void* x, int64_t rows, int64_t k, void* q, void* sf, void* stream);
+/* SwiGLU producer for MXFP8: bf16( table[gate] * up ) packed like rk_pack_mxfp8, `table` = SiLU evaluated on
+ * all 65536 bf16 bit patterns.  Replaces `robotics_mxfp8_swiglu::silu_mul_pack`
+ * (blackwell/csrc/mxfp8_swiglu.cu:20-117, blackwell/mxfp8_swiglu.py:43-60).
+ *   gate_up bf16 [rows, 2 * inter] contiguous, gate first; inter % 32 == 0;
+ *   q e4m3 [rows, inter]; sf rk_sf_bytes(rows, inter / 32) bytes, every byte written. */
+int rk_swiglu_pack_mxfp8(const void* gate_up, int64_t rows, int64_t inter, const void* silu_table, void* q, void* sf,
+                         void* stream);
+
 /* out = bf16( sum over blocks (sfa * sfb * sum_k a*b) (+ bias[n]) ).  Replaces `robotics_mxfp8::linear`
  * (blackwell/csrc/mxfp8_cutlass_linear.cu:107-258).  k % 32 == 0, n % 8 == 0. */
 int rk_gemm_mxfp8(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias, void* out,

@@ -209,3 +209,15 @@ def rel_frobenius(actual, expected):
     e = np.asarray(expected, dtype=np.float64)
     d = np.asarray(actual, dtype=np.float64) - e
     return float(np.sqrt((d * d).sum()) / max(np.sqrt((e * e).sum()), 1e-30))
+
+
+def silu_mul_pack_mxfp8(gate_up, inter, table):
+    """`robotics_mxfp8_swiglu::silu_mul_pack` (blackwell/csrc/mxfp8_swiglu.cu:20-78): the value packed is
+    bf16( table[bits(gate)] * up ), `table` the 65536 SiLU values as float32; then `pack_mxfp8`.
+    gate_up float32 [rows, 2 * inter] holding bf16 values, gate first.  -> (codes, scales, swizzled)."""
+    from .formats import bf16_bits, bf16_round
+
+    gate_up = np.asarray(gate_up, dtype=np.float32)
+    gate, up = gate_up[:, :inter], gate_up[:, inter:]
+    silu = np.asarray(table, dtype=np.float32)[bf16_bits(gate).astype(np.int64)]
+    return pack_mxfp8(bf16_round((silu * up).astype(np.float32)))

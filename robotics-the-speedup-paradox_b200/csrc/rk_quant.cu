@@ -576,9 +576,12 @@ __device__ __forceinline__ uint32_t ue8m0_roundup(float x) {
 
 // MXFP8: eight lanes per 32-element block, four elements per lane.  The thread grid covers the
 // padded scale-factor domain so that every byte of the SF buffer is written.
+// SWIGLU: x is [rows, 2 k] (gate first, then up) and the packed value is bf16(table[gate] * up), `table`
+// being SiLU on all 65536 bf16 bit patterns (blackwell/csrc/mxfp8_swiglu.cu:20-78).
+template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 pack_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long k, uint8_t* __restrict__ q,
-                  uint8_t* __restrict__ sf) {
+                  uint8_t* __restrict__ sf, const __nv_bfloat16* __restrict__ table) {
   pdl_launch_dependents();  // every thread, before any return: see launch_pdl
   pdl_wait();
   const long long groups_padded = (k + 127) / 128 * 4;
@@ -595,9 +598,20 @@ pack_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long
     return;
   }
   const long long base = row * k + group * 32 + lane8 * 4;
-  const uint2 u = *reinterpret_cast<const uint2*>(x + base);
-  float v[4] = {bf16_bits_to_float(u.x & 0xFFFFu), bf16_bits_to_float(u.x >> 16), bf16_bits_to_float(u.y & 0xFFFFu),
-                bf16_bits_to_float(u.y >> 16)};
+  float v[4];
+  if constexpr (SWIGLU) {
+    const long long in = row * 2 * k + group * 32 + lane8 * 4;
+    const uint2 g = *reinterpret_cast<const uint2*>(x + in);
+    const uint2 u = *reinterpret_cast<const uint2*>(x + in + k);
+    const uint32_t gb[4] = {g.x & 0xFFFFu, g.x >> 16, g.y & 0xFFFFu, g.y >> 16};
+    const uint32_t ub[4] = {u.x & 0xFFFFu, u.x >> 16, u.y & 0xFFFFu, u.y >> 16};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = round_bf16(__fmul_rn(__bfloat162float(table[gb[i]]), bf16_bits_to_float(ub[i])));
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(x + base);
+    v[0] = bf16_bits_to_float(u.x & 0xFFFFu), v[1] = bf16_bits_to_float(u.x >> 16);
+    v[2] = bf16_bits_to_float(u.y & 0xFFFFu), v[3] = bf16_bits_to_float(u.y >> 16);
+  }
   float amax = 0.0f;
   unsigned invalid = 0;
 #pragma unroll
@@ -1252,9 +1266,22 @@ extern "C" int rk_pack_mxfp8(const void* x, int64_t rows, int64_t k, void* q, vo
   if (!aligned16(x) || !aligned16(q)) return fail(RK_EINVAL, "rk_pack_mxfp8: pointers must be 16-byte aligned");
   const long long blocks32 = ((rows + 127) / 128 * 128) * ((k + 127) / 128 * 4);
   const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
-  launch_pdl(pack_mxfp8_kernel, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x), rows, k,
-                                                         static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
+  launch_pdl(pack_mxfp8_kernel<false>, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(x), rows, k,
+             static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), nullptr);
   return check_launch("pack_mxfp8");
+}
+
+extern "C" int rk_swiglu_pack_mxfp8(const void* gate_up, int64_t rows, int64_t inter, const void* silu_table, void* q,
+                                    void* sf, void* stream) {
+  const char* who = "rk_swiglu_pack_mxfp8";
+  if (!gate_up || !silu_table || !q || !sf) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || inter < 32 || inter % 32 != 0) return fail(RK_EINVAL, "%s: the intermediate size must be a positive multiple of 32", who);
+  if (!aligned16(gate_up) || !aligned16(q)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  const long long blocks32 = ((rows + 127) / 128 * 128) * ((inter + 127) / 128 * 4);
+  const unsigned grid = static_cast<unsigned>((blocks32 * 8 + 255) / 256);
+  launch_pdl(pack_mxfp8_kernel<true>, grid, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+             static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<const __nv_bfloat16*>(silu_table));
+  return check_launch(who);
 }
 
 extern "C" int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float* global_scale, void* q, void* sf,

@@ -60,6 +60,7 @@ SIGNATURES = {
     "rk_peer_close": (_int, [_vp]),
     "rk_peer_free": (_int, [_vp]),
     "rk_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_swiglu_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "rk_swiglu_pack_nvfp4_layout": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "rk_pack_mxfp4_weight": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
     "rk_pack_mxfp8_act_w4a8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),

@@ -337,3 +337,52 @@ def test_cuda_swiglu_chains_match_reference_kernels(GX, maker):
             assert patched_sha(GX, tag + "_sf", sf.cpu().numpy())[0] == str(GX[tag + "_sf_sha"])
             out = PM.Fp4MxLinear.from_linear(lin, "linear", "down").forward_swiglu(gate_up, inter, interleaved)
             assert (bits(out) != GX[tag + "_out"]).mean() < 0.02
+
+
+# ------------------------------------------------------------------ third fixture file: the table-SiLU SwiGLU producer for MXFP8
+SILU = GOLDEN / "blackwell_golden_silu.npz"
+needs_silu = pytest.mark.skipif(not SILU.exists(), reason="blackwell_golden_silu.npz has not been generated")
+
+
+@pytest.fixture(scope="module")
+def GS():
+    return np.load(SILU)
+
+
+@needs_silu
+def test_oracle_silu_mul_pack_matches_reference_kernel(GS, maker):
+    """`robotics_mxfp8_swiglu::silu_mul_pack` (blackwell/csrc/mxfp8_swiglu.cu) on a B200 against the numpy
+    restatement, with the SiLU table the reference was given: codes and scale bytes, bit for bit."""
+    from oracle.formats import bf16_from_bits
+
+    table = bf16_from_bits(GS["silu_table_bits"])
+    for name, rows, inter in maker.SILU_CASES:
+        gate_up = maker.silu_inputs(name, rows, inter).float().numpy()
+        codes, _, swizzled = OB.silu_mul_pack_mxfp8(gate_up, inter, table)
+        tag = "silu_" + name
+        assert int(GS[tag + "_codes_diff_count"]) == 0 and int(GS[tag + "_sf_diff_count"]) == 0
+        assert sha(codes) == str(GS[tag + "_codes_sha"]), name
+        assert sha(swizzled) == str(GS[tag + "_sf_sha"]), name
+        if name == "small":
+            assert np.array_equal(codes.reshape(-1), GS[tag + "_codes"].reshape(-1)) and np.array_equal(swizzled, GS[tag + "_sf"].reshape(-1))
+            assert OB.unswizzle_sf(swizzled, rows, inter // 32)[3, 0] == 255  # the block with the infinity
+
+
+@needs_silu
+@pytest.mark.gpu
+def test_cuda_silu_mul_pack_matches_reference_kernel(GS, maker):
+    from rk_b200 import mxfp8_swiglu as MS
+
+    table = MS.make_bf16_silu_table(torch.device("cuda:0"))
+    assert np.array_equal(table.view(torch.int16).cpu().numpy().view(np.uint16), GS["silu_table_bits"])
+    for name, rows, inter in maker.SILU_CASES:
+        gate_up = _dev(maker.silu_inputs(name, rows, inter))
+        q, sf = MS.silu_mul_pack_mxfp8(gate_up.reshape(1, rows, 2 * inter), inter, table)
+        assert q.shape == (1, rows, inter) and q.dtype == torch.float8_e4m3fn
+        tag = "silu_" + name
+        assert sha(q.view(torch.uint8).cpu().numpy()) == str(GS[tag + "_codes_sha"]), name
+        assert sha(sf.cpu().numpy()) == str(GS[tag + "_sf_sha"]), name
+    with pytest.raises(ValueError):
+        MS.silu_mul_pack_mxfp8(gate_up[:, :100], 50, table)
+    with pytest.raises(ValueError):
+        MS.silu_mul_pack_mxfp8(gate_up, inter, table[:100])
