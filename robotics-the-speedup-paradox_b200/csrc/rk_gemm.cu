@@ -302,7 +302,7 @@ Plan make_plan(int kind, int64_t m, int64_t n, int kblocks, int tactic) {
   return pl;
 }
 
-template <int KIND>
+template <int KIND, bool RESIDUAL = false>
 int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out, const GemmParams& p,
               const Plan& pl, cudaStream_t st) {
   static bool configured_dev[64] = {};
@@ -310,7 +310,7 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
   cudaGetDevice(&dev);
   bool& configured = configured_dev[dev & 63];
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(rk_gemm_tc_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(rk_gemm_tc_kernel<KIND, RESIDUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBudget + 1024);
     if (e != cudaSuccess) return fail(RK_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
@@ -329,7 +329,7 @@ int launch_tc(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMa
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_kernel<KIND>, tm_a, tm_b, tm_out, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rk_gemm_tc_kernel<KIND, RESIDUAL>, tm_a, tm_b, tm_out, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(RK_ECUDA, "rk_gemm_tc_kernel launch: %s", cudaGetErrorString(e));
@@ -692,11 +692,15 @@ int run_tc(const TcArgs& a) {
     return launch_tc_peer(tm_a, tm_b, maps, p, pl, a.stream);
   }
   switch (a.kind) {
-    case KIND_I8: return launch_tc<KIND_I8>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_I8:
+      return a.residual != nullptr ? launch_tc<KIND_I8, true>(tm_a, tm_b, tm_out, p, pl, a.stream)
+                                   : launch_tc<KIND_I8>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_F8: return launch_tc<KIND_F8>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_MXF8: return launch_tc<KIND_MXF8>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_NVF4: return launch_tc<KIND_NVF4>(tm_a, tm_b, tm_out, p, pl, a.stream);
-    case KIND_I4: return launch_tc<KIND_I4>(tm_a, tm_b, tm_out, p, pl, a.stream);
+    case KIND_I4:
+      return a.residual != nullptr ? launch_tc<KIND_I4, true>(tm_a, tm_b, tm_out, p, pl, a.stream)
+                                   : launch_tc<KIND_I4>(tm_a, tm_b, tm_out, p, pl, a.stream);
     case KIND_F8P: return launch_tc<KIND_F8P>(tm_a, tm_b, tm_out, p, pl, a.stream);
     default: return launch_tc<KIND_MX48>(tm_a, tm_b, tm_out, p, pl, a.stream);
   }

@@ -392,7 +392,9 @@ __device__ __forceinline__ void multicast_store_region(const GemmParams& p, cons
 
 // The kernel body.  The tensor maps are kernel parameters of the callers below (`peer_maps`: the
 // store descriptors of the column-parallel mode, one per rank, or null).
-template <int KIND>
+// RESIDUAL: the epilogue applies GemmParams::residual (a separate instantiation: the 64 values it keeps
+// in flight would otherwise cost every launch of the kind its registers).
+template <int KIND, bool RESIDUAL = false>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_out,
                                              const CUtensorMap* peer_maps, const GemmParams& p) {
   using T = KindTraits<KIND>;
@@ -888,11 +890,9 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
               v1[j] = finish_value<BK>(r1[j], s_act_scalar, s_wgt_scalar, has_bias, row_bias);
             }
           }
-          if constexpr (BK == KIND_I8) {  // (only the integer entry points offer the residual epilogue)
-            if (p.residual != nullptr) {  // swapped tile: this thread's channel, columns are activation rows
-              with_residual16(p, v0, row_b0 + c0, lim_b, ra, ra_ok, true);
-              with_residual16(p, v1, row_b0 + c0 + 16, lim_b, ra, ra_ok, true);
-            }
+          if constexpr (RESIDUAL) {  // swapped tile: this thread's channel, columns are activation rows
+            with_residual16(p, v0, row_b0 + c0, lim_b, ra, ra_ok, true);
+            with_residual16(p, v1, row_b0 + c0 + 16, lim_b, ra, ra_ok, true);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) srow[(c0 + j) * 128 + et] = __float2bfloat16_rn(v0[j]);
@@ -946,9 +946,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
                                         p.swap ? row_bias : vec_bias[cc + c0 + j]);
             }
           }
-          if constexpr (BK == KIND_I8) {
-            if (p.residual != nullptr) with_residual16(p, v, row_b0 + cc + c0, lim_b, ra, ra_ok, p.swap != 0);
-          }
+          if constexpr (RESIDUAL) with_residual16(p, v, row_b0 + cc + c0, lim_b, ra, ra_ok, p.swap != 0);
           if (p.swap) {
             __nv_bfloat16* const srow = reinterpret_cast<__nv_bfloat16*>(stage);
 #pragma unroll
@@ -1100,9 +1098,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
           } else {
             val = finish_value<BK>(total, s_act_scalar, s_wgt_scalar, has_bias, bias_v);
           }
-          if constexpr (BK == KIND_I8) {
-            if (p.residual != nullptr) val = with_residual(p, val, static_cast<int>(om), static_cast<int>(on));
-          }
+          if constexpr (RESIDUAL) val = with_residual(p, val, static_cast<int>(om), static_cast<int>(on));
           p.out[om * p.ldo + on] = __float2bfloat16_rn(val);
         }
       }
@@ -1120,11 +1116,11 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
   }
 }
 
-template <int KIND>
+template <int KIND, bool RESIDUAL = false>
 __global__ void __launch_bounds__(KindTraits<KIND>::kThreads, 1)
 rk_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
-  gemm_tc_body<KIND>(tm_a, tm_b, tm_out, nullptr, p);
+  gemm_tc_body<KIND, RESIDUAL>(tm_a, tm_b, tm_out, nullptr, p);
 }
 
 // The per-tensor FP8 GEMM in column-parallel mode: one store descriptor per rank instead of one output map.
