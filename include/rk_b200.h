@@ -370,6 +370,16 @@ int rk_pack_nvfp4(const void* x, int64_t rows, int64_t k, const float* global_sc
  * NULL; q uint8 [rows, k/2]; sf: rk_sf_bytes(rows, k/16) bytes, fully written; k % 32 == 0, k <= 8192. */
 int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k,
                           float eps, void* sum_out, void* norm_out, void* q, void* sf, void* stream);
+/* The producers of the two entry points above on their own: (residual add +) RMSNorm with bf16 rounding
+ * after `* inv` and after `* weight` -> bf16 (`robotics_cutlass_fp4::rms_norm_bf16`, `add_rms_norm_bf16`,
+ * blackwell/csrc/fp4_cutlass_linear.cu:429-476,2472-2536); k % 16 == 0; with a residual, sum_out receives
+ * bf16(x + residual).  And SwiGLU in the reference's bf16x2 steps -> bf16 [rows, inter]
+ * (`silu_mul_bf16`, :944-995,1988-2043), gate_up [rows, 2 * inter] in the plain or the 64-column
+ * interleaved layout; inter % 8 == 0. */
+int rk_rmsnorm_bf16(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k, float eps,
+                    void* sum_out, void* norm_out, void* stream);
+int rk_silu_mul_bf16(const void* gate_up, int64_t rows, int64_t inter, int interleaved, void* out, void* stream);
+
 /* SwiGLU packed straight to NVFP4: a = gate * rcp(1 + exp(-gate)) * up with every step rounded to
  * bf16 (the reference evaluates it in packed bf16 arithmetic), then blocks as rk_pack_nvfp4.
  * Replaces the packing half of `linear_forward_swiglu_gemm_bf16`

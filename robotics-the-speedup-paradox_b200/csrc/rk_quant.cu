@@ -920,8 +920,25 @@ swiglu_pack_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate_up, long long ro
   sf[sfi] = code;
 }
 
+// SwiGLU alone, bf16 in the reference's bf16x2 steps (blackwell/csrc/fp4_cutlass_linear.cu:944-995,
+// `silu_mul_bf16`): eight outputs per thread; either gate/up layout.
+__global__ void __launch_bounds__(256)
+silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ gate_up, long long rows, long long inter, int interleaved,
+                     __nv_bfloat16* __restrict__ out) {
+  pdl_launch_dependents();  // every thread, before any return: see launch_pdl
+  pdl_wait();
+  const long long total = rows * inter;
+  for (long long idx = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    float v[8];
+    load8_swiglu<true>(gate_up, inter, idx, 8, v, interleaved != 0);  // inter % 8 == 0: a vector never straddles rows
+    store8(out + idx, true, 8, v);
+  }
+}
+
 // (residual add +) RMSNorm feeding a per-tensor FP8 quantizer (FMT 0: writes the bf16 results and the
-// tensor's absolute maximum) or an NVFP4 packer (FMT 1: packs straight from registers).  Arithmetic
+// tensor's absolute maximum), an NVFP4 packer (FMT 1: packs straight from registers) or nothing (FMT 2: the
+// plain norm of blackwell/csrc/fp4_cutlass_linear.cu:429-476).  Arithmetic
 // of blackwell/csrc/fp8_cutlass_linear.cu:145-203 and blackwell/csrc/fp4_cutlass_linear.cu:843-929:
 // s = bf16(x + residual); r = rsqrt(mean(s^2) + eps); y = bf16( bf16(s * r) * weight ).
 // One CTA per row (FMT 1: per row of the 128-row padded scale-factor domain), row cached in registers.
@@ -980,6 +997,7 @@ rmsnorm_producer_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       if (norm_out != nullptr) store8(norm_out + xoff + idx, true, 8, vals[it]);
     }
   }
+  if (FMT == 2) return;  // the plain norm: the bf16 result is the output
   if (FMT == 0) {
     const float m = block_reduce(local_max, true, scratch);
     if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(m));
@@ -1356,6 +1374,34 @@ extern "C" int rk_rmsnorm_pack_nvfp4(const void* x, const void* residual, const 
       b(x), b(residual), b(weight), static_cast<int>(rows), static_cast<int>(k), eps,
       static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), nullptr, static_cast<uint8_t*>(q),
       static_cast<uint8_t*>(sf));
+  return check_launch(who);
+}
+
+extern "C" int rk_rmsnorm_bf16(const void* x, const void* residual, const void* weight, int64_t rows, int64_t k, float eps,
+                               void* sum_out, void* norm_out, void* stream) {
+  const char* who = "rk_rmsnorm_bf16";
+  if (!x || !weight || !norm_out || (residual && !sum_out)) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || k < 16 || k % 16 != 0 || k > rk::kCachedK) return fail(RK_EINVAL, "%s: k must be a multiple of 16, at most %d", who, rk::kCachedK);
+  if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || !aligned16(norm_out) ||
+      (sum_out && !aligned16(sum_out)))
+    return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  auto b = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+  launch_pdl(rk::rmsnorm_producer_kernel<2>, static_cast<unsigned>(rows), rk::kRowThreads, as_stream(stream),
+             b(x), b(residual), b(weight), static_cast<int>(rows), static_cast<int>(k), eps,
+             static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), nullptr, nullptr, nullptr);
+  return check_launch(who);
+}
+
+extern "C" int rk_silu_mul_bf16(const void* gate_up, int64_t rows, int64_t inter, int interleaved, void* out, void* stream) {
+  const char* who = "rk_silu_mul_bf16";
+  if (!gate_up || !out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (rows < 1 || inter < 8 || inter % 8 != 0) return fail(RK_EINVAL, "%s: the intermediate size must be a positive multiple of 8", who);
+  if (interleaved && inter % 64 != 0) return fail(RK_EINVAL, "%s: the interleaved layout needs a multiple of 64 columns", who);
+  if (!aligned16(gate_up) || !aligned16(out)) return fail(RK_EINVAL, "%s: pointers must be 16-byte aligned", who);
+  const long long vectors = rows * inter / 8;
+  const unsigned blocks = static_cast<unsigned>(std::min<long long>((vectors + 255) / 256, 148LL * 8));
+  launch_pdl(rk::silu_mul_bf16_kernel, blocks, 256, as_stream(stream), static_cast<const __nv_bfloat16*>(gate_up), rows, inter,
+             interleaved, static_cast<__nv_bfloat16*>(out));
   return check_launch(who);
 }
 

@@ -60,6 +60,8 @@ SIGNATURES = {
     "rk_peer_close": (_int, [_vp]),
     "rk_peer_free": (_int, [_vp]),
     "rk_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
+    "rk_rmsnorm_bf16": (_int, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "rk_silu_mul_bf16": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
     "rk_swiglu_pack_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "rk_swiglu_pack_nvfp4_layout": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "rk_pack_mxfp4_weight": (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),

@@ -95,6 +95,46 @@ def add_rms_norm_fp4_quant_bf16(x, residual, weight, epsilon, write_normalized=T
     return summed, normalized, q, sf
 
 
+def cutlass_silu_mul_bf16(gate_up, intermediate_size, interleaved=False):
+    """SiLU(gate) * up in the reference's bf16 steps -> bf16 [..., inter] (`robotics_cutlass_fp4::silu_mul_bf16`,
+    blackwell/fp4_linear.py:378-384); gate_up [..., 2 * inter], gate first, or the 64-column interleaved layout."""
+    inter = int(intermediate_size)
+    if not gate_up.is_cuda or gate_up.dtype != torch.bfloat16 or not gate_up.is_contiguous() or gate_up.numel() == 0:
+        raise ValueError("gate_up must be a non-empty contiguous CUDA BF16 tensor")
+    if inter <= 0 or inter % 8 or gate_up.shape[-1] != 2 * inter or (interleaved and inter % 64):
+        raise ValueError("gate_up last dimension must equal 2 * intermediate_size (a multiple of 8; 64 when interleaved)")
+    rows = gate_up.numel() // (2 * inter)
+    out = torch.empty((*gate_up.shape[:-1], inter), dtype=torch.bfloat16, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        code = _lib.load().rk_silu_mul_bf16(_lib.ptr(gate_up), rows, inter, 1 if interleaved else 0, _lib.ptr(out),
+                                            _lib.stream_ptr(gate_up.device))
+    _lib.check(code, "cutlass_silu_mul_bf16")
+    return out
+
+
+def add_rms_norm_bf16(x, residual, weight, epsilon):
+    """(residual add +) RMSNorm with bf16 rounding after each product (`robotics_cutlass_fp4::rms_norm_bf16` /
+    `add_rms_norm_bf16`): -> normalized, or (summed, normalized) with a residual."""
+    for t, what in ((x, "input"), (weight, "weight")) + (((residual, "residual"),) if residual is not None else ()):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError(f"rms_norm_bf16 {what} must be a contiguous CUDA BF16 tensor")
+    k = x.shape[-1]
+    if k % 16 or weight.shape != (k,) or (residual is not None and residual.shape != x.shape):
+        raise ValueError("rms_norm_bf16 requires [..., K] inputs with K divisible by 16 and weight [K]")
+    rows = x.numel() // k
+    summed = torch.empty_like(x) if residual is not None else None
+    normalized = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        code = _lib.load().rk_rmsnorm_bf16(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), rows, k, float(epsilon),
+                                           _lib.ptr(summed), _lib.ptr(normalized), _lib.stream_ptr(x.device))
+    _lib.check(code, "rms_norm_bf16")
+    return normalized if residual is None else (summed, normalized)
+
+
+def rms_norm_bf16(x, weight, epsilon):
+    return add_rms_norm_bf16(x, None, weight, epsilon)
+
+
 class PackedNvfp4Activation:
     """An activation that already is NVFP4 (codes, swizzled block scales, fp32 per-tensor scale or None):
     what a fused norm hands to the `Fp4CutlassLinear` layers that read it.  `shape` is the shape of

@@ -240,3 +240,53 @@ def test_gate_up_swiglu_module_feeds_the_down_projection(H):
     ref = (ref.to(torch.bfloat16) @ down.weight.t()).float()
     assert float((got.float() - ref).norm() / ref.norm()) < 0.35  # two chained 4-bit GEMMs
 
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_silu_mul_bf16_equals_the_packers_producer(H, interleaved):
+    """`silu_mul_bf16` on its own: the oracle's bf16-step SwiGLU, and exactly the values the NVFP4 SwiGLU
+    packer quantizes (packing this output gives the fused packer's bytes)."""
+    from oracle import blockscale as OB
+    from rk_b200 import fp4_linear as P4
+
+    rows, inter = 70, 192
+    gate_up = (H.randn_bf16((2, rows // 2, 2 * inter), 2.0, 41)).to(H.DEVICE)
+    out = P4.cutlass_silu_mul_bf16(gate_up, inter, interleaved)
+    assert out.shape == (2, rows // 2, inter)
+    flat = H.to_np(gate_up).reshape(rows, 2 * inter)
+    plain = OB.deinterleave_gate_up(flat, inter) if interleaved else flat
+    # the device's exp and reciprocal round a few values the other way at a bf16 boundary (as in the packer tests)
+    _nearly_identical(H.to_np(out).reshape(rows, inter), OB.swiglu_bf16_steps(plain, inter), 1e-2)
+    q, sf = P4.pack_nvfp4(out.reshape(rows, inter))
+    q2, sf2 = P4.pack_swiglu_nvfp4(gate_up.reshape(rows, 2 * inter), inter, interleaved)
+    assert torch.equal(q, q2) and torch.equal(sf, sf2)
+    with pytest.raises(ValueError):
+        P4.cutlass_silu_mul_bf16(gate_up, inter + 8)
+    with pytest.raises(ValueError):
+        P4.cutlass_silu_mul_bf16(gate_up[..., :200].contiguous(), 100, True)
+
+
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_rms_norm_bf16_equals_the_producers_norm(H, with_residual):
+    """The plain norm: the sum is exact; the normalized tensor is the one the FP8 / NVFP4 norm producers write."""
+    from oracle import fp8 as OF
+    from rk_b200 import fp4_linear as P4
+
+    rows, k = 45, 1024
+    x, res = H.randn_bf16((rows, k), 1.0, 51).to(H.DEVICE), H.randn_bf16((rows, k), 1.0, 52).to(H.DEVICE)
+    w = (1.0 + 0.1 * H.randn_bf16((k,), 1.0, 53).float()).to(torch.bfloat16).to(H.DEVICE)
+    if with_residual:
+        summed, normed = P4.add_rms_norm_bf16(x, res, w, 1e-6)
+        want_sum, want = OF.rms_norm(H.to_np(x), H.to_np(res), H.to_np(w), 1e-6)
+        assert np.array_equal(H.to_np(summed), want_sum)
+        ref_sum, ref_norm, _, _ = P4.add_rms_norm_fp4_quant_bf16(x, res, w, 1e-6)
+        assert torch.equal(summed, ref_sum)
+    else:
+        normed = P4.rms_norm_bf16(x, w, 1e-6)
+        _, want = OF.rms_norm(H.to_np(x), None, H.to_np(w), 1e-6)
+        _, ref_norm, _, _ = P4.add_rms_norm_fp4_quant_bf16(x, None, w, 1e-6)
+    assert torch.equal(normed, ref_norm)
+    got = H.to_np(normed)
+    assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()  # summation order of mean(x^2)
+    with pytest.raises(ValueError):
+        P4.rms_norm_bf16(x[:, :40].contiguous(), w[:40], 1e-6)
