@@ -244,6 +244,34 @@ def test_gemma_rmsnorm_tensor_scale_ignores_non_finite_and_refuses_bad_arguments
         gemma_rms_norm_pack_nvfp4(x[:, :40].contiguous(), w[:40], 1e-6)  # K % 32
 
 
+def test_rmsnorm_tensor_scale_adaptive_mode_equals_the_quantizing_norm(H):
+    """Adaptive weights (scale / shift rows per batch entry) and a residual through `rk_rmsnorm_tensor_scale`: the
+    stream and the normalized tensor are bit for bit those of `rk_rmsnorm_quant_rows` (the same kernel body),
+    and the scale is the maximum of that tensor over the divisor."""
+    from rk_b200 import _lib
+    from rk_b200.modulation import prepare_rmsnorm
+
+    rows, k, tokens = 150, 1024, 50
+    x, res = H.randn_bf16((rows, k), 1.0, 61).to(H.DEVICE), H.randn_bf16((rows, k), 1.0, 62).to(H.DEVICE)
+    w, sh = H.randn_bf16((rows // tokens, k), 0.2, 63).to(H.DEVICE), H.randn_bf16((rows // tokens, k), 0.2, 64).to(H.DEVICE)
+    _, want_sum, want_norm = prepare_rmsnorm(x, w, 8, eps=1e-6, residual=res, shift=sh, tokens=tokens, return_sum=True,
+                                             return_normed=True)
+    summed, normed = torch.empty_like(x), torch.empty_like(x)
+    scale = torch.empty(1, dtype=torch.float32, device=H.DEVICE)
+    ws = _lib.workspace(H.DEVICE, _lib.WORKSPACE_HEADER)
+    _lib.check(_lib.load().rk_rmsnorm_tensor_scale(_lib.ptr(x), _lib.ptr(res), _lib.ptr(w), _lib.ptr(sh), tokens, rows, k, 1e-6, 448.0,
+                                                   _lib.ptr(summed), _lib.ptr(normed), _lib.ptr(scale), _lib.ptr(ws), ws.numel(),
+                                                   _lib.stream_ptr(H.DEVICE)), "adaptive norm + scale")
+    assert torch.equal(summed, want_sum) and torch.equal(normed, want_norm)
+    assert scale.item() == np.float32(normed.float().abs().max().item()) / np.float32(448.0)
+    assert _lib.read_status(ws) == 0
+    # the staging words are clear again: a second call gives the same scale
+    _lib.check(_lib.load().rk_rmsnorm_tensor_scale(_lib.ptr(x), _lib.ptr(res), _lib.ptr(w), _lib.ptr(sh), tokens, rows, k, 1e-6, 448.0,
+                                                   _lib.ptr(summed), _lib.ptr(normed), _lib.ptr(scale), _lib.ptr(ws), ws.numel(),
+                                                   _lib.stream_ptr(H.DEVICE)), "second call")
+    assert scale.item() == np.float32(normed.float().abs().max().item()) / np.float32(448.0)
+
+
 @pytest.mark.parametrize("global_scale", [True, False])
 def test_fp4_forward_gelu_equals_tensor_ops(H, global_scale):
     """`Fp4CutlassLinear.forward_gelu`: table GELU * up + amax in one kernel, packer, GEMM - the same
