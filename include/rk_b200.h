@@ -412,6 +412,17 @@ int rk_gemm_nvfp4_swiglu(const void* a, const void* sfa, const float* ga, const 
                          const float* gb, void* q_out, void* sf_out, int64_t m, int64_t n, int64_t k, int tactic,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* The MXFP8 sibling: gate/up projection in MXFP8 (operands as for rk_gemm_mxfp8, weight rows interleaved in blocks
+ * of 64: up rows, then their gate rows) whose epilogue applies the table-SiLU SwiGLU producer and packs the
+ * activation to MXFP8 - bit for bit rk_gemm_mxfp8 -> bf16 -> rk_swiglu_pack_mxfp8 on the de-interleaved result.
+ * Replaces `cute_mxfp8_swiglu.cutlass_swiglu_mxfp8_packed` (blackwell/cute_mxfp8_swiglu.py:138-224; the CuTe-DSL
+ * kernel's multicast loads are not restated).
+ *   n = 2 * inter, n % 256 == 0; q_out e4m3 [m, inter]; sf_out rk_sf_bytes(m, inter / 32) bytes, every byte of
+ *   the blocks of 128 rows that hold rows < m written; silu_table bf16 [65536]. */
+int rk_gemm_mxfp8_swiglu(const void* a, const void* sfa, const void* b_interleaved, const void* sfb, const void* silu_table,
+                         void* q_out, void* sf_out, int64_t m, int64_t n, int64_t k, int tactic, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
 /* The same with a choice of gate/up layout: interleaved != 0 reads blocks of 128 columns holding 64 up
  * values followed by their 64 gate values (the layout of a fused gate/up projection,
  * blackwell/csrc/fp4_cutlass_linear.cu:958-965, 1051-1143); inter % 64 == 0 then. */

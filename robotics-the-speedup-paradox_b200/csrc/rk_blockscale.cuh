@@ -18,6 +18,31 @@ __device__ __forceinline__ long long sf_offset(long long row, long long group, l
   return ((row / 128) * kt + group / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + group % 4;
 }
 
+__device__ __forceinline__ float rcp_approx_ftz(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// smallest power of two >= x as a biased exponent byte (x >= 0, finite)
+__device__ __forceinline__ uint32_t ue8m0_roundup(float x) {
+  const uint32_t b = __float_as_uint(x);
+  const uint32_t e = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
+  uint32_t r = e == 0 ? (mant > 0x400000u ? 1u : 0u) : e + (mant != 0u ? 1u : 0u);
+  return r > 254u ? 254u : r;
+}
+
+// MXFP8 block of 32 (blackwell/csrc/mxfp8_common.cuh:12-32): the UE8M0 scale byte of a block with absolute
+// maximum `amax` (255 when the block holds a non-finite value), and the multiplier 2^(127 - e) that goes with it,
+// built as the exponent byte 254 - e (255 stays NaN, 0 becomes the subnormal 2^-127).
+__device__ __forceinline__ uint32_t mxfp8_block_scale(float amax, bool invalid) {
+  return invalid ? 255u : ue8m0_roundup(__fmul_rn(amax, rcp_approx_ftz(448.0f)));
+}
+__device__ __forceinline__ float mxfp8_inverse_scale(uint32_t e) {
+  const uint32_t ie = (254u - e) & 255u;
+  return ie == 255u ? __uint_as_float(0x7FC00000u) : (ie == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(ie << 23));
+}
+
 // SwiGLU in bf16 steps, as the reference's NVFP4 producer evaluates it with packed bf16 arithmetic
 // (blackwell/csrc/fp4_cutlass_linear.cu:1029-1033): every intermediate is rounded to bf16.
 __device__ __forceinline__ float swiglu_bf16_steps(float gate, float up) {

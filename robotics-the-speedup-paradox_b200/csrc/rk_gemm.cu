@@ -448,6 +448,7 @@ struct TcArgs {
   bool wgt_u4 = false;   // KIND_MXF8 with packed e2m1 weights [n, k / 2]: TMA expands them into the MMA's padded layout
   void* swiglu_q = nullptr;   // KIND_NVF4, interleaved gate/up weights: the epilogue packs silu(gate) * up to NVFP4
   void* swiglu_sf = nullptr;  //   (codes and swizzled scale factors) instead of writing bf16
+  const void* swiglu_table = nullptr;  // KIND_MXF8 with a SiLU table: the epilogue packs bf16(table[gate] * up) to MXFP8 instead
   int kind;
   const void* act;       // [m, k_bytes] bytes
   const void* wgt;       // [n, k_bytes] bytes
@@ -549,7 +550,8 @@ int run_tc(const TcArgs& a) {
     p2.out = static_cast<__nv_bfloat16*>(a.out);
     p2.sw_q = static_cast<uint8_t*>(a.swiglu_q);
     p2.sw_sf = static_cast<uint8_t*>(a.swiglu_sf);
-    p2.sw_kt = static_cast<int>(a.n / 128);
+    p2.sw_table = static_cast<const __nv_bfloat16*>(a.swiglu_table);
+    p2.sw_kt = a.swiglu_table != nullptr ? static_cast<int>((a.n / 2 / 32 + 3) / 4) : static_cast<int>(a.n / 128);
     p2.status = ws.status;
     CUtensorMap t_act, t_wgt, t_out, t_sfa, t_sfb;
     rc = make_map_2d(&t_act, a.act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.k_bytes, a.m, a.k_bytes, kStageKBytes, kTileA,
@@ -1088,6 +1090,37 @@ extern "C" int rk_gemm_nvfp4_swiglu(const void* a, const void* sfa, const float*
   t.sf_kt = static_cast<int>((k / 16 + 3) / 4);
   t.swiglu_q = q_out;
   t.swiglu_sf = sf_out;
+  t.tactic = (tactic & 4) | 2;
+  t.workspace = workspace;
+  t.workspace_bytes = workspace_bytes;
+  t.stream = as_stream(stream);
+  t.who = who;
+  return run_tc(t);
+}
+
+extern "C" int rk_gemm_mxfp8_swiglu(const void* a, const void* sfa, const void* b_interleaved, const void* sfb,
+                                    const void* silu_table, void* q_out, void* sf_out, int64_t m, int64_t n, int64_t k,
+                                    int tactic, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "rk_gemm_mxfp8_swiglu";
+  if (k < 32 || k % 32 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 32", who);
+  if (n < 256 || n % 256 != 0) return fail(RK_EINVAL, "%s: n (gate and up rows together) must be a multiple of 256", who);
+  if (!sfa || !sfb || !silu_table || !q_out || !sf_out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!aligned16(sfa) || !aligned16(sfb) || !aligned16(q_out) || !aligned16(sf_out))
+    return fail(RK_EINVAL, "%s: buffers must be 16-byte aligned", who);
+  TcArgs t{};
+  t.kind = KIND_MXF8;
+  t.act = a;
+  t.wgt = b_interleaved;
+  t.m = m;
+  t.n = n;
+  t.k_bytes = k;
+  t.mma_bytes_last = static_cast<int>(k % 128 == 0 ? 128 : k % 128);
+  t.sf_act = static_cast<const uint8_t*>(sfa);
+  t.sf_wgt = static_cast<const uint8_t*>(sfb);
+  t.sf_kt = static_cast<int>((k + 127) / 128);
+  t.swiglu_q = q_out;
+  t.swiglu_sf = sf_out;
+  t.swiglu_table = silu_table;
   t.tactic = (tactic & 4) | 2;
   t.workspace = workspace;
   t.workspace_bytes = workspace_bytes;

@@ -56,7 +56,10 @@ struct Gemm2Params {
   // is set the tile never leaves as bf16 - the epilogue forms silu(gate) * up and packs it to NVFP4.
   uint8_t* sw_q;     // [m, n / 4] bytes: two e2m1 codes per byte of the [m, n / 2] activation
   uint8_t* sw_sf;    // its UE4M3 scale factors in the swizzled 128 x 4 layout
-  int sw_kt;         // 512-byte scale chunks per 128-row block of that buffer = (n / 2) / 64
+  int sw_kt;         // 512-byte scale chunks per 128-row block of that buffer = (n / 2) / 64 (NVFP4), (n / 2) / 128 (MXFP8)
+  // sw_table set: MXFP8 output instead - bf16(table[gate] * up) with the 65536-entry SiLU table, blocks of 32
+  // channels, e4m3 codes [m, n / 2] bytes and UE8M0 scale bytes (the `silu_mul_pack` producer fused behind the GEMM)
+  const __nv_bfloat16* sw_table;
   int tiles_m, tiles_n;  // pair tiles: 256 x bn
   long long ldo;
   const float* scale_act;
@@ -441,6 +444,60 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         // share a row: each takes one of the group's four blocks.
         const float alpha = s_act_scalar * s_wgt_scalar;
         const int rows_sf = (p.m + 127) & ~127;  // the scale buffer covers whole 128-row blocks; padding rows get zeros
+        if (p.sw_table != nullptr) {
+          // ---- MXFP8 output: blocks of 32 channels = two warp sets; the sets of a pair exchange their 16 channels'
+          // maximum (and whether a value was not finite) through shared memory, then each converts its own half
+          float* const part_max = reinterpret_cast<float*>(smem_gen + out_stage_off);  // [4 sets][128 rows]
+          uint32_t* const part_bad = reinterpret_cast<uint32_t*>(part_max + 4 * 128);    // [4 sets][128 rows]
+          for (int cc = 0; cc < p.bn; cc += 128) {
+            const int col0 = row_b0 + cc;
+            const int ch0 = col0 >> 1;
+            const int c0 = set * 16;
+            uint32_t ru[16], rg[16];
+            __syncwarp();
+            tmem_ld_16(t_acc + cc + c0, ru);
+            tmem_ld_16(t_acc + cc + 64 + c0, rg);
+            tc_wait_ld();
+            float v[16];
+            float amax = 0.0f;
+            uint32_t bad = 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float up = round_bf16(__fmul_rn(alpha, __uint_as_float(ru[j])));
+              const float gate = round_bf16(__fmul_rn(alpha, __uint_as_float(rg[j])));
+              v[j] = round_bf16(__fmul_rn(__bfloat162float(p.sw_table[__float_as_uint(gate) >> 16]), up));
+              amax = fmaxf(amax, fabsf(v[j]));
+              bad |= !(fabsf(v[j]) <= 3.4028234664e38f);
+            }
+            part_max[set * 128 + et] = amax;
+            part_bad[set * 128 + et] = bad;
+            epi_sync(epi_threads);
+            amax = fmaxf(amax, part_max[(set ^ 1) * 128 + et]);
+            bad |= part_bad[(set ^ 1) * 128 + et];
+            const uint32_t e = mxfp8_block_scale(amax, bad != 0);
+            const float inverse = mxfp8_inverse_scale(e);
+            uint32_t w[4];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              w[q4] = 0;
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                w[q4] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fmul_rn(v[4 * q4 + i], inverse), __NV_SATFINITE, __NV_E4M3))
+                         << (8 * i);
+            }
+            if (ok && col0 < p.n) {
+              if (ra < p.m)
+                *reinterpret_cast<uint4*>(p.sw_q + static_cast<long long>(ra) * (p.n >> 1) + ch0 + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+              if ((set & 1) == 0 && ra < rows_sf)
+                p.sw_sf[sf_offset(ra, (ch0 >> 5) + (set >> 1), p.sw_kt)] = ra < p.m ? static_cast<uint8_t>(e) : static_cast<uint8_t>(0);
+            }
+            epi_sync(epi_threads);  // the exchange words are free again
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(ab == 0 ? acc_empty_leader0 : acc_empty_leader1);
+          continue;
+        }
         for (int cc = 0; cc < p.bn; cc += 128) {
           const int col0 = row_b0 + cc;       // first output column of this 128-column group
           const int ch0 = col0 >> 1;          // first activation channel of the group

@@ -560,20 +560,6 @@ to_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long elements, const flo
 }
 
 // ------------------------------------------------------------------ block-scale packers
-__device__ __forceinline__ float rcp_approx_ftz(float x) {
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-
-// smallest power of two >= x as a biased exponent byte (x >= 0, finite)
-__device__ __forceinline__ uint32_t ue8m0_roundup(float x) {
-  const uint32_t b = __float_as_uint(x);
-  const uint32_t e = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
-  uint32_t r = e == 0 ? (mant > 0x400000u ? 1u : 0u) : e + (mant != 0u ? 1u : 0u);
-  return r > 254u ? 254u : r;
-}
-
 // MXFP8: eight lanes per 32-element block, four elements per lane.  The thread grid covers the
 // padded scale-factor domain so that every byte of the SF buffer is written.
 // SWIGLU: x is [rows, 2 k] (gate first, then up) and the packed value is bf16(table[gate] * up), `table`
@@ -624,12 +610,9 @@ pack_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long long rows, long long
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 8));
     invalid |= __shfl_xor_sync(0xffffffffu, invalid, o, 8);
   }
-  const uint32_t e = invalid ? 255u : ue8m0_roundup(__fmul_rn(amax, rcp_approx_ftz(448.0f)));
+  const uint32_t e = mxfp8_block_scale(amax, invalid != 0);
   if (lane8 == 0) sf[sfi] = static_cast<uint8_t>(e);
-  // inverse scale 2^(127 - e) built as the byte 254 - e (255 stays NaN)
-  const uint32_t ie = (254u - e) & 255u;
-  const float inverse = ie == 255u ? __uint_as_float(0x7FC00000u)
-                                   : (ie == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(ie << 23));
+  const float inverse = mxfp8_inverse_scale(e);
   uint32_t out = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i)

@@ -117,6 +117,17 @@ class Bench:
             calls = [(lambda sp, b=b: lib.rk_gemm_nvfp4_swiglu(L.ptr(a), L.ptr(sfa), None, L.ptr(b), L.ptr(sfb), None, L.ptr(q),
                                                                 L.ptr(sfo), m, n, k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
             nbytes = (m * k + n * k) // 2 + m * n // 4 + (m + n) * k // 16 + m * n // 32
+        elif kind == "mxfp8sw":  # MXFP8 gate/up GEMM with the table-SiLU SwiGLU producer + MXFP8 re-pack in the epilogue
+            ws = L.gemm_workspace(L.OP_MXFP8, dev, m, n, k)
+            sfa = torch.full((lib.rk_sf_bytes(m, k // 32),), 127, dtype=torch.uint8, device=dev)
+            sfb = torch.full((lib.rk_sf_bytes(n, k // 32),), 127, dtype=torch.uint8, device=dev)
+            raw = torch.arange(65536, device=dev, dtype=torch.int32).to(torch.uint16)
+            table = torch.nn.functional.silu(raw.view(torch.bfloat16)).contiguous()
+            q = torch.empty((m, n // 2), dtype=torch.uint8, device=dev)
+            sfo = torch.empty(lib.rk_sf_bytes(m, n // 64), dtype=torch.uint8, device=dev)
+            calls = [(lambda sp, b=b: lib.rk_gemm_mxfp8_swiglu(L.ptr(a), L.ptr(sfa), L.ptr(b), L.ptr(sfb), L.ptr(table), L.ptr(q),
+                                                                L.ptr(sfo), m, n, k, tactic, L.ptr(ws), ws.numel(), sp)) for b in bs]
+            nbytes = m * k + n * k + m * n // 2 + (m + n) * k // 32 + m * n // 64
         elif kind == "fp8p":  # bf16 activations converted inside the kernel
             ws = L.gemm_workspace(L.OP_FP8, dev, m, n, k)
             x = torch.randn(m, k, device=dev).to(torch.bfloat16)

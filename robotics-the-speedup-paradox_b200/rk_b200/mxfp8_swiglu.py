@@ -42,3 +42,42 @@ def silu_mul_pack_mxfp8(gate_up, intermediate_size, silu_table):
                                         _lib.stream_ptr(gate_up.device))
     _lib.check(code, "silu_mul_pack_mxfp8")
     return packed, scales
+
+
+_TABLES = {}
+
+
+def cutlass_swiglu_mxfp8_packed(packed_input, input_scale, packed_interleaved_weight, weight_scale, silu_table=None):
+    """MXFP8 gate/up GEMM + SwiGLU + MXFP8 output in one kernel (`rk_gemm_mxfp8_swiglu`); the call shape of the
+    reference's ``cute_mxfp8_swiglu.cutlass_swiglu_mxfp8_packed``.  The weight rows are interleaved in blocks of
+    64 (64 up rows, then their 64 gate rows: `rk_b200.fp4_linear.interleave_gate_up_rows` before packing).
+    Returns (e4m3 [M, N / 2], swizzled UE8M0 scale bytes) - exactly `mxfp8_linear` followed by `silu_mul_pack_mxfp8`."""
+    if packed_input.dtype != torch.float8_e4m3fn or packed_interleaved_weight.dtype != torch.float8_e4m3fn:
+        raise TypeError("MXFP8 operands must use torch.float8_e4m3fn")
+    if input_scale.dtype != torch.uint8 or weight_scale.dtype != torch.uint8:
+        raise TypeError("MXFP8 scale factors must be uint8 E8M0 payloads")
+    tensors = (packed_input, input_scale, packed_interleaved_weight, weight_scale)
+    if not all(t.is_cuda and t.is_contiguous() for t in tensors) or len({t.device for t in tensors}) != 1:
+        raise ValueError("MXFP8 operands must be contiguous CUDA tensors on one device")
+    if packed_input.ndim != 2 or packed_interleaved_weight.ndim != 2:
+        raise ValueError("MXFP8 operands must be rank two")
+    m, k = packed_input.shape
+    n = packed_interleaved_weight.shape[0]
+    if packed_interleaved_weight.shape[1] != k or n % 256 or k % 32:
+        raise ValueError(f"invalid MXFP8 Gate-Up shape M={m}, N={n}, K={k}")
+    device = packed_input.device
+    if silu_table is None:
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        if key not in _TABLES:
+            _TABLES[key] = make_bf16_silu_table(device)
+        silu_table = _TABLES[key]
+    lib = _lib.load()
+    packed = torch.empty((m, n // 2), dtype=torch.float8_e4m3fn, device=device)
+    scales = torch.empty(lib.rk_sf_bytes(m, n // 2 // 32), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        ws = _lib.gemm_workspace(_lib.OP_MXFP8, device, m, n, k)
+        code = lib.rk_gemm_mxfp8_swiglu(_lib.ptr(packed_input), _lib.ptr(input_scale), _lib.ptr(packed_interleaved_weight),
+                                        _lib.ptr(weight_scale), _lib.ptr(silu_table), _lib.ptr(packed), _lib.ptr(scales), m, n, k,
+                                        0, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(device))
+    _lib.check(code, "cutlass_swiglu_mxfp8_packed")
+    return packed, scales

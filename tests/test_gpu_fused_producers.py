@@ -290,3 +290,43 @@ def test_rms_norm_bf16_equals_the_producers_norm(H, with_residual):
     assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()  # summation order of mean(x^2)
     with pytest.raises(ValueError):
         P4.rms_norm_bf16(x[:, :40].contiguous(), w[:40], 1e-6)
+
+
+@pytest.mark.parametrize("shape", [(300, 512, 256), (816, 1024, 2048), (100, 256, 96)])
+def test_mxfp8_gemm_with_swiglu_epilogue_equals_the_two_launches(H, shape):
+    """`rk_gemm_mxfp8_swiglu`: the gate/up GEMM whose epilogue applies the table-SiLU SwiGLU producer and packs to
+    MXFP8 gives the bytes of `mxfp8_linear` -> bf16 -> `silu_mul_pack_mxfp8` (the accumulators are the same; the
+    [M, 2 * inter] bf16 tensor is never written)."""
+    from rk_b200 import fp8_linear as P8
+    from rk_b200 import mxfp8_swiglu as MS
+    from rk_b200.cute_mxfp8_swiglu import cutlass_swiglu_mxfp8_packed
+    from rk_b200.fp4_linear import interleave_gate_up_rows
+
+    m, n, k = shape
+    inter = n // 2
+    x = H.randn_bf16((m, k), 1.0, 91).to(H.DEVICE)
+    w = H.randn_bf16((n, k), 0.05, 92).to(H.DEVICE)  # rows: gate (inter), then up (inter)
+    table = MS.make_bf16_silu_table(H.DEVICE)
+    a, sfa = P8.mxfp8_pack(x)
+    b, sfb = P8.mxfp8_pack(w)
+    gate_up = P8.mxfp8_linear(a, sfa, b, sfb)
+    want_q, want_sf = MS.silu_mul_pack_mxfp8(gate_up, inter, table)
+    bi, sfbi = P8.mxfp8_pack(interleave_gate_up_rows(w, inter))
+    q, sf = cutlass_swiglu_mxfp8_packed(a, sfa, bi, sfbi, table)
+    assert q.shape == (m, inter)
+    assert torch.equal(q.view(torch.uint8), want_q.view(torch.uint8))
+    assert torch.equal(sf, want_sf)
+    q2, sf2 = cutlass_swiglu_mxfp8_packed(a, sfa, bi, sfbi)  # the table built on demand is the same one
+    assert torch.equal(q2.view(torch.uint8), want_q.view(torch.uint8)) and torch.equal(sf2, want_sf)
+
+
+def test_mxfp8_swiglu_gemm_refuses_bad_shapes(H):
+    from rk_b200 import fp8_linear as P8
+    from rk_b200 import mxfp8_swiglu as MS
+
+    a, sfa = P8.mxfp8_pack(H.randn_bf16((64, 128), 1.0, 1).to(H.DEVICE))
+    b, sfb = P8.mxfp8_pack(H.randn_bf16((384, 128), 1.0, 2).to(H.DEVICE))  # 384 % 256 != 0
+    with pytest.raises(ValueError):
+        MS.cutlass_swiglu_mxfp8_packed(a, sfa, b, sfb)
+    with pytest.raises(TypeError):
+        MS.cutlass_swiglu_mxfp8_packed(a.view(torch.uint8), sfa, b, sfb)
