@@ -286,9 +286,18 @@ class PrefixWorkload:
                 if param.dim() >= 2:
                     param.copy_((torch.randn(param.shape, generator=gen, device=device) * 0.02).to(param.dtype))
         self.model = model
+        # RK_BENCH_ONE_GEMM_GATE_UP=1: gate and up as ONE NVFP4 GEMM with GELU * up in its epilogue (built from the
+        # bf16 weights before they are swapped) instead of two projections + the GELU * up kernel - measured
+        # neutral (3.607 against 3.614 ms per pass), so the per-linear path that the parity tests pin stays the default
+        from rk_b200.gemma_stack import build_fused_gate_up_fp4, enable_fused_gate_up
+
+        self.one_gemm_gate_up = os.environ.get("RK_BENCH_ONE_GEMM_GATE_UP") == "1"
+        fused_gate_up = build_fused_gate_up_fp4(model, global_scale=True) if self.one_gemm_gate_up else None
         self.context = quantize_linears(model, "fp4", scopes=("text",), selector=prefix_scope, fp4_global_scale=True,
                                         shared_quant=True)  # q/k/v and gate/up share one packed activation each
         self.report = self.context.__enter__()
+        if fused_gate_up is not None:
+            enable_fused_gate_up(model, fused_gate_up)
         for p_ in model.parameters():  # the bf16 originals are not needed while the benchmark runs
             p_.requires_grad_(False)
         # elementwise work between the GEMMs as a serving stack runs it: add + norm + amax in one kernel in
@@ -321,7 +330,10 @@ class PrefixWorkload:
     def close(self):
         from rk_b200.gemma_stack import unfuse_norm_quantize
 
+        from rk_b200.gemma_stack import disable_fused_gate_up
+
         unfuse_norm_quantize(self.fused_norms)
+        disable_fused_gate_up(self.model)
         self.context.__exit__(None, None, None)
 
     def config(self):
@@ -331,6 +343,7 @@ class PrefixWorkload:
                 "linears_nvfp4": len(self.report["modules"]), "per_tensor_scale": True,
                 "step": "one prefix pass (all linears NVFP4, activations packed on the fly, bf16 attention)",
                 "fused_elementwise": "norm+amax -> packer, GELU*up+amax -> packer, rope -> preallocated KV caches",
+                "gate_up": "one NVFP4 GEMM, GELU*up + amax in its epilogue" if self.one_gemm_gate_up else "two GEMMs + GELU*up kernel",
                 "timing": "CUDA events around CUDA-graph replays",
                 "l2": "inputs larger than L2: 1.1 GB of packed weights per pass"}
 

@@ -412,6 +412,17 @@ int rk_gemm_nvfp4_swiglu(const void* a, const void* sfa, const float* ga, const 
                          const float* gb, void* q_out, void* sf_out, int64_t m, int64_t n, int64_t k, int tactic,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Gate/up projection in NVFP4 (operands as for rk_gemm_nvfp4_swiglu: weight rows interleaved in blocks of 64, up
+ * rows then their gate rows) whose epilogue writes the gated activation bf16( table[gate] * up ) - `table` a
+ * 65536-entry bf16 table of the activation function, the arithmetic of rk_lut_mul_tensor_scale - as a bf16
+ * matrix [m, n / 2] and, when scale_out is given, max(amax(out) / divisor, 1e-12): the GELU-gated MLP of the
+ * Gemma layers (models/pi05/modeling_gemma.py:115-128) in front of a per-tensor-scaled packer, without the
+ * [m, n] bf16 gate/up tensor.  Bit for bit rk_gemm_nvfp4 on the interleaved weight followed by
+ * rk_lut_mul_tensor_scale on the de-interleaved result.  Needs a workspace header. */
+int rk_gemm_nvfp4_gated_act(const void* a, const void* sfa, const float* ga, const void* b_interleaved, const void* sfb,
+                            const float* gb, const void* table, float divisor, void* out, float* scale_out, int64_t m,
+                            int64_t n, int64_t k, int tactic, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The MXFP8 sibling: gate/up projection in MXFP8 (operands as for rk_gemm_mxfp8, weight rows interleaved in blocks
  * of 64: up rows, then their gate rows) whose epilogue applies the table-SiLU SwiGLU producer and packs the
  * activation to MXFP8 - bit for bit rk_gemm_mxfp8 -> bf16 -> rk_swiglu_pack_mxfp8 on the de-interleaved result.

@@ -448,6 +448,7 @@ struct TcArgs {
   bool wgt_u4 = false;   // KIND_MXF8 with packed e2m1 weights [n, k / 2]: TMA expands them into the MMA's padded layout
   void* swiglu_q = nullptr;   // KIND_NVF4, interleaved gate/up weights: the epilogue packs silu(gate) * up to NVFP4
   void* swiglu_sf = nullptr;  //   (codes and swizzled scale factors) instead of writing bf16
+  int swiglu_mode = 0;  // Gemm2Params::sw_mode
   const void* swiglu_table = nullptr;  // KIND_MXF8 with a SiLU table: the epilogue packs bf16(table[gate] * up) to MXFP8 instead
   int kind;
   const void* act;       // [m, k_bytes] bytes
@@ -551,6 +552,7 @@ int run_tc(const TcArgs& a) {
     p2.sw_q = static_cast<uint8_t*>(a.swiglu_q);
     p2.sw_sf = static_cast<uint8_t*>(a.swiglu_sf);
     p2.sw_table = static_cast<const __nv_bfloat16*>(a.swiglu_table);
+    p2.sw_mode = a.swiglu_mode;
     p2.sw_kt = a.swiglu_table != nullptr ? static_cast<int>((a.n / 2 / 32 + 3) / 4) : static_cast<int>(a.n / 128);
     p2.status = ws.status;
     CUtensorMap t_act, t_wgt, t_out, t_sfa, t_sfb;
@@ -1098,6 +1100,45 @@ extern "C" int rk_gemm_nvfp4_swiglu(const void* a, const void* sfa, const float*
   return run_tc(t);
 }
 
+extern "C" int rk_gemm_nvfp4_gated_act(const void* a, const void* sfa, const float* ga, const void* b_interleaved,
+                                       const void* sfb, const float* gb, const void* table, float divisor, void* out,
+                                       float* scale_out, int64_t m, int64_t n, int64_t k, int tactic, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  const char* who = "rk_gemm_nvfp4_gated_act";
+  if (k < 64 || k % 64 != 0) return fail(RK_EINVAL, "%s: k must be a positive multiple of 64", who);
+  if (n < 128 || n % 128 != 0) return fail(RK_EINVAL, "%s: n (gate and up rows together) must be a multiple of 128", who);
+  if (!sfa || !sfb || !table || !out) return fail(RK_EINVAL, "%s: null pointer", who);
+  if (!aligned16(sfa) || !aligned16(sfb) || !aligned16(out)) return fail(RK_EINVAL, "%s: buffers must be 16-byte aligned", who);
+  if (scale_out != nullptr && !(divisor > 0.0f)) return fail(RK_EINVAL, "%s: the divisor must be positive", who);
+  if (!workspace || workspace_bytes < RK_WORKSPACE_HEADER) return fail(RK_EWORKSPACE, "%s: workspace too small", who);
+  unsigned* staging = scale_out != nullptr ? reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + 64) : nullptr;
+  TcArgs t{};
+  t.kind = KIND_NVF4;
+  t.act = a;
+  t.wgt = b_interleaved;
+  t.m = m;
+  t.n = n;
+  t.k_bytes = k / 2;
+  t.mma_bytes_last = static_cast<int>((k / 2) % 128 == 0 ? 128 : (k / 2) % 128);
+  t.scale_act = ga;
+  t.scale_wgt = gb;
+  t.sf_act = static_cast<const uint8_t*>(sfa);
+  t.sf_wgt = static_cast<const uint8_t*>(sfb);
+  t.sf_kt = static_cast<int>((k / 16 + 3) / 4);
+  t.swiglu_q = out;
+  t.swiglu_sf = staging;
+  t.swiglu_table = table;
+  t.swiglu_mode = 2;
+  t.tactic = (tactic & 4) | 2;
+  t.workspace = workspace;
+  t.workspace_bytes = workspace_bytes;
+  t.stream = as_stream(stream);
+  t.who = who;
+  const int rc = run_tc(t);
+  if (rc != RK_OK || staging == nullptr) return rc;
+  return launch_finalize_scale(staging, divisor, scale_out, as_stream(stream));
+}
+
 extern "C" int rk_gemm_mxfp8_swiglu(const void* a, const void* sfa, const void* b_interleaved, const void* sfb,
                                     const void* silu_table, void* q_out, void* sf_out, int64_t m, int64_t n, int64_t k,
                                     int tactic, void* workspace, size_t workspace_bytes, void* stream) {
@@ -1121,6 +1162,7 @@ extern "C" int rk_gemm_mxfp8_swiglu(const void* a, const void* sfa, const void* 
   t.swiglu_q = q_out;
   t.swiglu_sf = sf_out;
   t.swiglu_table = silu_table;
+  t.swiglu_mode = 1;
   t.tactic = (tactic & 4) | 2;
   t.workspace = workspace;
   t.workspace_bytes = workspace_bytes;

@@ -60,6 +60,10 @@ struct Gemm2Params {
   // sw_table set: MXFP8 output instead - bf16(table[gate] * up) with the 65536-entry SiLU table, blocks of 32
   // channels, e4m3 codes [m, n / 2] bytes and UE8M0 scale bytes (the `silu_mul_pack` producer fused behind the GEMM)
   const __nv_bfloat16* sw_table;
+  // sw_mode 0: NVFP4 pack of SwiGLU in bf16 steps; 1: MXFP8 pack of bf16(table[gate] * up); 2: the bf16 product
+  // bf16(table[gate] * up) itself, [m, n / 2] at sw_q, and the maximum of its finite magnitudes into the word
+  // sw_sf points at (atomicMax on float bits; null: not collected) - what a per-tensor-scaled packer needs next
+  int sw_mode;
   int tiles_m, tiles_n;  // pair tiles: 256 x bn
   long long ldo;
   const float* scale_act;
@@ -186,6 +190,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int verdict_epi[2];
+  __shared__ unsigned sw_amax_bits;  // sw_mode 2: this CTA's maximum so far
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -212,6 +217,7 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       mbar_init(smem_u32(&bar_acc_empty[b]), p.sw_q != nullptr ? 8 * kGemm2SwigluSets : 8);  // the epilogue warps of both CTAs of the pair
     }
     abort_flag = 0;
+    sw_amax_bits = 0u;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
@@ -444,7 +450,50 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         // share a row: each takes one of the group's four blocks.
         const float alpha = s_act_scalar * s_wgt_scalar;
         const int rows_sf = (p.m + 127) & ~127;  // the scale buffer covers whole 128-row blocks; padding rows get zeros
-        if (p.sw_table != nullptr) {
+        if (p.sw_mode == 2) {
+          // ---- the activation itself as bf16 (the arithmetic of the table mode of the row quantizers) + its maximum
+          __nv_bfloat16* const prod = reinterpret_cast<__nv_bfloat16*>(p.sw_q);
+          float amax = 0.0f;
+          for (int cc = 0; cc < p.bn; cc += 128) {
+            const int col0 = row_b0 + cc;
+            const int ch0 = col0 >> 1;
+            const int c0 = set * 16;
+            uint32_t ru[16], rg[16];
+            __syncwarp();
+            tmem_ld_16(t_acc + cc + c0, ru);
+            tmem_ld_16(t_acc + cc + 64 + c0, rg);
+            tc_wait_ld();
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float v2[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const float up = round_bf16(__fmul_rn(alpha, __uint_as_float(ru[j + u])));
+                const float gate = round_bf16(__fmul_rn(alpha, __uint_as_float(rg[j + u])));
+                v2[u] = round_bf16(__fmul_rn(__bfloat162float(p.sw_table[__float_as_uint(gate) >> 16]), up));
+                const float a = fabsf(v2[u]);
+                if (a <= 3.4028234664e38f && ra < p.m && col0 < p.n) amax = fmaxf(amax, a);
+              }
+              w[j >> 1] = (__float_as_uint(v2[0]) >> 16) | (__float_as_uint(v2[1]) & 0xFFFF0000u);
+            }
+            if (ok && col0 < p.n && ra < p.m) {
+              uint4* const dst = reinterpret_cast<uint4*>(prod + static_cast<long long>(ra) * (p.n >> 1) + ch0 + c0);
+              dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(ab == 0 ? acc_empty_leader0 : acc_empty_leader1);
+          if (p.sw_sf != nullptr) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0 && ok && amax > 0.0f) atomicMax(&sw_amax_bits, __float_as_uint(amax));
+          }
+          continue;
+        }
+        if (p.sw_mode == 1) {
           // ---- MXFP8 output: blocks of 32 channels = two warp sets; the sets of a pair exchange their 16 channels'
           // maximum (and whether a value was not finite) through shared memory, then each converts its own half
           float* const part_max = reinterpret_cast<float*>(smem_gen + out_stage_off);  // [4 sets][128 rows]
@@ -573,6 +622,10 @@ rk_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       }
     }
     if (et == 0) tma_store_wait_read<0>();  // the staging memory has been read; the writes drain after the CTA has left
+    if (p.sw_mode == 2 && p.sw_sf != nullptr) {
+      epi_sync(epi_threads);  // every warp has added its maximum
+      if (threadIdx.x == 64 && sw_amax_bits != 0u) atomicMax(reinterpret_cast<unsigned*>(p.sw_sf), sw_amax_bits);
+    }
   }
 
   // ---------------------------------------------------------------- teardown

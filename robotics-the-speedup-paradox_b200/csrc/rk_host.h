@@ -26,6 +26,10 @@ inline int check_launch(const char* what) {
   return RK_OK;
 }
 
+// rk_quant.cu: scale = max(staged maximum / divisor, 1e-12) from the staging word of a workspace header
+// (cleared for the next call); for entry points of other translation units whose kernels collect a maximum.
+int launch_finalize_scale(unsigned* staging, float divisor, float* scale_out, cudaStream_t stream);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int64_t round_up(int64_t v, int64_t q) { return (v + q - 1) / q * q; }

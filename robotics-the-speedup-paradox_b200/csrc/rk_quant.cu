@@ -1053,6 +1053,13 @@ int launch_quant_rows(const void* x, int64_t rows, int64_t total_rows, int64_t k
 }  // namespace
 }  // namespace rk
 
+namespace rk {
+int launch_finalize_scale(unsigned* staging, float divisor, float* scale_out, cudaStream_t stream) {
+  launch_pdl(finalize_scale_kernel, 1, 1, stream, staging, divisor, scale_out);
+  return check_launch("finalize_scale");
+}
+}  // namespace rk
+
 using namespace rk;
 
 extern "C" int rk_quant_rows(const void* x, int64_t rows, int64_t k, int64_t x_stride, const void* up,

@@ -76,6 +76,7 @@ SIGNATURES = {
     "rk_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_gemm_nvfp4_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_gemm_mxfp8_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "rk_gemm_nvfp4_gated_act": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "rk_rope_cache_update": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _int,
                                     _vp, _vp, _i64, _i64, _vp]),
     "rk_rope_cache_update_vt": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp,

@@ -272,6 +272,87 @@ def linear_swiglu_packed_gemm(a, sfa, ga, b_interleaved, sfb, gb, k, tactic=0):
     return q, sf
 
 
+def linear_gated_act_gemm(a, sfa, ga, b_interleaved, sfb, gb, k, table, divisor=None, tactic=0):
+    """NVFP4 gate/up projection whose epilogue writes bf16(table[gate] * up) (`rk_gemm_nvfp4_gated_act`): packed
+    activations [M, K/2] x interleaved packed weight [2 * inter, K/2] -> (bf16 [M, inter], per-tensor scale
+    max(amax / divisor, 1e-12) or None without a divisor)."""
+    m, n = a.shape[0], b_interleaved.shape[0]
+    if n % 128:
+        raise ValueError("the fused gated projection needs 2 * inter to be a multiple of 128")
+    out = torch.empty((m, n // 2), device=a.device, dtype=torch.bfloat16)
+    scale = torch.empty(1, device=a.device, dtype=torch.float32) if divisor is not None else None
+    with torch.cuda.device(a.device):
+        ws = _lib.gemm_workspace(_lib.OP_NVFP4, a.device, m, n, k)
+        code = _lib.load().rk_gemm_nvfp4_gated_act(_lib.ptr(a), _lib.ptr(sfa), _lib.ptr(ga), _lib.ptr(b_interleaved), _lib.ptr(sfb),
+                                                   _lib.ptr(gb), _lib.ptr(table), float(divisor or 1.0), _lib.ptr(out),
+                                                   _lib.ptr(scale), m, n, k, tactic, _lib.ptr(ws), ws.numel(),
+                                                   _lib.stream_ptr(a.device))
+    _lib.check(code, "linear_gated_act_gemm")
+    return out, scale
+
+
+class Fp4GateUpGelu(torch.nn.Module):
+    """The gate and up projections of a GELU-gated MLP as ONE NVFP4 GEMM whose epilogue writes
+    GELU(gate) * up (the 65536-entry bf16 table of the integer layers' `forward_gelu`) and collects the
+    tensor's maximum: `forward_into(down, x)` packs that product and runs the down projection, and the
+    [M, 2 * inter] bf16 gate/up tensor never exists.  The fused weight is packed as one tensor (one
+    per-tensor scale for both halves when `global_scale`), its rows in the 64-row interleaved order."""
+
+    def __init__(self, packed, scales, weight_global, in_features, intermediate_size, approximate="tanh"):
+        super().__init__()
+        self.register_buffer("packed_weight", packed)
+        self.register_buffer("weight_scale", scales)
+        self.register_buffer("weight_global_scale", weight_global)
+        self.in_features = in_features
+        self.intermediate_size = intermediate_size
+        self.approximate = approximate
+        self.fp4_backend = "b200_tcgen05_nvfp4_gelu" + ("_global" if weight_global is not None else "")
+
+    @classmethod
+    def from_linears(cls, gate, up, global_scale=False, approximate="tanh"):
+        if gate.weight.shape != up.weight.shape or gate.bias is not None or up.bias is not None:
+            raise ValueError("gate and up must be bias-free linears of the same shape")
+        if not gate.weight.is_cuda or gate.weight.dtype != torch.bfloat16:
+            raise ValueError("Fp4GateUpGelu requires CUDA BF16 weights")
+        require_fp4_backend(gate.weight.device)
+        inter, k = gate.weight.shape
+        if inter % 64 or k % 64:
+            raise ValueError("Fp4GateUpGelu requires intermediate_size % 64 == 0 and in_features % 64 == 0")
+        fused = interleave_gate_up_rows(torch.cat([gate.weight.detach(), up.weight.detach()], dim=0), inter)
+        weight_global = tensor_global_scale(fused) if global_scale else None
+        packed, scales = pack_nvfp4(fused, weight_global)
+        return cls(packed, scales, weight_global, k, inter, approximate)
+
+    def pack_input(self, x):
+        if isinstance(x, PackedNvfp4Activation):
+            return x.packs_for(self)
+        if x.shape[-1] != self.in_features:
+            raise ValueError("Wrong input feature count")
+        flat = x.reshape(-1, self.in_features)
+        flat = flat if flat.is_contiguous() else flat.contiguous()
+        ga = tensor_global_scale(flat) if self.weight_global_scale is not None else None
+        q, sf = pack_nvfp4(flat, ga)
+        return q, sf, ga
+
+    def forward(self, x):
+        """-> (bf16 [rows, inter] GELU(gate) * up, its per-tensor scale or None)."""
+        from .integer import prepare_gelu
+
+        q, sf, ga = self.pack_input(x)
+        table = prepare_gelu(q.device, torch.bfloat16, self.approximate)
+        return linear_gated_act_gemm(q, sf, ga, self.packed_weight, self.weight_scale, self.weight_global_scale, self.in_features,
+                                     table, 6.0 * 448.0 if self.weight_global_scale is not None else None)
+
+    def forward_into(self, down, x):
+        """The whole MLP: this projection, the packer, `down.forward_packed` (an `Fp4CutlassLinear` with the same
+        per-tensor-scale setting)."""
+        if (down.weight_global_scale is None) != (self.weight_global_scale is None) or down.in_features != self.intermediate_size:
+            raise ValueError("the down projection does not match this gate/up projection")
+        product, scale = self(x)
+        q, sf = pack_nvfp4(product, scale)
+        return down.forward_packed(q, sf, scale, x.shape[:-1])
+
+
 class Fp4CutlassLinear(torch.nn.Module):
     def __init__(self, packed, scales, weight_global, bias, in_features, out_features, role, target_name):
         super().__init__()

@@ -252,6 +252,8 @@ class GemmaAttention(nn.Module):
 
 
 class GemmaMLP(nn.Module):
+    fused_gate_up = None  # an `Fp4GateUpGelu` built from gate_proj / up_proj (see `build_fused_gate_up_fp4`), or None
+
     def __init__(self, cfg):
         super().__init__()
         self.gate_proj = nn.Linear(cfg.width, cfg.mlp_dim, bias=False)
@@ -260,6 +262,8 @@ class GemmaMLP(nn.Module):
 
     def forward(self, x, residual=None):
         """`residual` = (stream, gate): the down projection's epilogue returns stream + mlp (* gate)."""
+        if self.fused_gate_up is not None and residual is None:
+            return self.fused_gate_up.forward_into(self.down_proj, x)  # one GEMM for gate and up, GELU * up in its epilogue
         gate, up = self.gate_proj(x), self.up_proj(x)
         fused = getattr(self.down_proj, "forward_gelu", None)
         if residual is not None:
@@ -477,6 +481,29 @@ def unfuse_norm_quantize(norms):
     for norm in norms:
         norm.fused_bits = None
         norm.fused_fp4 = None
+
+
+def build_fused_gate_up_fp4(stack, global_scale=True):
+    """One `Fp4GateUpGelu` per layer from the bf16 gate / up linears (call it BEFORE `quantize_linears` swaps them).
+    Returns the modules; `enable_fused_gate_up` switches a stack over to them, `disable_fused_gate_up` back."""
+    from .fp4_linear import Fp4GateUpGelu
+
+    return [Fp4GateUpGelu.from_linears(layer.mlp.gate_proj, layer.mlp.up_proj, global_scale=global_scale)
+            for layer in stack.layers]
+
+
+def enable_fused_gate_up(stack, fused_modules):
+    from .fp4_linear import Fp4CutlassLinear
+
+    for layer, fused in zip(stack.layers, fused_modules):
+        if not isinstance(layer.mlp.down_proj, Fp4CutlassLinear):
+            raise ValueError("the fused gate/up projection feeds an NVFP4 down projection: quantize the stack first")
+        layer.mlp.fused_gate_up = fused
+
+
+def disable_fused_gate_up(stack):
+    for layer in stack.layers:
+        layer.mlp.fused_gate_up = None
 
 
 def fuse_norm_pack_fp4(stack):

@@ -330,3 +330,39 @@ def test_mxfp8_swiglu_gemm_refuses_bad_shapes(H):
         MS.cutlass_swiglu_mxfp8_packed(a, sfa, b, sfb)
     with pytest.raises(TypeError):
         MS.cutlass_swiglu_mxfp8_packed(a.view(torch.uint8), sfa, b, sfb)
+
+
+@pytest.mark.parametrize("global_scale", [True, False])
+@pytest.mark.parametrize("shape", [(300, 256, 256), (816, 1024, 2048), (70, 128, 192)])
+def test_nvfp4_gate_up_gemm_with_gelu_epilogue_equals_the_two_launches(H, shape, global_scale):
+    """`rk_gemm_nvfp4_gated_act`: the fused gate/up GEMM writes GELU(gate) * up and the tensor's scale exactly as
+    the plain GEMM on the same interleaved weight followed by `rk_lut_mul_tensor_scale` does."""
+    from rk_b200 import fp4_linear as P4
+    from rk_b200.integer import prepare_gelu
+
+    m, inter, k = shape
+    torch.manual_seed(7)
+    gate = torch.nn.Linear(k, inter, bias=False, device=H.DEVICE, dtype=torch.bfloat16)
+    up = torch.nn.Linear(k, inter, bias=False, device=H.DEVICE, dtype=torch.bfloat16)
+    fused = P4.Fp4GateUpGelu.from_linears(gate, up, global_scale=global_scale)
+    x = (H.randn_bf16((m, k), 1.0, 17) * 3).to(torch.bfloat16).to(H.DEVICE)
+    q, sf, ga = fused.pack_input(x)
+    y = P4.linear_forward_packed_gemm_bf16(q, sf, ga, fused.packed_weight, fused.weight_scale, fused.weight_global_scale, None, k)
+    blocks = y.view(m, inter // 64, 2, 64)  # of every 128 columns: 64 up values, then their 64 gate values
+    up_y, gate_y = blocks[:, :, 0, :].reshape(m, inter), blocks[:, :, 1, :].reshape(m, inter)
+    table = prepare_gelu(x.device, torch.bfloat16, "tanh")
+    want, want_scale = P4.table_mul_tensor_scale(gate_y, up_y, table, 6.0 * 448.0 if global_scale else None)
+    got, got_scale = fused(x)
+    assert got.shape == (m, inter) and torch.equal(got, want)
+    assert torch.equal(want, torch.nn.functional.gelu(gate_y, approximate="tanh") * up_y)
+    if global_scale:
+        assert got_scale.item() == want_scale.item()
+        again, scale_again = fused(x)  # the staging word is clear again
+        assert torch.equal(again, want) and scale_again.item() == want_scale.item()
+    else:
+        assert got_scale is None
+    # the whole MLP through the down projection
+    down = P4.Fp4CutlassLinear.from_linear(torch.nn.Linear(inter, 264, bias=False, device=H.DEVICE, dtype=torch.bfloat16), "linear",
+                                           "down", global_scale=global_scale)
+    out = fused.forward_into(down, x.reshape(1, m, k))
+    assert out.shape == (1, m, 264) and torch.equal(out.reshape(m, 264), down(want))

@@ -420,3 +420,36 @@ def test_prefix_pass_with_fused_norm_packers_and_cache_writes(H):
                 assert rel < 2e-2, rel
                 assert kv3[0][0].data_ptr() == caches[0][0].data_ptr()
     assert all(n.fused_fp4 is None for n in norms)
+
+
+def test_prefix_pass_with_one_gemm_for_gate_and_up(H):
+    """Gate and up as ONE NVFP4 GEMM with GELU * up in its epilogue (`Fp4GateUpGelu`): another quantization of the
+    same two weights (one per-tensor scale for both halves), so the pass stays close to the one with separate
+    projections; together with the fused norms it runs from packed activations end to end."""
+    from rk_b200.gemma_stack import (GemmaConfig, GemmaStack, build_fused_gate_up_fp4, disable_fused_gate_up,
+                                     enable_fused_gate_up, fuse_norm_pack_fp4, prefix_scope, unfuse_norm_quantize)
+    from rk_b200.optimizations import quantize_linears
+
+    cfg = GemmaConfig(width=256, mlp_dim=1024, depth=2, num_heads=2, num_kv_heads=1, head_dim=128)
+    model = GemmaStack(cfg).to(torch.bfloat16).init_random(3).to(H.DEVICE).eval()
+    x = H.randn_bf16((1, 200, 256), 1.0, 8).to(H.DEVICE)
+    pos = torch.arange(200, device=H.DEVICE)[None]
+    with torch.no_grad():
+        for gs in (True, False):
+            fused_modules = build_fused_gate_up_fp4(model, global_scale=gs)
+            with quantize_linears(model, "fp4", scopes=("text",), selector=prefix_scope, shared_quant=True, fp4_global_scale=gs):
+                plain, _ = model(x, pos)
+                enable_fused_gate_up(model, fused_modules)
+                try:
+                    one_gemm, _ = model(x, pos)
+                    norms = fuse_norm_pack_fp4(model)
+                    with_norms, _ = model(x, pos)
+                    unfuse_norm_quantize(norms)
+                finally:
+                    disable_fused_gate_up(model)
+                assert torch.equal(model(x, pos)[0], plain)
+            for out in (one_gemm, with_norms):
+                rel = ((out.float() - plain.float()).norm() / plain.float().norm()).item()
+                assert rel < 5e-2, rel
+    with pytest.raises(ValueError):
+        enable_fused_gate_up(model, fused_modules)  # bf16 down projections
